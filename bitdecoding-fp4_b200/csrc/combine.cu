@@ -1,0 +1,49 @@
+// LSE-weighted merge of split-KV (or multi-GPU KV-shard) partial outputs into BF16.
+// One CTA per (row, query head), one thread per channel; a partial is added only under a
+// positive weight so an unwritten slot (its LSE is -inf) can never leak into the output
+// (src/nvfp4_decode_kernel/split_k_combine.py:47-83).
+#include "common.cuh"
+#include "host.h"
+
+namespace bdfp4 {
+
+constexpr int kMaxRegisterParts = 32;
+
+__global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ partial_out,
+                                                      const float* __restrict__ partial_lse, int parts, int rows,
+                                                      int heads_q, __nv_bfloat16* __restrict__ out,
+                                                      int64_t out_row_stride) {
+  const int head = blockIdx.x;
+  const int row = blockIdx.y;
+  const int channel = threadIdx.x;
+  const int64_t lse_stride = (int64_t)rows * heads_q;
+  const int64_t out_stride = lse_stride * kHeadDim;
+  const float* lse = partial_lse + (int64_t)row * heads_q + head;
+  const float* values = partial_out + ((int64_t)row * heads_q + head) * kHeadDim + channel;
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  float lse_max = -INFINITY;
+  for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, lse[s * lse_stride]);
+  if (lse_max == -INFINITY) lse_max = 0.0f;
+  float weight_sum = 0.0f;
+  for (int s = 0; s < parts; ++s) weight_sum += exp2f(lse[s * lse_stride] * kLog2e - lse_max * kLog2e);
+  const float inverse = (weight_sum == 0.0f || weight_sum != weight_sum) ? 0.0f : 1.0f / weight_sum;
+  float acc = 0.0f;
+  // split order, so a given set of partials always sums to the same bits
+  for (int s = 0; s < parts; ++s) {
+    const float scale = exp2f(lse[s * lse_stride] * kLog2e - lse_max * kLog2e) * inverse;
+    if (scale > 0.0f) acc = acc + scale * values[s * out_stride];
+  }
+  out[(int64_t)row * out_row_stride + head * kHeadDim + channel] = __float2bfloat16_rn(acc);
+}
+
+}  // namespace bdfp4
+
+extern "C" int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
+                             int32_t heads_q, void* out, int64_t out_row_stride, void* stream) {
+  if (!partial_out || !partial_lse || !out || parts < 1 || rows < 1 || heads_q < 1) return BDFP4_E_ARG;
+  if (out_row_stride < (int64_t)heads_q * bdfp4::kHeadDim) return BDFP4_E_ARG;
+  bdfp4::combine_kernel<<<dim3(heads_q, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      partial_out, partial_lse, parts, rows, heads_q, static_cast<__nv_bfloat16*>(out), out_row_stride);
+  return bdfp4::cuda_status(cudaGetLastError());
+}

@@ -1,0 +1,224 @@
+// Shared device helpers: NVFP4 conversions and the block-scale search.
+//
+// The arithmetic follows the quantizer of OpenBitSys/BitDecoding-FP4
+// (src/nvfp4_decode_kernel/_block_scale.py:218-327) operation for operation, because
+// its results feed an argmin whose candidates are often one float apart:
+//   scale   = E4M3_rn_satfinite(amax * fl32(1/divisor))        (a multiply, not a divide)
+//   inverse = 1.0f / (scale + 1e-30f)                           (IEEE division)
+//   codes   = cvt.rn.satfinite.e2m1x2.f32(x * inverse)
+//   error   = sum_i fma(d_i, d_i, error), d_i = fma(mag_i, scale, -x_i), in element order,
+//             with mag_i read back from the stored nibble
+//   a later candidate wins only on a strictly smaller error.
+// Every step is spelled with a rounding-explicit intrinsic so nvcc can neither contract
+// nor reassociate it.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bdfp4 {
+
+constexpr int kPage = 128;
+constexpr int kHeadDim = 128;
+constexpr int kGroup = 16;
+constexpr int kGroupsPerVec = kHeadDim / kGroup;  // 8
+constexpr int kMaxCandidates = 3;
+
+struct ScaleCandidates {
+  int count;
+  float reciprocal[kMaxCandidates];  // fl32(1/divisor), tie-break order
+};
+
+__host__ __device__ inline ScaleCandidates scale_candidates(int mode) {
+  ScaleCandidates c;
+  c.count = 1;
+  c.reciprocal[0] = (float)(1.0 / 6.0);
+  c.reciprocal[1] = (float)(1.0 / 4.0);
+  c.reciprocal[2] = (float)(1.0 / 6.5);
+  if (mode == 1) c.count = 2;
+  if (mode == 2) c.count = 3;
+  return c;
+}
+
+// Two floats -> one byte of two E2M1 codes; `lo` lands in the low nibble.
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+  uint16_t out;
+  asm("{\n\t.reg .b8 b;\n\tcvt.rn.satfinite.e2m1x2.f32 b, %1, %2;\n\tcvt.u16.u8 %0, b;\n\t}"
+      : "=h"(out)
+      : "f"(hi), "f"(lo));
+  return (uint32_t)out;
+}
+
+__device__ __forceinline__ uint32_t pack_e2m1x8(const float* v) {
+  return cvt_e2m1x2(v[0], v[1]) | (cvt_e2m1x2(v[2], v[3]) << 8) | (cvt_e2m1x2(v[4], v[5]) << 16) |
+         (cvt_e2m1x2(v[6], v[7]) << 24);
+}
+
+// One byte of two E2M1 codes -> their two values (low nibble first).
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
+  uint32_t pair;
+  asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(pair) : "r"(byte & 0xffu));
+  __half2 h = *reinterpret_cast<__half2*>(&pair);
+  return __half22float2(h);
+}
+
+// float -> E4M3 byte, round-to-nearest-even, saturating at 448.
+__device__ __forceinline__ uint32_t cvt_e4m3(float x) {
+  uint16_t out;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(out) : "f"(0.0f), "f"(x));
+  return (uint32_t)(out & 0xffu);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+  uint32_t pair;
+  uint16_t in = (uint16_t)(byte & 0xffu);
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(in));
+  __half2 h = *reinterpret_cast<__half2*>(&pair);
+  return __low2float(h);
+}
+
+struct GroupCodes {
+  float scale;    // the E4M3 value the group stores, as a float
+  uint32_t lo;    // elements 0..7, element 0 in the lowest nibble
+  uint32_t hi;    // elements 8..15
+};
+
+// One candidate over one group of sixteen values: codes and squared error.
+__device__ __forceinline__ void round_trip16(const float* x, float scale, uint32_t& lo, uint32_t& hi,
+                                             float& error) {
+  const float inverse = __fdiv_rn(1.0f, __fadd_rn(scale, 1.0e-30f));
+  float scaled[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) scaled[i] = __fmul_rn(x[i], inverse);
+  lo = pack_e2m1x8(scaled);
+  hi = pack_e2m1x8(scaled + 8);
+  error = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t word = (i < 4) ? lo : hi;
+    const float2 m0 = e2m1x2_to_float2(word >> (8 * (i & 3)));
+    const int e = 2 * i;
+    float d = __fmaf_rn(m0.x, scale, -x[e]);
+    error = __fmaf_rn(d, d, error);
+    d = __fmaf_rn(m0.y, scale, -x[e + 1]);
+    error = __fmaf_rn(d, d, error);
+  }
+}
+
+__device__ __forceinline__ float candidate_scale(float amax, float reciprocal) {
+  return e4m3_to_float(cvt_e4m3(__fmul_rn(amax, reciprocal)));
+}
+
+// The group's winning scale and codes under `cand` (first candidate wins ties).
+__device__ __forceinline__ GroupCodes quantize_group16(const float* x, const ScaleCandidates& cand) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(x[i], -x[i]));
+  GroupCodes best;
+  float best_error;
+  best.scale = candidate_scale(amax, cand.reciprocal[0]);
+  round_trip16(x, best.scale, best.lo, best.hi, best_error);
+  for (int c = 1; c < cand.count; ++c) {
+    const float scale = candidate_scale(amax, cand.reciprocal[c]);
+    uint32_t lo, hi;
+    float error;
+    round_trip16(x, scale, lo, hi, error);
+    if (error < best_error) {
+      best.scale = scale;
+      best.lo = lo;
+      best.hi = hi;
+      best_error = error;
+    }
+  }
+  return best;
+}
+
+// x - decode(codes) * scale for one group, one rounding per element
+// (src/nvfp4_decode_kernel/_block_scale.py:602-623).
+__device__ __forceinline__ void group_residual16(const float* x, const GroupCodes& q, float* residual) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t word = (i < 4) ? q.lo : q.hi;
+    const float2 m = e2m1x2_to_float2(word >> (8 * (i & 3)));
+    residual[2 * i] = __fmaf_rn(-m.x, q.scale, x[2 * i]);
+    residual[2 * i + 1] = __fmaf_rn(-m.y, q.scale, x[2 * i + 1]);
+  }
+}
+
+// Sixteen BF16 values (32 bytes, 16-byte aligned) -> FP32.
+__device__ __forceinline__ void load_bf16x16(const __nv_bfloat16* p, float* out) {
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void store_bf16x16(__nv_bfloat16* p, const float* v) {
+  uint4 a, b;
+  a.x = pack_bf16x2(v[0], v[1]);
+  a.y = pack_bf16x2(v[2], v[3]);
+  a.z = pack_bf16x2(v[4], v[5]);
+  a.w = pack_bf16x2(v[6], v[7]);
+  b.x = pack_bf16x2(v[8], v[9]);
+  b.y = pack_bf16x2(v[10], v[11]);
+  b.z = pack_bf16x2(v[12], v[13]);
+  b.w = pack_bf16x2(v[14], v[15]);
+  reinterpret_cast<uint4*>(p)[0] = a;
+  reinterpret_cast<uint4*>(p)[1] = b;
+}
+
+// Round sixteen FP32 values to BF16 and back, in place.
+__device__ __forceinline__ void round_to_bf16(float* v) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+}
+
+// Unnormalised Sylvester-Hadamard butterflies over one 128-channel head held by 8 adjacent
+// lanes, sixteen channels each (lane `group` owns channels 16*group..16*group+15). Index bits
+// are taken lowest first and each stage maps (a, c) -> (a + c, a - c) in FP32, which is the
+// order of src/nvfp4_decode_kernel/quantize_q_kernel.py:105-135 and of
+// src/nvfp4_decode_kernel/quantize_kv_kernel.py:123-162.
+__device__ __forceinline__ void hadamard_butterflies(float* v, int group) {
+#pragma unroll
+  for (int bit = 0; bit < 4; ++bit) {
+    const int stride = 1 << bit;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if ((j & stride) == 0) {
+        const float lo = v[j], hi = v[j + stride];
+        v[j] = __fadd_rn(lo, hi);
+        v[j + stride] = __fsub_rn(lo, hi);
+      }
+    }
+  }
+#pragma unroll
+  for (int bit = 0; bit < 3; ++bit) {
+    const int mask = 1 << bit;
+    const bool upper = (group & mask) != 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float own = v[j];
+      const float partner = __shfl_xor_sync(0xffffffffu, own, mask);
+      v[j] = upper ? __fsub_rn(partner, own) : __fadd_rn(own, partner);
+    }
+  }
+}
+
+constexpr float kInvSqrt128 = 0.08838834764831845f;  // fl32(1/sqrt(128))
+
+// Byte offset of (row, group) inside one head's 1024-byte scale tile.
+__host__ __device__ __forceinline__ int scale_tile_offset(int row, int group) {
+  return (group >> 2) * 512 + (row & 31) * 16 + (row >> 5) * 4 + (group & 3);
+}
+
+}  // namespace bdfp4

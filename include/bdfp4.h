@@ -1,0 +1,246 @@
+/*
+ * bdfp4 — C ABI of the B200 (sm_100a) NVFP4 KV-cache quantize-on-write and paged
+ * FP4 decode-attention kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (passed as void*), launches on that stream, never synchronises, and — unless a
+ * comment says otherwise — never allocates. The return value is a status code:
+ * 0 on success, a negative BDFP4_E_* value when the host-side argument check
+ * refused the call (nothing was launched), or BDFP4_E_CUDA when a CUDA runtime
+ * call failed. Device-detected problems (a bounded wait that ran out, a page id
+ * outside the cache) are OR-ed into the caller's optional `error_word`.
+ *
+ * Each declaration cites the interface of OpenBitSys/BitDecoding-FP4 it replaces,
+ * as path:line inside that project.
+ */
+#ifndef BDFP4_H_
+#define BDFP4_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BDFP4_PAGE_TOKENS 128 /* tokens per FP4 page (src/nvfp4_decode_kernel/_decode.py:23) */
+#define BDFP4_HEAD_DIM 128    /* channels per head (src/nvfp4_decode_kernel/_decode.py:24) */
+#define BDFP4_GROUP 16        /* values per E4M3 scale */
+#define BDFP4_MAX_SINK 16     /* src/nvfp4_decode_kernel/interface.py:17 */
+
+/* status codes */
+#define BDFP4_OK 0
+#define BDFP4_E_ARG (-1)      /* a size, pointer or alignment contract is violated */
+#define BDFP4_E_UNSUPPORTED (-2) /* a valid request this build has no kernel for */
+#define BDFP4_E_CUDA (-3)     /* a CUDA runtime/driver call failed; see bdfp4_last_cuda_error */
+#define BDFP4_E_DEVICE (-4)   /* the current device is not sm_100-family */
+
+/* bits a kernel may OR into *error_word */
+#define BDFP4_DEV_WAIT_TIMEOUT 1u /* a bounded mbarrier wait gave up */
+#define BDFP4_DEV_BAD_PAGE 2u     /* a page id outside [0, pages) was clamped */
+
+/* NVFP4 scale-candidate sets (src/nvfp4_decode_kernel/scale_mode.py:18-22) */
+#define BDFP4_SCALE_AMAX6 0            /* (6) */
+#define BDFP4_SCALE_FOUR_SIX 1         /* (6, 4) */
+#define BDFP4_SCALE_FOUR_SIX_SIXHALF 2 /* (6, 4, 6.5) */
+
+/* softmax-probability scale rules (src/nvfp4_decode_kernel/p_scale.py:29-40) */
+#define BDFP4_P_AMAX6 0              /* amax/6 */
+#define BDFP4_P_AMAX2_OR_AMAX6 1     /* amax/2 when amax <= tau else amax/6 */
+#define BDFP4_P_AMAX2_OR_AMAX6_C8 2  /* the same on 8*p, LSE corrected by -3 ln 2 (default) */
+
+/* key_shift element types */
+#define BDFP4_SHIFT_NONE 0
+#define BDFP4_SHIFT_F32 1
+#define BDFP4_SHIFT_BF16 2
+
+int bdfp4_version(void);
+const char* bdfp4_status_string(int status);
+/* Text of the last CUDA error this library saw on the calling thread ("" if none). */
+const char* bdfp4_last_cuda_error(void);
+/* 0 when the current device can run these kernels (compute capability 10.x), else BDFP4_E_DEVICE.
+ * Replaces the device check of src/nvfp4_decode_kernel/_decode.py:730-741. */
+int bdfp4_check_device(void);
+
+/*
+ * K/V page quantize-on-write plus BF16 tail/sink token writes: one call covers the three
+ * roles of the reference's writer launch.
+ * Replaces KVCacheWriter.__call__ (src/nvfp4_decode_kernel/quantize_kv_kernel.py:984-1038),
+ * its kernel roles _key_page/_value_page/_tail_token (:165-339) and the per-layer "seal"
+ * form with a [4, layers] base-address table (:579-583).
+ *
+ * Page interior layouts (fixed; only the page pitch is free):
+ *   K codes  u8 [128 tok][H][64]          byte = channels (2b, 2b+1), even channel in the low nibble
+ *   V codes  u8 [H][128 ch][64]           byte = tokens (2b, 2b+1)
+ *   scales   u8 [H][2][32][4][4]          byte of (row r, group g, head h) =
+ *            h*1024 + (g/4)*512 + (r%32)*16 + (r/32)*4 + g%4; r = token for K, channel for V,
+ *            g = channel group for K, token group for V.
+ */
+typedef struct bdfp4_kv_write_args {
+  /* source: [tokens, H, 128] BF16, dense within a token; pitch in elements (multiple of 8) */
+  const void* key;   /* NULL: no K role */
+  const void* value; /* NULL: no V role */
+  int64_t key_token_pitch;
+  int64_t value_token_pitch;
+  int64_t source_tokens_total; /* tokens in key/value (per-layer writer: all layers, back to back) */
+  int32_t heads;               /* KV heads H */
+  /* destination regions of ONE layer; ignored when `bases` is given */
+  void* key_codes;
+  void* key_scales;
+  void* value_codes;
+  void* value_scales;
+  int64_t key_codes_pitch; /* bytes between pages, multiple of 16 */
+  int64_t key_scales_pitch;
+  int64_t value_codes_pitch;
+  int64_t value_scales_pitch;
+  /* per-layer form: device int64 [4][layers] addresses (K codes, K scales, V codes, V scales) */
+  const int64_t* bases;
+  int32_t layers; /* 1 unless `bases` */
+  /* work table: item w reads 128 tokens from source_tokens[w], writes page destination_pages[w]
+   * (negative: skip). Device int32 [work_items]. */
+  const int32_t* source_tokens;
+  const int32_t* destination_pages;
+  int32_t work_items;
+  int32_t key_scale_mode;   /* BDFP4_SCALE_* */
+  int32_t value_scale_mode; /* BDFP4_SCALE_* */
+  /* K transform: Hadamard rotation and/or subtraction of key_shift[layer][H][128] */
+  int32_t rotate_key;
+  const void* key_shift;
+  int32_t key_shift_type; /* BDFP4_SHIFT_* */
+  int32_t layer;          /* selects key_shift / tail layer of a one-layer call */
+  /* tail role (NULL tail_key: none): tail buffers BF16 [layers][slots][128+sink_tokens][H][128] */
+  void* tail_key;
+  void* tail_value;
+  int64_t tail_layer_stride; /* elements */
+  int64_t tail_slot_stride;  /* elements */
+  int32_t sink_tokens;
+  const int32_t* query_start_loc; /* [rows+1] */
+  const int32_t* seq_lens;        /* [rows] */
+  const int32_t* seqused_fp4;     /* [rows] */
+  const int32_t* row_to_slot;     /* [rows] */
+  int32_t rows;
+  int32_t decode_rows;
+  int32_t first_row;
+  int32_t* error_word; /* optional */
+} bdfp4_kv_write_args;
+
+int bdfp4_kv_write(const bdfp4_kv_write_args* args, void* stream);
+
+/*
+ * Decode-query quantization (one or two NVFP4 terms, optional Hadamard), the padded BF16
+ * copy of the query, and optionally this step's K/V token into the BF16 tail.
+ * Replaces quantize_decode_q_to_padded_fp4 (src/nvfp4_decode_kernel/quantize_q_kernel.py:681-1110)
+ * and its kernel _quantize_query_kernel (:364-428), including the DecodeTailWrite side
+ * (src/nvfp4_decode_kernel/interface.py:45-69).
+ *
+ * query_codes   u8 [rows][1][Hq][64]
+ * query_scales  u8 storage [rows][1][Hq][2][32][4][4]; head h writes row (h % G) of the tile of
+ *               KV head h / G, whose 1024 bytes start at (row*Hq + h/G)*1024
+ *               (src/nvfp4_decode_kernel/_quantize.py:100-132). Unwritten bytes must already be zero.
+ * query_padded  BF16 [rows][128][Hq][128], only [:, 0] written (NULL: skip)
+ */
+typedef struct bdfp4_quantize_query_args {
+  const void* query; /* BF16 [src_rows][Hq][128] */
+  int64_t query_row_stride;  /* elements, multiple of 8 */
+  int64_t query_head_stride; /* elements, multiple of 8 */
+  const int32_t* row_indices; /* optional [rows]: source row of each output row */
+  int32_t rows;
+  int32_t heads_q;
+  int32_t heads_kv;
+  int32_t scale_mode; /* BDFP4_SCALE_* */
+  int32_t rotate;     /* Hadamard on the query */
+  void* query_codes;
+  void* query_scales;
+  void* query_codes_second; /* NULL: one term */
+  void* query_scales_second;
+  void* query_padded;
+  /* fused tail write (tail_key NULL: none) */
+  const void* new_key;   /* BF16 [>=rows][H][128] */
+  const void* new_value;
+  int64_t new_key_token_pitch;
+  int64_t new_value_token_pitch;
+  void* tail_key;   /* one layer: BF16 [slots][128+sink_tokens][H][128] */
+  void* tail_value;
+  int64_t tail_slot_stride; /* elements */
+  const int32_t* row_to_slot;
+  const int32_t* seq_lens;
+  const int32_t* seqused_fp4;
+  int32_t rotate_key;
+  const float* key_shift; /* FP32 [H][128], already in the rotated basis; NULL: none */
+  int32_t sink_tokens;
+} bdfp4_quantize_query_args;
+
+int bdfp4_quantize_query(const bdfp4_quantize_query_args* args, void* stream);
+
+/*
+ * Paged FP4 decode attention, one query token per row.
+ * Replaces decode_fp4 / decode_fp4_split (src/nvfp4_decode_kernel/_decode.py:697-1456) and the
+ * kernel FP4DecodeKernel (src/nvfp4_decode_kernel/fp4_decode_kernel.py:147-7953) in the one
+ * configuration the reference instantiates (head_dim 128, page 128, one query token,
+ * transposed scores, BF16 tail and sink from the paged BF16 buffer).
+ *
+ * Blocks are merged in the reference's order: the BF16 tail, FP4 pages newest to oldest, the
+ * BF16 sink. With num_splits > 1 split s owns pages [s*c, min((s+1)*c, n)), c = ceil(n/num_splits),
+ * and writes a normalised FP32 partial and a natural-log LSE (-inf when it had nothing);
+ * the tail and sink belong to split 0, or to an extra last split when bf16_split != 0
+ * (src/nvfp4_decode_kernel/interface.py:24-42). bdfp4_combine then produces the BF16 output.
+ */
+typedef struct bdfp4_decode_args {
+  int32_t rows;
+  int32_t heads_q;
+  int32_t heads_kv;
+  /* query operands as bdfp4_quantize_query wrote them */
+  const void* query_codes;
+  const void* query_scales;
+  const void* query_codes_second; /* NULL: one term */
+  const void* query_scales_second;
+  const void* query_padded; /* BF16 [rows][128][Hq][128]; required with a tail */
+  /* FP4 cache regions */
+  const void* key_codes;
+  const void* key_scales;
+  const void* value_codes;
+  const void* value_scales;
+  int64_t key_codes_pitch; /* bytes */
+  int64_t key_scales_pitch;
+  int64_t value_codes_pitch;
+  int64_t value_scales_pitch;
+  int32_t pages; /* pages in the cache regions */
+  const int32_t* page_table; /* int32 [rows][page_table_stride] */
+  int64_t page_table_stride;
+  int32_t max_pages_per_row;
+  const int32_t* seqused_fp4; /* [rows], multiples of 128 */
+  /* BF16 tail + sink (tail_key NULL: none): [slots][128 (+16 if seqused_sink)][H][128] */
+  const void* tail_key;
+  const void* tail_value;
+  int64_t tail_slot_stride; /* elements */
+  int32_t tail_slots;
+  const int32_t* tail_slot_ids;    /* [rows]; negative: no tail for the row */
+  const int32_t* seqused_residual; /* [rows] in [0,128] */
+  const int32_t* seqused_sink;     /* [rows] in [0,16]; NULL: no sink */
+  float softmax_scale;
+  int32_t p_scale_mode; /* BDFP4_P_* */
+  float p_scale_tau;    /* threshold of the amax2_or_amax6 rules (default 21/1024) */
+  /* outputs */
+  void* out; /* BF16 [rows][Hq][128] with row stride out_row_stride (elements); used when num_splits == 1 */
+  int64_t out_row_stride;
+  int32_t num_splits;
+  int32_t bf16_split;  /* 1: tail+sink get a split of their own (index num_splits) */
+  float* partial_out;  /* FP32 [parts][rows][Hq][128], parts = num_splits + bf16_split */
+  float* partial_lse;  /* FP32 [parts][rows][Hq] */
+  int32_t* error_word; /* optional */
+} bdfp4_decode_args;
+
+int bdfp4_decode(const bdfp4_decode_args* args, void* stream);
+
+/*
+ * LSE-weighted merge of FP32 partial outputs into BF16.
+ * Replaces combine_split_partials / SplitKCombine (src/nvfp4_decode_kernel/split_k_combine.py:13-136).
+ * The same call merges partials gathered from several GPUs.
+ * partial_out FP32 [parts][rows][Hq][128], partial_lse FP32 [parts][rows][Hq], out BF16 [rows][Hq][128].
+ */
+int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
+                  int32_t heads_q, void* out, int64_t out_row_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BDFP4_H_ */
