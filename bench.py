@@ -1,0 +1,437 @@
+"""Benchmark of the NVFP4 decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one decode step of one attention layer over the whole batch: the step's query is
+quantized to NVFP4 (two terms), each sequence's new K/V token is written into its BF16 tail
+(fused into the same launch), then paged FP4 decode attention runs over the FP4 pages, the
+BF16 tail and the BF16 sink. The N=1 workload is the Qwen3-4B-shaped configuration: 32 query /
+8 KV heads, head_dim 128, batch 64, 65,536 tokens per sequence, randomly shuffled block table,
+4 sink + 128 recent BF16 tokens, K/V/Q BF16 from N(0,1) with four lognormal(0,1.5) outlier
+channels per KV head of K. With N GPUs the KV heads are partitioned over the ranks (as tensor
+parallelism does) with no collective: every rank runs the same batch on its head group, and
+the step time is the maximum over ranks.
+
+Prints one JSON line (rank 0). `value` is microseconds per step with inputs resident in HBM;
+`e2e` is the same step driven from pinned host buffers, with the host->device copy of the
+step's query and new K/V token and the device->host copy of its output inside the timed region.
+`--impl reference` times the CPU restatement of the reference's algorithm (oracle/) on a bounded
+sample of the same workload, on all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "bitdecoding-fp4_b200"))
+
+import torch  # noqa: E402
+
+HEADS_Q, HEADS_KV, BATCH, CONTEXT = 32, 8, 64, 65536
+SINK_USED, SINK_ROWS = 4, 16
+WORKLOAD_NAME = "qwen3-4b-shape decode layer: 32q/8kv heads, d128, batch 64, ctx 65536, page 128"
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        clocks = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples if len(s) >= 6 for i in range(4) if s[2 + i] == "Active"})
+        return {
+            "sm_mhz": int(statistics.median(clocks)) if clocks else None,
+            "sm_max_mhz": int(self.samples[0][1]) if self.samples and self.samples[0][1].isdigit() else None,
+            "reasons": reasons,
+            "samples": len(clocks),
+        }
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's algorithm on a bounded sample
+# ---------------------------------------------------------------------------------------------
+
+def cpu_sample_step(context: int, threads: int, repeats: int = 1, seed: int = 0):
+    """One decode step of a (1 row, 1 KV head = 4 query heads, `context` tokens) slice on the CPU.
+
+    The cache is quantized once up front (not timed); the timed step quantizes the query, puts
+    the new K token into the cache basis, and runs kernel-order attention over the FP4 pages, the
+    BF16 tail and the sink, which includes dequantizing every page as the reference's CPU path does.
+    Returns seconds per step.
+    """
+    from oracle import nvfp4_oracle as oracle
+
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(seed)
+    sink, fp4, tail = min(context, SINK_USED), ((context - 1) // 128) * 128, context - ((context - 1) // 128) * 128
+    pages = fp4 // 128
+    k = torch.randn(context, 1, 128, generator=gen)
+    k[:, 0, torch.randperm(128, generator=gen)[:4]] *= torch.exp(1.5 * torch.randn(4, generator=gen))
+    k = k.to(torch.bfloat16)
+    v = torch.randn(context, 1, 128, generator=gen).to(torch.bfloat16)
+    kc, ks = oracle.quantize_key_pages(k[:fp4].reshape(pages, 128, 1, 128), "four_six", rotate=True)
+    vc, vs = oracle.quantize_value_pages(v[:fp4].reshape(pages, 128, 1, 128), "amax6")
+    tail_k = torch.zeros(1, 144, 1, 128, dtype=torch.bfloat16)
+    tail_v = torch.zeros_like(tail_k)
+    basis = oracle.key_cache_basis(k, rotate=True, shift=None)
+    tail_k[0, :tail], tail_v[0, :tail] = basis[fp4:], v[fp4:]
+    tail_k[0, 128:128 + sink], tail_v[0, 128:128 + sink] = basis[:sink], v[:sink]
+    q = torch.randn(1, 4, 128, generator=gen).to(torch.bfloat16)
+    table = torch.arange(pages, dtype=torch.int32)[None]
+    meta = dict(
+        page_table=table, seqused_fp4=torch.tensor([fp4], dtype=torch.int32), tail_key=tail_k, tail_value=tail_v,
+        tail_slot_ids=torch.zeros(1, dtype=torch.int32), seqused_residual=torch.tensor([tail], dtype=torch.int32),
+        seqused_sink=torch.tensor([sink], dtype=torch.int32),
+    )
+    start = time.perf_counter()
+    for _ in range(repeats):
+        qq = oracle.quantize_query(q, 1, scale_mode="amax6", terms=2, rotate=True)
+        tail_k[0, tail - 1] = oracle.key_cache_basis(k[-1:], rotate=True, shift=None)[0]
+        tail_v[0, tail - 1] = v[-1]
+        oracle.decode_reference(query_values=qq["values"], query_padded=qq["padded"], key_codes=kc, key_scales=ks,
+                                value_codes=vc, value_scales=vs, heads_kv=1, softmax_scale=128 ** -0.5, **meta)
+    return (time.perf_counter() - start) / repeats
+
+
+def cpu_baseline(heads_kv_local: int, sample_context: int = 8192) -> dict:
+    threads = os.cpu_count() or 1
+    seconds = cpu_sample_step(sample_context, threads)
+    units = BATCH * heads_kv_local * (CONTEXT / sample_context)
+    return {
+        "value": seconds * units * 1e6,
+        "unit": "us/step",
+        "cores": threads,
+        "kind": "port",
+        "sample": (f"oracle port, 1 row x 1 KV head (4 query heads) x {sample_context} tokens took {seconds:.3f} s "
+                   f"on {threads} threads; scaled by {units:.0f} (batch x KV heads x context ratio) to the full step"),
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    heads_local = HEADS_KV // args.gpus
+    threads = os.cpu_count() or 1
+    sample_context = 4096
+    for _ in range(args.warmup):
+        cpu_sample_step(sample_context, threads)
+    times = [cpu_sample_step(sample_context, threads, seed=i) for i in range(args.steps)]
+    seconds = sum(times) / len(times)
+    units = BATCH * heads_local * (CONTEXT / sample_context)
+    value = seconds * units * 1e6
+    line = {
+        "impl": "reference", "metric": "decode_attn_us_per_step", "value": value, "unit": "us/step",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": value / 1e3,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD_NAME, "kv_heads_per_rank": heads_local, "sink_tokens": SINK_USED},
+        "cpu_baseline": {
+            "value": value, "unit": "us/step", "cores": threads, "kind": "port",
+            "sample": (f"each step: 1 row x 1 KV head x {sample_context} tokens ({seconds:.3f} s on {threads} threads), "
+                       f"scaled by {units:.0f} to the rank's full step"),
+        },
+        "e2e": {"value": value, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
+def run_ours(args) -> None:
+    import torch.distributed as dist
+
+    from bdfp4.workload import build_workload
+    from nvfp4_decode_kernel import DecodeTailWrite, fp4_decode, split_partial_count
+    from nvfp4_decode_kernel._decode import _multiprocessor_count
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run, one rank per GPU")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if HEADS_KV % world:
+        raise SystemExit(f"{HEADS_KV} KV heads do not partition over {world} ranks")
+    heads_kv = HEADS_KV // world
+    heads_q = HEADS_Q // world
+    rows, context = BATCH, args.context
+
+    w = build_workload(rows=rows, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[context] * rows,
+                       sink_tokens=SINK_ROWS, seed=1000 + rank, device=device, key_scale_mode="four_six",
+                       value_scale_mode="amax6", rotate=True)
+    w.seqused_sink.clamp_(max=SINK_USED)
+    w.sink_tokens = SINK_USED
+    algorithmic_bytes = w.algorithmic_bytes()
+    sms = _multiprocessor_count(local_rank)
+    # split count from the batch width only, as the serving plugin chooses it
+    ctas = rows * heads_kv
+    budget = min(sms // ctas, 32)
+    splits = 1
+    while splits * 2 <= budget:
+        splits *= 2
+    filled = sms // ctas - 1
+    if splits < filled < 2 * splits:
+        splits = filled
+    if args.splits:
+        splits = args.splits
+    parts = split_partial_count(rows, heads_kv, splits, residual=True, sms=sms)
+
+    gen = torch.Generator(device=device).manual_seed(77 + rank)
+    new_key = torch.randn(rows, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+    new_value = torch.randn(rows, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+    seq_lens = torch.full((rows,), context, dtype=torch.int32, device=device)
+    scratch = dict(
+        query_padded_scratch=torch.zeros(rows, 128, heads_q, 128, dtype=torch.bfloat16, device=device),
+        query_fp4_scratch=torch.zeros(rows, 1, heads_q, 64, dtype=torch.uint8, device=device),
+        query_scales_scratch=torch.zeros(rows, 1, heads_q, 2, 32, 4, 4, dtype=torch.uint8, device=device),
+        query_fp4_second_scratch=torch.zeros(rows, 1, heads_q, 64, dtype=torch.uint8, device=device),
+        query_scales_second_scratch=torch.zeros(rows, 1, heads_q, 2, 32, 4, 4, dtype=torch.uint8, device=device),
+    )
+    if splits > 1:
+        scratch["split_partial_scratch"] = torch.empty(parts * rows * heads_q * 128, device=device)
+        scratch["split_lse_scratch"] = torch.empty(parts * rows * heads_q, device=device)
+    out = torch.empty(rows, heads_q, 128, dtype=torch.bfloat16, device=device)
+
+    def step(query, key_token, value_token):
+        tail = DecodeTailWrite(key_token, value_token, w.tail_key[0], w.tail_value[0], w.slot_ids, seq_lens,
+                               w.seqused_fp4, True, None, SINK_ROWS)
+        return fp4_decode(
+            query, *w.regions, w.page_table, w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
+            residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
+            seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, out=out, trusted_metadata=True,
+            num_splits=splits, query_terms=2, scale_mode="amax6", query_rotation="hadamard", tail_write=tail,
+            **scratch)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(value: float) -> float:
+        if world == 1:
+            return value
+        t = torch.tensor([value], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident arm ----------------------------------------------------------------
+    for _ in range(args.warmup):
+        step(w.query, new_key, new_value)
+    barrier()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        begin.record()
+        for _ in range(args.steps):
+            step(w.query, new_key, new_value)
+        end.record()
+        barrier()
+    step_ms = max_over_ranks(begin.elapsed_time(end) / args.steps)
+
+    # ---- decode kernel alone, for the roofline (events on the launching stream) ---------------
+    from nvfp4_decode_kernel._quantize import quantize_query
+
+    quantized = quantize_query(
+        w.query, query_padded_out=scratch["query_padded_scratch"], heads_kv=heads_kv,
+        query_fp4_scratch=scratch["query_fp4_scratch"], query_scales_scratch=scratch["query_scales_scratch"],
+        query_fp4_second_scratch=scratch["query_fp4_second_scratch"],
+        query_scales_second_scratch=scratch["query_scales_second_scratch"], query_terms=2, rotation="hadamard")
+    import bdfp4
+    from nvfp4_decode_kernel import _decode as decode_module
+
+    kernel_args = bdfp4.DecodeArgs()
+    decode_module._fill_args(
+        kernel_args, rows=rows, heads_q=heads_q, heads_kv=heads_kv, page_count=w.regions[0].shape[0],
+        query_fp4=quantized[0], query_scales=quantized[1], query_fp4_second=quantized[2],
+        query_scales_second=quantized[3], query_padded_bf16=scratch["query_padded_scratch"],
+        key_pages_fp4=w.regions[0], key_scales=w.regions[1], value_pages_fp4=w.regions[2], value_scales=w.regions[3],
+        fp4_page_table=w.page_table, seqused_fp4=w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
+        residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
+        seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, softmax_scale=128 ** -0.5)
+    kernel_args.num_splits = splits
+    kernel_args.bf16_split = int(parts > splits)
+    if splits > 1:
+        kernel_args.partial_out = scratch["split_partial_scratch"].data_ptr()
+        kernel_args.partial_lse = scratch["split_lse_scratch"].data_ptr()
+    kernel_args.out, kernel_args.out_row_stride = out.data_ptr(), out.stride(0)
+    stream = bdfp4.current_stream(device)
+    kernel_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                     for _ in range(args.steps)]
+    for _ in range(max(3, args.warmup)):
+        bdfp4.decode(kernel_args, stream)
+    barrier()
+    for a, b in kernel_events:
+        a.record()
+        bdfp4.decode(kernel_args, stream)
+        b.record()
+    barrier()
+    kernel_ms = max_over_ranks(statistics.mean(a.elapsed_time(b) for a, b in kernel_events))
+
+    # ---- end-to-end arm: host buffers in, host buffer out, copies inside the timed region ------
+    host_query = w.query.cpu().pin_memory()
+    host_key, host_value = new_key.cpu().pin_memory(), new_value.cpu().pin_memory()
+    host_out = torch.empty(rows, heads_q, 128, dtype=torch.bfloat16).pin_memory()
+    dev_query, dev_key, dev_value = torch.empty_like(w.query), torch.empty_like(new_key), torch.empty_like(new_value)
+
+    def e2e_step():
+        dev_query.copy_(host_query, non_blocking=True)
+        dev_key.copy_(host_key, non_blocking=True)
+        dev_value.copy_(host_value, non_blocking=True)
+        result = step(dev_query, dev_key, dev_value)
+        host_out.copy_(result, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    begin.record()
+    for _ in range(args.steps):
+        e2e_step()
+    end.record()
+    barrier()
+    e2e_ms = max_over_ranks(begin.elapsed_time(end) / args.steps)
+    h2d = host_query.numel() * 2 + host_key.numel() * 2 + host_value.numel() * 2
+    d2h = host_out.numel() * 2
+
+    # ---- quantize-on-write throughput (bulk page quantize, K and V) ---------------------------
+    from nvfp4_decode_kernel.quantize_kv_kernel import KVCacheWriter
+
+    q_pages = 2048
+    source_k = torch.randn(q_pages * 128, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+    source_v = torch.randn(q_pages * 128, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+    writer = KVCacheWriter(regions=w.regions, key_scale_mode="four_six", value_scale_mode="amax6", rotate_key=True)
+    work_src = torch.arange(q_pages, dtype=torch.int32, device=device) * 128
+    work_dst = w.page_table[0, :q_pages].contiguous()
+    for _ in range(3):
+        writer(source_k, source_v, w.regions, work_src, work_dst)
+    barrier()
+    begin.record()
+    for _ in range(5):
+        writer(source_k, source_v, w.regions, work_src, work_dst)
+    end.record()
+    barrier()
+    quant_ms = begin.elapsed_time(end) / 5
+    quant_bytes = q_pages * heads_kv * 2 * (32768 + 9216)
+    quantize_gbs = quant_bytes / (quant_ms * 1e-3) / 1e9
+
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, algorithmic_bytes)
+        total_bytes = sum(gathered)
+    else:
+        total_bytes = algorithmic_bytes
+    peak, peak_kind = measured_peak_gbs()
+    achieved = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
+    clocks = sampler.summary()
+    if rank == 0:
+        line = {
+            "metric": "decode_attn_us_per_step",
+            "value": step_ms * 1e3,
+            "unit": "us/step",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": step_ms,
+            "higher_is_better": False,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate",
+            "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD_NAME if context == CONTEXT else f"{WORKLOAD_NAME} [context overridden: {context}]",
+                "partition": f"{heads_kv} of {HEADS_KV} KV heads per rank, no collective",
+                "sink_tokens": SINK_USED, "recent_tokens": 128, "num_splits": splits,
+                "query": "two NVFP4 terms, Hadamard", "key_scale_mode": "four_six", "p_scale_mode": "amax2_or_amax6_c8",
+                "l2": "inputs (4.8 GB per step over all ranks) exceed the 126 MB L2; no flush needed",
+            },
+            "hbm_tb_s": total_bytes / (step_ms * 1e-3) / 1e12,
+            "decode_kernel_us": kernel_ms * 1e3,
+            "quantize_gb_s": quantize_gbs,
+            "roofline": {
+                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_kind": f"of {peak_kind}",
+                "kernel": "decode_kernel", "algorithmic_bytes_per_launch": algorithmic_bytes,
+            },
+            "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * (2 + (1 if splits > 1 else 0)),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(heads_kv)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--context", type=int, default=CONTEXT, help="override the context length (profiling only)")
+    parser.add_argument("--splits", type=int, default=0, help="override the split-KV count")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,180 @@
+"""ctypes binding of ``libbdfp4.so`` (declared in ``include/bdfp4.h``).
+
+The library is the product: there is no Python or CPU fallback. Importing this module
+without a built ``lib/libbdfp4.so`` raises, and so does a call that returns a non-zero status.
+Build with ``python bitdecoding-fp4_b200/build.py``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libbdfp4.so"
+
+OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE = 0, -1, -2, -3, -4
+DEV_WAIT_TIMEOUT, DEV_BAD_PAGE = 1, 2
+SCALE_MODE_IDS = {"amax6": 0, "four_six": 1, "four_six_sixhalf": 2}
+P_MODE_IDS = {"amax6": 0, "amax2_or_amax6": 1, "amax2_or_amax6_c8": 2}
+SHIFT_NONE, SHIFT_F32, SHIFT_BF16 = 0, 1, 2
+
+EXPORTS = (
+    "bdfp4_version",
+    "bdfp4_status_string",
+    "bdfp4_last_cuda_error",
+    "bdfp4_check_device",
+    "bdfp4_kv_write",
+    "bdfp4_quantize_query",
+    "bdfp4_decode",
+    "bdfp4_combine",
+)
+
+
+class LibraryMissingError(RuntimeError):
+    """``libbdfp4.so`` has not been built."""
+
+
+class KvWriteArgs(Structure):
+    _fields_ = [
+        ("key", c_void_p), ("value", c_void_p),
+        ("key_token_pitch", c_int64), ("value_token_pitch", c_int64),
+        ("source_tokens_total", c_int64),
+        ("heads", c_int32),
+        ("key_codes", c_void_p), ("key_scales", c_void_p),
+        ("value_codes", c_void_p), ("value_scales", c_void_p),
+        ("key_codes_pitch", c_int64), ("key_scales_pitch", c_int64),
+        ("value_codes_pitch", c_int64), ("value_scales_pitch", c_int64),
+        ("bases", c_void_p), ("layers", c_int32),
+        ("source_tokens", c_void_p), ("destination_pages", c_void_p), ("work_items", c_int32),
+        ("key_scale_mode", c_int32), ("value_scale_mode", c_int32),
+        ("rotate_key", c_int32), ("key_shift", c_void_p), ("key_shift_type", c_int32), ("layer", c_int32),
+        ("tail_key", c_void_p), ("tail_value", c_void_p),
+        ("tail_layer_stride", c_int64), ("tail_slot_stride", c_int64),
+        ("sink_tokens", c_int32),
+        ("query_start_loc", c_void_p), ("seq_lens", c_void_p), ("seqused_fp4", c_void_p),
+        ("row_to_slot", c_void_p),
+        ("rows", c_int32), ("decode_rows", c_int32), ("first_row", c_int32),
+        ("error_word", c_void_p),
+    ]
+
+
+class QuantizeQueryArgs(Structure):
+    _fields_ = [
+        ("query", c_void_p), ("query_row_stride", c_int64), ("query_head_stride", c_int64),
+        ("row_indices", c_void_p),
+        ("rows", c_int32), ("heads_q", c_int32), ("heads_kv", c_int32),
+        ("scale_mode", c_int32), ("rotate", c_int32),
+        ("query_codes", c_void_p), ("query_scales", c_void_p),
+        ("query_codes_second", c_void_p), ("query_scales_second", c_void_p),
+        ("query_padded", c_void_p),
+        ("new_key", c_void_p), ("new_value", c_void_p),
+        ("new_key_token_pitch", c_int64), ("new_value_token_pitch", c_int64),
+        ("tail_key", c_void_p), ("tail_value", c_void_p), ("tail_slot_stride", c_int64),
+        ("row_to_slot", c_void_p), ("seq_lens", c_void_p), ("seqused_fp4", c_void_p),
+        ("rotate_key", c_int32), ("key_shift", c_void_p), ("sink_tokens", c_int32),
+    ]
+
+
+class DecodeArgs(Structure):
+    _fields_ = [
+        ("rows", c_int32), ("heads_q", c_int32), ("heads_kv", c_int32),
+        ("query_codes", c_void_p), ("query_scales", c_void_p),
+        ("query_codes_second", c_void_p), ("query_scales_second", c_void_p),
+        ("query_padded", c_void_p),
+        ("key_codes", c_void_p), ("key_scales", c_void_p),
+        ("value_codes", c_void_p), ("value_scales", c_void_p),
+        ("key_codes_pitch", c_int64), ("key_scales_pitch", c_int64),
+        ("value_codes_pitch", c_int64), ("value_scales_pitch", c_int64),
+        ("pages", c_int32),
+        ("page_table", c_void_p), ("page_table_stride", c_int64), ("max_pages_per_row", c_int32),
+        ("seqused_fp4", c_void_p),
+        ("tail_key", c_void_p), ("tail_value", c_void_p), ("tail_slot_stride", c_int64),
+        ("tail_slots", c_int32),
+        ("tail_slot_ids", c_void_p), ("seqused_residual", c_void_p), ("seqused_sink", c_void_p),
+        ("softmax_scale", c_float), ("p_scale_mode", c_int32), ("p_scale_tau", c_float),
+        ("out", c_void_p), ("out_row_stride", c_int64),
+        ("num_splits", c_int32), ("bf16_split", c_int32),
+        ("partial_out", c_void_p), ("partial_lse", c_void_p),
+        ("error_word", c_void_p),
+    ]
+
+
+_lib = None
+
+
+def library() -> ctypes.CDLL:
+    """The loaded shared library; raises :class:`LibraryMissingError` when it was not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise LibraryMissingError(
+            f"{LIB_PATH} is missing: build it with `python bitdecoding-fp4_b200/build.py` "
+            "(there is no CPU or Python fallback)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.bdfp4_version.restype = c_int32
+    lib.bdfp4_status_string.restype = c_char_p
+    lib.bdfp4_status_string.argtypes = [c_int32]
+    lib.bdfp4_last_cuda_error.restype = c_char_p
+    lib.bdfp4_check_device.restype = c_int32
+    lib.bdfp4_kv_write.restype = c_int32
+    lib.bdfp4_kv_write.argtypes = [POINTER(KvWriteArgs), c_void_p]
+    lib.bdfp4_quantize_query.restype = c_int32
+    lib.bdfp4_quantize_query.argtypes = [POINTER(QuantizeQueryArgs), c_void_p]
+    lib.bdfp4_decode.restype = c_int32
+    lib.bdfp4_decode.argtypes = [POINTER(DecodeArgs), c_void_p]
+    lib.bdfp4_combine.restype = c_int32
+    lib.bdfp4_combine.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]
+    _lib = lib
+    return lib
+
+
+class KernelError(RuntimeError):
+    """A library call returned a non-zero status."""
+
+    def __init__(self, name: str, status: int):
+        lib = library()
+        text = lib.bdfp4_status_string(status).decode()
+        if status == E_CUDA:
+            text += ": " + lib.bdfp4_last_cuda_error().decode()
+        super().__init__(f"{name} failed with status {status} ({text})")
+        self.status = status
+
+
+def check(name: str, status: int) -> None:
+    if status != OK:
+        raise KernelError(name, status)
+
+
+def ptr(tensor) -> int | None:
+    """Device (or host) address of a torch tensor, None for None."""
+    return None if tensor is None else tensor.data_ptr()
+
+
+def current_stream(device) -> int:
+    import torch
+
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def kv_write(args: KvWriteArgs, stream: int) -> None:
+    check("bdfp4_kv_write", library().bdfp4_kv_write(ctypes.byref(args), stream))
+
+
+def quantize_query(args: QuantizeQueryArgs, stream: int) -> None:
+    check("bdfp4_quantize_query", library().bdfp4_quantize_query(ctypes.byref(args), stream))
+
+
+def decode(args: DecodeArgs, stream: int) -> None:
+    check("bdfp4_decode", library().bdfp4_decode(ctypes.byref(args), stream))
+
+
+def combine(partial_out, partial_lse, parts: int, rows: int, heads_q: int, out, out_row_stride: int,
+            stream: int) -> None:
+    check(
+        "bdfp4_combine",
+        library().bdfp4_combine(ptr(partial_out), ptr(partial_lse), parts, rows, heads_q, ptr(out),
+                                out_row_stride, stream),
+    )

@@ -1,0 +1,167 @@
+"""Seeded synthetic decode workloads: a paged NVFP4 KV cache filled through the writer kernels.
+
+Stands in for real model activations with the distributions the benchmark configuration names:
+K, V and Q are BF16 draws from N(0,1); each KV head of K has four outlier channels (fixed for the
+whole run) scaled by a lognormal(0, 1.5) factor; the block table is a random permutation of the
+physical blocks, with block 0 left unused as the serving engine's null block. The cache uses the
+serving engine's block layout: one flat ``[blocks, 2*128*H*72]`` byte tensor whose four regions
+(K codes, K scales, V codes, V scales) are strided views
+(src/nvfp4_vllm/layout.py:87-130 of OpenBitSys/BitDecoding-FP4).
+
+A sequence of ``n`` tokens holds ``fp4 = ((n-1)//128)*128`` tokens in FP4 pages, the remaining
+``n - fp4`` (1..128) in its BF16 rolling tail and its first ``min(n, sink)`` tokens again in the
+BF16 sink (src/nvfp4_vllm/control.py:62-89).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+PAGE = 128
+HEAD_DIM = 128
+
+
+def carve_cache(blocks: torch.Tensor, heads: int):
+    """Four region views of a flat ``[num_blocks, 2*128*H*72]`` u8 cache."""
+    num_blocks, block_bytes = blocks.shape
+    assert block_bytes == 2 * PAGE * heads * 72
+    pitch = blocks.stride(0)
+    base = blocks
+    key_codes = base.as_strided((num_blocks, PAGE, heads, 64), (pitch, heads * 64, 64, 1), base.storage_offset())
+    key_scales = base.as_strided(
+        (num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024), base.storage_offset() + 8192 * heads
+    )
+    value_codes = base.as_strided(
+        (num_blocks, heads, HEAD_DIM, 64), (pitch, HEAD_DIM * 64, 64, 1), base.storage_offset() + 9216 * heads
+    )
+    value_scales = base.as_strided(
+        (num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024), base.storage_offset() + 17408 * heads
+    )
+    return key_codes, key_scales, value_codes, value_scales
+
+
+def split_lengths(seq_len: int, sink_tokens: int):
+    sink = min(seq_len, sink_tokens)
+    fp4 = ((seq_len - 1) // PAGE) * PAGE if seq_len else 0
+    return sink, fp4, seq_len - fp4
+
+
+@dataclass
+class Workload:
+    rows: int
+    heads_q: int
+    heads_kv: int
+    seq_lens: list
+    sink_tokens: int
+    device: torch.device
+    blocks: torch.Tensor = None
+    regions: tuple = None
+    page_table: torch.Tensor = None
+    seqused_fp4: torch.Tensor = None
+    seqused_residual: torch.Tensor = None
+    seqused_sink: torch.Tensor = None
+    tail_key: torch.Tensor = None      # [1, slots, 128+sink, H, 128]
+    tail_value: torch.Tensor = None
+    slot_ids: torch.Tensor = None
+    query: torch.Tensor = None
+    key_shift: torch.Tensor | None = None
+    rotate: bool = False
+    outlier_scale: torch.Tensor = None  # [H, 128] multiplicative factors applied to K
+    kept: dict = field(default_factory=dict)  # raw BF16 K/V of each row when keep_source
+
+    def algorithmic_bytes(self) -> int:
+        """Bytes one decode step must move: FP4 K/V codes and scales, BF16 tail and sink rows,
+        query in, output out, and the page-table entries consumed."""
+        total = 0
+        for n in self.seq_lens:
+            sink, fp4, tail = split_lengths(n, self.sink_tokens)
+            total += fp4 * self.heads_kv * 144 + (tail + sink) * self.heads_kv * 512 + (fp4 // PAGE) * 4
+        return total + self.rows * self.heads_q * HEAD_DIM * 2 * 2
+
+
+def build_workload(
+    *, rows: int, heads_q: int, heads_kv: int, seq_lens, sink_tokens: int = 16, seed: int = 0,
+    device="cuda", key_scale_mode: str = "amax6", value_scale_mode: str = "amax6", rotate: bool = False,
+    key_shift: bool = False, shuffle: bool = True, keep_source: bool = False, chunk_pages: int = 256,
+) -> Workload:
+    """Generate K/V, quantize them into a paged cache with ``KVCacheWriter`` and fill the BF16
+    tail and sink, sequence by sequence so that temporaries stay bounded."""
+    from nvfp4_decode_kernel.quantize_kv_kernel import KVCacheWriter
+
+    device = torch.device(device)
+    seq_lens = [int(n) for n in seq_lens]
+    assert len(seq_lens) == rows
+    gen = torch.Generator(device=device).manual_seed(seed)
+    w = Workload(rows, heads_q, heads_kv, seq_lens, sink_tokens, device, rotate=rotate)
+    pages_per_row = [split_lengths(n, sink_tokens)[1] // PAGE for n in seq_lens]
+    max_pages = max(1, max(pages_per_row))
+    num_blocks = 1 + sum(pages_per_row)
+    w.blocks = torch.zeros(num_blocks, 2 * PAGE * heads_kv * 72, dtype=torch.uint8, device=device)
+    w.regions = carve_cache(w.blocks, heads_kv)
+    order = torch.randperm(num_blocks - 1, generator=gen, device=device) + 1 if shuffle else torch.arange(
+        1, num_blocks, device=device)
+    w.page_table = torch.zeros(rows, max_pages, dtype=torch.int32, device=device)
+    tail_rows = PAGE + sink_tokens
+    w.tail_key = torch.zeros(1, rows, tail_rows, heads_kv, HEAD_DIM, dtype=torch.bfloat16, device=device)
+    w.tail_value = torch.zeros_like(w.tail_key)
+    w.slot_ids = torch.arange(rows, dtype=torch.int32, device=device)
+    # outlier channels: 4 per KV head, fixed for the run
+    w.outlier_scale = torch.ones(heads_kv, HEAD_DIM, device=device)
+    for h in range(heads_kv):
+        channels = torch.randperm(HEAD_DIM, generator=gen, device=device)[:4]
+        w.outlier_scale[h, channels] = torch.exp(1.5 * torch.randn(4, generator=gen, device=device))
+    if key_shift:
+        w.key_shift = (0.25 * torch.randn(1, heads_kv, HEAD_DIM, generator=gen, device=device)).float()
+    writer = KVCacheWriter(
+        regions=w.regions, key_scale_mode=key_scale_mode, value_scale_mode=value_scale_mode,
+        rotate_key=rotate, key_shift=w.key_shift, tail_key=w.tail_key, tail_value=w.tail_value,
+        sink_tokens=sink_tokens,
+    )
+    cursor = 0
+    fp4_list, tail_list, sink_list = [], [], []
+    for row, n in enumerate(seq_lens):
+        sink, fp4, tail = split_lengths(n, sink_tokens)
+        fp4_list.append(fp4)
+        tail_list.append(tail)
+        sink_list.append(sink)
+        pages = fp4 // PAGE
+        ids = order[cursor:cursor + pages].to(torch.int32)
+        cursor += pages
+        w.page_table[row, :pages] = ids
+        kept_k, kept_v = [], []
+        # FP4 pages, in chunks; the chunk that holds the sequence's last tokens also writes the tail
+        starts = list(range(0, fp4, chunk_pages * PAGE)) or [0]
+        for start in starts:
+            stop = min(fp4, start + chunk_pages * PAGE)
+            last = start == starts[-1]
+            tokens_here = (n - start) if last else (stop - start)
+            k = torch.randn(tokens_here, heads_kv, HEAD_DIM, generator=gen, device=device)
+            k = (k * w.outlier_scale).to(torch.bfloat16)
+            v = torch.randn(tokens_here, heads_kv, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+            if keep_source:
+                kept_k.append(k)
+                kept_v.append(v)
+            chunk = (stop - start) // PAGE
+            source_tokens = torch.arange(chunk, dtype=torch.int32, device=device) * PAGE
+            destination = ids[start // PAGE:start // PAGE + chunk].contiguous()
+            if last or (start == 0 and sink):
+                # a one-row "prefill" whose computed prefix is `start`: tail candidates cover the
+                # rolling page past the FP4 prefix and the sink positions this chunk holds
+                qsl = torch.tensor([0, tokens_here], dtype=torch.int32, device=device)
+                seq = torch.tensor([start + tokens_here], dtype=torch.int32, device=device)
+                used = torch.tensor([fp4 if last else start + tokens_here], dtype=torch.int32, device=device)
+                slot = torch.tensor([row], dtype=torch.int32, device=device)
+                writer(k, v, w.regions, source_tokens, destination, qsl, seq, used, slot, 0, 0, 0)
+            else:
+                empty = torch.zeros(0, dtype=torch.int32, device=device)
+                qsl = torch.zeros(1, dtype=torch.int32, device=device)
+                writer(k, v, w.regions, source_tokens, destination, qsl, empty, empty, empty, 0, 0, 0)
+        if keep_source:
+            w.kept[row] = (torch.cat(kept_k), torch.cat(kept_v))
+    w.seqused_fp4 = torch.tensor(fp4_list, dtype=torch.int32, device=device)
+    w.seqused_residual = torch.tensor(tail_list, dtype=torch.int32, device=device)
+    w.seqused_sink = torch.tensor(sink_list, dtype=torch.int32, device=device)
+    w.query = torch.randn(rows, heads_q, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    return w

@@ -1,0 +1,852 @@
+// Paged FP4 decode attention for sm_100a.
+//
+// One CTA serves one (decode row, KV head[, split]). Per 128-token page it streams
+//   K codes 8 KB + K scales 1 KB and V codes 8 KB + V scales 1 KB
+// from HBM with TMA into shared-memory rings, and runs two block-scaled tcgen05 MMAs with
+// accumulators in tensor memory:
+//   S^T[token, q] = K[token, :] . Q[q, :]       A = K page  (128 x 128 E2M1), B = Q tile
+//   O^T[chan,  q] = V^T[chan, :] . P[q, :]      A = V page  (128 x 128 E2M1), B = P tile
+// Both are M = 128, K = 128 (two K = 64 instructions). Transposed this way a softmax thread
+// owns one token (TMEM lane) and the G query heads of the KV head are a handful of columns.
+//
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (one thread) and TMEM owner, warps 2-5
+// softmax: they read S^T with tcgen05.ld, keep the online-softmax statistics, quantize the
+// probabilities to E2M1 + E4M3 scales straight into the shared-memory B operand of the PV MMA,
+// and accumulate each page's O^T (read back from TMEM) in registers. The BF16 tail (first) and
+// sink (last) blocks are at most 144 tokens and are merged by the same warps with plain FMAs.
+//
+// Block order, masks, the stale-maximum rule and the probability scale rule follow
+// src/nvfp4_decode_kernel/fp4_decode_kernel.py:4830-5055,5352-5854 of OpenBitSys/BitDecoding-FP4.
+#include <cmath>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+#include "host.h"
+#include "tcgen05.cuh"
+
+namespace bdfp4 {
+
+constexpr int kStageBytes = 8192 + 1024;  // codes + scales of one K or V page-head
+constexpr int kNP = 16;                   // N of the PV MMA (query rows, padded)
+constexpr int kTmemColumns = 256;
+constexpr float kRescaleThreshold = 8.0f;  // src/nvfp4_decode_kernel/fp4_decode_kernel.py:93
+
+// TMEM column map (each scale-factor block sits on a 16-column boundary)
+constexpr int kColS = 0;      // 2 stages x NQ (<= 32) columns
+constexpr int kColO = 64;     // 2 stages x 16
+constexpr int kColSFQ = 96;   // 8
+constexpr int kColSFK = 112;  // 2 stages x 16 (8 used)
+constexpr int kColSFV = 144;
+constexpr int kColSFP = 176;
+
+struct DecodeParams {
+  int rows, heads_q, heads_kv, ratio;
+  const uint8_t* q_codes[2];
+  const uint8_t* q_scales[2];
+  const __nv_bfloat16* q_padded;
+  const uint8_t* k_scales;
+  const uint8_t* v_scales;
+  int64_t k_scales_pitch, v_scales_pitch;
+  int pages;
+  const int32_t* page_table;
+  int64_t page_table_stride;
+  int max_pages;
+  const int32_t* seqused_fp4;
+  const __nv_bfloat16* tail_key;
+  const __nv_bfloat16* tail_value;
+  int64_t tail_slot_stride;
+  int tail_slots;
+  const int32_t* tail_slot_ids;
+  const int32_t* seqused_residual;
+  const int32_t* seqused_sink;
+  float scale_log2;
+  int p_mode;
+  float tau;
+  __nv_bfloat16* out;
+  int64_t out_row_stride;
+  int num_splits, bf16_split, parts;
+  float* partial_out;
+  float* partial_lse;
+  int32_t* error_word;
+};
+
+template <int GP>
+struct DecodeSmem {
+  static constexpr int kStages = GP == 16 ? 4 : 5;
+  alignas(1024) uint8_t k_stage[kStages][kStageBytes];
+  alignas(1024) uint8_t v_stage[kStages][kStageBytes];
+  alignas(1024) uint8_t q_tile[32 * 64];
+  alignas(1024) uint8_t p_tile[2][kNP * 64];
+  alignas(1024) uint8_t q_sf[1024];
+  alignas(1024) uint8_t p_sf[2][1024];
+  float q_bf16[GP][128];  // BF16 query of the tail/sink blocks, widened
+  float p_bf16[GP][128];  // BF16-rounded probabilities of a tail/sink block
+  float red[2][4][GP];
+  float sum_red[4][GP];
+  uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ bool softmax_vote_any(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+// Physical byte offset of logical byte `offset` in a K-major tile of 64-byte rows under the
+// 64-byte swizzle: the 16-byte chunk index is XORed with bits [7,9) of the offset.
+__device__ __forceinline__ int swizzle64(int offset) { return offset ^ (((offset >> 7) & 3) << 4); }
+
+// Scale of one group of sixteen probabilities from its maximum
+// (src/nvfp4_decode_kernel/_fa4/softmax.py:80-112).
+__device__ __forceinline__ float probability_scale(float maximum, int p_mode, float tau) {
+  float scale = __fmul_rn(maximum, (float)(1.0 / 6.0));
+  if (p_mode != BDFP4_P_AMAX6 && maximum <= tau) scale = __fmul_rn(maximum, 0.5f);
+  return scale;
+}
+
+// Online-softmax state of one softmax thread: the statistics of the KV head's GP query heads
+// (row_max identical in every thread, row_sum a per-thread partial) and the output
+// accumulator of the thread's channel.
+template <int GP>
+struct SoftmaxState {
+  float row_max[GP];
+  float row_sum[GP];
+  float o_acc[GP];
+  bool first;
+};
+
+// Update the running maxima with a block's maxima; returns the factors the previous
+// accumulations must be multiplied by and the maximum the block's probabilities are formed
+// against (scaled to log2 units, with the c8 shift folded in).
+template <int GP>
+__device__ __forceinline__ void update_max(SoftmaxState<GP>& st, const float* block_max, float scale_log2,
+                                           float shift, float* acc, float* max_scaled) {
+#pragma unroll
+  for (int j = 0; j < GP; ++j) {
+    float new_max, safe;
+    if (st.first) {
+      new_max = block_max[j];
+      safe = new_max == -INFINITY ? 0.0f : new_max;
+      acc[j] = 0.0f;
+    } else {
+      const float old_max = st.row_max[j];
+      new_max = fmaxf(old_max, block_max[j]);
+      safe = new_max == -INFINITY ? 0.0f : new_max;
+      const float growth = (old_max - safe) * scale_log2;
+      if (growth >= -kRescaleThreshold) {
+        new_max = old_max;
+        safe = old_max;
+        acc[j] = 1.0f;
+      } else {
+        acc[j] = ex2_approx(growth);
+      }
+    }
+    st.row_max[j] = new_max;
+    max_scaled[j] = safe * scale_log2 - shift;
+  }
+}
+
+// A BF16 block (the rolling tail or the sink) merged with plain FMAs by the 128 softmax threads:
+// thread `t` scores token `t`, then accumulates channel `t`. `rows0` is the first row of the
+// block inside the slot's buffer, positions outside [mask_below, length) are masked.
+template <int GP>
+__device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP>& sm, const DecodeParams& p, int t,
+                                           int warp_q, int lane, const __nv_bfloat16* key_rows,
+                                           const __nv_bfloat16* value_rows, int mask_below, int length, float shift,
+                                           int& red_buf) {
+  const int64_t row_elems = (int64_t)p.heads_kv * kHeadDim;
+  float s[GP];
+  const bool valid = t >= mask_below && t < length;
+#pragma unroll
+  for (int j = 0; j < GP; ++j) s[j] = valid ? 0.0f : -INFINITY;
+  if (valid) {
+    const uint4* krow = reinterpret_cast<const uint4*>(key_rows + (int64_t)t * row_elems);
+#pragma unroll 4
+    for (int c = 0; c < 16; ++c) {
+      const uint4 raw = __ldg(krow + c);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      float k[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        k[2 * i] = __uint_as_float(w[i] << 16);
+        k[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][c * 8]);
+        const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][c * 8 + 4]);
+        float a = s[j];
+        a = fmaf(k[0], q0.x, a);
+        a = fmaf(k[1], q0.y, a);
+        a = fmaf(k[2], q0.z, a);
+        a = fmaf(k[3], q0.w, a);
+        a = fmaf(k[4], q1.x, a);
+        a = fmaf(k[5], q1.y, a);
+        a = fmaf(k[6], q1.z, a);
+        a = fmaf(k[7], q1.w, a);
+        s[j] = a;
+      }
+    }
+  }
+  float block_max[GP];
+#pragma unroll
+  for (int j = 0; j < GP; ++j) {
+    float m = s[j];
+#pragma unroll
+    for (int step = 1; step < 32; step <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, step));
+    block_max[j] = m;
+  }
+  if (lane < GP) {
+    float mine = block_max[0];
+#pragma unroll
+    for (int j = 1; j < GP; ++j) mine = lane == j ? block_max[j] : mine;
+    sm.red[red_buf][warp_q][lane] = mine;
+  }
+  softmax_barrier();
+#pragma unroll
+  for (int j = 0; j < GP; ++j)
+    block_max[j] = fmaxf(fmaxf(sm.red[red_buf][0][j], sm.red[red_buf][1][j]),
+                         fmaxf(sm.red[red_buf][2][j], sm.red[red_buf][3][j]));
+  red_buf ^= 1;
+  float acc[GP], max_scaled[GP];
+  update_max<GP>(st, block_max, p.scale_log2, shift, acc, max_scaled);
+  st.first = false;
+#pragma unroll
+  for (int j = 0; j < GP; ++j) {
+    const float prob = ex2_approx(s[j] * p.scale_log2 - max_scaled[j]);
+    st.row_sum[j] = st.row_sum[j] * acc[j] + prob;
+    sm.p_bf16[j][t] = __bfloat162float(__float2bfloat16_rn(prob));
+    st.o_acc[j] *= acc[j];
+  }
+  softmax_barrier();
+  const __nv_bfloat16* vcol = value_rows + t;
+  for (int token = 0; token < length; ++token) {
+    const float v = __bfloat162float(vcol[(int64_t)token * row_elems]);
+#pragma unroll
+    for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(sm.p_bf16[j][token], v, st.o_acc[j]);
+  }
+  softmax_barrier();  // p_bf16 is reused by the next BF16 block
+}
+
+template <int GP, int TERMS>
+__global__ void __launch_bounds__(192) decode_kernel(const __grid_constant__ CUtensorMap k_map,
+                                                     const __grid_constant__ CUtensorMap v_map, const DecodeParams p) {
+  using Smem = DecodeSmem<GP>;
+  constexpr int KS = Smem::kStages;
+  constexpr int NQ = GP <= 8 ? 16 : 32;  // N of the QK MMA: term 0 in columns [0, GP), term 1 from NQ/2
+  constexpr int LD = GP <= 4 ? 4 : (GP <= 8 ? 8 : 16);
+  extern __shared__ uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- which work ---------------------------------------------------------------------------
+  const int part = blockIdx.x % p.parts;
+  const int kv_head = (blockIdx.x / p.parts) % p.heads_kv;
+  const int row = blockIdx.x / (p.parts * p.heads_kv);
+  const int G = p.ratio;
+  const int total_pages = min(p.seqused_fp4[row] / kPage, p.max_pages);
+  int first_page = 0, last_page = total_pages;
+  bool with_bf16 = p.tail_key != nullptr;
+  if (p.num_splits > 1) {
+    if (part < p.num_splits) {
+      const int chunk = (total_pages + p.num_splits - 1) / p.num_splits;
+      first_page = min(part * chunk, total_pages);
+      last_page = min(first_page + chunk, total_pages);
+      with_bf16 = with_bf16 && !p.bf16_split && part == 0;
+    } else {
+      first_page = last_page = 0;
+    }
+  }
+  const int num_pages = last_page - first_page;
+  int slot = -1, tail_len = 0, sink_len = 0;
+  if (p.tail_key) {
+    slot = p.tail_slot_ids[row];
+    if (slot >= 0 && slot < p.tail_slots) {
+      tail_len = min(max(p.seqused_residual[row], 0), kPage);
+      if (p.seqused_sink) sink_len = min(max(p.seqused_sink[row], 0), BDFP4_MAX_SINK);
+    } else {
+      slot = 0;
+    }
+  }
+
+  // ---- set-up -------------------------------------------------------------------------------
+  if (tid == 0) {
+    for (int s = 0; s < KS; ++s) {
+      tc::mbar_init(&sm.k_full[s], 1);
+      tc::mbar_init(&sm.k_empty[s], 1);
+      tc::mbar_init(&sm.v_full[s], 1);
+      tc::mbar_init(&sm.v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      tc::mbar_init(&sm.s_full[s], 1);
+      tc::mbar_init(&sm.s_empty[s], 128);
+      tc::mbar_init(&sm.p_full[s], 128);
+      tc::mbar_init(&sm.p_empty[s], 1);
+      tc::mbar_init(&sm.o_full[s], 1);
+      tc::mbar_init(&sm.o_empty[s], 128);
+    }
+    sm.abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tensormap(&k_map);
+    tc::prefetch_tensormap(&v_map);
+  }
+  // Q tile (B operand of QK), its scale atoms, zeroed P buffers, widened BF16 query
+  for (int i = tid; i < (32 * 64 + 2 * kNP * 64 + 1024 + 2 * 1024) / 16; i += 192) {
+    uint4* base;
+    int index = i;
+    if (index < 128) {
+      base = reinterpret_cast<uint4*>(sm.q_tile);
+    } else if (index < 128 + 128) {
+      base = reinterpret_cast<uint4*>(sm.p_tile);
+      index -= 128;
+    } else if (index < 256 + 64) {
+      base = reinterpret_cast<uint4*>(sm.q_sf);
+      index -= 256;
+    } else {
+      base = reinterpret_cast<uint4*>(sm.p_sf);
+      index -= 320;
+    }
+    base[index] = make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  for (int i = tid; i < TERMS * G * 4; i += 192) {  // 16-byte chunks of the query codes
+    const int chunk = i & 3;
+    const int g = (i >> 2) % G;
+    const int term = (i >> 2) / G;
+    const int n = term * (NQ / 2) + g;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q_codes[term] +
+                                                         ((int64_t)row * p.heads_q + kv_head * G + g) * 64) + chunk);
+    *reinterpret_cast<uint4*>(sm.q_tile + swizzle64(n * 64 + chunk * 16)) = v;
+  }
+  for (int i = tid; i < TERMS * G * 2; i += 192) {  // 4 scale bytes of (term, head, atom)
+    const int atom = i & 1;
+    const int g = (i >> 1) % G;
+    const int term = (i >> 1) / G;
+    const int n = term * (NQ / 2) + g;
+    const uint8_t* tile = p.q_scales[term] + ((int64_t)row * p.heads_q + kv_head) * 1024;
+    *reinterpret_cast<uint32_t*>(sm.q_sf + atom * 512 + n * 16) =
+        __ldg(reinterpret_cast<const uint32_t*>(tile + atom * 512 + g * 16));
+  }
+  if (with_bf16) {
+    for (int i = tid; i < GP * 128; i += 192) {
+      const int g = i >> 7, c = i & 127;
+      float v = 0.0f;
+      if (g < G)
+        v = __bfloat162float(p.q_padded[(((int64_t)row * kPage) * p.heads_q + kv_head * G + g) * kHeadDim + c]);
+      sm.q_bf16[g][c] = v;
+    }
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(&sm.tmem_base, kTmemColumns);
+    tc::tmem_relinquish();
+  }
+  tc::fence_proxy_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (warp == 0) {
+    // ---- TMA producer -----------------------------------------------------------------------
+    int issued = 0;
+    for (int base = 0; base < num_pages; base += 32) {
+      const int count = min(32, num_pages - base);
+      int my_page = 0;
+      if (lane < count) {
+        const int logical = last_page - 1 - (base + lane);
+        my_page = p.page_table[(int64_t)row * p.page_table_stride + logical];
+        if (my_page < 0 || my_page >= p.pages) {
+          if (p.error_word) atomicOr(p.error_word, (int)BDFP4_DEV_BAD_PAGE);
+          my_page = min(max(my_page, 0), p.pages - 1);
+        }
+      }
+      bool ok = true;
+      for (int j = 0; j < count && ok; ++j) {
+        const int page = __shfl_sync(0xffffffffu, my_page, j);
+        if (lane == 0) {
+          const int i = base + j;
+          const int s = i % KS;
+          const uint32_t parity = ((i / KS) & 1) ^ 1;
+          ok = tc::mbar_wait(&sm.k_empty[s], parity, abort_flag);
+          if (ok) {
+            tc::mbar_expect_tx(&sm.k_full[s], kStageBytes);
+            tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
+            tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 1024, 1024,
+                          &sm.k_full[s]);
+            ok = tc::mbar_wait(&sm.v_empty[s], parity, abort_flag);
+          }
+          if (ok) {
+            tc::mbar_expect_tx(&sm.v_full[s], kStageBytes);
+            tc::tma_load_3d(sm.v_stage[s], &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page);
+            tc::bulk_load(sm.v_stage[s] + 8192, p.v_scales + (int64_t)page * p.v_scales_pitch + kv_head * 1024, 1024,
+                          &sm.v_full[s]);
+            issued = i + 1;
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      }
+      if (!ok) break;
+    }
+    // After a give-up, wait (bounded) until every copy already in flight has landed, so that no
+    // bulk copy can write into this CTA's shared memory after it exits.
+    if (lane == 0 && *abort_flag) {
+      const uint64_t start = tc::global_timer_ns();
+      for (int i = max(0, issued - KS); i < issued; ++i) {
+        const int s = i % KS;
+        const uint32_t parity = (i / KS) & 1;
+        while (!tc::mbar_try_wait(&sm.k_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
+        }
+        while (!tc::mbar_try_wait(&sm.v_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ---------------------------------------------------------------------------
+    if (lane == 0 && num_pages > 0) {
+      constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, NQ);
+      constexpr uint32_t idesc_pv = tc::nvf4_idesc(128, kNP);
+      const uint32_t q_addr = tc::smem_u32(sm.q_tile);
+      tc::cp_sf_atom(tmem + kColSFQ, tc::sf_atom_desc(tc::smem_u32(sm.q_sf)));
+      tc::cp_sf_atom(tmem + kColSFQ + 4, tc::sf_atom_desc(tc::smem_u32(sm.q_sf) + 512));
+      auto issue_pv = [&](int m) -> bool {
+        const int s = m % KS;
+        const int b = m & 1;
+        const uint32_t ring_parity = (m / KS) & 1;
+        const uint32_t pair_parity = (m >> 1) & 1;
+        if (!tc::mbar_wait(&sm.v_full[s], ring_parity, abort_flag)) return false;
+        if (!tc::mbar_wait(&sm.p_full[b], pair_parity, abort_flag)) return false;
+        tc::fence_after_sync();
+        const uint32_t v_addr = tc::smem_u32(sm.v_stage[s]);
+        const uint32_t p_addr = tc::smem_u32(sm.p_tile[b]);
+        tc::cp_sf_atom(tmem + kColSFV + 16 * b, tc::sf_atom_desc(v_addr + 8192));
+        tc::cp_sf_atom(tmem + kColSFV + 16 * b + 4, tc::sf_atom_desc(v_addr + 8192 + 512));
+        tc::cp_sf_atom(tmem + kColSFP + 16 * b, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b])));
+        tc::cp_sf_atom(tmem + kColSFP + 16 * b + 4, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b]) + 512));
+        if (!tc::mbar_wait(&sm.o_empty[b], pair_parity ^ 1, abort_flag)) return false;
+        tc::fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+          tc::mma_nvf4(tmem + kColO + 16 * b, tc::fp4_tile_desc(v_addr, k), tc::fp4_tile_desc(p_addr, k), idesc_pv,
+                       tmem + kColSFV + 16 * b + 4 * k, tmem + kColSFP + 16 * b + 4 * k, k != 0);
+        tc::commit(&sm.o_full[b]);
+        tc::commit(&sm.v_empty[s]);
+        tc::commit(&sm.p_empty[b]);
+        return true;
+      };
+      bool ok = true;
+      for (int i = 0; i < num_pages && ok; ++i) {
+        const int s = i % KS;
+        const int b = i & 1;
+        ok = tc::mbar_wait(&sm.k_full[s], (i / KS) & 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_sync();
+        const uint32_t k_addr = tc::smem_u32(sm.k_stage[s]);
+        tc::cp_sf_atom(tmem + kColSFK + 16 * b, tc::sf_atom_desc(k_addr + 8192));
+        tc::cp_sf_atom(tmem + kColSFK + 16 * b + 4, tc::sf_atom_desc(k_addr + 8192 + 512));
+        ok = tc::mbar_wait(&sm.s_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+          tc::mma_nvf4(tmem + kColS + NQ * b, tc::fp4_tile_desc(k_addr, k), tc::fp4_tile_desc(q_addr, k), idesc_qk,
+                       tmem + kColSFK + 16 * b + 4 * k, tmem + kColSFQ + 4 * k, k != 0);
+        tc::commit(&sm.s_full[b]);
+        tc::commit(&sm.k_empty[s]);
+        if (i > 0) ok = issue_pv(i - 1);
+      }
+      if (ok) issue_pv(num_pages - 1);
+    }
+  } else {
+    // ---- softmax / accumulate -----------------------------------------------------------------
+    const int warp_q = warp & 3;        // TMEM lane quarter this warp may read
+    const int t = warp_q * 32 + lane;   // token (S^T lane) and channel (O^T lane) of this thread
+    const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
+    const float shift = p.p_mode == BDFP4_P_AMAX2_OR_AMAX6_C8 ? 3.0f : 0.0f;
+    SoftmaxState<GP> st;
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      st.row_max[j] = -INFINITY;
+      st.row_sum[j] = 0.0f;
+      st.o_acc[j] = 0.0f;
+    }
+    st.first = true;
+    int red_buf = 0;
+    const __nv_bfloat16* tail_k = p.tail_key ? p.tail_key + (int64_t)slot * p.tail_slot_stride + kv_head * kHeadDim : nullptr;
+    const __nv_bfloat16* tail_v = p.tail_value ? p.tail_value + (int64_t)slot * p.tail_slot_stride + kv_head * kHeadDim : nullptr;
+    const int64_t row_elems = (int64_t)p.heads_kv * kHeadDim;
+
+    if (with_bf16) {
+      // While page zero has not been sealed the rolling page still holds the sink's tokens.
+      const int mask_below = total_pages == 0 ? sink_len : 0;
+      bf16_block<GP>(st, sm, p, t, warp_q, lane, tail_k, tail_v, mask_below, tail_len, shift, red_buf);
+    }
+
+    float acc_prev[GP];
+#pragma unroll
+    for (int j = 0; j < GP; ++j) acc_prev[j] = 1.0f;
+    bool stop = false;
+    for (int i = 0; i < num_pages && !stop; ++i) {
+      const int b = i & 1;
+      const uint32_t parity = (i >> 1) & 1;
+      const int logical_page = last_page - 1 - i;
+      tc::mbar_wait(&sm.s_full[b], parity, abort_flag);
+      tc::fence_after_sync();
+      float s[GP];
+      {
+        float raw[LD];
+        tc::tmem_ld<LD>(lane_base + kColS + NQ * b, raw);
+        if (TERMS == 2) {
+          float raw2[LD];
+          tc::tmem_ld<LD>(lane_base + kColS + NQ * b + NQ / 2, raw2);
+          tc::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < GP; ++j) s[j] = raw[j] + raw2[j];
+        } else {
+          tc::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < GP; ++j) s[j] = raw[j];
+        }
+      }
+      tc::fence_before_sync();
+      tc::mbar_arrive(&sm.s_empty[b]);
+      if (logical_page == 0 && t < sink_len) {
+#pragma unroll
+        for (int j = 0; j < GP; ++j) s[j] = -INFINITY;
+      }
+      // does any row's maximum grow past the threshold? (a NaN difference counts as growth)
+      bool grows = true;
+      if (!st.first) {
+        bool own = *abort_flag != 0;
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          const float grown = (st.row_max[j] - fmaxf(st.row_max[j], s[j])) * p.scale_log2;
+          own = own || !(grown >= -kRescaleThreshold);
+        }
+        grows = softmax_vote_any(own);
+      }
+      float group_max[GP];
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        float m = s[j];
+#pragma unroll
+        for (int step = 1; step < 16; step <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, step));
+        group_max[j] = m;
+      }
+      float acc[GP], max_scaled[GP];
+      if (grows) {
+        float block_max[GP];
+#pragma unroll
+        for (int j = 0; j < GP; ++j) block_max[j] = fmaxf(group_max[j], __shfl_xor_sync(0xffffffffu, group_max[j], 16));
+        if (lane < GP) {
+          float mine = block_max[0];
+#pragma unroll
+          for (int j = 1; j < GP; ++j) mine = lane == j ? block_max[j] : mine;
+          sm.red[red_buf][warp_q][lane] = mine;
+        }
+        softmax_barrier();
+#pragma unroll
+        for (int j = 0; j < GP; ++j)
+          block_max[j] = fmaxf(fmaxf(sm.red[red_buf][0][j], sm.red[red_buf][1][j]),
+                               fmaxf(sm.red[red_buf][2][j], sm.red[red_buf][3][j]));
+        red_buf ^= 1;
+        update_max<GP>(st, block_max, p.scale_log2, shift, acc, max_scaled);
+        stop = *abort_flag != 0;  // uniform: every thread reads it after the same barrier
+      } else {
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          acc[j] = 1.0f;
+          const float safe = st.row_max[j] == -INFINITY ? 0.0f : st.row_max[j];
+          max_scaled[j] = safe * p.scale_log2 - shift;
+        }
+      }
+      st.first = false;
+      uint32_t words[GP];
+      float group_scale[GP];
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        const float prob = ex2_approx(s[j] * p.scale_log2 - max_scaled[j]);
+        st.row_sum[j] = st.row_sum[j] * acc[j] + prob;
+        const float maximum = ex2_approx(group_max[j] * p.scale_log2 - max_scaled[j]);
+        const float scale = probability_scale(maximum, p.p_mode, p.tau);
+        group_scale[j] = scale;
+        const float q = prob * rcp_approx(fmaxf(scale, 1e-20f));
+        uint32_t word = (cvt_e2m1x2(q, 0.0f) & 0xfu) << (4 * (lane & 7));
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+        word |= __shfl_xor_sync(0xffffffffu, word, 4);
+        words[j] = word;
+      }
+      // the PV MMA of two pages ago must be done with this P buffer
+      tc::mbar_wait(&sm.p_empty[b], parity ^ 1, abort_flag);
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        if ((lane & 7) == (j & 7))
+          *reinterpret_cast<uint32_t*>(sm.p_tile[b] + swizzle64(j * 64 + (t >> 3) * 4)) = words[j];
+        if ((lane & 15) == j) {
+          const int group = t >> 4;
+          sm.p_sf[b][(group >> 2) * 512 + j * 16 + (group & 3)] = (uint8_t)cvt_e4m3(group_scale[j]);
+        }
+      }
+      tc::fence_proxy_async_smem();
+      tc::mbar_arrive(&sm.p_full[b]);
+
+      if (i > 0) {  // fold in the previous page's O^T
+        const int pb = (i - 1) & 1;
+        tc::mbar_wait(&sm.o_full[pb], ((i - 1) >> 1) & 1, abort_flag);
+        tc::fence_after_sync();
+        float o[LD];
+        tc::tmem_ld<LD>(lane_base + kColO + 16 * pb, o);
+        tc::tmem_wait_ld();
+        tc::fence_before_sync();
+        tc::mbar_arrive(&sm.o_empty[pb]);
+#pragma unroll
+        for (int j = 0; j < GP; ++j) st.o_acc[j] = st.o_acc[j] * acc_prev[j] + o[j];
+      }
+#pragma unroll
+      for (int j = 0; j < GP; ++j) acc_prev[j] = acc[j];
+    }
+    if (num_pages > 0) {
+      const int pb = (num_pages - 1) & 1;
+      tc::mbar_wait(&sm.o_full[pb], ((num_pages - 1) >> 1) & 1, abort_flag);
+      tc::fence_after_sync();
+      float o[LD];
+      tc::tmem_ld<LD>(lane_base + kColO + 16 * pb, o);
+      tc::tmem_wait_ld();
+      tc::fence_before_sync();
+#pragma unroll
+      for (int j = 0; j < GP; ++j) st.o_acc[j] = st.o_acc[j] * acc_prev[j] + o[j];
+    }
+    if (with_bf16 && p.seqused_sink) {
+      bf16_block<GP>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,
+                     tail_v + (int64_t)kPage * row_elems, 0, sink_len, shift, red_buf);
+    }
+
+    // ---- normalise and write ------------------------------------------------------------------
+    float total[GP];
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      float v = st.row_sum[j];
+#pragma unroll
+      for (int step = 1; step < 32; step <<= 1) v += __shfl_xor_sync(0xffffffffu, v, step);
+      total[j] = v;
+    }
+    if (lane < GP) {
+      float mine = total[0];
+#pragma unroll
+      for (int j = 1; j < GP; ++j) mine = lane == j ? total[j] : mine;
+      sm.sum_red[warp_q][lane] = mine;
+    }
+    softmax_barrier();
+#pragma unroll
+    for (int j = 0; j < GP; ++j)
+      total[j] = (sm.sum_red[0][j] + sm.sum_red[1][j]) + (sm.sum_red[2][j] + sm.sum_red[3][j]);
+    const bool skip = p.num_splits > 1 && part == p.num_splits && p.tail_key == nullptr;
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      if (j < G && !skip) {
+        const bool empty = total[j] == 0.0f || total[j] != total[j];
+        const float value = empty ? 0.0f : st.o_acc[j] * (1.0f / total[j]);
+        const int head = kv_head * G + j;
+        if (p.num_splits == 1) {
+          p.out[(int64_t)row * p.out_row_stride + head * kHeadDim + t] = __float2bfloat16_rn(value);
+        } else {
+          p.partial_out[(((int64_t)part * p.rows + row) * p.heads_q + head) * kHeadDim + t] = value;
+          if (t == j) {
+            const float safe = st.row_max[j] == -INFINITY ? 0.0f : st.row_max[j];
+            const float lse = empty ? -INFINITY
+                                    : (safe * p.scale_log2 + log2f(total[j]) - shift) * 0.6931471805599453f;
+            p.partial_lse[((int64_t)part * p.rows + row) * p.heads_q + head] = lse;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown -------------------------------------------------------------------------------
+  tc::fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && sm.abort_flag && p.error_word) atomicOr(p.error_word, (int)BDFP4_DEV_WAIT_TIMEOUT);
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, kTmemColumns);
+  }
+}
+
+// ---- host -------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &status) == cudaSuccess &&
+        status == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(entry);
+  });
+  return fn;
+}
+
+template <int GP, int TERMS>
+static cudaError_t launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
+                                 cudaStream_t stream) {
+  const int smem = (int)sizeof(DecodeSmem<GP>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int grid = p.rows * p.heads_kv * p.parts;
+  decode_kernel<GP, TERMS><<<grid, 192, smem, stream>>>(k_map, v_map, p);
+  return cudaGetLastError();
+}
+
+}  // namespace bdfp4
+
+using namespace bdfp4;
+
+extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
+  if (!a) return BDFP4_E_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (a->rows < 1 || a->heads_q < 1 || a->heads_kv < 1 || a->heads_q % a->heads_kv) return BDFP4_E_ARG;
+  const int ratio = a->heads_q / a->heads_kv;
+  if (ratio > 16) return BDFP4_E_UNSUPPORTED;
+  if (!a->query_codes || !a->query_scales) return BDFP4_E_ARG;
+  if ((a->query_codes_second == nullptr) != (a->query_scales_second == nullptr)) return BDFP4_E_ARG;
+  if (!a->key_codes || !a->key_scales || !a->value_codes || !a->value_scales) return BDFP4_E_ARG;
+  if (a->pages < 1 || !a->page_table || !a->seqused_fp4 || a->max_pages_per_row < 0) return BDFP4_E_ARG;
+  if (a->page_table_stride < a->max_pages_per_row) return BDFP4_E_ARG;
+  auto misaligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
+  if (misaligned(a->query_codes) || misaligned(a->query_scales) || misaligned(a->key_codes) ||
+      misaligned(a->key_scales) || misaligned(a->value_codes) || misaligned(a->value_scales))
+    return BDFP4_E_ARG;
+  if (a->key_codes_pitch % 16 || a->key_scales_pitch % 16 || a->value_codes_pitch % 16 ||
+      a->value_scales_pitch % 16)
+    return BDFP4_E_ARG;
+  if (a->key_codes_pitch < (int64_t)kPage * a->heads_kv * 64 || a->value_codes_pitch < (int64_t)a->heads_kv * 8192 ||
+      a->key_scales_pitch < (int64_t)a->heads_kv * 1024 || a->value_scales_pitch < (int64_t)a->heads_kv * 1024)
+    return BDFP4_E_ARG;
+  const bool tail = a->tail_key != nullptr;
+  if (tail) {
+    if (!a->tail_value || !a->tail_slot_ids || !a->seqused_residual || !a->query_padded || a->tail_slots < 1)
+      return BDFP4_E_ARG;
+    if (misaligned(a->tail_key) || misaligned(a->tail_value) || misaligned(a->query_padded)) return BDFP4_E_ARG;
+  }
+  if (!(a->softmax_scale > 0.0f) || !isfinite(a->softmax_scale)) return BDFP4_E_ARG;
+  if (a->p_scale_mode < 0 || a->p_scale_mode > 2) return BDFP4_E_ARG;
+  if (a->num_splits < 1) return BDFP4_E_ARG;
+  const bool own_bf16 = a->num_splits > 1 && a->bf16_split != 0;
+  if (a->num_splits == 1) {
+    if (!a->out || a->out_row_stride < (int64_t)a->heads_q * kHeadDim) return BDFP4_E_ARG;
+  } else if (!a->partial_out || !a->partial_lse) {
+    return BDFP4_E_ARG;
+  }
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return BDFP4_E_CUDA;
+
+  CUtensorMap k_map, v_map;
+  {
+    // K codes: [pages][128 tok][H][64 B]; one box = one head of one page, 128 rows of 64 bytes
+    const cuuint64_t dims[4] = {64, (cuuint64_t)a->heads_kv, kPage, (cuuint64_t)a->pages};
+    const cuuint64_t strides[3] = {64, (cuuint64_t)a->heads_kv * 64, (cuuint64_t)a->key_codes_pitch};
+    const cuuint32_t box[4] = {64, 1, kPage, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    if (encode(&k_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(a->key_codes), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return BDFP4_E_ARG;
+  }
+  {
+    // V codes: [pages][H * 128 ch][64 B]
+    const cuuint64_t dims[3] = {64, (cuuint64_t)a->heads_kv * kHeadDim, (cuuint64_t)a->pages};
+    const cuuint64_t strides[2] = {64, (cuuint64_t)a->value_codes_pitch};
+    const cuuint32_t box[3] = {64, kHeadDim, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    if (encode(&v_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(a->value_codes), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return BDFP4_E_ARG;
+  }
+
+  DecodeParams p{};
+  p.rows = a->rows;
+  p.heads_q = a->heads_q;
+  p.heads_kv = a->heads_kv;
+  p.ratio = ratio;
+  p.q_codes[0] = static_cast<const uint8_t*>(a->query_codes);
+  p.q_scales[0] = static_cast<const uint8_t*>(a->query_scales);
+  p.q_codes[1] = static_cast<const uint8_t*>(a->query_codes_second);
+  p.q_scales[1] = static_cast<const uint8_t*>(a->query_scales_second);
+  p.q_padded = static_cast<const __nv_bfloat16*>(a->query_padded);
+  p.k_scales = static_cast<const uint8_t*>(a->key_scales);
+  p.v_scales = static_cast<const uint8_t*>(a->value_scales);
+  p.k_scales_pitch = a->key_scales_pitch;
+  p.v_scales_pitch = a->value_scales_pitch;
+  p.pages = a->pages;
+  p.page_table = a->page_table;
+  p.page_table_stride = a->page_table_stride;
+  p.max_pages = a->max_pages_per_row;
+  p.seqused_fp4 = a->seqused_fp4;
+  p.tail_key = static_cast<const __nv_bfloat16*>(a->tail_key);
+  p.tail_value = static_cast<const __nv_bfloat16*>(a->tail_value);
+  p.tail_slot_stride = a->tail_slot_stride;
+  p.tail_slots = a->tail_slots;
+  p.tail_slot_ids = a->tail_slot_ids;
+  p.seqused_residual = a->seqused_residual;
+  p.seqused_sink = tail ? a->seqused_sink : nullptr;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.p_mode = a->p_scale_mode;
+  p.tau = a->p_scale_tau;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.out_row_stride = a->out_row_stride;
+  p.num_splits = a->num_splits;
+  p.bf16_split = own_bf16 ? 1 : 0;
+  p.parts = a->num_splits + (own_bf16 ? 1 : 0);
+  p.partial_out = a->partial_out;
+  p.partial_lse = a->partial_lse;
+  p.error_word = a->error_word;
+
+  const bool two = a->query_codes_second != nullptr;
+  cudaError_t e;
+  if (ratio <= 4)
+    e = two ? launch_decode<4, 2>(k_map, v_map, p, stream) : launch_decode<4, 1>(k_map, v_map, p, stream);
+  else if (ratio <= 8)
+    e = two ? launch_decode<8, 2>(k_map, v_map, p, stream) : launch_decode<8, 1>(k_map, v_map, p, stream);
+  else
+    e = two ? launch_decode<16, 2>(k_map, v_map, p, stream) : launch_decode<16, 1>(k_map, v_map, p, stream);
+  return bdfp4::cuda_status(e);
+}

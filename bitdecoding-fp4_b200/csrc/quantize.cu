@@ -448,7 +448,8 @@ extern "C" int bdfp4_kv_write(const bdfp4_kv_write_args* a, void* stream_handle)
   if (per_layer && a->source_tokens_total % layers) return BDFP4_E_ARG;
   if (write_tail) {
     if (a->sink_tokens < 0 || a->sink_tokens > BDFP4_MAX_SINK) return BDFP4_E_ARG;
-    if (!a->query_start_loc || !a->seq_lens || !a->seqused_fp4 || !a->row_to_slot) return BDFP4_E_ARG;
+    if (a->rows > 0 && (!a->query_start_loc || !a->seq_lens || !a->seqused_fp4 || !a->row_to_slot))
+      return BDFP4_E_ARG;
     if (a->rows < 0 || a->decode_rows < 0 || a->decode_rows > a->rows || a->first_row < 0 ||
         a->first_row > a->decode_rows)
       return BDFP4_E_ARG;

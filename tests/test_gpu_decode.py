@@ -1,0 +1,214 @@
+"""Paged FP4 decode attention (through the package API and the C ABI) against the CPU oracle.
+
+Tolerance (BASELINE north_star): max |err| <= 1e-2 and mean relative error <= 1e-3, both in
+BF16, against the oracle that models the kernel's own operands (FP4 query terms, FP4
+probabilities, block order, stale-maximum rule). The kernel uses ex2.approx / rcp.approx, so
+agreement is statistical rather than bitwise.
+"""
+
+import math
+
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_REL = 1e-2, 1e-3
+
+
+def _scale_tiles(blocks_cpu, heads, offset):
+    """[blocks, H, 1024] scale bytes of the region starting at ``offset`` of each flat block."""
+    return blocks_cpu[:, offset:offset + heads * 1024].reshape(-1, heads, 1024)
+
+
+def _cpu_cache(w):
+    blocks = w.blocks.cpu()
+    h = w.heads_kv
+    key_codes = blocks[:, :8192 * h].reshape(-1, 128, h, 64)
+    key_scales = _scale_tiles(blocks, h, 8192 * h)
+    value_codes = blocks[:, 9216 * h:17408 * h].reshape(-1, h, 128, 64)
+    value_scales = _scale_tiles(blocks, h, 17408 * h)
+    return key_codes, key_scales, value_codes, value_scales
+
+
+def _oracle_decode(w, *, terms, scale_mode, rotate, num_splits=1, bf16_split=False, with_tail=True,
+                   p_mode="amax2_or_amax6_c8"):
+    kc, ks, vc, vs = _cpu_cache(w)
+    q = oracle.quantize_query(w.query.cpu(), w.heads_kv, scale_mode=scale_mode, terms=terms, rotate=rotate)
+    kwargs = {}
+    if with_tail:
+        kwargs = dict(tail_key=w.tail_key[0].cpu(), tail_value=w.tail_value[0].cpu(),
+                      tail_slot_ids=w.slot_ids.cpu(), seqused_residual=w.seqused_residual.cpu(),
+                      seqused_sink=w.seqused_sink.cpu() if w.sink_tokens else None)
+    return oracle.decode_reference(
+        query_values=q["values"], query_padded=q["padded"], key_codes=kc, key_scales=ks, value_codes=vc,
+        value_scales=vs, page_table=w.page_table.cpu(), seqused_fp4=w.seqused_fp4.cpu(), heads_kv=w.heads_kv,
+        softmax_scale=128 ** -0.5, p_mode=p_mode, num_splits=num_splits, bf16_split=bf16_split, **kwargs)
+
+
+def _check(got, want, label=""):
+    got, want = got.float().cpu(), want.float()
+    assert torch.isfinite(got).all(), label
+    err = (got - want).abs()
+    mean_rel = float(err.mean() / want.abs().mean().clamp_min(1e-12))
+    assert float(err.max()) <= MAX_ABS, f"{label} max abs err {float(err.max()):.3e}"
+    assert mean_rel <= MEAN_REL, f"{label} mean rel err {mean_rel:.3e}"
+    return float(err.max()), mean_rel
+
+
+def _decode(w, *, terms=1, scale_mode="amax6", rotate=False, num_splits=1, with_tail=True, **extra):
+    from nvfp4_decode_kernel import fp4_decode
+
+    kwargs = dict(extra)
+    if with_tail:
+        kwargs.update(residual_key_pages_bf16=w.tail_key[0], residual_value_pages_bf16=w.tail_value[0],
+                      residual_page_ids=w.slot_ids, seqused_residual=w.seqused_residual)
+        if w.sink_tokens:
+            kwargs.update(seqused_sink=w.seqused_sink)
+    return fp4_decode(w.query, *w.regions, w.page_table, w.seqused_fp4, query_terms=terms,
+                      scale_mode=scale_mode, query_rotation="hadamard" if rotate else "none",
+                      num_splits=num_splits, **kwargs)
+
+
+def test_cache_fill_matches_oracle():
+    """The workload builder's writer calls: pages land where the block table says, the rolling
+    tail and the sink hold the right tokens (K in the cache basis)."""
+    from bdfp4.workload import build_workload
+
+    w = build_workload(rows=3, heads_q=8, heads_kv=2, seq_lens=[700, 130, 9], sink_tokens=16, seed=4,
+                       key_scale_mode="four_six", value_scale_mode="amax6", rotate=True, key_shift=True,
+                       keep_source=True, chunk_pages=2)
+    kc, ks, vc, vs = _cpu_cache(w)
+    shift = w.key_shift[0].cpu()
+    for row, n in enumerate(w.seq_lens):
+        k, v = (t.cpu() for t in w.kept[row])
+        sink, fp4, tail = oracle.split_sequence_length(n)
+        assert (int(w.seqused_fp4[row]), int(w.seqused_residual[row]), int(w.seqused_sink[row])) == (fp4, tail, sink)
+        pages = fp4 // 128
+        ids = w.page_table[row, :pages].cpu().long()
+        if pages:
+            want_kc, want_ks = oracle.quantize_key_pages(k[:fp4].reshape(pages, 128, 2, 128), "four_six",
+                                                         rotate=True, shift=shift)
+            want_vc, want_vs = oracle.quantize_value_pages(v[:fp4].reshape(pages, 128, 2, 128), "amax6")
+            assert torch.equal(kc[ids], want_kc) and torch.equal(ks[ids], want_ks)
+            assert torch.equal(vc[ids], want_vc) and torch.equal(vs[ids], want_vs)
+        basis = oracle.key_cache_basis(k, rotate=True, shift=shift)
+        assert torch.equal(w.tail_key[0, row, :tail].cpu(), basis[fp4:n])
+        assert torch.equal(w.tail_value[0, row, :tail].cpu(), v[fp4:n])
+        assert torch.equal(w.tail_key[0, row, 128:128 + sink].cpu(), basis[:sink])
+        assert torch.equal(w.tail_value[0, row, 128:128 + sink].cpu(), v[:sink])
+
+
+@pytest.mark.parametrize("heads_q,heads_kv", [(8, 2), (16, 2), (32, 2)])
+@pytest.mark.parametrize("terms", [1, 2])
+def test_decode_pages_only(heads_q, heads_kv, terms):
+    """FP4 pages alone (no BF16 residual): 1-5 pages per row, one row with none."""
+    from bdfp4.workload import build_workload
+
+    w = build_workload(rows=4, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[641, 129, 385, 100], sink_tokens=0,
+                       seed=heads_q + terms)
+    out = _decode(w, terms=terms, with_tail=False)
+    want, _, _ = _oracle_decode(w, terms=terms, scale_mode="amax6", rotate=False, with_tail=False)
+    rows_with_pages = [0, 1, 2]
+    _check(out[rows_with_pages], want[rows_with_pages], f"G={heads_q // heads_kv} terms={terms}")
+    assert float(out[3].float().abs().sum()) == 0.0  # no FP4 tokens, no residual: nothing attends
+
+
+@pytest.mark.parametrize("sink_tokens", [16, 4, 0])
+def test_decode_config1_shape(sink_tokens):
+    """BASELINE config 1: batch 4, 8 query / 2 KV heads, contexts uniform in [512, 2048], BF16 sink
+    and rolling tail, the recipe the reference serves with (two query terms, Hadamard, four_six K,
+    key shift)."""
+    from bdfp4.workload import build_workload
+
+    gen = torch.Generator().manual_seed(0)
+    lens = torch.randint(512, 2049, (4,), generator=gen).tolist()
+    w = build_workload(rows=4, heads_q=8, heads_kv=2, seq_lens=lens, sink_tokens=sink_tokens, seed=1,
+                       key_scale_mode="four_six", rotate=True, key_shift=True)
+    if sink_tokens not in (0, 16):
+        # the decode entry takes the sink in rows [128, 144) of a 144-row buffer
+        pad = torch.zeros(1, 4, 144, 2, 128, dtype=torch.bfloat16, device="cuda")
+        pad_v = pad.clone()
+        pad[:, :, :128 + sink_tokens] = w.tail_key
+        pad_v[:, :, :128 + sink_tokens] = w.tail_value
+        w.tail_key, w.tail_value = pad, pad_v
+    out = _decode(w, terms=2, scale_mode="four_six", rotate=True)
+    want, _, _ = _oracle_decode(w, terms=2, scale_mode="four_six", rotate=True)
+    _check(out, want, f"sink={sink_tokens}")
+
+
+def test_decode_edge_rows():
+    """Tail only (no page yet, sink masked inside the rolling page), exactly one full page,
+    a row without a tail slot, a one-token sequence."""
+    from bdfp4.workload import build_workload
+
+    w = build_workload(rows=5, heads_q=8, heads_kv=2, seq_lens=[100, 128, 129, 1, 300], sink_tokens=16, seed=7)
+    w.slot_ids[4] = -1  # a row the control plane gave no slot: only its FP4 pages attend
+    out = _decode(w, terms=1)
+    want, _, _ = _oracle_decode(w, terms=1, scale_mode="amax6", rotate=False)
+    _check(out, want, "edge rows")
+
+
+@pytest.mark.parametrize("num_splits", [2, 3, 8])
+def test_decode_split_kv(num_splits):
+    from bdfp4.workload import build_workload
+
+    w = build_workload(rows=2, heads_q=8, heads_kv=2, seq_lens=[1500, 260], sink_tokens=16, seed=num_splits)
+    out = _decode(w, terms=2, num_splits=num_splits)
+    unsplit = _decode(w, terms=2)
+    want, _, _ = _oracle_decode(w, terms=2, scale_mode="amax6", rotate=False, num_splits=num_splits,
+                                bf16_split=True)
+    _check(out, want, f"splits={num_splits}")
+    # parts quantise P against their own running maxima: split and unsplit differ by FP4-P noise
+    rel = ((out.float() - unsplit.float()).abs().mean() / unsplit.float().abs().mean()).item()
+    assert rel < 0.1, rel
+
+
+def test_decode_caller_buffers_and_error_word():
+    """Caller-owned output and scratch; nothing else is written."""
+    from bdfp4.workload import build_workload
+    from nvfp4_decode_kernel import split_partial_count
+
+    w = build_workload(rows=3, heads_q=8, heads_kv=2, seq_lens=[400, 900, 131], sink_tokens=16, seed=12)
+    rows, hq = 3, 8
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    parts = split_partial_count(rows, 2, 4, residual=True, sms=sms)
+    out = torch.full((rows + 2, hq, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    scratch = dict(
+        query_padded_scratch=torch.zeros(rows + 1, 128, hq, 128, dtype=torch.bfloat16, device="cuda"),
+        query_fp4_scratch=torch.full((rows + 1, 1, hq, 64), 255, dtype=torch.uint8, device="cuda"),
+        query_scales_scratch=torch.zeros(rows + 1, 1, hq, 2, 32, 4, 4, dtype=torch.uint8, device="cuda"),
+        split_partial_scratch=torch.full((parts * rows * hq * 128,), float("nan"), device="cuda"),
+        split_lse_scratch=torch.full((parts * rows * hq,), float("nan"), device="cuda"),
+    )
+    got = _decode(w, terms=1, num_splits=4, out=out, trusted_metadata=True, **scratch)
+    assert got.data_ptr() == out.data_ptr() and got.shape[0] == rows
+    assert bool((out[rows:] == 7.0).all())
+    want, _, _ = _oracle_decode(w, terms=1, scale_mode="amax6", rotate=False, num_splits=4, bf16_split=True)
+    _check(got, want, "caller buffers")
+
+
+def test_plain_attention_distance_reported():
+    """Distance to the plain dequantise-then-attend result (BF16 query, exact softmax): reported,
+    and bounded loosely, because the FP4 probability operand alone costs about 9e-2 mean-rel."""
+    from bdfp4.workload import build_workload
+
+    w = build_workload(rows=1, heads_q=8, heads_kv=2, seq_lens=[2048], sink_tokens=16, seed=21, keep_source=True)
+    out = _decode(w, terms=2).float().cpu()
+    kc, ks, vc, vs = _cpu_cache(w)
+    ids = w.page_table[0, :15].cpu().long()
+    q = w.query[0].cpu().float()
+    k_src, v_src = (t.cpu().float() for t in w.kept[0])
+    errs = []
+    for h in range(2):
+        k = oracle.dequantize_key_pages(kc[ids][:, :, h:h + 1], ks[ids][:, h:h + 1]).reshape(-1, 128)
+        v = oracle.dequantize_value_pages(vc[ids][:, h:h + 1], vs[ids][:, h:h + 1]).reshape(-1, 128)
+        k[:16], v[:16] = k_src[:16, h], v_src[:16, h]
+        k = torch.cat([k, k_src[1920:, h]])
+        v = torch.cat([v, v_src[1920:, h]])
+        want = oracle.plain_attention(q[4 * h:4 * h + 4], k, v, 128 ** -0.5)
+        errs.append(((out[4 * h:4 * h + 4] - want).abs().mean() / want.abs().mean()).item())
+    print(f"mean-rel distance to plain dequantise-then-attend: {max(errs):.3e}")
+    assert max(errs) < 0.3
