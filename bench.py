@@ -348,12 +348,12 @@ def run_ours(args) -> None:
     # ---- quantize-on-write throughput (bulk page quantize, K and V) ---------------------------
     from nvfp4_decode_kernel.quantize_kv_kernel import KVCacheWriter
 
-    q_pages = 2048
+    q_pages = min(2048, w.page_table.numel())
     source_k = torch.randn(q_pages * 128, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
     source_v = torch.randn(q_pages * 128, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
     writer = KVCacheWriter(regions=w.regions, key_scale_mode="four_six", value_scale_mode="amax6", rotate_key=True)
     work_src = torch.arange(q_pages, dtype=torch.int32, device=device) * 128
-    work_dst = w.page_table[0, :q_pages].contiguous()
+    work_dst = w.page_table.reshape(-1)[:q_pages].contiguous()
     for _ in range(3):
         writer(source_k, source_v, w.regions, work_src, work_dst)
     barrier()

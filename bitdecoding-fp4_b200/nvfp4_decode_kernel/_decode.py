@@ -259,8 +259,8 @@ def _validate(
                 f"seqused_residual values must lie in [0, {PAGE_SIZE}]",
             )
             _check_device_values(
-                (seqused_residual > 0) & ((residual_page_ids < 0) | (residual_page_ids >= expected_residual[0])),
-                f"residual_page_ids of rows with a residual must lie in [0, {expected_residual[0]})",
+                (residual_page_ids < 0) | (residual_page_ids >= expected_residual[0]),
+                "residual_page_ids contains an out-of-range physical page ID",
             )
             if seqused_sink is not None:
                 _check_device_values(

@@ -146,7 +146,9 @@ def test_decode_edge_rows():
 
     w = build_workload(rows=5, heads_q=8, heads_kv=2, seq_lens=[100, 128, 129, 1, 300], sink_tokens=16, seed=7)
     w.slot_ids[4] = -1  # a row the control plane gave no slot: only its FP4 pages attend
-    out = _decode(w, terms=1)
+    with pytest.raises(ValueError):
+        _decode(w, terms=1)  # a negative slot id is refused unless the metadata is trusted
+    out = _decode(w, terms=1, trusted_metadata=True)
     want, _, _ = _oracle_decode(w, terms=1, scale_mode="amax6", rotate=False)
     _check(out, want, "edge rows")
 
@@ -209,6 +211,6 @@ def test_plain_attention_distance_reported():
         k = torch.cat([k, k_src[1920:, h]])
         v = torch.cat([v, v_src[1920:, h]])
         want = oracle.plain_attention(q[4 * h:4 * h + 4], k, v, 128 ** -0.5)
-        errs.append(((out[4 * h:4 * h + 4] - want).abs().mean() / want.abs().mean()).item())
+        errs.append(((out[0, 4 * h:4 * h + 4] - want).abs().mean() / want.abs().mean()).item())
     print(f"mean-rel distance to plain dequantise-then-attend: {max(errs):.3e}")
     assert max(errs) < 0.3
