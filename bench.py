@@ -50,28 +50,58 @@ def measured_peak_gbs() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event reasons (read-only NVML queries) while a region runs."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index = index
-        self.samples: list[list[str]] = []
+        self.period = period_s
+        self.clocks: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = self.index
+            if visible:
+                entries = [e.strip() for e in visible.split(",") if e.strip()]
+                if self.index < len(entries) and entries[self.index].isdigit():
+                    physical = int(entries[self.index])
+            handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            while not self._stop.is_set():
+                self.clocks.append(int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self._stop.wait(self.period)
+        except Exception:
+            self._run_smi()
+
+    def _run_smi(self):
+        query = ("clocks.sm,clocks.max.sm,clocks_event_reasons.sw_power_cap,clocks_event_reasons.hw_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.hw_thermal_slowdown")
+        names = ["sw_power_cap", "hw_slowdown", "sw_thermal_slowdown", "hw_thermal_slowdown"]
         while not self._stop.is_set():
             try:
                 out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={query}", "--format=csv,noheader,nounits"],
                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([x.strip() for x in out.splitlines()[0].split(",")])
+                fields = [x.strip() for x in out.splitlines()[0].split(",")]
+                self.clocks.append(int(fields[0]))
+                self.max_mhz = int(fields[1])
+                self.reasons.update(n for n, f in zip(names, fields[2:]) if f == "Active")
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.05)
 
     def __enter__(self):
         self._thread.start()
@@ -82,14 +112,11 @@ class ClockSampler:
         self._thread.join(timeout=10)
 
     def summary(self) -> dict:
-        clocks = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for s in self.samples if len(s) >= 6 for i in range(4) if s[2 + i] == "Active"})
         return {
-            "sm_mhz": int(statistics.median(clocks)) if clocks else None,
-            "sm_max_mhz": int(self.samples[0][1]) if self.samples and self.samples[0][1].isdigit() else None,
-            "reasons": reasons,
-            "samples": len(clocks),
+            "sm_mhz": int(statistics.median(self.clocks)) if self.clocks else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.clocks),
         }
 
 

@@ -29,16 +29,22 @@ namespace bdfp4 {
 
 constexpr int kStageBytes = 8192 + 1024;  // codes + scales of one K or V page-head
 constexpr int kNP = 16;                   // N of the PV MMA (query rows, padded)
-constexpr int kTmemColumns = 256;
 constexpr float kRescaleThreshold = 8.0f;  // src/nvfp4_decode_kernel/fp4_decode_kernel.py:93
 
-// TMEM column map (each scale-factor block sits on a 16-column boundary)
-constexpr int kColS = 0;      // 2 stages x NQ (<= 32) columns
-constexpr int kColO = 64;     // 2 stages x 16
-constexpr int kColSFQ = 96;   // 8
-constexpr int kColSFK = 112;  // 2 stages x 16 (8 used)
-constexpr int kColSFV = 144;
-constexpr int kColSFP = 176;
+// TMEM column map for a QK MMA of N = NQ columns: two S stages, two O stages (16 columns each),
+// then the scale-factor blocks (8 columns = two 4-column atoms each): Q, K x2, V x2, P x2.
+// 120 columns at NQ = 16 (128 allocated, so four CTAs share an SM's 512), 152 at NQ = 32.
+template <int NQ>
+struct TmemMap {
+  static constexpr int kS = 0;
+  static constexpr int kO = 2 * NQ;
+  static constexpr int kSFQ = kO + 32;
+  static constexpr int kSFK = kSFQ + 8;
+  static constexpr int kSFV = kSFK + 16;
+  static constexpr int kSFP = kSFV + 16;
+  static constexpr int kUsed = kSFP + 16;
+  static constexpr int kAlloc = kUsed <= 128 ? 128 : 256;
+};
 
 struct DecodeParams {
   int rows, heads_q, heads_kv, ratio;
@@ -71,12 +77,13 @@ struct DecodeParams {
   int32_t* error_word;
 };
 
-template <int GP>
+template <int GP, int STAGES>
 struct DecodeSmem {
-  static constexpr int kStages = GP == 16 ? 4 : 5;
+  static constexpr int kStages = STAGES;
+  static constexpr int kNQ = GP <= 8 ? 16 : 32;
   alignas(1024) uint8_t k_stage[kStages][kStageBytes];
   alignas(1024) uint8_t v_stage[kStages][kStageBytes];
-  alignas(1024) uint8_t q_tile[32 * 64];
+  alignas(1024) uint8_t q_tile[kNQ * 64];
   alignas(1024) uint8_t p_tile[2][kNP * 64];
   alignas(1024) uint8_t q_sf[1024];
   alignas(1024) uint8_t p_sf[2][1024];
@@ -174,8 +181,8 @@ __device__ __forceinline__ void update_max(SoftmaxState<GP>& st, const float* bl
 // A BF16 block (the rolling tail or the sink) merged with plain FMAs by the 128 softmax threads:
 // thread `t` scores token `t`, then accumulates channel `t`. `rows0` is the first row of the
 // block inside the slot's buffer, positions outside [mask_below, length) are masked.
-template <int GP>
-__device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP>& sm, const DecodeParams& p, int t,
+template <int GP, int STAGES>
+__device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, STAGES>& sm, const DecodeParams& p, int t,
                                            int warp_q, int lane, const __nv_bfloat16* key_rows,
                                            const __nv_bfloat16* value_rows, int mask_below, int length, float shift,
                                            int& red_buf) {
@@ -253,12 +260,17 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP>&
   softmax_barrier();  // p_bf16 is reused by the next BF16 block
 }
 
-template <int GP, int TERMS>
-__global__ void __launch_bounds__(192) decode_kernel(const __grid_constant__ CUtensorMap k_map,
-                                                     const __grid_constant__ CUtensorMap v_map, const DecodeParams p) {
-  using Smem = DecodeSmem<GP>;
+template <int GP, int TERMS, int STAGES>
+__global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
+    decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                  const DecodeParams p) {
+  using Smem = DecodeSmem<GP, STAGES>;
   constexpr int KS = Smem::kStages;
-  constexpr int NQ = GP <= 8 ? 16 : 32;  // N of the QK MMA: term 0 in columns [0, GP), term 1 from NQ/2
+  constexpr int NQ = Smem::kNQ;  // N of the QK MMA: term 0 in columns [0, GP), term 1 from NQ/2
+  using Map = TmemMap<NQ>;
+  constexpr int kColS = Map::kS, kColO = Map::kO, kColSFQ = Map::kSFQ, kColSFK = Map::kSFK, kColSFV = Map::kSFV,
+                kColSFP = Map::kSFP;
+  constexpr int kTmemColumns = Map::kAlloc;
   constexpr int LD = GP <= 4 ? 4 : (GP <= 8 ? 8 : 16);
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -319,20 +331,21 @@ __global__ void __launch_bounds__(192) decode_kernel(const __grid_constant__ CUt
     tc::prefetch_tensormap(&v_map);
   }
   // Q tile (B operand of QK), its scale atoms, zeroed P buffers, widened BF16 query
-  for (int i = tid; i < (32 * 64 + 2 * kNP * 64 + 1024 + 2 * 1024) / 16; i += 192) {
+  constexpr int kQChunks = NQ * 64 / 16;
+  for (int i = tid; i < kQChunks + (2 * kNP * 64 + 1024 + 2 * 1024) / 16; i += 192) {
     uint4* base;
     int index = i;
-    if (index < 128) {
+    if (index < kQChunks) {
       base = reinterpret_cast<uint4*>(sm.q_tile);
-    } else if (index < 128 + 128) {
+    } else if (index < kQChunks + 128) {
       base = reinterpret_cast<uint4*>(sm.p_tile);
-      index -= 128;
-    } else if (index < 256 + 64) {
+      index -= kQChunks;
+    } else if (index < kQChunks + 128 + 64) {
       base = reinterpret_cast<uint4*>(sm.q_sf);
-      index -= 256;
+      index -= kQChunks + 128;
     } else {
       base = reinterpret_cast<uint4*>(sm.p_sf);
-      index -= 320;
+      index -= kQChunks + 192;
     }
     base[index] = make_uint4(0, 0, 0, 0);
   }
@@ -507,7 +520,7 @@ __global__ void __launch_bounds__(192) decode_kernel(const __grid_constant__ CUt
     if (with_bf16) {
       // While page zero has not been sealed the rolling page still holds the sink's tokens.
       const int mask_below = total_pages == 0 ? sink_len : 0;
-      bf16_block<GP>(st, sm, p, t, warp_q, lane, tail_k, tail_v, mask_below, tail_len, shift, red_buf);
+      bf16_block<GP, STAGES>(st, sm, p, t, warp_q, lane, tail_k, tail_v, mask_below, tail_len, shift, red_buf);
     }
 
     float acc_prev[GP];
@@ -646,7 +659,7 @@ __global__ void __launch_bounds__(192) decode_kernel(const __grid_constant__ CUt
       for (int j = 0; j < GP; ++j) st.o_acc[j] = st.o_acc[j] * acc_prev[j] + o[j];
     }
     if (with_bf16 && p.seqused_sink) {
-      bf16_block<GP>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,
+      bf16_block<GP, STAGES>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,
                      tail_v + (int64_t)kPage * row_elems, 0, sink_len, shift, red_buf);
     }
 
@@ -720,19 +733,41 @@ static EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-template <int GP, int TERMS>
-static cudaError_t launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
-                                 cudaStream_t stream) {
-  const int smem = (int)sizeof(DecodeSmem<GP>) + 1024;
+template <int GP, int TERMS, int STAGES>
+static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
+                                        cudaStream_t stream) {
+  const int smem = (int)sizeof(DecodeSmem<GP, STAGES>) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int grid = p.rows * p.heads_kv * p.parts;
-  decode_kernel<GP, TERMS><<<grid, 192, smem, stream>>>(k_map, v_map, p);
+  decode_kernel<GP, TERMS, STAGES><<<grid, 192, smem, stream>>>(k_map, v_map, p);
   return cudaGetLastError();
+}
+
+// Ring depth follows the grid: a launch with more than two CTAs per SM is given two K and two V
+// stages per CTA so that four CTAs (and their four independent softmax chains) share an SM and
+// the whole grid is resident at once; a smaller launch gets deeper rings instead.
+template <int GP, int TERMS>
+static cudaError_t launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
+                                 cudaStream_t stream) {
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  }
+  const int grid = p.rows * p.heads_kv * p.parts;
+  if constexpr (GP <= 8) {
+    if (grid > 2 * sms) return launch_decode_staged<GP, TERMS, 2>(k_map, v_map, p, stream);
+    return launch_decode_staged<GP, TERMS, 5>(k_map, v_map, p, stream);
+  } else {
+    return launch_decode_staged<GP, TERMS, 4>(k_map, v_map, p, stream);
+  }
 }
 
 }  // namespace bdfp4
