@@ -13,7 +13,8 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libbdfp4.so"
 
-OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE = 0, -1, -2, -3, -4
+OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_TOO_LARGE = 0, -1, -2, -3, -4, -5
+STATIC_SCRATCH_BYTES = 8 << 20
 DEV_WAIT_TIMEOUT, DEV_BAD_PAGE = 1, 2
 SCALE_MODE_IDS = {"amax6": 0, "four_six": 1, "four_six_sixhalf": 2}
 P_MODE_IDS = {"amax6": 0, "amax2_or_amax6": 1, "amax2_or_amax6_c8": 2}
@@ -28,6 +29,7 @@ EXPORTS = (
     "bdfp4_quantize_query",
     "bdfp4_decode",
     "bdfp4_combine",
+    "bdfp4_decode_split_static",
 )
 
 
@@ -127,6 +129,8 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_decode.argtypes = [POINTER(DecodeArgs), c_void_p]
     lib.bdfp4_combine.restype = c_int32
     lib.bdfp4_combine.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]
+    lib.bdfp4_decode_split_static.restype = c_int32
+    lib.bdfp4_decode_split_static.argtypes = [POINTER(DecodeArgs), c_void_p]
     _lib = lib
     return lib
 
@@ -178,3 +182,11 @@ def combine(partial_out, partial_lse, parts: int, rows: int, heads_q: int, out, 
         library().bdfp4_combine(ptr(partial_out), ptr(partial_lse), parts, rows, heads_q, ptr(out),
                                 out_row_stride, stream),
     )
+
+
+def decode_split_static(args: DecodeArgs, stream: int) -> None:
+    """Split-KV decode + merge whose partial buffers live in the library's own fixed device array
+    (``STATIC_SCRATCH_BYTES``): for callers that may not allocate device memory when they decode.
+    Raises :class:`KernelError` with ``E_TOO_LARGE`` when the partials would not fit. Calls share
+    the array, so run them on one stream; make the first call on a device outside stream capture."""
+    check("bdfp4_decode_split_static", library().bdfp4_decode_split_static(ctypes.byref(args), stream))

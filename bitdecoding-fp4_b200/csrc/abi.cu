@@ -25,6 +25,7 @@ extern "C" const char* bdfp4_status_string(int status) {
     case BDFP4_E_UNSUPPORTED: return "request is valid but this build has no kernel for it";
     case BDFP4_E_CUDA: return "a CUDA call failed";
     case BDFP4_E_DEVICE: return "the current device is not an sm_100-family GPU";
+    case BDFP4_E_TOO_LARGE: return "the request exceeds a fixed-capacity buffer of the library";
     default: return "unknown status";
   }
 }

@@ -885,3 +885,64 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
     e = two ? launch_decode<16, 2>(k_map, v_map, p, stream) : launch_decode<16, 1>(k_map, v_map, p, stream);
   return bdfp4::cuda_status(e);
 }
+
+// ---- split decode without caller-provided scratch ----------------------------------------------
+//
+// Some callers of this library are not allowed to allocate device memory at the point where they
+// decode: an engine that has handed all of its HBM budget to the KV cache and runs with allocation
+// disabled, a plugin that is entered from inside a host framework's memory-pool critical section,
+// or an embedding without access to the framework's allocator at all. The split path of
+// bdfp4_decode needs a place for its FP32 partial outputs and log-sum-exps; here that place is a
+// fixed array inside the library's own device image, so the call allocates nothing.
+namespace bdfp4 {
+
+constexpr size_t kStaticScratchFloats = BDFP4_STATIC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_split_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_split_scratch_address[kMaxDevices] = {};
+static std::mutex g_split_scratch_mutex;
+
+// The device address of g_split_scratch on the current device. In host code the array's name is
+// only a handle for the runtime, never an address a kernel may be given, so the address is looked
+// up once per device (with that device current) and remembered.
+static cudaError_t split_scratch_address(float** out) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_split_scratch_mutex);
+  if (!g_split_scratch_address[device]) {
+    float* address = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_split_scratch);
+    if (e != cudaSuccess) return e;
+    g_split_scratch_address[device] = address;
+  }
+  *out = g_split_scratch_address[device];
+  return cudaSuccess;
+}
+
+}  // namespace bdfp4
+
+extern "C" int bdfp4_decode_split_static(const bdfp4_decode_args* a, void* stream) {
+  if (!a) return BDFP4_E_ARG;
+  if (a->num_splits < 2 || a->rows < 1 || a->heads_q < 1 || !a->out) return BDFP4_E_ARG;
+  if (a->out_row_stride < (int64_t)a->heads_q * kHeadDim) return BDFP4_E_ARG;
+  bdfp4_decode_args local = *a;
+  // An extra part for the BF16 blocks exists only when there are BF16 blocks: a part that nothing
+  // writes would leave the previous call's log-sum-exp in the shared array.
+  local.bf16_split = (a->bf16_split != 0 && a->tail_key != nullptr) ? 1 : 0;
+  const int64_t parts = (int64_t)a->num_splits + local.bf16_split;
+  const int64_t lse_floats = parts * a->rows * a->heads_q;
+  const int64_t out_floats = lse_floats * kHeadDim;
+  if (out_floats + lse_floats > (int64_t)kStaticScratchFloats) return BDFP4_E_TOO_LARGE;
+  float* scratch = nullptr;
+  cudaError_t e = split_scratch_address(&scratch);
+  if (e != cudaSuccess) return bdfp4::cuda_status(e);
+  local.partial_out = scratch;
+  local.partial_lse = scratch + out_floats;
+  const int status = bdfp4_decode(&local, stream);
+  if (status != BDFP4_OK) return status;
+  return bdfp4_combine(local.partial_out, local.partial_lse, (int32_t)parts, a->rows, a->heads_q, a->out,
+                       a->out_row_stride, stream);
+}

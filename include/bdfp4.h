@@ -33,6 +33,7 @@ extern "C" {
 #define BDFP4_E_UNSUPPORTED (-2) /* a valid request this build has no kernel for */
 #define BDFP4_E_CUDA (-3)     /* a CUDA runtime/driver call failed; see bdfp4_last_cuda_error */
 #define BDFP4_E_DEVICE (-4)   /* the current device is not sm_100-family */
+#define BDFP4_E_TOO_LARGE (-5) /* the request does not fit a fixed-capacity buffer of the library */
 
 /* bits a kernel may OR into *error_word */
 #define BDFP4_DEV_WAIT_TIMEOUT 1u /* a bounded mbarrier wait gave up */
@@ -239,6 +240,31 @@ int bdfp4_decode(const bdfp4_decode_args* args, void* stream);
  */
 int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
                   int32_t heads_q, void* out, int64_t out_row_stride, void* stream);
+
+/*
+ * Split-KV decode for callers that must not allocate device memory. It has no counterpart in the
+ * reference, whose split path always takes (or allocates) its partial buffers through torch.
+ *
+ * Who needs it: a serving engine that has given its whole HBM budget to the KV cache and decodes
+ * with its allocator frozen, a plugin entered while the host framework holds its memory pool, or an
+ * embedding that has no access to the framework's allocator. For them the FP32 partial outputs and
+ * log-sum-exps of the split path live in a fixed array inside this library's device image instead of
+ * in caller memory: BDFP4_STATIC_SCRATCH_BYTES on every GPU that loads the library, held until the
+ * process exits. The call runs bdfp4_decode with `num_splits` (>= 2) parts into that array and then
+ * bdfp4_combine into `out`; `partial_out` / `partial_lse` of `args` are ignored. It calls no
+ * cudaMalloc/cudaFree and no allocating library routine.
+ *
+ * Limit: (num_splits + bf16_split) * rows * heads_q * 129 floats must fit in the array, otherwise
+ * BDFP4_E_TOO_LARGE is returned and nothing is launched (8 MiB: e.g. 64 rows x 32 heads x 7 parts).
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current); make that first call outside any stream capture.
+ * The array is shared by every call and keeps the previous call's contents. Nothing in it has to
+ * start at zero: each part writes its log-sum-exp on every call (-inf when it had no work) and the
+ * merge adds a partial only under a positive weight. Two calls that overlap on the GPU (different
+ * streams, or different host threads) race on the array; serialise them on one stream.
+ */
+#define BDFP4_STATIC_SCRATCH_BYTES (8u << 20)
+int bdfp4_decode_split_static(const bdfp4_decode_args* args, void* stream);
 
 #ifdef __cplusplus
 }
