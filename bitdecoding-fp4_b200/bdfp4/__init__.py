@@ -30,6 +30,9 @@ EXPORTS = (
     "bdfp4_decode",
     "bdfp4_combine",
     "bdfp4_decode_split_static",
+    "bdfp4_control_step",
+    "bdfp4_work_table",
+    "bdfp4_tail_reset",
 )
 
 
@@ -102,6 +105,18 @@ class DecodeArgs(Structure):
     ]
 
 
+class ControlArgs(Structure):
+    _fields_ = [
+        ("block_table", c_void_p), ("block_table_stride", c_int64), ("block_table_columns", c_int32),
+        ("seq_lens", c_void_p), ("query_start_loc", c_void_p),
+        ("slot_keys", c_void_p), ("slot_last_seq", c_void_p), ("slot_last_seen", c_void_p), ("step", c_void_p),
+        ("row_to_slot", c_void_p), ("token_to_slot", c_void_p),
+        ("seqused_sink", c_void_p), ("seqused_fp4", c_void_p), ("seqused_residual", c_void_p),
+        ("promotion_source_tokens", c_void_p), ("promotion_pages", c_void_p), ("error_code", c_void_p),
+        ("num_reqs", c_int32), ("num_actual_tokens", c_int32), ("num_slots", c_int32), ("sink_tokens", c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -129,6 +144,14 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_decode.argtypes = [POINTER(DecodeArgs), c_void_p]
     lib.bdfp4_combine.restype = c_int32
     lib.bdfp4_combine.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]
+    lib.bdfp4_control_step.restype = c_int32
+    lib.bdfp4_control_step.argtypes = [POINTER(ControlArgs), c_void_p]
+    lib.bdfp4_work_table.restype = c_int32
+    lib.bdfp4_work_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int32,
+                                     c_int32, c_void_p]
+    lib.bdfp4_tail_reset.restype = c_int32
+    lib.bdfp4_tail_reset.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int64, c_void_p, c_void_p,
+                                     c_void_p, c_int32, c_void_p]
     lib.bdfp4_decode_split_static.restype = c_int32
     lib.bdfp4_decode_split_static.argtypes = [POINTER(DecodeArgs), c_void_p]
     _lib = lib
@@ -190,3 +213,27 @@ def decode_split_static(args: DecodeArgs, stream: int) -> None:
     Raises :class:`KernelError` with ``E_TOO_LARGE`` when the partials would not fit. Calls share
     the array, so run them on one stream; make the first call on a device outside stream capture."""
     check("bdfp4_decode_split_static", library().bdfp4_decode_split_static(ctypes.byref(args), stream))
+
+
+def control_step(args: ControlArgs, stream: int) -> None:
+    check("bdfp4_control_step", library().bdfp4_control_step(ctypes.byref(args), stream))
+
+
+def work_table(query_start_loc, seqused_fp4, row_to_slot, block_table, source_tokens, destination_pages,
+               num_reqs: int, columns_per_row: int, stream: int) -> None:
+    check(
+        "bdfp4_work_table",
+        library().bdfp4_work_table(ptr(query_start_loc), ptr(seqused_fp4), ptr(row_to_slot), ptr(block_table),
+                                   block_table.stride(0), ptr(source_tokens), ptr(destination_pages), num_reqs,
+                                   columns_per_row, stream),
+    )
+
+
+def tail_reset(tail_key, tail_value, query_start_loc, seq_lens, row_to_slot, num_reqs: int, stream: int) -> None:
+    layers, _, tokens, heads, head_dim = tail_key.shape
+    check(
+        "bdfp4_tail_reset",
+        library().bdfp4_tail_reset(ptr(tail_key), ptr(tail_value), tail_key.stride(0), tail_key.stride(1), layers,
+                                   tokens * heads * head_dim, ptr(query_start_loc), ptr(seq_lens), ptr(row_to_slot),
+                                   num_reqs, stream),
+    )

@@ -31,20 +31,17 @@ constexpr int kStageBytes = 8192 + 1024;  // codes + scales of one K or V page-h
 constexpr int kNP = 16;                   // N of the PV MMA (query rows, padded)
 constexpr float kRescaleThreshold = 8.0f;  // src/nvfp4_decode_kernel/fp4_decode_kernel.py:93
 
-// TMEM column map for a QK MMA of N = NQ columns: two S stages, two O stages (16 columns each),
-// then the scale-factor blocks (8 columns = two 4-column atoms each): Q, K x2, V x2, P x2.
-// 120 columns at NQ = 16 (128 allocated, so four CTAs share an SM's 512), 152 at NQ = 32.
-template <int NQ>
-struct TmemMap {
-  static constexpr int kS = 0;
-  static constexpr int kO = 2 * NQ;
-  static constexpr int kSFQ = kO + 32;
-  static constexpr int kSFK = kSFQ + 8;
-  static constexpr int kSFV = kSFK + 16;
-  static constexpr int kSFP = kSFV + 16;
-  static constexpr int kUsed = kSFP + 16;
-  static constexpr int kAlloc = kUsed <= 128 ? 128 : 256;
-};
+// TMEM column map (32-bit columns): two S^T stages and two O^T stages of 16 columns, then the
+// scale-factor blocks, 8 columns (two 4-column atoms) each: Q term 0, Q term 1, K x2, V x2, P x2.
+// 128 columns in all, so four CTAs share an SM's 512.
+constexpr int kNQ = 16;  // N of the QK MMA (query heads of one KV head, padded)
+constexpr int kColS = 0;
+constexpr int kColO = 32;
+constexpr int kColSFQ = 64;
+constexpr int kColSFK = 80;
+constexpr int kColSFV = 96;
+constexpr int kColSFP = 112;
+constexpr int kTmemColumns = 128;
 
 struct DecodeParams {
   int rows, heads_q, heads_kv, ratio;
@@ -80,12 +77,11 @@ struct DecodeParams {
 template <int GP, int STAGES>
 struct DecodeSmem {
   static constexpr int kStages = STAGES;
-  static constexpr int kNQ = GP <= 8 ? 16 : 32;
   alignas(1024) uint8_t k_stage[kStages][kStageBytes];
   alignas(1024) uint8_t v_stage[kStages][kStageBytes];
-  alignas(1024) uint8_t q_tile[kNQ * 64];
+  alignas(1024) uint8_t q_tile[2][kNQ * 64];  // one B operand per query term
   alignas(1024) uint8_t p_tile[2][kNP * 64];
-  alignas(1024) uint8_t q_sf[1024];
+  alignas(1024) uint8_t q_sf[2][1024];
   alignas(1024) uint8_t p_sf[2][1024];
   float q_bf16[GP][128];  // BF16 query of the tail/sink blocks, widened
   float p_bf16[GP][128];  // BF16-rounded probabilities of a tail/sink block
@@ -266,12 +262,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
                   const DecodeParams p) {
   using Smem = DecodeSmem<GP, STAGES>;
   constexpr int KS = Smem::kStages;
-  constexpr int NQ = Smem::kNQ;  // N of the QK MMA: term 0 in columns [0, GP), term 1 from NQ/2
-  using Map = TmemMap<NQ>;
-  constexpr int kColS = Map::kS, kColO = Map::kO, kColSFQ = Map::kSFQ, kColSFK = Map::kSFK, kColSFV = Map::kSFV,
-                kColSFP = Map::kSFP;
-  constexpr int kTmemColumns = Map::kAlloc;
-  constexpr int LD = GP <= 4 ? 4 : (GP <= 8 ? 8 : 16);
+  constexpr int LD = GP;  // columns one tcgen05.ld brings (4, 8 or 16)
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -331,41 +322,27 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     tc::prefetch_tensormap(&v_map);
   }
   // Q tile (B operand of QK), its scale atoms, zeroed P buffers, widened BF16 query
-  constexpr int kQChunks = NQ * 64 / 16;
-  for (int i = tid; i < kQChunks + (2 * kNP * 64 + 1024 + 2 * 1024) / 16; i += 192) {
-    uint4* base;
-    int index = i;
-    if (index < kQChunks) {
-      base = reinterpret_cast<uint4*>(sm.q_tile);
-    } else if (index < kQChunks + 128) {
-      base = reinterpret_cast<uint4*>(sm.p_tile);
-      index -= kQChunks;
-    } else if (index < kQChunks + 128 + 64) {
-      base = reinterpret_cast<uint4*>(sm.q_sf);
-      index -= kQChunks + 128;
-    } else {
-      base = reinterpret_cast<uint4*>(sm.p_sf);
-      index -= kQChunks + 192;
-    }
-    base[index] = make_uint4(0, 0, 0, 0);
+  // zero the Q tiles, P tiles and both scale-atom buffers (contiguous 1 KB blocks)
+  {
+    uint4* blocks[4] = {reinterpret_cast<uint4*>(sm.q_tile), reinterpret_cast<uint4*>(sm.p_tile),
+                        reinterpret_cast<uint4*>(sm.q_sf), reinterpret_cast<uint4*>(sm.p_sf)};
+    for (int i = tid; i < 4 * 128; i += 192) blocks[i >> 7][i & 127] = make_uint4(0, 0, 0, 0);
   }
   __syncthreads();
   for (int i = tid; i < TERMS * G * 4; i += 192) {  // 16-byte chunks of the query codes
     const int chunk = i & 3;
     const int g = (i >> 2) % G;
     const int term = (i >> 2) / G;
-    const int n = term * (NQ / 2) + g;
     const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q_codes[term] +
                                                          ((int64_t)row * p.heads_q + kv_head * G + g) * 64) + chunk);
-    *reinterpret_cast<uint4*>(sm.q_tile + swizzle64(n * 64 + chunk * 16)) = v;
+    *reinterpret_cast<uint4*>(sm.q_tile[term] + swizzle64(g * 64 + chunk * 16)) = v;
   }
   for (int i = tid; i < TERMS * G * 2; i += 192) {  // 4 scale bytes of (term, head, atom)
     const int atom = i & 1;
     const int g = (i >> 1) % G;
     const int term = (i >> 1) / G;
-    const int n = term * (NQ / 2) + g;
     const uint8_t* tile = p.q_scales[term] + ((int64_t)row * p.heads_q + kv_head) * 1024;
-    *reinterpret_cast<uint32_t*>(sm.q_sf + atom * 512 + n * 16) =
+    *reinterpret_cast<uint32_t*>(sm.q_sf[term] + atom * 512 + g * 16) =
         __ldg(reinterpret_cast<const uint32_t*>(tile + atom * 512 + g * 16));
   }
   if (with_bf16) {
@@ -445,11 +422,14 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   } else if (warp == 1) {
     // ---- MMA issuer ---------------------------------------------------------------------------
     if (lane == 0 && num_pages > 0) {
-      constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, NQ);
+      constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, kNQ);
       constexpr uint32_t idesc_pv = tc::nvf4_idesc(128, kNP);
       const uint32_t q_addr = tc::smem_u32(sm.q_tile);
-      tc::cp_sf_atom(tmem + kColSFQ, tc::sf_atom_desc(tc::smem_u32(sm.q_sf)));
-      tc::cp_sf_atom(tmem + kColSFQ + 4, tc::sf_atom_desc(tc::smem_u32(sm.q_sf) + 512));
+#pragma unroll
+      for (int term = 0; term < TERMS; ++term) {
+        tc::cp_sf_atom(tmem + kColSFQ + 8 * term, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[term])));
+        tc::cp_sf_atom(tmem + kColSFQ + 8 * term + 4, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[term]) + 512));
+      }
       auto issue_pv = [&](int m) -> bool {
         const int s = m % KS;
         const int b = m & 1;
@@ -460,16 +440,16 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         tc::fence_after_sync();
         const uint32_t v_addr = tc::smem_u32(sm.v_stage[s]);
         const uint32_t p_addr = tc::smem_u32(sm.p_tile[b]);
-        tc::cp_sf_atom(tmem + kColSFV + 16 * b, tc::sf_atom_desc(v_addr + 8192));
-        tc::cp_sf_atom(tmem + kColSFV + 16 * b + 4, tc::sf_atom_desc(v_addr + 8192 + 512));
-        tc::cp_sf_atom(tmem + kColSFP + 16 * b, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b])));
-        tc::cp_sf_atom(tmem + kColSFP + 16 * b + 4, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b]) + 512));
+        tc::cp_sf_atom(tmem + kColSFV + 8 * b, tc::sf_atom_desc(v_addr + 8192));
+        tc::cp_sf_atom(tmem + kColSFV + 8 * b + 4, tc::sf_atom_desc(v_addr + 8192 + 512));
+        tc::cp_sf_atom(tmem + kColSFP + 8 * b, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b])));
+        tc::cp_sf_atom(tmem + kColSFP + 8 * b + 4, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b]) + 512));
         if (!tc::mbar_wait(&sm.o_empty[b], pair_parity ^ 1, abort_flag)) return false;
         tc::fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 2; ++k)
           tc::mma_nvf4(tmem + kColO + 16 * b, tc::fp4_tile_desc(v_addr, k), tc::fp4_tile_desc(p_addr, k), idesc_pv,
-                       tmem + kColSFV + 16 * b + 4 * k, tmem + kColSFP + 16 * b + 4 * k, k != 0);
+                       tmem + kColSFV + 8 * b + 4 * k, tmem + kColSFP + 8 * b + 4 * k, k != 0);
         tc::commit(&sm.o_full[b]);
         tc::commit(&sm.v_empty[s]);
         tc::commit(&sm.p_empty[b]);
@@ -483,15 +463,20 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         if (!ok) break;
         tc::fence_after_sync();
         const uint32_t k_addr = tc::smem_u32(sm.k_stage[s]);
-        tc::cp_sf_atom(tmem + kColSFK + 16 * b, tc::sf_atom_desc(k_addr + 8192));
-        tc::cp_sf_atom(tmem + kColSFK + 16 * b + 4, tc::sf_atom_desc(k_addr + 8192 + 512));
+        tc::cp_sf_atom(tmem + kColSFK + 8 * b, tc::sf_atom_desc(k_addr + 8192));
+        tc::cp_sf_atom(tmem + kColSFK + 8 * b + 4, tc::sf_atom_desc(k_addr + 8192 + 512));
         ok = tc::mbar_wait(&sm.s_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc::fence_after_sync();
+        // both query terms accumulate into the same S^T columns: K.Q0 + K.Q1 in FP32
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-          tc::mma_nvf4(tmem + kColS + NQ * b, tc::fp4_tile_desc(k_addr, k), tc::fp4_tile_desc(q_addr, k), idesc_qk,
-                       tmem + kColSFK + 16 * b + 4 * k, tmem + kColSFQ + 4 * k, k != 0);
+        for (int term = 0; term < TERMS; ++term) {
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+            tc::mma_nvf4(tmem + kColS + kNQ * b, tc::fp4_tile_desc(k_addr, k),
+                         tc::fp4_tile_desc(q_addr + term * (kNQ * 64), k), idesc_qk,
+                         tmem + kColSFK + 8 * b + 4 * k, tmem + kColSFQ + 8 * term + 4 * k, (term | k) != 0);
+        }
         tc::commit(&sm.s_full[b]);
         tc::commit(&sm.k_empty[s]);
         if (i > 0) ok = issue_pv(i - 1);
@@ -526,6 +511,41 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     float acc_prev[GP];
 #pragma unroll
     for (int j = 0; j < GP; ++j) acc_prev[j] = 1.0f;
+    // Which row's group maximum this lane ends up holding after the reduce-scatter below: step i
+    // hands the upper half of the rows still held to the lanes whose bit i is set.
+    constexpr int LOG = GP == 4 ? 2 : (GP == 8 ? 3 : 4);
+    int own_row = 0;
+#pragma unroll
+    for (int i = 0; i < LOG; ++i) own_row += ((lane >> i) & 1) * (GP >> (i + 1));
+    const float headroom = kRescaleThreshold / p.scale_log2;  // score growth the stale maximum tolerates
+    float threshold[GP];   // a score above this forces the running maximum to move
+    float max_scaled[GP];  // running maximum in log2 units with the c8 shift folded in
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      const float safe = st.row_max[j] == -INFINITY ? 0.0f : st.row_max[j];
+      max_scaled[j] = safe * p.scale_log2 - shift;
+      threshold[j] = 0.0f;
+    }
+    float own_max_scaled = 0.0f;
+    auto refresh_thresholds = [&]() {
+      own_max_scaled = max_scaled[0];
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        threshold[j] = st.row_max[j] + headroom;
+        own_max_scaled = own_row == j ? max_scaled[j] : own_max_scaled;
+      }
+    };
+    refresh_thresholds();
+    // constant parts of this thread's shared-memory addresses
+    const int group = t >> 4;
+    const int sf_offset = (group >> 2) * 512 + own_row * 16 + (group & 3);
+    const bool stores_sf = (lane & 15) < GP;
+    // after the nibble transpose a lane of an 8-lane cluster holds one row's codes for 4 (GP = 4)
+    // or 8 (GP = 8) consecutive tokens
+    const int pack_row = GP == 4 ? (((lane & 1) << 1) | ((lane >> 1) & 1))
+                                 : (((lane & 1) << 2) | (lane & 2) | ((lane >> 2) & 1));
+    const int pack_offset = GP == 4 ? swizzle64(pack_row * 64 + (t >> 2) * 2) : swizzle64(pack_row * 64 + (t >> 3) * 4);
+
     bool stop = false;
     for (int i = 0; i < num_pages && !stop; ++i) {
       const int b = i & 1;
@@ -534,56 +554,72 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       tc::mbar_wait(&sm.s_full[b], parity, abort_flag);
       tc::fence_after_sync();
       float s[GP];
-      {
-        float raw[LD];
-        tc::tmem_ld<LD>(lane_base + kColS + NQ * b, raw);
-        if (TERMS == 2) {
-          float raw2[LD];
-          tc::tmem_ld<LD>(lane_base + kColS + NQ * b + NQ / 2, raw2);
-          tc::tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < GP; ++j) s[j] = raw[j] + raw2[j];
-        } else {
-          tc::tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < GP; ++j) s[j] = raw[j];
-        }
-      }
+      tc::tmem_ld<LD>(lane_base + kColS + kNQ * b, s);
+      tc::tmem_wait_ld();
       tc::fence_before_sync();
       tc::mbar_arrive(&sm.s_empty[b]);
       if (logical_page == 0 && t < sink_len) {
 #pragma unroll
         for (int j = 0; j < GP; ++j) s[j] = -INFINITY;
       }
-      // does any row's maximum grow past the threshold? (a NaN difference counts as growth)
+      // does any row's maximum have to move? one predicate per thread, one barrier-wide OR
       bool grows = true;
       if (!st.first) {
         bool own = *abort_flag != 0;
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
-          const float grown = (st.row_max[j] - fmaxf(st.row_max[j], s[j])) * p.scale_log2;
-          own = own || !(grown >= -kRescaleThreshold);
-        }
+        for (int j = 0; j < GP; ++j) own = own || s[j] > threshold[j];
         grows = softmax_vote_any(own);
       }
-      float group_max[GP];
+      float acc[GP];
+      float own_group_max;  // maximum of row `own_row` over this lane's 16-token scale group
+      if constexpr (GP <= 8) {
+        // reduce-scatter: GP - 1 shuffles leave each lane with one row's maximum over GP lanes,
+        // the remaining butterfly steps finish that row's 16-lane group
+        float held[GP];
 #pragma unroll
-      for (int j = 0; j < GP; ++j) {
-        float m = s[j];
+        for (int j = 0; j < GP; ++j) held[j] = s[j];
 #pragma unroll
-        for (int step = 1; step < 16; step <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, step));
-        group_max[j] = m;
+        for (int step = 0; step < LOG; ++step) {
+          const int half = GP >> (step + 1);
+          const bool upper = (lane >> step) & 1;
+#pragma unroll
+          for (int k = 0; k < half; ++k) {
+            const float send = upper ? held[k] : held[k + half];
+            const float keep = upper ? held[k + half] : held[k];
+            held[k] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 1 << step));
+          }
+        }
+        own_group_max = held[0];
+#pragma unroll
+        for (int step = LOG; step < 4; ++step)
+          own_group_max = fmaxf(own_group_max, __shfl_xor_sync(0xffffffffu, own_group_max, 1 << step));
+      } else {
+        own_group_max = 0.0f;  // GP = 16 keeps every row's group maximum (below)
       }
-      float acc[GP], max_scaled[GP];
+      float group_max[GP];
+      if constexpr (GP > 8) {
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          float m = s[j];
+#pragma unroll
+          for (int step = 1; step < 16; step <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, step));
+          group_max[j] = m;
+        }
+      }
       if (grows) {
         float block_max[GP];
+        if constexpr (GP <= 8) {
+          const float warp_max = fmaxf(own_group_max, __shfl_xor_sync(0xffffffffu, own_group_max, 16));
+          if (lane < GP) sm.red[red_buf][warp_q][own_row] = warp_max;
+        } else {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) block_max[j] = fmaxf(group_max[j], __shfl_xor_sync(0xffffffffu, group_max[j], 16));
-        if (lane < GP) {
-          float mine = block_max[0];
+          for (int j = 0; j < GP; ++j) block_max[j] = fmaxf(group_max[j], __shfl_xor_sync(0xffffffffu, group_max[j], 16));
+          if (lane < GP) {
+            float mine = block_max[0];
 #pragma unroll
-          for (int j = 1; j < GP; ++j) mine = lane == j ? block_max[j] : mine;
-          sm.red[red_buf][warp_q][lane] = mine;
+            for (int j = 1; j < GP; ++j) mine = lane == j ? block_max[j] : mine;
+            sm.red[red_buf][warp_q][lane] = mine;
+          }
         }
         softmax_barrier();
 #pragma unroll
@@ -592,41 +628,97 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
                                fmaxf(sm.red[red_buf][2][j], sm.red[red_buf][3][j]));
         red_buf ^= 1;
         update_max<GP>(st, block_max, p.scale_log2, shift, acc, max_scaled);
+        refresh_thresholds();
         stop = *abort_flag != 0;  // uniform: every thread reads it after the same barrier
+#pragma unroll
+        for (int j = 0; j < GP; ++j) st.row_sum[j] *= acc[j];
       } else {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
-          acc[j] = 1.0f;
-          const float safe = st.row_max[j] == -INFINITY ? 0.0f : st.row_max[j];
-          max_scaled[j] = safe * p.scale_log2 - shift;
-        }
+        for (int j = 0; j < GP; ++j) acc[j] = 1.0f;
       }
       st.first = false;
-      uint32_t words[GP];
-      float group_scale[GP];
+      float prob[GP];
 #pragma unroll
       for (int j = 0; j < GP; ++j) {
-        const float prob = ex2_approx(s[j] * p.scale_log2 - max_scaled[j]);
-        st.row_sum[j] = st.row_sum[j] * acc[j] + prob;
-        const float maximum = ex2_approx(group_max[j] * p.scale_log2 - max_scaled[j]);
-        const float scale = probability_scale(maximum, p.p_mode, p.tau);
-        group_scale[j] = scale;
-        const float q = prob * rcp_approx(fmaxf(scale, 1e-20f));
-        uint32_t word = (cvt_e2m1x2(q, 0.0f) & 0xfu) << (4 * (lane & 7));
-        word |= __shfl_xor_sync(0xffffffffu, word, 1);
-        word |= __shfl_xor_sync(0xffffffffu, word, 2);
-        word |= __shfl_xor_sync(0xffffffffu, word, 4);
-        words[j] = word;
+        prob[j] = ex2_approx(fmaf(s[j], p.scale_log2, -max_scaled[j]));
+        st.row_sum[j] += prob[j];
       }
-      // the PV MMA of two pages ago must be done with this P buffer
-      tc::mbar_wait(&sm.p_empty[b], parity ^ 1, abort_flag);
+      if constexpr (GP <= 8) {
+        // the lane holding a row's group maximum turns it into the group's scale once; the
+        // group's lanes fetch the reciprocal from it
+        const float maximum = ex2_approx(fmaf(own_group_max, p.scale_log2, -own_max_scaled));
+        const float own_scale = probability_scale(maximum, p.p_mode, p.tau);
+        const float own_inverse = rcp_approx(fmaxf(own_scale, 1e-20f));
+        const int cluster = lane & ~(GP - 1);
 #pragma unroll
-      for (int j = 0; j < GP; ++j) {
-        if ((lane & 7) == (j & 7))
-          *reinterpret_cast<uint32_t*>(sm.p_tile[b] + swizzle64(j * 64 + (t >> 3) * 4)) = words[j];
-        if ((lane & 15) == j) {
-          const int group = t >> 4;
-          sm.p_sf[b][(group >> 2) * 512 + j * 16 + (group & 3)] = (uint8_t)cvt_e4m3(group_scale[j]);
+        for (int j = 0; j < GP; ++j) {
+          int source = 0;  // the lane pattern whose own_row is j (bit reversal of j)
+#pragma unroll
+          for (int bit = 0; bit < LOG; ++bit) source |= ((j >> (LOG - 1 - bit)) & 1) << bit;
+          prob[j] *= __shfl_sync(0xffffffffu, own_inverse, cluster | source);
+        }
+        // E2M1 codes of this token: one byte per pair of rows, then a nibble transpose across the
+        // lanes of an 8-token cluster so that each lane stores one row's run of tokens
+        uint32_t codes = 0;
+#pragma unroll
+        for (int j = 0; j < GP; j += 2) codes |= cvt_e2m1x2(prob[j], prob[j + 1]) << (4 * j);
+        {
+          const uint32_t other = __shfl_xor_sync(0xffffffffu, codes, 1);
+          const bool odd = lane & 1;
+          const uint32_t even_token = (odd ? other : codes) >> (odd ? 2 * GP : 0);  // rows this lane keeps
+          const uint32_t odd_token = (odd ? codes : other) >> (odd ? 2 * GP : 0);
+          if constexpr (GP == 4) {
+            codes = (even_token & 0xfu) | ((odd_token & 0xfu) << 4) | ((even_token & 0xf0u) << 4) |
+                    ((odd_token & 0xf0u) << 8);
+          } else {
+            codes = (even_token & 0xfu) | ((odd_token & 0xfu) << 4) | ((even_token & 0xf0u) << 4) |
+                    ((odd_token & 0xf0u) << 8) | ((even_token & 0xf00u) << 8) | ((odd_token & 0xf00u) << 12) |
+                    ((even_token & 0xf000u) << 12) | ((odd_token & 0xf000u) << 16);
+          }
+        }
+        {
+          const uint32_t other = __shfl_xor_sync(0xffffffffu, codes, 2);
+          const bool upper = lane & 2;
+          if constexpr (GP == 4) {
+            codes = __byte_perm(codes, other, upper ? 0x0015 : 0x0040);
+          } else {
+            codes = __byte_perm(codes, other, upper ? 0x3726 : 0x5140);
+          }
+        }
+        if constexpr (GP == 8) {
+          const uint32_t other = __shfl_xor_sync(0xffffffffu, codes, 4);
+          codes = __byte_perm(codes, other, (lane & 4) ? 0x3276 : 0x5410);
+        }
+        // the PV MMA of two pages ago must be done with this P buffer
+        tc::mbar_wait(&sm.p_empty[b], parity ^ 1, abort_flag);
+        if constexpr (GP == 4) {
+          *reinterpret_cast<uint16_t*>(sm.p_tile[b] + pack_offset) = (uint16_t)codes;
+        } else {
+          *reinterpret_cast<uint32_t*>(sm.p_tile[b] + pack_offset) = codes;
+        }
+        if (stores_sf) sm.p_sf[b][sf_offset] = (uint8_t)cvt_e4m3(own_scale);
+      } else {
+        uint32_t words[GP];
+        float group_scale[GP];
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          const float maximum = ex2_approx(fmaf(group_max[j], p.scale_log2, -max_scaled[j]));
+          const float scale = probability_scale(maximum, p.p_mode, p.tau);
+          group_scale[j] = scale;
+          const float q = prob[j] * rcp_approx(fmaxf(scale, 1e-20f));
+          uint32_t word = (cvt_e2m1x2(q, 0.0f) & 0xfu) << (4 * (lane & 7));
+          word |= __shfl_xor_sync(0xffffffffu, word, 1);
+          word |= __shfl_xor_sync(0xffffffffu, word, 2);
+          word |= __shfl_xor_sync(0xffffffffu, word, 4);
+          words[j] = word;
+        }
+        tc::mbar_wait(&sm.p_empty[b], parity ^ 1, abort_flag);
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          if ((lane & 7) == (j & 7))
+            *reinterpret_cast<uint32_t*>(sm.p_tile[b] + swizzle64(j * 64 + (t >> 3) * 4)) = words[j];
+          if ((lane & 15) == j)
+            sm.p_sf[b][(group >> 2) * 512 + j * 16 + (group & 3)] = (uint8_t)cvt_e4m3(group_scale[j]);
         }
       }
       tc::fence_proxy_async_smem();
@@ -642,7 +734,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         tc::fence_before_sync();
         tc::mbar_arrive(&sm.o_empty[pb]);
 #pragma unroll
-        for (int j = 0; j < GP; ++j) st.o_acc[j] = st.o_acc[j] * acc_prev[j] + o[j];
+        for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
       }
 #pragma unroll
       for (int j = 0; j < GP; ++j) acc_prev[j] = acc[j];
@@ -656,7 +748,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       tc::tmem_wait_ld();
       tc::fence_before_sync();
 #pragma unroll
-      for (int j = 0; j < GP; ++j) st.o_acc[j] = st.o_acc[j] * acc_prev[j] + o[j];
+      for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
     }
     if (with_bf16 && p.seqused_sink) {
       bf16_block<GP, STAGES>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,

@@ -242,6 +242,67 @@ int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t pa
                   int32_t heads_q, void* out, int64_t out_row_stride, void* stream);
 
 /*
+ * One step of the device-side slot table that maps the rows of a batch to BF16 tail slots and
+ * derives each row's sink / FP4 / rolling-tail lengths and promotion target, with no value read
+ * back to the host. Replaces ControlPlane.prepare and its Triton kernel _control_kernel
+ * (src/nvfp4_vllm/control.py:140-370, 491-561).
+ *
+ * A row is keyed on column 0 of its block-table row. Rows i < num_reqs with seq_lens[i] > 0 and a
+ * key other than the null block 0 are live; a live row keeps the slot holding its key or takes
+ * the least recently seen slot no live row claimed. Outputs are written for indices [0, num_slots):
+ * row_to_slot (-1 for a dead row), seqused_sink = min(seq, sink_tokens), seqused_fp4 =
+ * ((seq-1)/128)*128, seqused_residual = seq - fp4, promotion_source_tokens = slot*(128+sink_tokens),
+ * promotion_pages = the block of page fp4/128 when seq % 128 == 0 else -1; token_to_slot for
+ * [0, num_actual_tokens). Violated assumptions are OR-ed into *error_code:
+ * 1 continuation prefill, 2 slot lost, 4 stale slot history, 8 no free slot, 16 duplicate key,
+ * 32 promotion column past the block table (src/nvfp4_vllm/control.py:107-124).
+ */
+typedef struct bdfp4_control_args {
+  const int32_t* block_table; /* int32 [>=num_reqs][block_table_stride] */
+  int64_t block_table_stride;
+  int32_t block_table_columns;
+  const int32_t* seq_lens;        /* [num_reqs] */
+  const int32_t* query_start_loc; /* [num_reqs + 1] */
+  int32_t* slot_keys;             /* [num_slots] persistent: block id owning the slot, -1 free */
+  int32_t* slot_last_seq;         /* [num_slots] persistent */
+  int32_t* slot_last_seen;        /* [num_slots] persistent: step the slot was last owned */
+  int32_t* step;                  /* [1] persistent counter */
+  int32_t* row_to_slot;           /* [num_slots] */
+  int32_t* token_to_slot;         /* [>= num_actual_tokens] */
+  int32_t* seqused_sink;          /* [num_slots] */
+  int32_t* seqused_fp4;
+  int32_t* seqused_residual;
+  int32_t* promotion_source_tokens;
+  int32_t* promotion_pages;
+  int32_t* error_code; /* [1] sticky */
+  int32_t num_reqs;    /* <= 256 */
+  int32_t num_actual_tokens;
+  int32_t num_slots;   /* <= 256 (the reference supports at most 128) */
+  int32_t sink_tokens;
+} bdfp4_control_args;
+
+int bdfp4_control_step(const bdfp4_control_args* args, void* stream);
+
+/*
+ * The quantizer's per-step page work table: slot (row, column) reads tokens
+ * query_start_loc[row] + 128*column and writes block_table[row][column] when the row is a fresh
+ * prefill (more than one token this step, a slot, column < seqused_fp4/128), else -1.
+ * Replaces _work_table_kernel (src/nvfp4_vllm/write.py:28-78).
+ */
+int bdfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4, const int32_t* row_to_slot,
+                     const int32_t* block_table, int64_t block_table_stride, int32_t* source_tokens,
+                     int32_t* destination_pages, int32_t num_reqs, int32_t columns_per_row, void* stream);
+
+/*
+ * Zero every layer's BF16 tail page (page_elems = (128+sink)*H*128 elements) of the rows that start
+ * a request this step (seq_len <= tokens brought), so a recycled slot never shows stale tokens.
+ * Replaces _tail_reset_kernel (src/nvfp4_vllm/write.py:81-165). Strides in elements.
+ */
+int bdfp4_tail_reset(void* tail_key, void* tail_value, int64_t layer_stride, int64_t slot_stride, int32_t layers,
+                     int64_t page_elems, const int32_t* query_start_loc, const int32_t* seq_lens,
+                     const int32_t* row_to_slot, int32_t num_reqs, void* stream);
+
+/*
  * Split-KV decode for callers that must not allocate device memory. It has no counterpart in the
  * reference, whose split path always takes (or allocates) its partial buffers through torch.
  *
