@@ -29,6 +29,7 @@ EXPORTS = (
     "bdfp4_quantize_query",
     "bdfp4_decode",
     "bdfp4_combine",
+    "bdfp4_combine_strided",
     "bdfp4_decode_split_static",
     "bdfp4_control_step",
     "bdfp4_work_table",
@@ -144,6 +145,9 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_decode.argtypes = [POINTER(DecodeArgs), c_void_p]
     lib.bdfp4_combine.restype = c_int32
     lib.bdfp4_combine.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]
+    lib.bdfp4_combine_strided.restype = c_int32
+    lib.bdfp4_combine_strided.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p,
+                                          c_int64, c_void_p]
     lib.bdfp4_control_step.restype = c_int32
     lib.bdfp4_control_step.argtypes = [POINTER(ControlArgs), c_void_p]
     lib.bdfp4_work_table.restype = c_int32
@@ -202,8 +206,18 @@ def combine(partial_out, partial_lse, parts: int, rows: int, heads_q: int, out, 
             stream: int) -> None:
     check(
         "bdfp4_combine",
+    "bdfp4_combine_strided",
         library().bdfp4_combine(ptr(partial_out), ptr(partial_lse), parts, rows, heads_q, ptr(out),
                                 out_row_stride, stream),
+    )
+
+
+def combine_strided(partial_out_ptr: int, out_part_stride: int, partial_lse_ptr: int, lse_part_stride: int,
+                    parts: int, rows: int, heads_q: int, out, out_row_stride: int, stream: int) -> None:
+    check(
+        "bdfp4_combine_strided",
+        library().bdfp4_combine_strided(partial_out_ptr, out_part_stride, partial_lse_ptr, lse_part_stride, parts,
+                                        rows, heads_q, ptr(out), out_row_stride, stream),
     )
 
 

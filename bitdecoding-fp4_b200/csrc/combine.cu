@@ -12,12 +12,11 @@ constexpr int kMaxRegisterParts = 32;
 __global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ partial_out,
                                                       const float* __restrict__ partial_lse, int parts, int rows,
                                                       int heads_q, __nv_bfloat16* __restrict__ out,
-                                                      int64_t out_row_stride) {
+                                                      int64_t out_row_stride, int64_t out_stride,
+                                                      int64_t lse_stride) {
   const int head = blockIdx.x;
   const int row = blockIdx.y;
   const int channel = threadIdx.x;
-  const int64_t lse_stride = (int64_t)rows * heads_q;
-  const int64_t out_stride = lse_stride * kHeadDim;
   const float* lse = partial_lse + (int64_t)row * heads_q + head;
   const float* values = partial_out + ((int64_t)row * heads_q + head) * kHeadDim + channel;
   constexpr float kLog2e = 1.4426950408889634f;
@@ -39,11 +38,21 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ 
 
 }  // namespace bdfp4
 
-extern "C" int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
-                             int32_t heads_q, void* out, int64_t out_row_stride, void* stream) {
+extern "C" int bdfp4_combine_strided(const float* partial_out, int64_t out_part_stride, const float* partial_lse,
+                                     int64_t lse_part_stride, int32_t parts, int32_t rows, int32_t heads_q,
+                                     void* out, int64_t out_row_stride, void* stream) {
   if (!partial_out || !partial_lse || !out || parts < 1 || rows < 1 || heads_q < 1) return BDFP4_E_ARG;
   if (out_row_stride < (int64_t)heads_q * bdfp4::kHeadDim) return BDFP4_E_ARG;
+  if (out_part_stride < (int64_t)rows * heads_q * bdfp4::kHeadDim || lse_part_stride < (int64_t)rows * heads_q)
+    return BDFP4_E_ARG;
   bdfp4::combine_kernel<<<dim3(heads_q, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial_out, partial_lse, parts, rows, heads_q, static_cast<__nv_bfloat16*>(out), out_row_stride);
+      partial_out, partial_lse, parts, rows, heads_q, static_cast<__nv_bfloat16*>(out), out_row_stride,
+      out_part_stride, lse_part_stride);
   return bdfp4::cuda_status(cudaGetLastError());
+}
+
+extern "C" int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
+                             int32_t heads_q, void* out, int64_t out_row_stride, void* stream) {
+  return bdfp4_combine_strided(partial_out, (int64_t)rows * heads_q * bdfp4::kHeadDim, partial_lse,
+                               (int64_t)rows * heads_q, parts, rows, heads_q, out, out_row_stride, stream);
 }

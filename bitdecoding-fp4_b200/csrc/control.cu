@@ -22,8 +22,8 @@ struct ControlParams {
   const int32_t* query_start_loc;
   int32_t* slot_keys;
   int32_t* slot_last_seq;
-  int32_t* slot_last_seen;
-  int32_t* step;
+  int64_t* slot_last_seen;
+  int64_t* step;
   int32_t* row_to_slot;
   int32_t* token_to_slot;
   int32_t* seqused_sink;
@@ -39,11 +39,13 @@ struct ControlParams {
 // (the physical block holding its first page), which stays fixed for the life of a request. Rows
 // that match a slot keep it; the others take the unclaimed slots, least recently seen first.
 __global__ void control_kernel(const ControlParams p) {
-  __shared__ int s_key[kMaxControl], s_slot_key[kMaxControl], s_slot_seen[kMaxControl], s_slot_seq[kMaxControl];
+  __shared__ int s_key[kMaxControl], s_slot_key[kMaxControl], s_slot_seq[kMaxControl];
+  __shared__ long long s_slot_seen[kMaxControl];
   __shared__ int s_matched[kMaxControl], s_needs[kMaxControl], s_need_rank[kMaxControl], s_free[kMaxControl];
   __shared__ int s_free_rank[kMaxControl], s_slot[kMaxControl], s_seq[kMaxControl], s_live[kMaxControl];
   __shared__ int s_q_begin[kMaxControl], s_q_end[kMaxControl];
-  __shared__ int s_errors, s_step;
+  __shared__ int s_errors;
+  __shared__ long long s_step;
   const int i = threadIdx.x;
   const int n = blockDim.x;
   if (i == 0) {
@@ -62,7 +64,7 @@ __global__ void control_kernel(const ControlParams p) {
   const int computed = seq - query_len;
   const int slot_key = is_slot ? p.slot_keys[i] : kFreeKey;
   const int slot_last_seq = is_slot ? p.slot_last_seq[i] : -1;
-  const int slot_last_seen = is_slot ? p.slot_last_seen[i] : -1;
+  const long long slot_last_seen = is_slot ? p.slot_last_seen[i] : -1;
   s_key[i] = key;
   s_seq[i] = seq;
   s_live[i] = live;

@@ -781,7 +781,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         const bool empty = total[j] == 0.0f || total[j] != total[j];
         const float value = empty ? 0.0f : st.o_acc[j] * (1.0f / total[j]);
         const int head = kv_head * G + j;
-        if (p.num_splits == 1) {
+        if (p.out != nullptr) {
           p.out[(int64_t)row * p.out_row_stride + head * kHeadDim + t] = __float2bfloat16_rn(value);
         } else {
           p.partial_out[(((int64_t)part * p.rows + row) * p.heads_q + head) * kHeadDim + t] = value;
@@ -897,8 +897,11 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   if (a->p_scale_mode < 0 || a->p_scale_mode > 2) return BDFP4_E_ARG;
   if (a->num_splits < 1) return BDFP4_E_ARG;
   const bool own_bf16 = a->num_splits > 1 && a->bf16_split != 0;
-  if (a->num_splits == 1) {
-    if (!a->out || a->out_row_stride < (int64_t)a->heads_q * kHeadDim) return BDFP4_E_ARG;
+  // One part may leave either as BF16 `out` or, when `out` is null, as an FP32 partial with its
+  // LSE (a KV-axis shard of a longer sequence whose partials are merged elsewhere).
+  const bool writes_out = a->num_splits == 1 && a->out != nullptr;
+  if (writes_out) {
+    if (a->out_row_stride < (int64_t)a->heads_q * kHeadDim) return BDFP4_E_ARG;
   } else if (!a->partial_out || !a->partial_lse) {
     return BDFP4_E_ARG;
   }
@@ -958,7 +961,7 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.p_mode = a->p_scale_mode;
   p.tau = a->p_scale_tau;
-  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.out = writes_out ? static_cast<__nv_bfloat16*>(a->out) : nullptr;
   p.out_row_stride = a->out_row_stride;
   p.num_splits = a->num_splits;
   p.bf16_split = own_bf16 ? 1 : 0;

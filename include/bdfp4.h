@@ -221,7 +221,9 @@ typedef struct bdfp4_decode_args {
   int32_t p_scale_mode; /* BDFP4_P_* */
   float p_scale_tau;    /* threshold of the amax2_or_amax6 rules (default 21/1024) */
   /* outputs */
-  void* out; /* BF16 [rows][Hq][128] with row stride out_row_stride (elements); used when num_splits == 1 */
+  void* out; /* BF16 [rows][Hq][128] with row stride out_row_stride (elements); used when num_splits == 1.
+              * NULL at num_splits == 1: the single part is written as a partial + LSE instead (one KV-axis
+              * shard of a longer sequence, to be merged by bdfp4_combine with the other shards' partials) */
   int64_t out_row_stride;
   int32_t num_splits;
   int32_t bf16_split;  /* 1: tail+sink get a split of their own (index num_splits) */
@@ -240,6 +242,16 @@ int bdfp4_decode(const bdfp4_decode_args* args, void* stream);
  */
 int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
                   int32_t heads_q, void* out, int64_t out_row_stride, void* stream);
+
+/*
+ * The same merge with explicit distances (in floats) between consecutive parts, for partials that
+ * arrive as one gathered record per part, e.g. [O | LSE] blocks received from other GPUs by one
+ * all-gather: the KV-axis split of a single long sequence across GPUs. Merge math as above
+ * (src/nvfp4_decode_kernel/split_k_combine.py:62-83); the reference has no multi-GPU merge.
+ */
+int bdfp4_combine_strided(const float* partial_out, int64_t out_part_stride, const float* partial_lse,
+                          int64_t lse_part_stride, int32_t parts, int32_t rows, int32_t heads_q, void* out,
+                          int64_t out_row_stride, void* stream);
 
 /*
  * One step of the device-side slot table that maps the rows of a batch to BF16 tail slots and
@@ -265,8 +277,8 @@ typedef struct bdfp4_control_args {
   const int32_t* query_start_loc; /* [num_reqs + 1] */
   int32_t* slot_keys;             /* [num_slots] persistent: block id owning the slot, -1 free */
   int32_t* slot_last_seq;         /* [num_slots] persistent */
-  int32_t* slot_last_seen;        /* [num_slots] persistent: step the slot was last owned */
-  int32_t* step;                  /* [1] persistent counter */
+  int64_t* slot_last_seen;        /* [num_slots] persistent: step the slot was last owned */
+  int64_t* step;                  /* [1] persistent counter */
   int32_t* row_to_slot;           /* [num_slots] */
   int32_t* token_to_slot;         /* [>= num_actual_tokens] */
   int32_t* seqused_sink;          /* [num_slots] */

@@ -140,6 +140,33 @@ def main() -> None:
     out["seq_split_sink4_page64"] = np.array(
         [control.split_sequence_length(n, sink_tokens=4, page_size=64) for n in lens], dtype=np.int64)
 
+    # 8. host split policies (pure Python; the modules that hold two of them import GPU-only
+    #    packages, so only the function's own source is executed)
+    import ast
+    import math as _math
+
+    def extract(path: Path, name: str):
+        tree = ast.parse(path.read_text())
+        node = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == name)
+        namespace = {"math": _math, "MAX_DECODE_SPLITS": 32}
+        exec(compile(ast.Module([node], []), str(path), "exec"), namespace)
+        return namespace[name]
+
+    ref_num_splits = extract(reference / "src/nvfp4_vllm/builder.py", "decode_num_splits")
+    ref_heuristic = extract(reference / "src/nvfp4_decode_kernel/_decode.py", "split_k_heuristic")
+    from nvfp4_decode_kernel.interface import split_partial_count as ref_partial_count
+
+    rows_grid = [1, 2, 3, 4, 7, 8, 16, 31, 32, 64, 128]
+    out["policy_decode_num_splits"] = np.array(
+        [(r, h, sms, ref_num_splits(r, h, sms)) for r in rows_grid for h in (1, 2, 4, 8) for sms in (132, 148)],
+        dtype=np.int64)
+    out["policy_split_k_heuristic"] = np.array(
+        [(r, h, pages, 148, ref_heuristic(r, h, pages, sms=148))
+         for r in rows_grid for h in (1, 4, 8) for pages in (1, 2, 7, 64, 511, 1023)], dtype=np.int64)
+    out["policy_split_partial_count"] = np.array(
+        [(r, h, s, int(res), 148, ref_partial_count(r, h, s, residual=res, sms=148))
+         for r in (1, 4, 16, 64) for h in (1, 8) for s in (1, 2, 4, 9) for res in (False, True)], dtype=np.int64)
+
     target = Path(__file__).resolve().parent / "reference_vectors.npz"
     np.savez_compressed(target, **out)
     print(f"wrote {target} ({target.stat().st_size} bytes, {len(out)} arrays)")
