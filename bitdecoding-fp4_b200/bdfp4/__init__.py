@@ -206,7 +206,6 @@ def combine(partial_out, partial_lse, parts: int, rows: int, heads_q: int, out, 
             stream: int) -> None:
     check(
         "bdfp4_combine",
-    "bdfp4_combine_strided",
         library().bdfp4_combine(ptr(partial_out), ptr(partial_lse), parts, rows, heads_q, ptr(out),
                                 out_row_stride, stream),
     )

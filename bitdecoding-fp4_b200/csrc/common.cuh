@@ -84,16 +84,19 @@ struct GroupCodes {
   uint32_t hi;    // elements 8..15
 };
 
-// One candidate over one group of sixteen values: codes and squared error.
-__device__ __forceinline__ void round_trip16(const float* x, float scale, uint32_t& lo, uint32_t& hi,
-                                             float& error) {
+// One candidate over one group of sixteen values: the codes it would store.
+__device__ __forceinline__ void encode16(const float* x, float scale, uint32_t& lo, uint32_t& hi) {
   const float inverse = __fdiv_rn(1.0f, __fadd_rn(scale, 1.0e-30f));
   float scaled[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) scaled[i] = __fmul_rn(x[i], inverse);
   lo = pack_e2m1x8(scaled);
   hi = pack_e2m1x8(scaled + 8);
-  error = 0.0f;
+}
+
+// Squared reconstruction error of stored codes, accumulated by FMA in element order.
+__device__ __forceinline__ float reconstruction_error16(const float* x, float scale, uint32_t lo, uint32_t hi) {
+  float error = 0.0f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const uint32_t word = (i < 4) ? lo : hi;
@@ -104,26 +107,75 @@ __device__ __forceinline__ void round_trip16(const float* x, float scale, uint32
     d = __fmaf_rn(m0.y, scale, -x[e + 1]);
     error = __fmaf_rn(d, d, error);
   }
+  return error;
 }
 
 __device__ __forceinline__ float candidate_scale(float amax, float reciprocal) {
   return e4m3_to_float(cvt_e4m3(__fmul_rn(amax, reciprocal)));
 }
 
-// The group's winning scale and codes under `cand` (first candidate wins ties).
+// Two candidates priced together: every multiply and FMA runs as one packed FP32x2 instruction
+// with candidate A in the low lane and B in the high lane. Each lane rounds on its own, so the
+// errors are bit for bit those of two scalar evaluations.
+__device__ __forceinline__ void price_two16(const float* x, float scale_a, float scale_b, uint32_t& lo_a,
+                                            uint32_t& hi_a, uint32_t& lo_b, uint32_t& hi_b, float& error_a,
+                                            float& error_b) {
+  const float2 scale = make_float2(scale_a, scale_b);
+  const float2 inverse = make_float2(__fdiv_rn(1.0f, __fadd_rn(scale_a, 1.0e-30f)),
+                                     __fdiv_rn(1.0f, __fadd_rn(scale_b, 1.0e-30f)));
+  float2 error = make_float2(0.0f, 0.0f);
+  uint32_t words_a[2] = {0, 0}, words_b[2] = {0, 0};
+#pragma unroll
+  for (int pair = 0; pair < 8; ++pair) {
+    const float x0 = x[2 * pair], x1 = x[2 * pair + 1];
+    const float2 s0 = __fmul2_rn(make_float2(x0, x0), inverse);
+    const float2 s1 = __fmul2_rn(make_float2(x1, x1), inverse);
+    const uint32_t byte_a = cvt_e2m1x2(s0.x, s1.x);
+    const uint32_t byte_b = cvt_e2m1x2(s0.y, s1.y);
+    words_a[pair >> 2] |= byte_a << (8 * (pair & 3));
+    words_b[pair >> 2] |= byte_b << (8 * (pair & 3));
+    const float2 mag_a = e2m1x2_to_float2(byte_a);
+    const float2 mag_b = e2m1x2_to_float2(byte_b);
+    float2 d = __ffma2_rn(make_float2(mag_a.x, mag_b.x), scale, make_float2(-x0, -x0));
+    error = __ffma2_rn(d, d, error);
+    d = __ffma2_rn(make_float2(mag_a.y, mag_b.y), scale, make_float2(-x1, -x1));
+    error = __ffma2_rn(d, d, error);
+  }
+  lo_a = words_a[0];
+  hi_a = words_a[1];
+  lo_b = words_b[0];
+  hi_b = words_b[1];
+  error_a = error.x;
+  error_b = error.y;
+}
+
+// The group's winning scale and codes under `cand` (first candidate wins ties). With a single
+// candidate there is nothing to compare, so no error is computed.
 __device__ __forceinline__ GroupCodes quantize_group16(const float* x, const ScaleCandidates& cand) {
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(x[i], -x[i]));
   GroupCodes best;
-  float best_error;
   best.scale = candidate_scale(amax, cand.reciprocal[0]);
-  round_trip16(x, best.scale, best.lo, best.hi, best_error);
-  for (int c = 1; c < cand.count; ++c) {
+  if (cand.count == 1) {
+    encode16(x, best.scale, best.lo, best.hi);
+    return best;
+  }
+  const float scale_b = candidate_scale(amax, cand.reciprocal[1]);
+  uint32_t lo_b, hi_b;
+  float best_error, error_b;
+  price_two16(x, best.scale, scale_b, best.lo, best.hi, lo_b, hi_b, best_error, error_b);
+  if (error_b < best_error) {
+    best.scale = scale_b;
+    best.lo = lo_b;
+    best.hi = hi_b;
+    best_error = error_b;
+  }
+  for (int c = 2; c < cand.count; ++c) {
     const float scale = candidate_scale(amax, cand.reciprocal[c]);
     uint32_t lo, hi;
-    float error;
-    round_trip16(x, scale, lo, hi, error);
+    encode16(x, scale, lo, hi);
+    const float error = reconstruction_error16(x, scale, lo, hi);
     if (error < best_error) {
       best.scale = scale;
       best.lo = lo;
@@ -204,12 +256,14 @@ __device__ __forceinline__ void hadamard_butterflies(float* v, int group) {
 #pragma unroll
   for (int bit = 0; bit < 3; ++bit) {
     const int mask = 1 << bit;
-    const bool upper = (group & mask) != 0;
+    // partner - own on the upper lane, own + partner on the lower: one FMA with a +-1 factor,
+    // which rounds exactly like the add or subtract it replaces
+    const float sign = (group & mask) != 0 ? -1.0f : 1.0f;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const float own = v[j];
       const float partner = __shfl_xor_sync(0xffffffffu, own, mask);
-      v[j] = upper ? __fsub_rn(partner, own) : __fadd_rn(own, partner);
+      v[j] = __fmaf_rn(own, sign, partner);
     }
   }
 }

@@ -54,6 +54,22 @@ def split_k_heuristic(rows: int, heads_kv: int, max_pages_per_row: int, *, sms: 
     return best
 
 
+def resident_num_splits(rows: int, heads_kv: int, *, sms: int, ctas_per_sm: int = 4, max_splits: int = 32) -> int:
+    """Split count that keeps the whole launch resident at ``ctas_per_sm`` CTAs per SM.
+
+    The decode kernel is bound by HBM only while enough independent CTAs stream at once: each CTA's
+    per-page softmax chain has a fixed latency, and four CTAs per SM (what the two-stage kernel
+    variant fits) hide it. With few (row, KV head) tiles (a small batch, or a KV-head slice of a
+    tensor-parallel rank) this asks for more partitions than ``split_k_heuristic`` or the serving
+    plugin's ``decode_num_splits`` would. Like them it uses the batch width only, never device
+    lengths, so it is safe under CUDA-graph replay. Not part of the reference's API.
+    """
+    tiles = rows * heads_kv
+    if tiles < 1 or sms < 1:
+        return 1
+    return max(1, min(max_splits, (ctas_per_sm * sms) // tiles))
+
+
 @functools.lru_cache(maxsize=None)
 def _multiprocessor_count(device_index: int) -> int:
     return torch.cuda.get_device_properties(device_index).multi_processor_count
