@@ -49,74 +49,74 @@ def measured_peak_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+_SAMPLER_SOURCE = r"""
+import sys, time
+index, period = int(sys.argv[1]), float(sys.argv[2])
+try:
+    import pynvml
+    pynvml.nvmlInit()
+    handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+    print("max", pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM), flush=True)
+    while True:
+        clock = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+        print(f"{time.time():.6f} {clock} {mask}", flush=True)
+        time.sleep(period)
+except Exception as error:
+    print("error", error, flush=True)
+"""
+
+
 class ClockSampler:
-    """Samples SM clocks and clock-event reasons (read-only NVML queries) while a region runs."""
+    """Samples SM clocks and clock-event reasons while a region runs, with read-only NVML queries
+    from a helper process (so the launching thread's hold on the interpreter cannot starve it)."""
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index: int, period_s: float = 0.002):
-        self.index = index
-        self.period = period_s
-        self.clocks: list[int] = []
-        self.reasons: set[str] = set()
-        self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self):
-        try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            physical = self.index
-            if visible:
-                entries = [e.strip() for e in visible.split(",") if e.strip()]
-                if self.index < len(entries) and entries[self.index].isdigit():
-                    physical = int(entries[self.index])
-            handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
-            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
-            while not self._stop.is_set():
-                self.clocks.append(int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
-                mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
-                for bit, name in self.REASONS.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-                self._stop.wait(self.period)
-        except Exception:
-            self._run_smi()
-
-    def _run_smi(self):
-        query = ("clocks.sm,clocks.max.sm,clocks_event_reasons.sw_power_cap,clocks_event_reasons.hw_slowdown,"
-                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.hw_thermal_slowdown")
-        names = ["sw_power_cap", "hw_slowdown", "sw_thermal_slowdown", "hw_thermal_slowdown"]
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={query}", "--format=csv,noheader,nounits"],
-                    capture_output=True, text=True, timeout=5).stdout.strip()
-                fields = [x.strip() for x in out.splitlines()[0].split(",")]
-                self.clocks.append(int(fields[0]))
-                self.max_mhz = int(fields[1])
-                self.reasons.update(n for n, f in zip(names, fields[2:]) if f == "Active")
-            except Exception:
-                pass
-            self._stop.wait(0.05)
+    def __init__(self, index: int, period_s: float = 0.001):
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        physical = index
+        if visible:
+            entries = [e.strip() for e in visible.split(",") if e.strip()]
+            if index < len(entries) and entries[index].isdigit():
+                physical = int(entries[index])
+        self.command = [sys.executable, "-c", _SAMPLER_SOURCE, str(physical), str(period_s)]
+        self.process = None
+        self.begin = self.end = 0.0
+        self.lines: list[str] = []
 
     def __enter__(self):
-        self._thread.start()
+        try:
+            self.process = subprocess.Popen(self.command, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.lines.append(self.process.stdout.readline())  # the "max" line: the helper is up
+        except Exception:
+            self.process = None
+        self.begin = time.time()
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        self._thread.join(timeout=10)
+        self.end = time.time()
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.lines.extend(self.process.communicate(timeout=10)[0].splitlines())
+            except Exception:
+                self.process.kill()
 
     def summary(self) -> dict:
+        clocks, reasons, max_mhz = [], set(), None
+        for line in self.lines:
+            fields = line.split()
+            if len(fields) == 2 and fields[0] == "max":
+                max_mhz = int(fields[1])
+            elif len(fields) == 3 and self.begin <= float(fields[0]) <= self.end:
+                clocks.append(int(fields[1]))
+                reasons.update(name for bit, name in self.REASONS.items() if int(fields[2]) & bit)
         return {
-            "sm_mhz": int(statistics.median(self.clocks)) if self.clocks else None,
-            "sm_max_mhz": self.max_mhz,
-            "reasons": sorted(self.reasons),
-            "samples": len(self.clocks),
+            "sm_mhz": int(statistics.median(clocks)) if clocks else None,
+            "sm_max_mhz": max_mhz,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
         }
 
 

@@ -1,0 +1,137 @@
+"""KV-axis sharding of one long sequence: shard partials from ``bdfp4_decode`` (``out = NULL``),
+``[O | LSE]`` records, ``bdfp4_combine_strided``. On one GPU the shards run one after another and
+their records are laid out as an all-gather would leave them; with two or more GPUs the same path
+runs as NCCL ranks (one process per GPU) through ``bdfp4.distributed.decode_kv_sharded``."""
+
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _shard_args(w, rank, world):
+    """Local cache view of ``rank``: its page range through a local page table; rank 0 owns the
+    sink, the last rank the rolling tail."""
+    from bdfp4.distributed import shard_pages
+
+    pages = int(w.seqused_fp4[0]) // 128
+    first, last = shard_pages(pages, world, rank)
+    table = w.page_table[:, first:last].contiguous()
+    if table.shape[1] == 0:
+        table = torch.zeros(w.rows, 1, dtype=torch.int32, device=w.device)
+    used = torch.full((w.rows,), (last - first) * 128, dtype=torch.int32, device=w.device)
+    residual = w.seqused_residual if rank == world - 1 else torch.zeros_like(w.seqused_residual)
+    sink = w.seqused_sink if rank == 0 else torch.zeros_like(w.seqused_sink)
+    return table, used, residual, sink, (first, last)
+
+
+def _oracle_sharded(w, world):
+    from tests.test_gpu_decode import _cpu_cache
+
+    kc, ks, vc, vs = _cpu_cache(w)
+    q = oracle.quantize_query(w.query.cpu(), w.heads_kv, terms=2)
+    outs, lses = [], []
+    for rank in range(world):
+        table, used, residual, sink, _ = _shard_args(w, rank, world)
+        _, partial, lse = oracle.decode_reference(
+            query_values=q["values"], query_padded=q["padded"], key_codes=kc, key_scales=ks, value_codes=vc,
+            value_scales=vs, page_table=table.cpu(), seqused_fp4=used.cpu(), heads_kv=w.heads_kv,
+            softmax_scale=128 ** -0.5, tail_key=w.tail_key[0].cpu(), tail_value=w.tail_value[0].cpu(),
+            tail_slot_ids=w.slot_ids.cpu(), seqused_residual=residual.cpu(), seqused_sink=sink.cpu())
+        outs.append(partial[0])
+        lses.append(lse[0])
+    return oracle.combine_partials(torch.stack(outs), torch.stack(lses))
+
+
+def _check(got, want):
+    err = (got.float().cpu() - want.float()).abs()
+    assert float(err.max()) <= 1e-2
+    assert float(err.mean() / want.float().abs().mean()) <= 1e-3
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_shards_on_one_gpu(world):
+    import bdfp4
+    from bdfp4.distributed import record_floats
+    from bdfp4.workload import build_workload
+    from nvfp4_decode_kernel import _decode
+    from nvfp4_decode_kernel._quantize import quantize_query
+
+    w = build_workload(rows=1, heads_q=8, heads_kv=2, seq_lens=[2500], sink_tokens=16, seed=5 + world)
+    rows, hq = w.rows, w.heads_q
+    padded = torch.zeros(rows, 128, hq, 128, dtype=torch.bfloat16, device="cuda")
+    quantized = quantize_query(w.query, query_padded_out=padded, heads_kv=w.heads_kv, query_terms=2)
+    record = record_floats(rows, hq)
+    gathered = torch.full((world * record,), float("nan"), device="cuda")
+    stream = bdfp4.current_stream(w.device)
+    for rank in range(world):
+        table, used, residual, sink, _ = _shard_args(w, rank, world)
+        a = bdfp4.DecodeArgs()
+        _decode._fill_args(
+            a, rows=rows, heads_q=hq, heads_kv=w.heads_kv, page_count=w.regions[0].shape[0],
+            query_fp4=quantized[0], query_scales=quantized[1], query_fp4_second=quantized[2],
+            query_scales_second=quantized[3], query_padded_bf16=padded, key_pages_fp4=w.regions[0],
+            key_scales=w.regions[1], value_pages_fp4=w.regions[2], value_scales=w.regions[3],
+            fp4_page_table=table, seqused_fp4=used, residual_key_pages_bf16=w.tail_key[0],
+            residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids, seqused_residual=residual,
+            seqused_sink=sink, softmax_scale=128 ** -0.5)
+        a.num_splits = 1  # out stays NULL: the part leaves as a partial + LSE
+        a.partial_out = gathered.data_ptr() + rank * record * 4
+        a.partial_lse = a.partial_out + rows * hq * 128 * 4
+        bdfp4.decode(a, stream)
+    out = torch.empty(rows, hq, 128, dtype=torch.bfloat16, device="cuda")
+    bdfp4.combine_strided(gathered.data_ptr(), record, gathered.data_ptr() + rows * hq * 128 * 4, record, world,
+                          rows, hq, out, out.stride(0), stream)
+    torch.cuda.synchronize()
+    _check(out, _oracle_sharded(w, world))
+
+
+def _nccl_worker(rank, world, port, result_dir):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "bitdecoding-fp4_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from bdfp4.distributed import decode_kv_sharded
+    from bdfp4.workload import build_workload
+
+    # every rank builds the same sequence (same seed); a real deployment holds only its shard
+    w = build_workload(rows=1, heads_q=8, heads_kv=2, seq_lens=[2500], sink_tokens=16, seed=77,
+                       device=f"cuda:{rank}")
+    table, used, residual, sink, _ = _shard_args(w, rank, world)
+    out = decode_kv_sharded(
+        w.query, *w.regions, table, used, residual_key_pages_bf16=w.tail_key[0],
+        residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids, seqused_residual=residual,
+        seqused_sink=sink, query_terms=2)
+    torch.cuda.synchronize()
+    torch.save(out.cpu(), os.path.join(result_dir, f"out{rank}.pt"))
+    if rank == 0:
+        torch.save(_oracle_sharded(w, world), os.path.join(result_dir, "want.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_shards_as_nccl_ranks(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    port = 29600 + (os.getpid() % 2000)
+    mp.start_processes(_nccl_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True,
+                       start_method="spawn")
+    want = torch.load(tmp_path / "want.pt")
+    outs = [torch.load(tmp_path / f"out{r}.pt") for r in range(world)]
+    for out in outs:
+        _check(out, want)
+        assert torch.equal(out, outs[0])  # every rank merges the same records in the same order
