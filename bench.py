@@ -166,17 +166,24 @@ def cpu_sample_step(context: int, threads: int, repeats: int = 1, seed: int = 0)
     return (time.perf_counter() - start) / repeats
 
 
-def cpu_baseline(heads_kv_local: int, sample_context: int = 8192) -> dict:
+def cpu_baseline(heads_kv_local: int, sample_context: int = 16384, budget_s: float = 12.0) -> dict:
+    """The oracle port timed for about `budget_s` seconds of CPU work on all host threads."""
     threads = os.cpu_count() or 1
-    seconds = cpu_sample_step(sample_context, threads)
+    cpu_sample_step(2048, threads)  # warm the allocator and thread pool
+    repeats, spent = 0, 0.0
+    while spent < budget_s:
+        spent += cpu_sample_step(sample_context, threads, seed=repeats)
+        repeats += 1
+    seconds = spent / repeats
     units = BATCH * heads_kv_local * (CONTEXT / sample_context)
     return {
         "value": seconds * units * 1e6,
         "unit": "us/step",
         "cores": threads,
         "kind": "port",
-        "sample": (f"oracle port, 1 row x 1 KV head (4 query heads) x {sample_context} tokens took {seconds:.3f} s "
-                   f"on {threads} threads; scaled by {units:.0f} (batch x KV heads x context ratio) to the full step"),
+        "sample": (f"oracle port (PyTorch CPU), {repeats} steps of 1 row x 1 KV head (4 query heads) x "
+                   f"{sample_context} tokens, {seconds:.3f} s each on {threads} threads ({spent:.1f} s in all); "
+                   f"scaled by {units:.0f} (batch x KV heads x context ratio) to the full step"),
     }
 
 
@@ -186,10 +193,17 @@ def run_reference(args) -> None:
         return
     heads_local = HEADS_KV // args.gpus
     threads = os.cpu_count() or 1
-    sample_context = 4096
+    sample_context = 16384
     for _ in range(args.warmup):
-        cpu_sample_step(sample_context, threads)
-    times = [cpu_sample_step(sample_context, threads, seed=i) for i in range(args.steps)]
+        cpu_sample_step(2048, threads)
+    # each timed step: the bounded sample repeated for about three seconds of CPU work
+    times = []
+    for i in range(args.steps):
+        spent, repeats = 0.0, 0
+        while spent < 3.0:
+            spent += cpu_sample_step(sample_context, threads, seed=i * 100 + repeats)
+            repeats += 1
+        times.append(spent / repeats)
     seconds = sum(times) / len(times)
     units = BATCH * heads_local * (CONTEXT / sample_context)
     value = seconds * units * 1e6

@@ -7,8 +7,6 @@
 
 namespace bdfp4 {
 
-constexpr int kMaxRegisterParts = 32;
-
 __global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ partial_out,
                                                       const float* __restrict__ partial_lse, int parts, int rows,
                                                       int heads_q, __nv_bfloat16* __restrict__ out,

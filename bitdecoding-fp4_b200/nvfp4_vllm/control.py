@@ -91,6 +91,8 @@ class ControlPlane:
         self.max_num_batched_tokens = max_num_batched_tokens
         self.page_size = page_size
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
 
         def slots(dtype, fill):
             return torch.full((self.num_slots,), fill, dtype=dtype, device=self.device)
