@@ -154,7 +154,7 @@ __device__ __forceinline__ void price_two16(const float* x, float scale_a, float
 __device__ __forceinline__ GroupCodes quantize_group16(const float* x, const ScaleCandidates& cand) {
   float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(x[i], -x[i]));
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
   GroupCodes best;
   best.scale = candidate_scale(amax, cand.reciprocal[0]);
   if (cand.count == 1) {
@@ -241,30 +241,45 @@ __device__ __forceinline__ void round_to_bf16(float* v) {
 // order of src/nvfp4_decode_kernel/quantize_q_kernel.py:105-135 and of
 // src/nvfp4_decode_kernel/quantize_kv_kernel.py:123-162.
 __device__ __forceinline__ void hadamard_butterflies(float* v, int group) {
+  // stride 1 inside each adjacent pair; the wider strides and the cross-lane stages work on
+  // adjacent pairs with packed FP32x2 instructions (each lane rounds like the scalar add or
+  // subtract: a - c == fma(c, -1, a) exactly)
+  float2 p[8];
 #pragma unroll
-  for (int bit = 0; bit < 4; ++bit) {
-    const int stride = 1 << bit;
+  for (int k = 0; k < 8; ++k) {
+    const float lo = v[2 * k], hi = v[2 * k + 1];
+    p[k] = make_float2(__fadd_rn(lo, hi), __fsub_rn(lo, hi));
+  }
+  const float2 minus = make_float2(-1.0f, -1.0f);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if ((j & stride) == 0) {
-        const float lo = v[j], hi = v[j + stride];
-        v[j] = __fadd_rn(lo, hi);
-        v[j + stride] = __fsub_rn(lo, hi);
+  for (int stride = 1; stride < 8; stride <<= 1) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if ((k & stride) == 0) {
+        const float2 lo = p[k], hi = p[k + stride];
+        p[k] = __fadd2_rn(lo, hi);
+        p[k + stride] = __ffma2_rn(hi, minus, lo);
       }
     }
   }
 #pragma unroll
   for (int bit = 0; bit < 3; ++bit) {
     const int mask = 1 << bit;
-    // partner - own on the upper lane, own + partner on the lower: one FMA with a +-1 factor,
-    // which rounds exactly like the add or subtract it replaces
+    // partner - own on the upper lane, own + partner on the lower
     const float sign = (group & mask) != 0 ? -1.0f : 1.0f;
+    const float2 sign2 = make_float2(sign, sign);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float own = v[j];
-      const float partner = __shfl_xor_sync(0xffffffffu, own, mask);
-      v[j] = __fmaf_rn(own, sign, partner);
+    for (int k = 0; k < 8; ++k) {
+      const float2 own = p[k];
+      const float2 partner = make_float2(__shfl_xor_sync(0xffffffffu, own.x, mask),
+                                         __shfl_xor_sync(0xffffffffu, own.y, mask));
+      p[k] = __ffma2_rn(own, sign2, partner);
     }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    v[2 * k] = p[k].x;
+    v[2 * k + 1] = p[k].y;
   }
 }
 

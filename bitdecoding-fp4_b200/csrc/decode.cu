@@ -189,30 +189,36 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
   for (int j = 0; j < GP; ++j) s[j] = valid ? 0.0f : -INFINITY;
   if (valid) {
     const uint4* krow = reinterpret_cast<const uint4*>(key_rows + (int64_t)t * row_elems);
-#pragma unroll 4
-    for (int c = 0; c < 16; ++c) {
-      const uint4 raw = __ldg(krow + c);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-      float k[8];
+    // Eight 16-byte loads are issued before the first is consumed: the block is latency-bound.
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      uint4 raw[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        k[2 * i] = __uint_as_float(w[i] << 16);
-        k[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-      }
+      for (int c = 0; c < 8; ++c) raw[c] = __ldg(krow + half * 8 + c);
 #pragma unroll
-      for (int j = 0; j < GP; ++j) {
-        const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][c * 8]);
-        const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][c * 8 + 4]);
-        float a = s[j];
-        a = fmaf(k[0], q0.x, a);
-        a = fmaf(k[1], q0.y, a);
-        a = fmaf(k[2], q0.z, a);
-        a = fmaf(k[3], q0.w, a);
-        a = fmaf(k[4], q1.x, a);
-        a = fmaf(k[5], q1.y, a);
-        a = fmaf(k[6], q1.z, a);
-        a = fmaf(k[7], q1.w, a);
-        s[j] = a;
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+        float k[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          k[2 * i] = __uint_as_float(w[i] << 16);
+          k[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][(half * 8 + c) * 8]);
+          const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][(half * 8 + c) * 8 + 4]);
+          float a = s[j];
+          a = fmaf(k[0], q0.x, a);
+          a = fmaf(k[1], q0.y, a);
+          a = fmaf(k[2], q0.z, a);
+          a = fmaf(k[3], q0.w, a);
+          a = fmaf(k[4], q1.x, a);
+          a = fmaf(k[5], q1.y, a);
+          a = fmaf(k[6], q1.z, a);
+          a = fmaf(k[7], q1.w, a);
+          s[j] = a;
+        }
       }
     }
   }
@@ -247,11 +253,21 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
     st.o_acc[j] *= acc[j];
   }
   softmax_barrier();
-  const __nv_bfloat16* vcol = value_rows + t;
-  for (int token = 0; token < length; ++token) {
-    const float v = __bfloat162float(vcol[(int64_t)token * row_elems]);
+  // Sixteen value loads in flight per batch (the loop is latency-bound); a batch that runs past
+  // `length` re-reads row `length - 1` and skips the accumulate.
+  const unsigned short* vcol = reinterpret_cast<const unsigned short*>(value_rows) + t;
+  for (int base = 0; base < length; base += 16) {
+    unsigned short raw[16];
 #pragma unroll
-    for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(sm.p_bf16[j][token], v, st.o_acc[j]);
+    for (int i = 0; i < 16; ++i) raw[i] = __ldg(vcol + (int64_t)min(base + i, length - 1) * row_elems);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (base + i < length) {
+        const float v = __uint_as_float((uint32_t)raw[i] << 16);
+#pragma unroll
+        for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(sm.p_bf16[j][base + i], v, st.o_acc[j]);
+      }
+    }
   }
   softmax_barrier();  // p_bf16 is reused by the next BF16 block
 }
