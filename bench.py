@@ -335,6 +335,7 @@ def run_ours(args) -> None:
         seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, softmax_scale=128 ** -0.5)
     kernel_args.num_splits = splits
     kernel_args.bf16_split = int(parts > splits)
+    kernel_args.bf16_page_cost = args.bf16_cost if args.bf16_cost >= 0 else decode_module.BF16_BLOCK_PAGE_COST
     if splits > 1:
         kernel_args.partial_out = scratch["split_partial_scratch"].data_ptr()
         kernel_args.partial_lse = scratch["split_lse_scratch"].data_ptr()
@@ -488,6 +489,8 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--context", type=int, default=CONTEXT, help="override the context length (profiling only)")
     parser.add_argument("--splits", type=int, default=0, help="override the split-KV count")
+    parser.add_argument("--bf16-cost", type=int, default=-1,
+                        help="pages split 0 is charged for the tail and sink (default: the library's)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     if args.warmup < 3:

@@ -103,6 +103,7 @@ class DecodeArgs(Structure):
         ("num_splits", c_int32), ("bf16_split", c_int32),
         ("partial_out", c_void_p), ("partial_lse", c_void_p),
         ("error_word", c_void_p),
+        ("bf16_page_cost", c_int32),
     ]
 
 

@@ -41,7 +41,7 @@ struct ControlParams {
 __global__ void control_kernel(const ControlParams p) {
   __shared__ int s_key[kMaxControl], s_slot_key[kMaxControl], s_slot_seq[kMaxControl];
   __shared__ long long s_slot_seen[kMaxControl];
-  __shared__ int s_matched[kMaxControl], s_needs[kMaxControl], s_need_rank[kMaxControl], s_free[kMaxControl];
+  __shared__ int s_matched[kMaxControl], s_needs[kMaxControl], s_free[kMaxControl];
   __shared__ int s_free_rank[kMaxControl], s_slot[kMaxControl], s_seq[kMaxControl], s_live[kMaxControl];
   __shared__ int s_q_begin[kMaxControl], s_q_end[kMaxControl];
   __shared__ int s_errors;
@@ -100,7 +100,6 @@ __global__ void control_kernel(const ControlParams p) {
   }
   const bool free_slot = is_slot && !claimed;
   s_free[i] = free_slot;
-  s_need_rank[i] = need_rank;
   __syncthreads();
   int free_rank = 0;
   for (int j = 0; j < n; ++j) {

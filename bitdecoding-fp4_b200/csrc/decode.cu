@@ -68,7 +68,7 @@ struct DecodeParams {
   float tau;
   __nv_bfloat16* out;
   int64_t out_row_stride;
-  int num_splits, bf16_split, parts;
+  int num_splits, bf16_split, parts, bf16_page_cost;
   float* partial_out;
   float* partial_lse;
   int32_t* error_word;
@@ -103,6 +103,10 @@ __device__ __forceinline__ float rcp_approx(float x) {
   float y;
   asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* address) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(address));
 }
 
 __device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -187,7 +191,51 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
   const bool valid = t >= mask_below && t < length;
 #pragma unroll
   for (int j = 0; j < GP; ++j) s[j] = valid ? 0.0f : -INFINITY;
-  if (valid) {
+  if (length <= 16) {
+    // A short block (the sink): eight lanes share a token, two 16-byte loads each, so the scores
+    // cost one load round trip; they travel to the token's own thread through p_bf16.
+    const int token = t >> 3, chunk = t & 7;
+    const bool scored = token >= mask_below && token < length;
+    float dot[GP];
+#pragma unroll
+    for (int j = 0; j < GP; ++j) dot[j] = 0.0f;
+    if (scored) {
+      const uint4* kpart = reinterpret_cast<const uint4*>(key_rows + (int64_t)token * row_elems + chunk * 16);
+      const uint4 raw[2] = {__ldg(kpart), __ldg(kpart + 1)};
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][chunk * 16 + c * 8]);
+          const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][chunk * 16 + c * 8 + 4]);
+          float a = dot[j];
+          a = fmaf(__uint_as_float(w[0] << 16), q0.x, a);
+          a = fmaf(__uint_as_float(w[0] & 0xffff0000u), q0.y, a);
+          a = fmaf(__uint_as_float(w[1] << 16), q0.z, a);
+          a = fmaf(__uint_as_float(w[1] & 0xffff0000u), q0.w, a);
+          a = fmaf(__uint_as_float(w[2] << 16), q1.x, a);
+          a = fmaf(__uint_as_float(w[2] & 0xffff0000u), q1.y, a);
+          a = fmaf(__uint_as_float(w[3] << 16), q1.z, a);
+          a = fmaf(__uint_as_float(w[3] & 0xffff0000u), q1.w, a);
+          dot[j] = a;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], 1);
+      dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], 2);
+      dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], 4);
+      if (chunk == 0) sm.p_bf16[j][token] = dot[j];
+    }
+    softmax_barrier();
+    if (valid) {
+#pragma unroll
+      for (int j = 0; j < GP; ++j) s[j] = sm.p_bf16[j][t];
+    }
+    softmax_barrier();  // p_bf16 is written again below
+  } else if (valid) {
     const uint4* krow = reinterpret_cast<const uint4*>(key_rows + (int64_t)t * row_elems);
     // Eight 16-byte loads are issued before the first is consumed: the block is latency-bound.
 #pragma unroll 1
@@ -253,20 +301,49 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
     st.o_acc[j] *= acc[j];
   }
   softmax_barrier();
-  // Sixteen value loads in flight per batch (the loop is latency-bound); a batch that runs past
-  // `length` re-reads row `length - 1` and skips the accumulate.
-  const unsigned short* vcol = reinterpret_cast<const unsigned short*>(value_rows) + t;
-  for (int base = 0; base < length; base += 16) {
-    unsigned short raw[16];
+  // PV. The loop is bound by load latency, so each lane keeps sixteen 8-byte loads in flight:
+  // a warp owns 32 channels, lane = (token phase lane >> 3, channel quad lane & 7) accumulates
+  // tokens phase, phase + 4, ... for its four channels. A masked position carries probability
+  // zero and reads row `length - 1`, so the loop has no bounds branch.
+  if (length > 0) {
+    const int phase = lane >> 3;
+    const uint2* vquad = reinterpret_cast<const uint2*>(value_rows + warp_q * 32 + (lane & 7) * 4);
+    const int64_t row_quads = row_elems / 4;
+    float part[GP][4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) raw[i] = __ldg(vcol + (int64_t)min(base + i, length - 1) * row_elems);
+    for (int j = 0; j < GP; ++j) part[j][0] = part[j][1] = part[j][2] = part[j][3] = 0.0f;
+#pragma unroll 1
+    for (int base = 0; base < length; base += 64) {
+      uint2 raw[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      if (base + i < length) {
-        const float v = __uint_as_float((uint32_t)raw[i] << 16);
+      for (int i = 0; i < 16; ++i) raw[i] = __ldg(vquad + (int64_t)min(base + phase + 4 * i, length - 1) * row_quads);
 #pragma unroll
-        for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(sm.p_bf16[j][base + i], v, st.o_acc[j]);
+      for (int i = 0; i < 16; ++i) {
+        const int token = base + phase + 4 * i;
+        const float v0 = __uint_as_float(raw[i].x << 16), v1 = __uint_as_float(raw[i].x & 0xffff0000u);
+        const float v2 = __uint_as_float(raw[i].y << 16), v3 = __uint_as_float(raw[i].y & 0xffff0000u);
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          const float pj = sm.p_bf16[j][token];
+          part[j][0] = fmaf(pj, v0, part[j][0]);
+          part[j][1] = fmaf(pj, v1, part[j][1]);
+          part[j][2] = fmaf(pj, v2, part[j][2]);
+          part[j][3] = fmaf(pj, v3, part[j][3]);
+        }
       }
+    }
+    // reduce-scatter over the four token phases (lane bits 3 and 4): bit 3 keeps channel pair
+    // 2*bit3, bit 4 keeps channel bit4 of that pair; then lane L fetches channel L of the warp.
+    const bool b3 = (lane >> 3) & 1, b4 = (lane >> 4) & 1;
+    const int holder = (lane >> 2) + 8 * ((lane >> 1) & 1) + 16 * (lane & 1);
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      const float send0 = b3 ? part[j][0] : part[j][2], send1 = b3 ? part[j][1] : part[j][3];
+      const float keep0 = b3 ? part[j][2] : part[j][0], keep1 = b3 ? part[j][3] : part[j][1];
+      const float pair0 = keep0 + __shfl_xor_sync(0xffffffffu, send0, 8);
+      const float pair1 = keep1 + __shfl_xor_sync(0xffffffffu, send1, 8);
+      const float one = (b4 ? pair1 : pair0) + __shfl_xor_sync(0xffffffffu, b4 ? pair0 : pair1, 16);
+      st.o_acc[j] += __shfl_sync(0xffffffffu, one, holder);
     }
   }
   softmax_barrier();  // p_bf16 is reused by the next BF16 block
@@ -287,18 +364,26 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   const int lane = tid & 31;
 
   // ---- which work ---------------------------------------------------------------------------
-  const int part = blockIdx.x % p.parts;
-  const int kv_head = (blockIdx.x / p.parts) % p.heads_kv;
-  const int row = blockIdx.x / (p.parts * p.heads_kv);
+  // Part-major order: the parts that also merge the BF16 blocks (part 0) are launched first.
+  const int tiles = p.rows * p.heads_kv;
+  int part = blockIdx.x / tiles;
+  if (p.bf16_split) part = (part + p.num_splits) % p.parts;
+  const int kv_head = (blockIdx.x % tiles) % p.heads_kv;
+  const int row = (blockIdx.x % tiles) / p.heads_kv;
   const int G = p.ratio;
   const int total_pages = min(p.seqused_fp4[row] / kPage, p.max_pages);
   int first_page = 0, last_page = total_pages;
   bool with_bf16 = p.tail_key != nullptr;
   if (p.num_splits > 1) {
     if (part < p.num_splits) {
-      const int chunk = (total_pages + p.num_splits - 1) / p.num_splits;
-      first_page = min(part * chunk, total_pages);
-      last_page = min(first_page + chunk, total_pages);
+      // Split 0 also merges the tail and the sink when they have no split of their own; it is
+      // then charged `bf16_page_cost` pages for them, so that every split ends at the same time
+      // (cost 0 is the even partition of src/nvfp4_decode_kernel/fp4_decode_kernel.py:4686-4746).
+      const int bias = (with_bf16 && !p.bf16_split) ? p.bf16_page_cost : 0;
+      const int chunk = (total_pages + bias + p.num_splits - 1) / p.num_splits;
+      const int first_chunk = max(chunk - bias, 0);
+      first_page = part == 0 ? 0 : min(first_chunk + (part - 1) * chunk, total_pages);
+      last_page = min(first_page + (part == 0 ? first_chunk : chunk), total_pages);
       with_bf16 = with_bf16 && !p.bf16_split && part == 0;
     } else {
       first_page = last_page = 0;
@@ -317,6 +402,16 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   }
 
   // ---- set-up -------------------------------------------------------------------------------
+  // The BF16 tail is read with plain loads whose latency is the block's whole cost: start its
+  // lines toward L2 now (two 128-byte lines per token for K and for V).
+  if (with_bf16) {
+    const int64_t row_bytes = (int64_t)p.heads_kv * kHeadDim * 2;
+    const int64_t head_offset = ((int64_t)slot * p.tail_slot_stride + kv_head * kHeadDim) * 2;
+    for (int i = tid; i < tail_len * 4; i += 192) {
+      const char* base = reinterpret_cast<const char*>((i & 2) ? p.tail_value : p.tail_key) + head_offset;
+      prefetch_l2(base + (int64_t)(i >> 2) * row_bytes + (i & 1) * 128);
+    }
+  }
   if (tid == 0) {
     for (int s = 0; s < KS; ++s) {
       tc::mbar_init(&sm.k_full[s], 1);
@@ -337,37 +432,98 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     tc::prefetch_tensormap(&k_map);
     tc::prefetch_tensormap(&v_map);
   }
-  // Q tile (B operand of QK), its scale atoms, zeroed P buffers, widened BF16 query
-  // zero the Q tiles, P tiles and both scale-atom buffers (contiguous 1 KB blocks)
+  // Warps 1-5 fetch the query operands into registers first, so that their load latency overlaps
+  // the zero fill, the barrier and warp 0's page-table read: one 16-byte chunk of query codes,
+  // one word of query scales and up to two 16-byte chunks of the BF16 query per thread.
+  const int qt = tid - 32;
+  const bool loads_codes = qt >= 0 && qt < TERMS * G * 4;
+  const bool loads_scales = qt >= 0 && qt < TERMS * G * 2;
+  uint4 code_chunk = make_uint4(0, 0, 0, 0);
+  uint32_t scale_word = 0;
+  uint4 bf16_chunk[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  if (loads_codes) {
+    const int g = (qt >> 2) % G, term = (qt >> 2) / G;
+    code_chunk = __ldg(reinterpret_cast<const uint4*>(p.q_codes[term] +
+                                                      ((int64_t)row * p.heads_q + kv_head * G + g) * 64) + (qt & 3));
+  }
+  if (loads_scales) {
+    const int g = (qt >> 1) % G, term = (qt >> 1) / G;
+    scale_word = __ldg(reinterpret_cast<const uint32_t*>(
+        p.q_scales[term] + ((int64_t)row * p.heads_q + kv_head) * 1024 + (qt & 1) * 512 + g * 16));
+  }
+  if (with_bf16 && qt >= 0) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = qt + 160 * k;  // 16-byte chunk: head i / 16, channels 8 * (i % 16) ...
+      if (i < G * 16)
+        bf16_chunk[k] = __ldg(reinterpret_cast<const uint4*>(
+            p.q_padded + (((int64_t)row * kPage) * p.heads_q + kv_head * G + (i >> 4)) * kHeadDim + (i & 15) * 8));
+    }
+  }
+  // zero the Q tiles, P tiles, both scale-atom buffers (contiguous 1 KB blocks) and the BF16 query
   {
     uint4* blocks[4] = {reinterpret_cast<uint4*>(sm.q_tile), reinterpret_cast<uint4*>(sm.p_tile),
                         reinterpret_cast<uint4*>(sm.q_sf), reinterpret_cast<uint4*>(sm.p_sf)};
     for (int i = tid; i < 4 * 128; i += 192) blocks[i >> 7][i & 127] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < GP * 32; i += 192) reinterpret_cast<uint4*>(sm.q_bf16)[i] = make_uint4(0, 0, 0, 0);
   }
   __syncthreads();
-  for (int i = tid; i < TERMS * G * 4; i += 192) {  // 16-byte chunks of the query codes
-    const int chunk = i & 3;
-    const int g = (i >> 2) % G;
-    const int term = (i >> 2) / G;
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q_codes[term] +
-                                                         ((int64_t)row * p.heads_q + kv_head * G + g) * 64) + chunk);
-    *reinterpret_cast<uint4*>(sm.q_tile[term] + swizzle64(g * 64 + chunk * 16)) = v;
+  // The first ring stages are requested before the rest of the set-up, which then overlaps the
+  // page-table read and the first copies.
+  auto request_key = [&](int i, int page) {  // one thread
+    const int s = i % KS;
+    tc::mbar_expect_tx(&sm.k_full[s], kStageBytes);
+    tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
+    tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 1024, 1024,
+                  &sm.k_full[s]);
+  };
+  auto request_value = [&](int i, int page) {
+    const int s = i % KS;
+    tc::mbar_expect_tx(&sm.v_full[s], kStageBytes);
+    tc::tma_load_3d(sm.v_stage[s], &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page);
+    tc::bulk_load(sm.v_stage[s] + 8192, p.v_scales + (int64_t)page * p.v_scales_pitch + kv_head * 1024, 1024,
+                  &sm.v_full[s]);
+  };
+  auto page_of = [&](int i) {  // physical page of the i-th page this CTA walks (newest first)
+    int page = p.page_table[(int64_t)row * p.page_table_stride + (last_page - 1 - i)];
+    if (page < 0 || page >= p.pages) {
+      if (p.error_word) atomicOr(p.error_word, (int)BDFP4_DEV_BAD_PAGE);
+      page = min(max(page, 0), p.pages - 1);
+    }
+    return page;
+  };
+  const int early = min(KS, num_pages);
+  if (warp == 0) {
+    const int my_page = lane < early ? page_of(lane) : 0;
+    for (int j = 0; j < early; ++j) {
+      const int page = __shfl_sync(0xffffffffu, my_page, j);
+      if (lane == 0) {
+        request_key(j, page);
+        request_value(j, page);
+      }
+    }
   }
-  for (int i = tid; i < TERMS * G * 2; i += 192) {  // 4 scale bytes of (term, head, atom)
-    const int atom = i & 1;
-    const int g = (i >> 1) % G;
-    const int term = (i >> 1) / G;
-    const uint8_t* tile = p.q_scales[term] + ((int64_t)row * p.heads_q + kv_head) * 1024;
-    *reinterpret_cast<uint32_t*>(sm.q_sf[term] + atom * 512 + g * 16) =
-        __ldg(reinterpret_cast<const uint32_t*>(tile + atom * 512 + g * 16));
+  if (loads_codes) {
+    const int g = (qt >> 2) % G, term = (qt >> 2) / G;
+    *reinterpret_cast<uint4*>(sm.q_tile[term] + swizzle64(g * 64 + (qt & 3) * 16)) = code_chunk;
   }
-  if (with_bf16) {
-    for (int i = tid; i < GP * 128; i += 192) {
-      const int g = i >> 7, c = i & 127;
-      float v = 0.0f;
-      if (g < G)
-        v = __bfloat162float(p.q_padded[(((int64_t)row * kPage) * p.heads_q + kv_head * G + g) * kHeadDim + c]);
-      sm.q_bf16[g][c] = v;
+  if (loads_scales) {
+    const int g = (qt >> 1) % G, term = (qt >> 1) / G;
+    *reinterpret_cast<uint32_t*>(sm.q_sf[term] + (qt & 1) * 512 + g * 16) = scale_word;
+  }
+  if (with_bf16 && qt >= 0) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = qt + 160 * k;
+      if (i < G * 16) {
+        const uint32_t w[4] = {bf16_chunk[k].x, bf16_chunk[k].y, bf16_chunk[k].z, bf16_chunk[k].w};
+        float* dst = &sm.q_bf16[i >> 4][(i & 15) * 8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          dst[2 * e] = __uint_as_float(w[e] << 16);
+          dst[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
     }
   }
   if (warp == 1) {
@@ -383,18 +539,10 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
 
   if (warp == 0) {
     // ---- TMA producer -----------------------------------------------------------------------
-    int issued = 0;
-    for (int base = 0; base < num_pages; base += 32) {
+    int issued = early;
+    for (int base = early; base < num_pages; base += 32) {
       const int count = min(32, num_pages - base);
-      int my_page = 0;
-      if (lane < count) {
-        const int logical = last_page - 1 - (base + lane);
-        my_page = p.page_table[(int64_t)row * p.page_table_stride + logical];
-        if (my_page < 0 || my_page >= p.pages) {
-          if (p.error_word) atomicOr(p.error_word, (int)BDFP4_DEV_BAD_PAGE);
-          my_page = min(max(my_page, 0), p.pages - 1);
-        }
-      }
+      const int my_page = lane < count ? page_of(base + lane) : 0;
       bool ok = true;
       for (int j = 0; j < count && ok; ++j) {
         const int page = __shfl_sync(0xffffffffu, my_page, j);
@@ -404,17 +552,11 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
           const uint32_t parity = ((i / KS) & 1) ^ 1;
           ok = tc::mbar_wait(&sm.k_empty[s], parity, abort_flag);
           if (ok) {
-            tc::mbar_expect_tx(&sm.k_full[s], kStageBytes);
-            tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
-            tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 1024, 1024,
-                          &sm.k_full[s]);
+            request_key(i, page);
             ok = tc::mbar_wait(&sm.v_empty[s], parity, abort_flag);
           }
           if (ok) {
-            tc::mbar_expect_tx(&sm.v_full[s], kStageBytes);
-            tc::tma_load_3d(sm.v_stage[s], &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page);
-            tc::bulk_load(sm.v_stage[s] + 8192, p.v_scales + (int64_t)page * p.v_scales_pitch + kv_head * 1024, 1024,
-                          &sm.v_full[s]);
+            request_value(i, page);
             issued = i + 1;
           }
         }
@@ -562,11 +704,21 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
                                  : (((lane & 1) << 2) | (lane & 2) | ((lane >> 2) & 1));
     const int pack_offset = GP == 4 ? swizzle64(pack_row * 64 + (t >> 2) * 2) : swizzle64(pack_row * 64 + (t >> 3) * 4);
 
+    // The sink is read last; its lines are sent toward L2 a few pages before the loop ends.
+    auto prefetch_sink = [&]() {
+      if (with_bf16 && p.seqused_sink && t < sink_len * 4) {
+        const __nv_bfloat16* base = ((t & 2) ? tail_v : tail_k) + (int64_t)(kPage + (t >> 2)) * row_elems;
+        prefetch_l2(reinterpret_cast<const char*>(base) + (t & 1) * 128);
+      }
+    };
+    if (num_pages < 3) prefetch_sink();
+
     bool stop = false;
     for (int i = 0; i < num_pages && !stop; ++i) {
       const int b = i & 1;
       const uint32_t parity = (i >> 1) & 1;
       const int logical_page = last_page - 1 - i;
+      if (i == num_pages - 3) prefetch_sink();
       tc::mbar_wait(&sm.s_full[b], parity, abort_flag);
       tc::fence_after_sync();
       float s[GP];
@@ -911,7 +1063,7 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   }
   if (!(a->softmax_scale > 0.0f) || !isfinite(a->softmax_scale)) return BDFP4_E_ARG;
   if (a->p_scale_mode < 0 || a->p_scale_mode > 2) return BDFP4_E_ARG;
-  if (a->num_splits < 1) return BDFP4_E_ARG;
+  if (a->num_splits < 1 || a->bf16_page_cost < 0) return BDFP4_E_ARG;
   const bool own_bf16 = a->num_splits > 1 && a->bf16_split != 0;
   // One part may leave either as BF16 `out` or, when `out` is null, as an FP32 partial with its
   // LSE (a KV-axis shard of a longer sequence whose partials are merged elsewhere).
@@ -981,6 +1133,7 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   p.out_row_stride = a->out_row_stride;
   p.num_splits = a->num_splits;
   p.bf16_split = own_bf16 ? 1 : 0;
+  p.bf16_page_cost = a->bf16_page_cost;
   p.parts = a->num_splits + (own_bf16 ? 1 : 0);
   p.partial_out = a->partial_out;
   p.partial_lse = a->partial_lse;

@@ -230,6 +230,12 @@ typedef struct bdfp4_decode_args {
   float* partial_out;  /* FP32 [parts][rows][Hq][128], parts = num_splits + bf16_split */
   float* partial_lse;  /* FP32 [parts][rows][Hq] */
   int32_t* error_word; /* optional */
+  /* Split-KV load balance, no reference counterpart: when split 0 also merges the tail and the sink
+   * (num_splits > 1, bf16_split == 0) it is charged this many pages for them: with
+   * c = ceil((n + cost) / num_splits) split 0 owns pages [0, max(c - cost, 0)) and split s >= 1 the
+   * next c pages. 0 keeps the reference's even partition. The merged output is the same up to the
+   * rounding of the partials. */
+  int32_t bf16_page_cost;
 } bdfp4_decode_args;
 
 int bdfp4_decode(const bdfp4_decode_args* args, void* stream);

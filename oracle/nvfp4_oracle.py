@@ -418,11 +418,16 @@ def kernel_order_blocks(*, scores_fp4, values_fp4, fp4_tokens: int, scores_tail=
     return blocks
 
 
-def split_page_range(pages: int, num_splits: int, split: int):
+def split_page_range(pages: int, num_splits: int, split: int, bf16_page_cost: int = 0):
     """Pages ``[first, last)`` of split ``split``: contiguous chunks of ceil(pages/num_splits)
-    (src/nvfp4_decode_kernel/_fa4/block_info.py:47-54)."""
-    chunk = -(-pages // num_splits) if pages else 0
-    first = min(split * chunk, pages)
+    (src/nvfp4_decode_kernel/_fa4/block_info.py:47-54). ``bf16_page_cost`` (not in the reference;
+    the CUDA path's load balance) charges split 0 that many pages for the tail and sink it also
+    merges: chunks of ceil((pages + cost)/num_splits), split 0 shortened by the cost."""
+    chunk = -(-(pages + bf16_page_cost) // num_splits) if (pages + bf16_page_cost) else 0
+    first_chunk = max(chunk - bf16_page_cost, 0)
+    if split == 0:
+        return 0, min(first_chunk, pages)
+    first = min(first_chunk + (split - 1) * chunk, pages)
     return first, min(first + chunk, pages)
 
 
@@ -430,7 +435,7 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
                      page_table, seqused_fp4, heads_kv: int, softmax_scale: float,
                      tail_key=None, tail_value=None, tail_slot_ids=None, seqused_residual=None,
                      seqused_sink=None, p_mode: str = "amax2_or_amax6_c8", tau: float = DEFAULT_P_TAU,
-                     num_splits: int = 1, bf16_split: bool = False,
+                     num_splits: int = 1, bf16_split: bool = False, bf16_page_cost: int = 0,
                      rescale_threshold: float = RESCALE_THRESHOLD):
     """Whole-batch decode attention from the packed cache, as the CUDA path is asked to compute it.
 
@@ -482,7 +487,8 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
                     if with_bf16 and not has_tail:
                         continue
                 else:
-                    page_range, with_bf16 = split_page_range(pages, num_splits, part), part == 0
+                    cost = bf16_page_cost if has_tail else 0
+                    page_range, with_bf16 = split_page_range(pages, num_splits, part, cost), part == 0
                 blocks = kernel_order_blocks(
                     scores_fp4=scores_fp4, values_fp4=v, fp4_tokens=fp4_tokens, scores_tail=scores_tail,
                     values_tail=values_tail, tail_tokens=tail_tokens, scores_sink=scores_sink,

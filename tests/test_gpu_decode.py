@@ -34,7 +34,7 @@ def _cpu_cache(w):
 
 
 def _oracle_decode(w, *, terms, scale_mode, rotate, num_splits=1, bf16_split=False, with_tail=True,
-                   p_mode="amax2_or_amax6_c8"):
+                   p_mode="amax2_or_amax6_c8", bf16_page_cost=0):
     kc, ks, vc, vs = _cpu_cache(w)
     q = oracle.quantize_query(w.query.cpu(), w.heads_kv, scale_mode=scale_mode, terms=terms, rotate=rotate)
     kwargs = {}
@@ -45,7 +45,8 @@ def _oracle_decode(w, *, terms, scale_mode, rotate, num_splits=1, bf16_split=Fal
     return oracle.decode_reference(
         query_values=q["values"], query_padded=q["padded"], key_codes=kc, key_scales=ks, value_codes=vc,
         value_scales=vs, page_table=w.page_table.cpu(), seqused_fp4=w.seqused_fp4.cpu(), heads_kv=w.heads_kv,
-        softmax_scale=128 ** -0.5, p_mode=p_mode, num_splits=num_splits, bf16_split=bf16_split, **kwargs)
+        softmax_scale=128 ** -0.5, p_mode=p_mode, num_splits=num_splits, bf16_split=bf16_split,
+        bf16_page_cost=bf16_page_cost, **kwargs)
 
 
 def _check(got, want, label=""):
@@ -166,6 +167,27 @@ def test_decode_split_kv(num_splits):
     # parts quantise P against their own running maxima: split and unsplit differ by FP4-P noise
     rel = ((out.float() - unsplit.float()).abs().mean() / unsplit.float().abs().mean()).item()
     assert rel < 0.1, rel
+
+
+@pytest.mark.parametrize("cost", [0, 6])
+def test_decode_split_kv_shared_bf16_split(cost, monkeypatch):
+    """A launch too wide to give the tail and sink CTAs of their own: split 0 merges them, under the
+    even partition and when it is charged `cost` pages for them (rows with fewer pages included)."""
+    from bdfp4.workload import build_workload
+    from nvfp4_decode_kernel import _decode as decode_module
+    from nvfp4_decode_kernel import split_partial_count
+
+    monkeypatch.setattr(decode_module, "BF16_BLOCK_PAGE_COST", cost)
+    BF16_BLOCK_PAGE_COST = cost
+    rows, splits = 80, 2
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert split_partial_count(rows, 2, splits, residual=True, sms=sms) == splits
+    lengths = [131 + 97 * (i % 23) + (2200 if i % 7 == 0 else 0) for i in range(rows)]
+    w = build_workload(rows=rows, heads_q=8, heads_kv=2, seq_lens=lengths, sink_tokens=16, seed=31)
+    out = _decode(w, terms=2, num_splits=splits)
+    want, _, _ = _oracle_decode(w, terms=2, scale_mode="amax6", rotate=False, num_splits=splits,
+                                bf16_split=False, bf16_page_cost=BF16_BLOCK_PAGE_COST)
+    _check(out, want, f"shared bf16 split, cost {cost}")
 
 
 def test_decode_caller_buffers_and_error_word():
