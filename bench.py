@@ -39,7 +39,7 @@ import torch  # noqa: E402
 
 HEADS_Q, HEADS_KV, BATCH, CONTEXT = 32, 8, 64, 65536
 SINK_USED, SINK_ROWS = 4, 16
-WORKLOAD_NAME = "qwen3-4b-shape decode layer: 32q/8kv heads, d128, batch 64, ctx 65536, page 128"
+WORKLOAD_NAME = "qwen3-4b-shape decode layer: 32q/8kv heads, d128, batch 64, ctx 65536, page {page}"
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -124,7 +124,7 @@ class ClockSampler:
 # CPU arm: the oracle port of the reference's algorithm on a bounded sample
 # ---------------------------------------------------------------------------------------------
 
-def cpu_sample_step(context: int, threads: int, repeats: int = 1, seed: int = 0):
+def cpu_sample_step(context: int, threads: int, repeats: int = 1, seed: int = 0, page_tokens: int = 64):
     """One decode step of a (1 row, 1 KV head = 4 query heads, `context` tokens) slice on the CPU.
 
     The cache is quantized once up front (not timed); the timed step quantizes the query, puts
@@ -137,13 +137,13 @@ def cpu_sample_step(context: int, threads: int, repeats: int = 1, seed: int = 0)
     torch.set_num_threads(threads)
     gen = torch.Generator().manual_seed(seed)
     sink, fp4, tail = min(context, SINK_USED), ((context - 1) // 128) * 128, context - ((context - 1) // 128) * 128
-    pages = fp4 // 128
+    pages = fp4 // page_tokens
     k = torch.randn(context, 1, 128, generator=gen)
     k[:, 0, torch.randperm(128, generator=gen)[:4]] *= torch.exp(1.5 * torch.randn(4, generator=gen))
     k = k.to(torch.bfloat16)
     v = torch.randn(context, 1, 128, generator=gen).to(torch.bfloat16)
-    kc, ks = oracle.quantize_key_pages(k[:fp4].reshape(pages, 128, 1, 128), "four_six", rotate=True)
-    vc, vs = oracle.quantize_value_pages(v[:fp4].reshape(pages, 128, 1, 128), "amax6")
+    kc, ks = oracle.quantize_key_pages(k[:fp4].reshape(pages, page_tokens, 1, 128), "four_six", rotate=True)
+    vc, vs = oracle.quantize_value_pages(v[:fp4].reshape(pages, page_tokens, 1, 128), "amax6")
     tail_k = torch.zeros(1, 144, 1, 128, dtype=torch.bfloat16)
     tail_v = torch.zeros_like(tail_k)
     basis = oracle.key_cache_basis(k, rotate=True, shift=None)
@@ -166,13 +166,14 @@ def cpu_sample_step(context: int, threads: int, repeats: int = 1, seed: int = 0)
     return (time.perf_counter() - start) / repeats
 
 
-def cpu_baseline(heads_kv_local: int, sample_context: int = 16384, budget_s: float = 12.0) -> dict:
+def cpu_baseline(heads_kv_local: int, sample_context: int = 16384, budget_s: float = 12.0,
+                 page_tokens: int = 64) -> dict:
     """The oracle port timed for about `budget_s` seconds of CPU work on all host threads."""
     threads = os.cpu_count() or 1
-    cpu_sample_step(2048, threads)  # warm the allocator and thread pool
+    cpu_sample_step(2048, threads, page_tokens=page_tokens)  # warm the allocator and thread pool
     repeats, spent = 0, 0.0
     while spent < budget_s:
-        spent += cpu_sample_step(sample_context, threads, seed=repeats)
+        spent += cpu_sample_step(sample_context, threads, seed=repeats, page_tokens=page_tokens)
         repeats += 1
     seconds = spent / repeats
     units = BATCH * heads_kv_local * (CONTEXT / sample_context)
@@ -195,13 +196,13 @@ def run_reference(args) -> None:
     threads = os.cpu_count() or 1
     sample_context = 16384
     for _ in range(args.warmup):
-        cpu_sample_step(2048, threads)
+        cpu_sample_step(2048, threads, page_tokens=args.page_tokens)
     # each timed step: the bounded sample repeated for about three seconds of CPU work
     times = []
     for i in range(args.steps):
         spent, repeats = 0.0, 0
         while spent < 3.0:
-            spent += cpu_sample_step(sample_context, threads, seed=i * 100 + repeats)
+            spent += cpu_sample_step(sample_context, threads, seed=i * 100 + repeats, page_tokens=args.page_tokens)
             repeats += 1
         times.append(spent / repeats)
     seconds = sum(times) / len(times)
@@ -212,7 +213,7 @@ def run_reference(args) -> None:
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": value / 1e3,
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAME, "kv_heads_per_rank": heads_local, "sink_tokens": SINK_USED},
+        "config": {"workload": WORKLOAD_NAME.format(page=args.page_tokens), "kv_heads_per_rank": heads_local, "sink_tokens": SINK_USED},
         "cpu_baseline": {
             "value": value, "unit": "us/step", "cores": threads, "kind": "port",
             "sample": (f"each step: 1 row x 1 KV head x {sample_context} tokens ({seconds:.3f} s on {threads} threads), "
@@ -252,7 +253,7 @@ def run_ours(args) -> None:
 
     w = build_workload(rows=rows, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[context] * rows,
                        sink_tokens=SINK_ROWS, seed=1000 + rank, device=device, key_scale_mode="four_six",
-                       value_scale_mode="amax6", rotate=True)
+                       value_scale_mode="amax6", rotate=True, page_tokens=args.page_tokens)
     w.seqused_sink.clamp_(max=SINK_USED)
     w.sink_tokens = SINK_USED
     algorithmic_bytes = w.algorithmic_bytes()
@@ -409,11 +410,12 @@ def run_ours(args) -> None:
     # ---- quantize-on-write throughput (bulk page quantize, K and V) ---------------------------
     from nvfp4_decode_kernel.quantize_kv_kernel import KVCacheWriter
 
-    q_pages = min(2048, w.page_table.numel())
-    source_k = torch.randn(q_pages * 128, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
-    source_v = torch.randn(q_pages * 128, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+    page_tokens = args.page_tokens
+    q_pages = min(2048 * (128 // page_tokens), w.page_table.numel())
+    source_k = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+    source_v = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
     writer = KVCacheWriter(regions=w.regions, key_scale_mode="four_six", value_scale_mode="amax6", rotate_key=True)
-    work_src = torch.arange(q_pages, dtype=torch.int32, device=device) * 128
+    work_src = torch.arange(q_pages, dtype=torch.int32, device=device) * page_tokens
     work_dst = w.page_table.reshape(-1)[:q_pages].contiguous()
     for _ in range(3):
         writer(source_k, source_v, w.regions, work_src, work_dst)
@@ -424,7 +426,7 @@ def run_ours(args) -> None:
     end.record()
     barrier()
     quant_ms = begin.elapsed_time(end) / 5
-    quant_bytes = q_pages * heads_kv * 2 * (32768 + 9216)
+    quant_bytes = q_pages * heads_kv * 2 * (page_tokens * 256 + page_tokens * 72)
     quantize_gbs = quant_bytes / (quant_ms * 1e-3) / 1e9
 
     if world > 1:
@@ -455,7 +457,8 @@ def run_ours(args) -> None:
             "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate",
             "data": "synthetic",
             "config": {
-                "workload": WORKLOAD_NAME if context == CONTEXT else f"{WORKLOAD_NAME} [context overridden: {context}]",
+                "workload": WORKLOAD_NAME.format(page=page_tokens) + (
+                    "" if context == CONTEXT else f" [context overridden: {context}]"),
                 "partition": f"{heads_kv} of {HEADS_KV} KV heads per rank, no collective",
                 "sink_tokens": SINK_USED, "recent_tokens": 128, "num_splits": splits,
                 "query": "two NVFP4 terms, Hadamard", "key_scale_mode": "four_six", "p_scale_mode": "amax2_or_amax6_c8",
@@ -475,7 +478,7 @@ def run_ours(args) -> None:
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(heads_kv)
+            line["cpu_baseline"] = cpu_baseline(heads_kv, page_tokens=page_tokens)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -491,6 +494,9 @@ def main() -> None:
     parser.add_argument("--splits", type=int, default=0, help="override the split-KV count")
     parser.add_argument("--bf16-cost", type=int, default=-1,
                         help="pages split 0 is charged for the tail and sink (default: the library's)")
+    parser.add_argument("--page-tokens", type=int, default=64, choices=[64, 128],
+                        help="tokens per cache page: 64 as the benchmark configuration names it, or the "
+                             "reference's 128")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     if args.warmup < 3:

@@ -62,6 +62,7 @@ class KvWriteArgs(Structure):
         ("row_to_slot", c_void_p),
         ("rows", c_int32), ("decode_rows", c_int32), ("first_row", c_int32),
         ("error_word", c_void_p),
+        ("page_tokens", c_int32),
     ]
 
 
@@ -104,6 +105,7 @@ class DecodeArgs(Structure):
         ("partial_out", c_void_p), ("partial_lse", c_void_p),
         ("error_word", c_void_p),
         ("bf16_page_cost", c_int32),
+        ("page_tokens", c_int32),
     ]
 
 

@@ -10,7 +10,8 @@ serving engine's block layout: one flat ``[blocks, 2*128*H*72]`` byte tensor who
 
 A sequence of ``n`` tokens holds ``fp4 = ((n-1)//128)*128`` tokens in FP4 pages, the remaining
 ``n - fp4`` (1..128) in its BF16 rolling tail and its first ``min(n, sink)`` tokens again in the
-BF16 sink (src/nvfp4_vllm/control.py:62-89).
+BF16 sink (src/nvfp4_vllm/control.py:62-89). With ``page_tokens=64`` (no reference counterpart)
+the cache is built from 64-token pages, two page-table entries per 128-token step.
 """
 
 from __future__ import annotations
@@ -23,22 +24,29 @@ PAGE = 128
 HEAD_DIM = 128
 
 
-def carve_cache(blocks: torch.Tensor, heads: int):
-    """Four region views of a flat ``[num_blocks, 2*128*H*72]`` u8 cache."""
+def carve_cache(blocks: torch.Tensor, heads: int, page_tokens: int = PAGE):
+    """Four region views of a flat ``[num_blocks, 2*page_tokens*H*72]`` u8 cache: K codes, K scales,
+    V codes, V scales at byte offsets 0, 64, 72 and 136 times ``page_tokens * H``."""
     num_blocks, block_bytes = blocks.shape
-    assert block_bytes == 2 * PAGE * heads * 72
+    assert page_tokens in (128, 64) and block_bytes == 2 * page_tokens * heads * 72
     pitch = blocks.stride(0)
-    base = blocks
-    key_codes = base.as_strided((num_blocks, PAGE, heads, 64), (pitch, heads * 64, 64, 1), base.storage_offset())
-    key_scales = base.as_strided(
-        (num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024), base.storage_offset() + 8192 * heads
-    )
+    base, origin = blocks, blocks.storage_offset()
+    codes, scales = page_tokens * 64 * heads, page_tokens * 8 * heads  # bytes of one region
+    key_codes = base.as_strided((num_blocks, page_tokens, heads, 64), (pitch, heads * 64, 64, 1), origin)
     value_codes = base.as_strided(
-        (num_blocks, heads, HEAD_DIM, 64), (pitch, HEAD_DIM * 64, 64, 1), base.storage_offset() + 9216 * heads
+        (num_blocks, heads, HEAD_DIM, page_tokens // 2), (pitch, HEAD_DIM * page_tokens // 2, page_tokens // 2, 1),
+        origin + codes + scales,
     )
-    value_scales = base.as_strided(
-        (num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024), base.storage_offset() + 17408 * heads
-    )
+    if page_tokens == PAGE:
+        key_scales = base.as_strided((num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024),
+                                     origin + codes)
+        value_scales = base.as_strided((num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024),
+                                       origin + 2 * codes + scales)
+    else:
+        key_scales = base.as_strided((num_blocks, 32, 2, 1, 4, 2, heads), (pitch, 8, 4, 512, 1, 256, 512),
+                                     origin + codes)
+        value_scales = base.as_strided((num_blocks, 32, 4, 1, 4, 1, heads), (pitch, 16, 4, 512, 1, 512, 512),
+                                       origin + 2 * codes + scales)
     return key_codes, key_scales, value_codes, value_scales
 
 
@@ -68,6 +76,7 @@ class Workload:
     query: torch.Tensor = None
     key_shift: torch.Tensor | None = None
     rotate: bool = False
+    page_tokens: int = PAGE
     outlier_scale: torch.Tensor = None  # [H, 128] multiplicative factors applied to K
     kept: dict = field(default_factory=dict)  # raw BF16 K/V of each row when keep_source
 
@@ -77,7 +86,7 @@ class Workload:
         total = 0
         for n in self.seq_lens:
             sink, fp4, tail = split_lengths(n, self.sink_tokens)
-            total += fp4 * self.heads_kv * 144 + (tail + sink) * self.heads_kv * 512 + (fp4 // PAGE) * 4
+            total += fp4 * self.heads_kv * 144 + (tail + sink) * self.heads_kv * 512 + (fp4 // self.page_tokens) * 4
         return total + self.rows * self.heads_q * HEAD_DIM * 2 * 2
 
 
@@ -85,6 +94,7 @@ def build_workload(
     *, rows: int, heads_q: int, heads_kv: int, seq_lens, sink_tokens: int = 16, seed: int = 0,
     device="cuda", key_scale_mode: str = "amax6", value_scale_mode: str = "amax6", rotate: bool = False,
     key_shift: bool = False, shuffle: bool = True, keep_source: bool = False, chunk_pages: int = 256,
+    page_tokens: int = PAGE,
 ) -> Workload:
     """Generate K/V, quantize them into a paged cache with ``KVCacheWriter`` and fill the BF16
     tail and sink, sequence by sequence so that temporaries stay bounded."""
@@ -94,13 +104,15 @@ def build_workload(
     seq_lens = [int(n) for n in seq_lens]
     assert len(seq_lens) == rows
     gen = torch.Generator(device=device).manual_seed(seed)
-    w = Workload(rows, heads_q, heads_kv, seq_lens, sink_tokens, device, rotate=rotate)
-    pages_per_row = [split_lengths(n, sink_tokens)[1] // PAGE for n in seq_lens]
+    w = Workload(rows, heads_q, heads_kv, seq_lens, sink_tokens, device, rotate=rotate, page_tokens=page_tokens)
+    pages_per_row = [split_lengths(n, sink_tokens)[1] // page_tokens for n in seq_lens]
     max_pages = max(1, max(pages_per_row))
     num_blocks = 1 + sum(pages_per_row)
-    w.blocks = torch.zeros(num_blocks, 2 * PAGE * heads_kv * 72, dtype=torch.uint8, device=device)
-    w.regions = carve_cache(w.blocks, heads_kv)
-    order = torch.randperm(num_blocks - 1, generator=gen, device=device) + 1 if shuffle else torch.arange(
+    w.blocks = torch.zeros(num_blocks, 2 * page_tokens * heads_kv * 72, dtype=torch.uint8, device=device)
+    w.regions = carve_cache(w.blocks, heads_kv, page_tokens)
+    # the block order has a generator of its own, so the token values do not depend on the page size
+    order_gen = torch.Generator(device=device).manual_seed(seed + 0x5EED)
+    order = torch.randperm(num_blocks - 1, generator=order_gen, device=device) + 1 if shuffle else torch.arange(
         1, num_blocks, device=device)
     w.page_table = torch.zeros(rows, max_pages, dtype=torch.int32, device=device)
     tail_rows = PAGE + sink_tokens
@@ -126,7 +138,7 @@ def build_workload(
         fp4_list.append(fp4)
         tail_list.append(tail)
         sink_list.append(sink)
-        pages = fp4 // PAGE
+        pages = fp4 // page_tokens
         ids = order[cursor:cursor + pages].to(torch.int32)
         cursor += pages
         w.page_table[row, :pages] = ids
@@ -143,9 +155,9 @@ def build_workload(
             if keep_source:
                 kept_k.append(k)
                 kept_v.append(v)
-            chunk = (stop - start) // PAGE
-            source_tokens = torch.arange(chunk, dtype=torch.int32, device=device) * PAGE
-            destination = ids[start // PAGE:start // PAGE + chunk].contiguous()
+            chunk = (stop - start) // page_tokens
+            source_tokens = torch.arange(chunk, dtype=torch.int32, device=device) * page_tokens
+            destination = ids[start // page_tokens:start // page_tokens + chunk].contiguous()
             if last or (start == 0 and sink):
                 # a one-row "prefill" whose computed prefix is `start`: tail candidates cover the
                 # rolling page past the FP4 prefix and the sink positions this chunk holds

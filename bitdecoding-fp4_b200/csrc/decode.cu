@@ -20,6 +20,7 @@
 #include <cmath>
 #include <cstdio>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "host.h"
@@ -349,7 +350,7 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
   softmax_barrier();  // p_bf16 is reused by the next BF16 block
 }
 
-template <int GP, int TERMS, int STAGES>
+template <int GP, int TERMS, int STAGES, int PT>
 __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                   const DecodeParams p) {
@@ -371,7 +372,10 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   const int kv_head = (blockIdx.x % tiles) % p.heads_kv;
   const int row = (blockIdx.x % tiles) / p.heads_kv;
   const int G = p.ratio;
-  const int total_pages = min(p.seqused_fp4[row] / kPage, p.max_pages);
+  // A "page" below is one 128-token step of the walk: one cache page, or with 64-token pages
+  // (PT = 64) two consecutive entries of the row's page table.
+  constexpr int kEntries = kPage / PT;
+  const int total_pages = min(p.seqused_fp4[row] / kPage, p.max_pages / kEntries);
   int first_page = 0, last_page = total_pages;
   bool with_bf16 = p.tail_key != nullptr;
   if (p.num_splits > 1) {
@@ -470,22 +474,43 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   __syncthreads();
   // The first ring stages are requested before the rest of the set-up, which then overlaps the
   // page-table read and the first copies.
-  auto request_key = [&](int i, int page) {  // one thread
+  auto request_key = [&](int i, int page, int page_b) {  // one thread
     const int s = i % KS;
     tc::mbar_expect_tx(&sm.k_full[s], kStageBytes);
-    tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
-    tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 1024, 1024,
-                  &sm.k_full[s]);
+    if constexpr (PT == 128) {
+      tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
+      tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 1024, 1024,
+                    &sm.k_full[s]);
+    } else {
+      // tokens 0-63 of the step come from the first entry, 64-127 from the second; the two 512-byte
+      // scale blocks land side by side and are interleaved into atoms by the MMA warp
+      tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
+      tc::tma_load_4d(sm.k_stage[s] + 4096, &k_map, &sm.k_full[s], 0, kv_head, 0, page_b);
+      tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 512, 512,
+                    &sm.k_full[s]);
+      tc::bulk_load(sm.k_stage[s] + 8192 + 512, p.k_scales + (int64_t)page_b * p.k_scales_pitch + kv_head * 512, 512,
+                    &sm.k_full[s]);
+    }
   };
-  auto request_value = [&](int i, int page) {
+  auto request_value = [&](int i, int page, int page_b) {
     const int s = i % KS;
     tc::mbar_expect_tx(&sm.v_full[s], kStageBytes);
-    tc::tma_load_3d(sm.v_stage[s], &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page);
-    tc::bulk_load(sm.v_stage[s] + 8192, p.v_scales + (int64_t)page * p.v_scales_pitch + kv_head * 1024, 1024,
-                  &sm.v_full[s]);
+    if constexpr (PT == 128) {
+      tc::tma_load_3d(sm.v_stage[s], &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page);
+      tc::bulk_load(sm.v_stage[s] + 8192, p.v_scales + (int64_t)page * p.v_scales_pitch + kv_head * 1024, 1024,
+                    &sm.v_full[s]);
+    } else {
+      // one [128 ch][32 B] tile and one scale atom per entry: the two K = 64 steps of the PV MMA
+      tc::tma_load_3d(sm.v_stage[s], &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page);
+      tc::tma_load_3d(sm.v_stage[s] + 4096, &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page_b);
+      tc::bulk_load(sm.v_stage[s] + 8192, p.v_scales + (int64_t)page * p.v_scales_pitch + kv_head * 512, 512,
+                    &sm.v_full[s]);
+      tc::bulk_load(sm.v_stage[s] + 8192 + 512, p.v_scales + (int64_t)page_b * p.v_scales_pitch + kv_head * 512, 512,
+                    &sm.v_full[s]);
+    }
   };
-  auto page_of = [&](int i) {  // physical page of the i-th page this CTA walks (newest first)
-    int page = p.page_table[(int64_t)row * p.page_table_stride + (last_page - 1 - i)];
+  auto page_of = [&](int i, int entry) {  // physical page of the i-th step this CTA walks (newest first)
+    int page = p.page_table[(int64_t)row * p.page_table_stride + (last_page - 1 - i) * kEntries + entry];
     if (page < 0 || page >= p.pages) {
       if (p.error_word) atomicOr(p.error_word, (int)BDFP4_DEV_BAD_PAGE);
       page = min(max(page, 0), p.pages - 1);
@@ -494,12 +519,14 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   };
   const int early = min(KS, num_pages);
   if (warp == 0) {
-    const int my_page = lane < early ? page_of(lane) : 0;
+    const int my_page = lane < early ? page_of(lane, 0) : 0;
+    const int my_page_b = (PT == 64 && lane < early) ? page_of(lane, 1) : 0;
     for (int j = 0; j < early; ++j) {
       const int page = __shfl_sync(0xffffffffu, my_page, j);
+      const int page_b = __shfl_sync(0xffffffffu, my_page_b, j);
       if (lane == 0) {
-        request_key(j, page);
-        request_value(j, page);
+        request_key(j, page, page_b);
+        request_value(j, page, page_b);
       }
     }
   }
@@ -542,21 +569,23 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     int issued = early;
     for (int base = early; base < num_pages; base += 32) {
       const int count = min(32, num_pages - base);
-      const int my_page = lane < count ? page_of(base + lane) : 0;
+      const int my_page = lane < count ? page_of(base + lane, 0) : 0;
+      const int my_page_b = (PT == 64 && lane < count) ? page_of(base + lane, 1) : 0;
       bool ok = true;
       for (int j = 0; j < count && ok; ++j) {
         const int page = __shfl_sync(0xffffffffu, my_page, j);
+        const int page_b = __shfl_sync(0xffffffffu, my_page_b, j);
         if (lane == 0) {
           const int i = base + j;
           const int s = i % KS;
           const uint32_t parity = ((i / KS) & 1) ^ 1;
           ok = tc::mbar_wait(&sm.k_empty[s], parity, abort_flag);
           if (ok) {
-            request_key(i, page);
+            request_key(i, page, page_b);
             ok = tc::mbar_wait(&sm.v_empty[s], parity, abort_flag);
           }
           if (ok) {
-            request_value(i, page);
+            request_value(i, page, page_b);
             issued = i + 1;
           }
         }
@@ -579,16 +608,21 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     }
   } else if (warp == 1) {
     // ---- MMA issuer ---------------------------------------------------------------------------
-    if (lane == 0 && num_pages > 0) {
+    // One thread issues every tcgen05 operation. With 64-token pages the whole warp stays in the
+    // loop: its 32 lanes interleave the two pages' K scale blocks into MMA atoms.
+    const bool issuer = lane == 0;
+    if (num_pages > 0 && (issuer || PT == 64)) {
       constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, kNQ);
       constexpr uint32_t idesc_pv = tc::nvf4_idesc(128, kNP);
       const uint32_t q_addr = tc::smem_u32(sm.q_tile);
+      if (issuer) {
 #pragma unroll
-      for (int term = 0; term < TERMS; ++term) {
-        tc::cp_sf_atom(tmem + kColSFQ + 8 * term, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[term])));
-        tc::cp_sf_atom(tmem + kColSFQ + 8 * term + 4, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[term]) + 512));
+        for (int term = 0; term < TERMS; ++term) {
+          tc::cp_sf_atom(tmem + kColSFQ + 8 * term, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[term])));
+          tc::cp_sf_atom(tmem + kColSFQ + 8 * term + 4, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[term]) + 512));
+        }
       }
-      auto issue_pv = [&](int m) -> bool {
+      auto issue_pv = [&](int m) -> bool {  // issuer only
         const int s = m % KS;
         const int b = m & 1;
         const uint32_t ring_parity = (m / KS) & 1;
@@ -605,9 +639,13 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         if (!tc::mbar_wait(&sm.o_empty[b], pair_parity ^ 1, abort_flag)) return false;
         tc::fence_after_sync();
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-          tc::mma_nvf4(tmem + kColO + 16 * b, tc::fp4_tile_desc(v_addr, k), tc::fp4_tile_desc(p_addr, k), idesc_pv,
+        for (int k = 0; k < 2; ++k) {
+          // 128-token page: one tile of 64-byte rows, K step k at +32 bytes. 64-token pages: one
+          // tile of 32-byte rows per page.
+          const uint64_t v_desc = PT == 128 ? tc::fp4_tile_desc(v_addr, k) : tc::fp4_half_tile_desc(v_addr + k * 4096);
+          tc::mma_nvf4(tmem + kColO + 16 * b, v_desc, tc::fp4_tile_desc(p_addr, k), idesc_pv,
                        tmem + kColSFV + 8 * b + 4 * k, tmem + kColSFP + 8 * b + 4 * k, k != 0);
+        }
         tc::commit(&sm.o_full[b]);
         tc::commit(&sm.v_empty[s]);
         tc::commit(&sm.p_empty[b]);
@@ -618,28 +656,50 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         const int s = i % KS;
         const int b = i & 1;
         ok = tc::mbar_wait(&sm.k_full[s], (i / KS) & 1, abort_flag);
-        if (!ok) break;
-        tc::fence_after_sync();
-        const uint32_t k_addr = tc::smem_u32(sm.k_stage[s]);
-        tc::cp_sf_atom(tmem + kColSFK + 8 * b, tc::sf_atom_desc(k_addr + 8192));
-        tc::cp_sf_atom(tmem + kColSFK + 8 * b + 4, tc::sf_atom_desc(k_addr + 8192 + 512));
-        ok = tc::mbar_wait(&sm.s_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        tc::fence_after_sync();
-        // both query terms accumulate into the same S^T columns: K.Q0 + K.Q1 in FP32
-#pragma unroll
-        for (int term = 0; term < TERMS; ++term) {
-#pragma unroll
-          for (int k = 0; k < 2; ++k)
-            tc::mma_nvf4(tmem + kColS + kNQ * b, tc::fp4_tile_desc(k_addr, k),
-                         tc::fp4_tile_desc(q_addr + term * (kNQ * 64), k), idesc_qk,
-                         tmem + kColSFK + 8 * b + 4 * k, tmem + kColSFQ + 8 * term + 4 * k, (term | k) != 0);
+        if constexpr (PT == 64) {
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          // K scales arrived as [page][atom][32 rows][8 B]; an atom row is 16 bytes, tokens 0-63
+          // (first page) in its low half and 64-127 in its high half. Every lane reads its four
+          // 8-byte pieces before any lane writes, so the exchange is done in place.
+          uint8_t* sf = sm.k_stage[s] + 8192;
+          const uint2 a0 = *reinterpret_cast<const uint2*>(sf + lane * 8);
+          const uint2 a1 = *reinterpret_cast<const uint2*>(sf + 256 + lane * 8);
+          const uint2 b0 = *reinterpret_cast<const uint2*>(sf + 512 + lane * 8);
+          const uint2 b1 = *reinterpret_cast<const uint2*>(sf + 768 + lane * 8);
+          __syncwarp();
+          *reinterpret_cast<uint4*>(sf + lane * 16) = make_uint4(a0.x, a0.y, b0.x, b0.y);
+          *reinterpret_cast<uint4*>(sf + 512 + lane * 16) = make_uint4(a1.x, a1.y, b1.x, b1.y);
+          tc::fence_proxy_async_smem();
+          __syncwarp();
+        } else {
+          if (!ok) break;
         }
-        tc::commit(&sm.s_full[b]);
-        tc::commit(&sm.k_empty[s]);
-        if (i > 0) ok = issue_pv(i - 1);
+        if (issuer) {
+          tc::fence_after_sync();
+          const uint32_t k_addr = tc::smem_u32(sm.k_stage[s]);
+          tc::cp_sf_atom(tmem + kColSFK + 8 * b, tc::sf_atom_desc(k_addr + 8192));
+          tc::cp_sf_atom(tmem + kColSFK + 8 * b + 4, tc::sf_atom_desc(k_addr + 8192 + 512));
+          ok = tc::mbar_wait(&sm.s_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
+          if (ok) {
+            tc::fence_after_sync();
+            // both query terms accumulate into the same S^T columns: K.Q0 + K.Q1 in FP32
+#pragma unroll
+            for (int term = 0; term < TERMS; ++term) {
+#pragma unroll
+              for (int k = 0; k < 2; ++k)
+                tc::mma_nvf4(tmem + kColS + kNQ * b, tc::fp4_tile_desc(k_addr, k),
+                             tc::fp4_tile_desc(q_addr + term * (kNQ * 64), k), idesc_qk,
+                             tmem + kColSFK + 8 * b + 4 * k, tmem + kColSFQ + 8 * term + 4 * k, (term | k) != 0);
+            }
+            tc::commit(&sm.s_full[b]);
+            tc::commit(&sm.k_empty[s]);
+            if (i > 0) ok = issue_pv(i - 1);
+          }
+        }
+        if constexpr (PT == 64) ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       }
-      if (ok) issue_pv(num_pages - 1);
+      if (issuer && ok) issue_pv(num_pages - 1);
     }
   } else {
     // ---- softmax / accumulate -----------------------------------------------------------------
@@ -993,26 +1053,26 @@ static EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-template <int GP, int TERMS, int STAGES>
+template <int GP, int TERMS, int STAGES, int PT>
 static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
                                         cudaStream_t stream) {
   const int smem = (int)sizeof(DecodeSmem<GP, STAGES>) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS, STAGES, PT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int grid = p.rows * p.heads_kv * p.parts;
-  decode_kernel<GP, TERMS, STAGES><<<grid, 192, smem, stream>>>(k_map, v_map, p);
+  decode_kernel<GP, TERMS, STAGES, PT><<<grid, 192, smem, stream>>>(k_map, v_map, p);
   return cudaGetLastError();
 }
 
 // Ring depth follows the grid: a launch with more than two CTAs per SM is given two K and two V
 // stages per CTA so that four CTAs (and their four independent softmax chains) share an SM and
 // the whole grid is resident at once; a smaller launch gets deeper rings instead.
-template <int GP, int TERMS>
+template <int GP, int TERMS, int PT>
 static cudaError_t launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
                                  cudaStream_t stream) {
   static int sms = 0;
@@ -1023,10 +1083,10 @@ static cudaError_t launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_
   }
   const int grid = p.rows * p.heads_kv * p.parts;
   if constexpr (GP <= 8) {
-    if (grid > 2 * sms) return launch_decode_staged<GP, TERMS, 2>(k_map, v_map, p, stream);
-    return launch_decode_staged<GP, TERMS, 5>(k_map, v_map, p, stream);
+    if (grid > 2 * sms) return launch_decode_staged<GP, TERMS, 2, PT>(k_map, v_map, p, stream);
+    return launch_decode_staged<GP, TERMS, 5, PT>(k_map, v_map, p, stream);
   } else {
-    return launch_decode_staged<GP, TERMS, 4>(k_map, v_map, p, stream);
+    return launch_decode_staged<GP, TERMS, 4, PT>(k_map, v_map, p, stream);
   }
 }
 
@@ -1052,8 +1112,12 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   if (a->key_codes_pitch % 16 || a->key_scales_pitch % 16 || a->value_codes_pitch % 16 ||
       a->value_scales_pitch % 16)
     return BDFP4_E_ARG;
-  if (a->key_codes_pitch < (int64_t)kPage * a->heads_kv * 64 || a->value_codes_pitch < (int64_t)a->heads_kv * 8192 ||
-      a->key_scales_pitch < (int64_t)a->heads_kv * 1024 || a->value_scales_pitch < (int64_t)a->heads_kv * 1024)
+  const int page_tokens = a->page_tokens == 0 ? kPage : a->page_tokens;
+  if (page_tokens != 128 && page_tokens != 64) return BDFP4_E_UNSUPPORTED;
+  // bytes per (page, head): codes 64 per token (K) or page_tokens / 2 per channel (V), scales 8 per token
+  const int64_t head_codes = (int64_t)page_tokens * 64, head_scales = (int64_t)page_tokens * 8;
+  if (a->key_codes_pitch < a->heads_kv * head_codes || a->value_codes_pitch < a->heads_kv * head_codes ||
+      a->key_scales_pitch < a->heads_kv * head_scales || a->value_scales_pitch < a->heads_kv * head_scales)
     return BDFP4_E_ARG;
   const bool tail = a->tail_key != nullptr;
   if (tail) {
@@ -1078,10 +1142,10 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
 
   CUtensorMap k_map, v_map;
   {
-    // K codes: [pages][128 tok][H][64 B]; one box = one head of one page, 128 rows of 64 bytes
-    const cuuint64_t dims[4] = {64, (cuuint64_t)a->heads_kv, kPage, (cuuint64_t)a->pages};
+    // K codes: [pages][page_tokens][H][64 B]; one box = one head of one page, rows of 64 bytes
+    const cuuint64_t dims[4] = {64, (cuuint64_t)a->heads_kv, (cuuint64_t)page_tokens, (cuuint64_t)a->pages};
     const cuuint64_t strides[3] = {64, (cuuint64_t)a->heads_kv * 64, (cuuint64_t)a->key_codes_pitch};
-    const cuuint32_t box[4] = {64, 1, kPage, 1};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)page_tokens, 1};
     const cuuint32_t elem[4] = {1, 1, 1, 1};
     if (encode(&k_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(a->key_codes), dims, strides, box, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1089,13 +1153,15 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
       return BDFP4_E_ARG;
   }
   {
-    // V codes: [pages][H * 128 ch][64 B]
-    const cuuint64_t dims[3] = {64, (cuuint64_t)a->heads_kv * kHeadDim, (cuuint64_t)a->pages};
-    const cuuint64_t strides[2] = {64, (cuuint64_t)a->value_codes_pitch};
-    const cuuint32_t box[3] = {64, kHeadDim, 1};
+    // V codes: [pages][H * 128 ch][page_tokens / 2 B]; the row is the swizzle span
+    const cuuint64_t row_bytes = (cuuint64_t)page_tokens / 2;
+    const cuuint64_t dims[3] = {row_bytes, (cuuint64_t)a->heads_kv * kHeadDim, (cuuint64_t)a->pages};
+    const cuuint64_t strides[2] = {row_bytes, (cuuint64_t)a->value_codes_pitch};
+    const cuuint32_t box[3] = {(cuuint32_t)row_bytes, kHeadDim, 1};
     const cuuint32_t elem[3] = {1, 1, 1};
     if (encode(&v_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(a->value_codes), dims, strides, box, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, page_tokens == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return BDFP4_E_ARG;
   }
@@ -1141,12 +1207,26 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
 
   const bool two = a->query_codes_second != nullptr;
   cudaError_t e;
-  if (ratio <= 4)
-    e = two ? launch_decode<4, 2>(k_map, v_map, p, stream) : launch_decode<4, 1>(k_map, v_map, p, stream);
-  else if (ratio <= 8)
-    e = two ? launch_decode<8, 2>(k_map, v_map, p, stream) : launch_decode<8, 1>(k_map, v_map, p, stream);
-  else
-    e = two ? launch_decode<16, 2>(k_map, v_map, p, stream) : launch_decode<16, 1>(k_map, v_map, p, stream);
+  auto launch = [&](auto gp, auto pt) {
+    constexpr int GP = decltype(gp)::value, PT = decltype(pt)::value;
+    return two ? launch_decode<GP, 2, PT>(k_map, v_map, p, stream) : launch_decode<GP, 1, PT>(k_map, v_map, p, stream);
+  };
+  using std::integral_constant;
+  if (page_tokens == 128) {
+    if (ratio <= 4)
+      e = launch(integral_constant<int, 4>{}, integral_constant<int, 128>{});
+    else if (ratio <= 8)
+      e = launch(integral_constant<int, 8>{}, integral_constant<int, 128>{});
+    else
+      e = launch(integral_constant<int, 16>{}, integral_constant<int, 128>{});
+  } else {
+    if (ratio <= 4)
+      e = launch(integral_constant<int, 4>{}, integral_constant<int, 64>{});
+    else if (ratio <= 8)
+      e = launch(integral_constant<int, 8>{}, integral_constant<int, 64>{});
+    else
+      e = launch(integral_constant<int, 16>{}, integral_constant<int, 64>{});
+  }
   return bdfp4::cuda_status(e);
 }
 

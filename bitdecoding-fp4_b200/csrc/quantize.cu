@@ -72,10 +72,18 @@ __device__ __forceinline__ void cache_basis16(float* v, int group, const void* s
   if (ROTATE || SHIFT_TYPE != BDFP4_SHIFT_NONE) round_to_bf16(v);
 }
 
-// One CTA = one head of one K page. 1024 scale groups, four per thread.
-template <int SHIFT_TYPE, bool ROTATE>
+// Byte of (token, channel group) inside a 64-token page's 512-byte K scale block: two half
+// atoms [group / 4][token % 32][token / 32][group % 4]. The decode kernel interleaves the halves
+// of two such pages into the 128-row atoms its MMA reads.
+__host__ __device__ __forceinline__ int key_scale_offset64(int token, int group) {
+  return (group >> 2) * 256 + (token & 31) * 8 + (token >> 5) * 4 + (group & 3);
+}
+
+// One CTA = one head of one K page of PT tokens: 8 * PT scale groups, PT / 32 per thread.
+template <int SHIFT_TYPE, bool ROTATE, int PT>
 __global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
-  __shared__ __align__(16) uint8_t scale_tile[1024];
+  constexpr int kScaleBytes = PT * 8;
+  __shared__ __align__(16) uint8_t scale_tile[kScaleBytes];
   const int item = blockIdx.x;
   const int grid_layer = blockIdx.z;
   const int layer = p.bases ? grid_layer : p.layer;
@@ -87,10 +95,10 @@ __global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
   uint8_t* codes = p.bases ? reinterpret_cast<uint8_t*>(p.bases[0 * p.layers + layer]) : p.region[0];
   uint8_t* scales = p.bases ? reinterpret_cast<uint8_t*>(p.bases[1 * p.layers + layer]) : p.region[1];
   codes += (int64_t)page * p.pitch[0];
-  scales += (int64_t)page * p.pitch[1] + head * 1024;
+  scales += (int64_t)page * p.pitch[1] + head * kScaleBytes;
 
 #pragma unroll 1
-  for (int it = 0; it < 4; ++it) {
+  for (int it = 0; it < PT / 32; ++it) {
     const int index = it * 256 + threadIdx.x;
     const int token = index >> 3;
     const int group = index & 7;
@@ -100,21 +108,32 @@ __global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
                                       ((int64_t)layer * p.heads + head) * kHeadDim + group * kGroup);
     const GroupCodes q = quantize_group16(v, p.key_cand);
     *reinterpret_cast<uint2*>(codes + ((int64_t)token * p.heads + head) * 64 + group * 8) = make_uint2(q.lo, q.hi);
-    scale_tile[scale_tile_offset(token, group)] = (uint8_t)cvt_e4m3(q.scale);
+    scale_tile[PT == 128 ? scale_tile_offset(token, group) : key_scale_offset64(token, group)] =
+        (uint8_t)cvt_e4m3(q.scale);
   }
   __syncthreads();
-  reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
+  if (threadIdx.x < kScaleBytes / 4)
+    reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
 }
 
-// One CTA = one head of one V page. Scale groups run along the page's 128 tokens, so the
-// [token][channel] tile is staged in shared memory and read back by columns.
-constexpr int kVCodePitch = 72;  // bytes per channel row in the staging buffer (bank spread)
+// One CTA = one head of one V page of PT tokens. Scale groups run along the page's tokens, so the
+// [token][channel] tile is staged in shared memory and read back by columns. A channel's codes
+// are PT / 2 bytes; its PT / 16 scales sit at the 128-token layout's offsets (one atom per 64 tokens).
+template <int PT>
+struct ValueTile {
+  static constexpr int kCodeBytes = PT / 2;         // per channel
+  static constexpr int kCodePitch = kCodeBytes + 8;  // staging pitch (bank spread)
+  static constexpr int kScaleBytes = PT * 8;
+  static constexpr int kSmem = PT * kHeadDim * 2 + kHeadDim * kCodePitch + kScaleBytes;
+};
 
+template <int PT>
 __global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) {
+  using T = ValueTile<PT>;
   extern __shared__ __align__(16) uint8_t smem[];
-  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [128][128]
-  uint8_t* code_tile = smem + kPage * kHeadDim * 2;              // [128][kVCodePitch]
-  uint8_t* scale_tile = code_tile + kHeadDim * kVCodePitch;      // [1024]
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [PT][128]
+  uint8_t* code_tile = smem + PT * kHeadDim * 2;                 // [128][kCodePitch]
+  uint8_t* scale_tile = code_tile + kHeadDim * T::kCodePitch;    // [kScaleBytes]
   const int item = blockIdx.x;
   const int grid_layer = blockIdx.z;
   const int layer = p.bases ? grid_layer : p.layer;
@@ -125,11 +144,11 @@ __global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) 
   const int64_t source_token = (int64_t)p.source_tokens[work] + (int64_t)grid_layer * p.source_layer_stride;
   uint8_t* codes = p.bases ? reinterpret_cast<uint8_t*>(p.bases[2 * p.layers + layer]) : p.region[2];
   uint8_t* scales = p.bases ? reinterpret_cast<uint8_t*>(p.bases[3 * p.layers + layer]) : p.region[3];
-  codes += (int64_t)page * p.pitch[2] + (int64_t)head * (kHeadDim * 64);
-  scales += (int64_t)page * p.pitch[3] + head * 1024;
+  codes += (int64_t)page * p.pitch[2] + (int64_t)head * (kHeadDim * T::kCodeBytes);
+  scales += (int64_t)page * p.pitch[3] + head * T::kScaleBytes;
 
 #pragma unroll
-  for (int it = 0; it < 8; ++it) {
+  for (int it = 0; it < PT / 16; ++it) {
     const int index = it * 256 + threadIdx.x;  // 16-byte chunk of the tile
     const int token = index >> 4;
     const int chunk = index & 15;
@@ -139,7 +158,7 @@ __global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) 
   }
   __syncthreads();
 #pragma unroll 1
-  for (int it = 0; it < 4; ++it) {
+  for (int it = 0; it < PT / 32; ++it) {
     const int index = it * 256 + threadIdx.x;
     const int channel = index & 127;
     const int group = index >> 7;  // token group
@@ -147,18 +166,20 @@ __global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) 
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(tile[(group * 16 + i) * kHeadDim + channel]);
     const GroupCodes q = quantize_group16(v, p.value_cand);
-    *reinterpret_cast<uint2*>(code_tile + channel * kVCodePitch + group * 8) = make_uint2(q.lo, q.hi);
+    *reinterpret_cast<uint2*>(code_tile + channel * T::kCodePitch + group * 8) = make_uint2(q.lo, q.hi);
     scale_tile[scale_tile_offset(channel, group)] = (uint8_t)cvt_e4m3(q.scale);
   }
   __syncthreads();
 #pragma unroll
-  for (int it = 0; it < 4; ++it) {
-    const int index = it * 256 + threadIdx.x;  // 8-byte chunk of the 8 KB code tile
-    const int channel = index >> 3;
-    const int chunk = index & 7;
-    reinterpret_cast<uint2*>(codes)[index] = *reinterpret_cast<const uint2*>(code_tile + channel * kVCodePitch + chunk * 8);
+  for (int it = 0; it < PT / 32; ++it) {
+    const int index = it * 256 + threadIdx.x;  // 8-byte chunk of the code tile
+    const int channel = index / (T::kCodeBytes / 8);
+    const int chunk = index % (T::kCodeBytes / 8);
+    reinterpret_cast<uint2*>(codes)[index] =
+        *reinterpret_cast<const uint2*>(code_tile + channel * T::kCodePitch + chunk * 8);
   }
-  reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
+  if (threadIdx.x < T::kScaleBytes / 4)
+    reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
 }
 
 // One 16-element group of one token's new K or V into the BF16 tail: at `offset` of the rolling
@@ -264,24 +285,33 @@ __global__ void __launch_bounds__(128) tail_token_kernel(const KvWriteParams p) 
   }
 }
 
+template <int PT>
+static cudaError_t launch_value_pages(const KvWriteParams& p, int page_items, cudaStream_t stream) {
+  const int smem = ValueTile<PT>::kSmem;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(value_page_kernel<PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  value_page_kernel<PT><<<dim3(page_items, 1, p.layers), 256, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
 template <int SHIFT_TYPE, bool ROTATE>
-static cudaError_t launch_kv_write(const KvWriteParams& p, cudaStream_t stream) {
+static cudaError_t launch_kv_write(const KvWriteParams& p, int page_tokens, cudaStream_t stream) {
   const int page_items = p.heads * p.work_items;
   if (p.key && (p.region[0] || p.bases) && page_items > 0) {
-    key_page_kernel<SHIFT_TYPE, ROTATE><<<dim3(page_items, 1, p.layers), 256, 0, stream>>>(p);
+    if (page_tokens == 64)
+      key_page_kernel<SHIFT_TYPE, ROTATE, 64><<<dim3(page_items, 1, p.layers), 256, 0, stream>>>(p);
+    else
+      key_page_kernel<SHIFT_TYPE, ROTATE, 128><<<dim3(page_items, 1, p.layers), 256, 0, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   if (p.value && (p.region[2] || p.bases) && page_items > 0) {
-    const int smem = kPage * kHeadDim * 2 + kHeadDim * kVCodePitch + 1024;
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(value_page_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return e;
-      configured = true;
-    }
-    value_page_kernel<<<dim3(page_items, 1, p.layers), 256, smem, stream>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = page_tokens == 64 ? launch_value_pages<64>(p, page_items, stream)
+                                      : launch_value_pages<128>(p, page_items, stream);
     if (e != cudaSuccess) return e;
   }
   if (p.tail_key) {
@@ -414,6 +444,8 @@ extern "C" int bdfp4_kv_write(const bdfp4_kv_write_args* a, void* stream_handle)
   if (!a) return BDFP4_E_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
   if (a->heads < 1 || a->work_items < 0) return BDFP4_E_ARG;
+  const int page_tokens = a->page_tokens == 0 ? kPage : a->page_tokens;
+  if (page_tokens != 128 && page_tokens != 64) return BDFP4_E_UNSUPPORTED;
   if (a->key_scale_mode < 0 || a->key_scale_mode > 2 || a->value_scale_mode < 0 || a->value_scale_mode > 2)
     return BDFP4_E_ARG;
   const bool per_layer = a->bases != nullptr;
@@ -498,15 +530,16 @@ extern "C" int bdfp4_kv_write(const bdfp4_kv_write_args* a, void* stream_handle)
   const bool rot = a->rotate_key != 0;
   switch (a->key_shift_type) {
     case BDFP4_SHIFT_F32:
-      e = rot ? launch_kv_write<BDFP4_SHIFT_F32, true>(p, stream) : launch_kv_write<BDFP4_SHIFT_F32, false>(p, stream);
+      e = rot ? launch_kv_write<BDFP4_SHIFT_F32, true>(p, page_tokens, stream)
+              : launch_kv_write<BDFP4_SHIFT_F32, false>(p, page_tokens, stream);
       break;
     case BDFP4_SHIFT_BF16:
-      e = rot ? launch_kv_write<BDFP4_SHIFT_BF16, true>(p, stream)
-              : launch_kv_write<BDFP4_SHIFT_BF16, false>(p, stream);
+      e = rot ? launch_kv_write<BDFP4_SHIFT_BF16, true>(p, page_tokens, stream)
+              : launch_kv_write<BDFP4_SHIFT_BF16, false>(p, page_tokens, stream);
       break;
     default:
-      e = rot ? launch_kv_write<BDFP4_SHIFT_NONE, true>(p, stream)
-              : launch_kv_write<BDFP4_SHIFT_NONE, false>(p, stream);
+      e = rot ? launch_kv_write<BDFP4_SHIFT_NONE, true>(p, page_tokens, stream)
+              : launch_kv_write<BDFP4_SHIFT_NONE, false>(p, page_tokens, stream);
   }
   return bdfp4::cuda_status(e);
 }

@@ -183,7 +183,7 @@ __device__ __forceinline__ void tmem_ld(uint32_t address, float* v) {
 // Shared-memory matrix descriptor (64-bit): start address >> 4 in [0,14), leading byte offset >> 4
 // in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48), swizzle mode in
 // [61,64) (0 none, 2 128B, 4 64B, 6 32B).
-constexpr uint64_t kSwizzleNone = 0, kSwizzle64B = 4;
+constexpr uint64_t kSwizzleNone = 0, kSwizzle64B = 4, kSwizzle32B = 6;
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_address, uint64_t swizzle, uint32_t stride_bytes,
                                               uint32_t leading_bytes) {
@@ -199,6 +199,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_address, uint64_t sw
 // 512 bytes apart. `k_step` selects the 64-value slice one MMA consumes (32 bytes).
 __device__ __forceinline__ uint64_t fp4_tile_desc(uint32_t smem_address, int k_step) {
   return smem_desc(smem_address + k_step * 32, kSwizzle64B, 512, 16);
+}
+
+// K-major FP4 operand tile of 32-byte rows (64 E2M1 values, exactly one MMA's K slice), 32-byte
+// swizzle, eight-row groups 256 bytes apart.
+__device__ __forceinline__ uint64_t fp4_half_tile_desc(uint32_t smem_address) {
+  return smem_desc(smem_address, kSwizzle32B, 256, 16);
 }
 
 // One 512-byte scale-factor atom (32 rows x 16 bytes) as the source of tcgen05.cp 32x128b.

@@ -19,6 +19,10 @@ from .interface import SINK_TOKENS, split_partial_count
 from .p_scale import BUILT_P_SCALE_MODES, resolve_p_scale_environment, resolve_p_scale_tau
 
 PAGE_SIZE = 128
+# Cache page sizes this build serves. 128 is the reference's only size; with 64-token pages (no
+# reference counterpart) a sequence still moves to FP4 in 128-token steps, two page-table entries
+# each, and the page size is read off the shape of ``key_pages_fp4``.
+CACHE_PAGE_SIZES = (128, 64)
 HEAD_DIM = 128
 SM100_MAJOR = 10
 MAX_QUERY_HEADS_PER_KV_HEAD = 16
@@ -143,18 +147,18 @@ def _validate(
     if (
         key_pages_fp4.dtype not in packed_types
         or key_pages_fp4.ndim != 4
-        or key_pages_fp4.shape[1] != PAGE_SIZE
+        or key_pages_fp4.shape[1] not in CACHE_PAGE_SIZES
         or key_pages_fp4.shape[3] * 2 != HEAD_DIM
     ):
         raise ValueError("key_pages_fp4 must be packed FP4 with shape [pages, 128, heads_kv, 64]")
-    page_count, _, heads_kv, _ = key_pages_fp4.shape
+    page_count, cache_page, heads_kv, _ = key_pages_fp4.shape
     if value_pages_fp4.dtype not in packed_types or tuple(value_pages_fp4.shape) != (
-        page_count, heads_kv, HEAD_DIM, PAGE_SIZE // 2,
+        page_count, heads_kv, HEAD_DIM, cache_page // 2,
     ):
-        raise ValueError("value_pages_fp4 must be packed FP4 with shape [pages, heads_kv, 128, 64]")
+        raise ValueError(f"value_pages_fp4 must be packed FP4 with shape [pages, heads_kv, 128, {cache_page // 2}]")
     for tensor, name, inner in (
         (key_pages_fp4, "key_pages_fp4", (heads_kv * 64, 64, 1)),
-        (value_pages_fp4, "value_pages_fp4", (HEAD_DIM * 64, 64, 1)),
+        (value_pages_fp4, "value_pages_fp4", (HEAD_DIM * cache_page // 2, cache_page // 2, 1)),
     ):
         if tensor.stride()[1:] != inner or tensor.stride(0) % 16 or tensor.data_ptr() % 16:
             raise ValueError(f"{name} must be dense within a page with a 16-byte page pitch")
@@ -168,7 +172,14 @@ def _validate(
             f"this build serves at most {MAX_QUERY_HEADS_PER_KV_HEAD} query heads per KV head, got {ratio}"
         )
     expected_query_sf = (32, 4, 1, 4, 2, heads_kv, rows)
-    expected_page_sf = (page_count, 32, 4, 1, 4, 2, heads_kv)
+    # scale regions as (pages, 32, 4, 1, 4, atoms, heads) views of [heads][atoms][32][4][4] bytes; a
+    # 64-token K page holds two half atoms, (pages, 32, 2, 1, 4, 2, heads) over [heads][2][32][2][4]
+    if cache_page == PAGE_SIZE:
+        expected_key_sf = expected_value_sf = (page_count, 32, 4, 1, 4, 2, heads_kv)
+        key_sf_strides = value_sf_strides = (16, 4, 1024, 1, 512, 1024)
+    else:
+        expected_key_sf, key_sf_strides = (page_count, 32, 2, 1, 4, 2, heads_kv), (8, 4, 512, 1, 256, 512)
+        expected_value_sf, value_sf_strides = (page_count, 32, 4, 1, 4, 1, heads_kv), (16, 4, 512, 1, 512, 512)
     query_sf_strides = (16, 4, heads_q * 1024, 1, 512, 1024, heads_q * 1024)
     for scales, name in ((query_scales, "query_scales"), (query_scales_second, "query_scales_second")):
         if scales is None:
@@ -180,12 +191,15 @@ def _validate(
             raise ValueError(f"{name} must use the layout returned by quantize_query")
         if scales.storage_offset() != 0 and scales.data_ptr() % 16:
             raise ValueError(f"{name} must start on a 16-byte boundary")
-    for scales, name in ((key_scales, "key_scales"), (value_scales, "value_scales")):
+    for scales, name, expected_page_sf, sf_strides in (
+        (key_scales, "key_scales", expected_key_sf, key_sf_strides),
+        (value_scales, "value_scales", expected_value_sf, value_sf_strides),
+    ):
         if tuple(scales.shape) != expected_page_sf:
             raise ValueError(f"{name} must have shape {expected_page_sf}")
         if scales.dtype not in (torch.uint8, torch.float8_e4m3fn):
             raise ValueError(f"{name} must hold E4M3 scale bytes")
-        if scales.stride()[1:] != (16, 4, 1024, 1, 512, 1024) or scales.stride(0) % 512:
+        if scales.stride()[1:] != sf_strides or scales.stride(0) % 512:
             raise ValueError(f"{name} must use the quantizer's scale layout with a 512-byte aligned page pitch")
     if (
         fp4_page_table.dtype is not torch.int32
@@ -196,13 +210,14 @@ def _validate(
         raise ValueError("fp4_page_table must be row-major INT32 with shape [rows, max_pages]")
     if seqused_fp4.dtype is not torch.int32 or tuple(seqused_fp4.shape) != (rows,) or not seqused_fp4.is_contiguous():
         raise ValueError("seqused_fp4 must be contiguous INT32 with shape [rows]")
-    max_fp4_tokens = fp4_page_table.shape[1] * PAGE_SIZE
+    entries_per_step = PAGE_SIZE // cache_page
+    max_fp4_tokens = fp4_page_table.shape[1] // entries_per_step * PAGE_SIZE
     if not trusted_metadata:
         _check_device_values(
             (seqused_fp4 < 0) | (seqused_fp4 > max_fp4_tokens) | (seqused_fp4 % PAGE_SIZE != 0),
             f"seqused_fp4 values must be page-aligned and in [0, {max_fp4_tokens}]",
         )
-        pages_used = (seqused_fp4 // PAGE_SIZE)[:, None]
+        pages_used = (seqused_fp4 // cache_page)[:, None]
         columns = torch.arange(fp4_page_table.shape[1], device=device)[None, :]
         consumed = columns < pages_used
         _check_device_values(
@@ -321,6 +336,7 @@ def _fill_args(
     a.key_codes_pitch, a.key_scales_pitch = key_pages_fp4.stride(0), key_scales.stride(0)
     a.value_codes_pitch, a.value_scales_pitch = value_pages_fp4.stride(0), value_scales.stride(0)
     a.pages = page_count
+    a.page_tokens = key_pages_fp4.shape[1]
     a.page_table = fp4_page_table.data_ptr()
     a.page_table_stride = fp4_page_table.stride(0)
     a.max_pages_per_row = fp4_page_table.shape[1]

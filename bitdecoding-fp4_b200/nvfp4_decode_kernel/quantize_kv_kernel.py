@@ -15,6 +15,9 @@ import bdfp4
 from .scale_mode import DEFAULT_SCALE_MODE, mode_id, scale_format, sf_vec_size
 
 PAGE_SIZE = 128
+# 64-token cache pages (no reference counterpart) are served too; the page size is read off the
+# shape of the destination regions (or of the BF16 pages given to quantize_*_pages).
+CACHE_PAGE_SIZES = (128, 64)
 HEAD_DIM = 128
 SF_VEC_SIZE = 16
 GROUPS_PER_ATOM = 4
@@ -38,7 +41,8 @@ def _dense_strides(shape: tuple) -> tuple:
     return tuple(reversed(strides))
 
 
-def _validate_destination(pages_fp4, scales, *, heads: int, inner_shape: tuple, rest_k: int) -> None:
+def _validate_destination(pages_fp4, scales, *, heads: int, inner_shape: tuple, rest_k: int,
+                          half_atoms: bool = False) -> None:
     """Only the page pitch of a destination is free; its interior is the decode kernel's layout."""
     if (
         pages_fp4.dtype is not torch.uint8
@@ -51,11 +55,16 @@ def _validate_destination(pages_fp4, scales, *, heads: int, inner_shape: tuple, 
             f"packed destination must be uint8 CUDA pages of {inner_shape}, "
             "dense within a page, 16-byte page pitch"
         )
+    # a 64-token K page holds half atoms: 32 rows x 2 column groups x 4 scales
+    scale_shape = (32, 2, 1, 4, rest_k, heads) if half_atoms else (32, 4, 1, 4, rest_k, heads)
+    scale_strides = (
+        (8, 4, rest_k * 256, 1, 256, rest_k * 256) if half_atoms else (16, 4, rest_k * 512, 1, 512, rest_k * 512)
+    )
     if (
         scales.dtype not in _SCALE_DTYPES
         or scales.device != pages_fp4.device
-        or tuple(scales.shape[1:]) != (32, 4, 1, 4, rest_k, heads)
-        or scales.stride()[1:] != (16, 4, rest_k * 512, 1, 512, rest_k * 512)
+        or tuple(scales.shape[1:]) != scale_shape
+        or scales.stride()[1:] != scale_strides
         or scales.stride(0) % 16
     ):
         raise ValueError("scale destination must use the quantizer's own scale layout")
@@ -95,6 +104,9 @@ class KVCacheWriter:
             raise ValueError("a writer needs K or V regions")
         heads = any_packed.shape[2 if key_packed is not None else 1]
         self.heads = heads
+        self.page_size = key_packed.shape[1] if key_packed is not None else value_packed.shape[3] * 2
+        if self.page_size not in CACHE_PAGE_SIZES:
+            raise ValueError(f"cache pages hold {PAGE_SIZE} (or 64) tokens, not {self.page_size}")
         self.key_scale_mode = key_scale_mode
         self.value_scale_mode = value_scale_mode
         formats = (scale_format(key_scale_mode), scale_format(value_scale_mode))
@@ -186,14 +198,14 @@ class KVCacheWriter:
         if key_pages_fp4 is not None:
             _validate_destination(
                 key_pages_fp4, key_scales, heads=self.heads,
-                inner_shape=(PAGE_SIZE, self.heads, HEAD_DIM // 2),
-                rest_k=scale_atoms(HEAD_DIM, self.key_scale_mode),
+                inner_shape=(self.page_size, self.heads, HEAD_DIM // 2),
+                rest_k=scale_atoms(HEAD_DIM, self.key_scale_mode), half_atoms=self.page_size == 64,
             )
         if value_pages_fp4 is not None:
             _validate_destination(
                 value_pages_fp4, value_scales, heads=self.heads,
-                inner_shape=(self.heads, HEAD_DIM, PAGE_SIZE // 2),
-                rest_k=scale_atoms(PAGE_SIZE, self.value_scale_mode),
+                inner_shape=(self.heads, HEAD_DIM, self.page_size // 2),
+                rest_k=scale_atoms(self.page_size, self.value_scale_mode),
             )
         return (key_pages_fp4, key_scales, value_pages_fp4, value_scales)
 
@@ -267,6 +279,7 @@ class KVCacheWriter:
             else bdfp4.SHIFT_F32 if self._key_shift.dtype is torch.float32 else bdfp4.SHIFT_BF16
         )
         a.layer = int(layer)
+        a.page_tokens = self.page_size
         if self.writes_tail:
             if any(t is None for t in (query_start_loc, seq_lens, seqused_fp4, row_to_slot)):
                 raise ValueError("a tail-writing call needs query_start_loc, seq_lens, seqused_fp4 and row_to_slot")
@@ -281,13 +294,13 @@ class KVCacheWriter:
         bdfp4.kv_write(a, bdfp4.current_stream(self._device))
 
 
-def _validate_pages(pages: torch.Tensor, name: str) -> tuple[int, int]:
+def _validate_pages(pages: torch.Tensor, name: str) -> tuple[int, int, int]:
     if pages.dtype is not torch.bfloat16 or not pages.is_cuda or not pages.is_contiguous() or pages.ndim != 4:
         raise ValueError(f"{name} must be contiguous BF16 CUDA with shape [pages, 128, heads, 128]")
     page_count, page_size, heads, head_dim = pages.shape
-    if page_count < 1 or page_size != PAGE_SIZE or head_dim != HEAD_DIM:
+    if page_count < 1 or page_size not in CACHE_PAGE_SIZES or head_dim != HEAD_DIM:
         raise ValueError(f"{name} must have shape [pages, 128, heads, 128]")
-    return page_count, heads
+    return page_count, heads, page_size
 
 
 def _allocate_scales(page_count: int, heads: int, rest_m: int, rest_k: int, device):
@@ -304,33 +317,44 @@ def _allocate_scales(page_count: int, heads: int, rest_m: int, rest_k: int, devi
     return storage, view
 
 
-def _identity_work(page_count: int, device):
+def _identity_work(page_count: int, device, page_size: int = PAGE_SIZE):
     pages = torch.arange(page_count, dtype=torch.int32, device=device)
-    return pages * PAGE_SIZE, pages
+    return pages * page_size, pages
 
 
 def quantize_key_pages(key_pages: torch.Tensor, scale_mode: str = DEFAULT_SCALE_MODE,
                        scale_geometry: str = "local"):
-    """BF16 K pages ``[pages,128,H,128]`` -> fresh E2M1 ``[pages,128,H,64]`` u8 and their scales."""
-    page_count, heads = _validate_pages(key_pages, "key_pages")
+    """BF16 K pages ``[pages,128,H,128]`` -> fresh E2M1 ``[pages,128,H,64]`` u8 and their scales
+    (``[pages,64,H,128]`` -> ``[pages,64,H,64]`` for 64-token pages)."""
+    page_count, heads, page_size = _validate_pages(key_pages, "key_pages")
     rest_k = scale_atoms(HEAD_DIM, scale_mode)
-    key_pages_fp4 = torch.empty(page_count, PAGE_SIZE, heads, HEAD_DIM // 2, dtype=torch.uint8,
+    key_pages_fp4 = torch.empty(page_count, page_size, heads, HEAD_DIM // 2, dtype=torch.uint8,
                                 device=key_pages.device)
-    _, key_scales = _allocate_scales(page_count, heads, 1, rest_k, key_pages.device)
+    if page_size == PAGE_SIZE:
+        _, key_scales = _allocate_scales(page_count, heads, 1, rest_k, key_pages.device)
+    else:
+        storage = torch.empty(page_count * heads * rest_k * 256, dtype=torch.uint8, device=key_pages.device)
+        key_scales = storage.as_strided(
+            (page_count, 32, 2, 1, 4, rest_k, heads),
+            (heads * rest_k * 256, 8, 4, rest_k * 256, 1, 256, rest_k * 256),
+        )
     regions = (key_pages_fp4, key_scales, None, None)
     writer = KVCacheWriter(regions=regions, key_scale_mode=scale_mode, key_scale_geometry=scale_geometry)
-    writer(key_pages.reshape(-1, heads, HEAD_DIM), None, regions, *_identity_work(page_count, key_pages.device))
+    writer(key_pages.reshape(-1, heads, HEAD_DIM), None, regions,
+           *_identity_work(page_count, key_pages.device, page_size))
     return key_pages_fp4, key_scales.view(scale_dtype(scale_mode))
 
 
 def quantize_value_pages(value_pages: torch.Tensor, scale_mode: str = DEFAULT_SCALE_MODE):
-    """BF16 V pages ``[pages,128,H,128]`` -> fresh E2M1 ``[pages,H,128,64]`` u8 and their scales."""
-    page_count, heads = _validate_pages(value_pages, "value_pages")
-    rest_k = scale_atoms(PAGE_SIZE, scale_mode)
-    value_pages_fp4 = torch.empty(page_count, heads, HEAD_DIM, PAGE_SIZE // 2, dtype=torch.uint8,
+    """BF16 V pages ``[pages,128,H,128]`` -> fresh E2M1 ``[pages,H,128,64]`` u8 and their scales
+    (``[pages,64,H,128]`` -> ``[pages,H,128,32]`` for 64-token pages)."""
+    page_count, heads, page_size = _validate_pages(value_pages, "value_pages")
+    rest_k = scale_atoms(page_size, scale_mode)
+    value_pages_fp4 = torch.empty(page_count, heads, HEAD_DIM, page_size // 2, dtype=torch.uint8,
                                   device=value_pages.device)
     _, value_scales = _allocate_scales(page_count, heads, HEAD_DIM // 128, rest_k, value_pages.device)
     regions = (None, None, value_pages_fp4, value_scales)
     writer = KVCacheWriter(regions=regions, value_scale_mode=scale_mode)
-    writer(None, value_pages.reshape(-1, heads, HEAD_DIM), regions, *_identity_work(page_count, value_pages.device))
+    writer(None, value_pages.reshape(-1, heads, HEAD_DIM), regions,
+           *_identity_work(page_count, value_pages.device, page_size))
     return value_pages_fp4, value_scales.view(scale_dtype(scale_mode))

@@ -75,6 +75,18 @@ int bdfp4_check_device(void);
  *   scales   u8 [H][2][32][4][4]          byte of (row r, group g, head h) =
  *            h*1024 + (g/4)*512 + (r%32)*16 + (r/32)*4 + g%4; r = token for K, channel for V,
  *            g = channel group for K, token group for V.
+ *
+ * 64-token pages (page_tokens = 64; the reference has none, src/nvfp4_decode_kernel/_decode.py:23 pins 128).
+ * A sequence still moves to FP4 in 128-token steps (seqused_fp4 stays a multiple of 128), each step
+ * filling two entries of the row's page table, older 64 tokens first; codes and scale values are
+ * those of the 128-token page holding the same tokens, only the byte placement differs:
+ *   K codes  u8 [64 tok][H][64]
+ *   V codes  u8 [H][128 ch][32]           byte = tokens (2b, 2b+1)
+ *   K scales u8 [H][2][32][2][4]          byte of (token t, group g, head h) =
+ *            h*512 + (g/4)*256 + (t%32)*8 + (t/32)*4 + g%4   (two half atoms; the decode kernel
+ *            interleaves the halves of a step's two pages into the 128-row atoms of its MMA)
+ *   V scales u8 [H][32][4][4]             byte of (channel c, token group g < 4, head h) =
+ *            h*512 + (c%32)*16 + (c/32)*4 + g
  */
 typedef struct bdfp4_kv_write_args {
   /* source: [tokens, H, 128] BF16, dense within a token; pitch in elements (multiple of 8) */
@@ -122,6 +134,9 @@ typedef struct bdfp4_kv_write_args {
   int32_t decode_rows;
   int32_t first_row;
   int32_t* error_word; /* optional */
+  /* Tokens per cache page: 0 or 128 (the reference's only size), or 64 (see "64-token pages"):
+   * a work item then reads 64 tokens. The BF16 tail keeps its 128 rolling rows either way. */
+  int32_t page_tokens;
 } bdfp4_kv_write_args;
 
 int bdfp4_kv_write(const bdfp4_kv_write_args* args, void* stream);
@@ -236,6 +251,8 @@ typedef struct bdfp4_decode_args {
    * next c pages. 0 keeps the reference's even partition. The merged output is the same up to the
    * rounding of the partials. */
   int32_t bf16_page_cost;
+  /* Tokens per cache page: 0 or 128 (the reference's only size), or 64 (see "64-token pages"). */
+  int32_t page_tokens;
 } bdfp4_decode_args;
 
 int bdfp4_decode(const bdfp4_decode_args* args, void* stream);

@@ -211,34 +211,63 @@ def unpack_scale_tile(tile: torch.Tensor, rows: int = 128) -> torch.Tensor:
     return e4m3_from_bytes(picked).reshape(*tile.shape[:-1], rows, 8)
 
 
+def key_scale_offsets64() -> torch.Tensor:
+    """``[64 tokens, 8 groups]`` byte offsets inside one head's 512-byte K scale block of a
+    64-token page: two half atoms ``[group // 4][token % 32][token // 32][group % 4]``. The
+    reference has no 64-token page (src/nvfp4_decode_kernel/_decode.py:23 pins 128); this is the
+    CUDA path's own layout, whose values must equal those of the 128-token page."""
+    t = torch.arange(64)[:, None]
+    g = torch.arange(8)[None, :]
+    return (g // 4) * 256 + (t % 32) * 8 + (t // 32) * 4 + (g % 4)
+
+
 def quantize_key_pages(key_pages: torch.Tensor, scale_mode: str = "amax6", *, rotate: bool = False,
                        shift: torch.Tensor | None = None):
     """``[pages, 128, H, 128]`` BF16 -> (codes u8 ``[pages,128,H,64]``, scales u8 ``[pages,H,1024]``).
-    Groups run along channels (src/nvfp4_decode_kernel/quantize_kv_kernel.py:165-221)."""
+    Groups run along channels (src/nvfp4_decode_kernel/quantize_kv_kernel.py:165-221).
+    A 64-token page ``[pages, 64, H, 128]`` gives codes ``[pages,64,H,64]`` and scales ``[pages,H,512]``."""
     basis = key_cache_basis(key_pages, rotate=rotate, shift=shift)
-    codes, scales = quantize_last_axis(basis, scale_mode)  # scales [pages,128,H,8]
+    codes, scales = quantize_last_axis(basis, scale_mode)  # scales [pages,tok,H,8]
+    if key_pages.shape[1] == 64:
+        by_head = e4m3_bytes(scales).permute(0, 2, 1, 3)  # [pages,H,64,8]
+        block = torch.zeros(*by_head.shape[:2], 512, dtype=torch.uint8)
+        block[..., key_scale_offsets64().reshape(-1)] = by_head.reshape(*by_head.shape[:2], 512)
+        return pack_nibbles(codes), block
     return pack_nibbles(codes), pack_scale_tile(scales.permute(0, 2, 1, 3))
 
 
 def quantize_value_pages(value_pages: torch.Tensor, scale_mode: str = "amax6"):
     """``[pages, 128, H, 128]`` BF16 -> (codes u8 ``[pages,H,128,64]``, scales u8 ``[pages,H,1024]``).
     Groups run along the page's tokens (src/nvfp4_decode_kernel/quantize_kv_kernel.py:224-255,
-    src/nvfp4_decode_kernel/reference.py:479-525)."""
+    src/nvfp4_decode_kernel/reference.py:479-525). A 64-token page gives codes ``[pages,H,128,32]``
+    and scales ``[pages,H,512]``: the first atom of the 128-token tile (token groups 0-3)."""
     by_channel = value_pages.permute(0, 2, 3, 1)  # [pages,H,ch,tok]
-    codes, scales = quantize_last_axis(by_channel, scale_mode)  # scales [pages,H,ch,8]
+    codes, scales = quantize_last_axis(by_channel, scale_mode)  # scales [pages,H,ch,tok/16]
+    if value_pages.shape[1] == 64:
+        padded = torch.cat([scales, torch.zeros_like(scales)], dim=-1)
+        return pack_nibbles(codes), pack_scale_tile(padded)[..., :512].contiguous()
     return pack_nibbles(codes), pack_scale_tile(scales)
 
 
 def dequantize_key_pages(codes: torch.Tensor, scale_tiles: torch.Tensor) -> torch.Tensor:
-    """Inverse layout walk: -> FP32 ``[pages, 128, H, 128]``."""
-    nib = unpack_nibbles(codes)  # [pages,128,H,128]
-    scales = unpack_scale_tile(scale_tiles).permute(0, 2, 1, 3)  # [pages,128,H,8]
+    """Inverse layout walk: -> FP32 ``[pages, tokens, H, 128]`` (tokens = 128, or 64 from the
+    64-token layout, told apart by the code tensor's shape)."""
+    nib = unpack_nibbles(codes)  # [pages,tok,H,128]
+    if codes.shape[1] == 64:
+        picked = scale_tiles[..., key_scale_offsets64().reshape(-1)]
+        scales = e4m3_from_bytes(picked).reshape(*scale_tiles.shape[:-1], 64, 8).permute(0, 2, 1, 3)
+    else:
+        scales = unpack_scale_tile(scale_tiles).permute(0, 2, 1, 3)  # [pages,128,H,8]
     return dequantize_last_axis(nib, scales)
 
 
 def dequantize_value_pages(codes: torch.Tensor, scale_tiles: torch.Tensor) -> torch.Tensor:
     nib = unpack_nibbles(codes)  # [pages,H,ch,tok]
-    scales = unpack_scale_tile(scale_tiles)  # [pages,H,ch,8]
+    if codes.shape[-1] == 32:
+        padded = torch.cat([scale_tiles, torch.zeros_like(scale_tiles)], dim=-1)
+        scales = unpack_scale_tile(padded)[..., :4]  # [pages,H,ch,4]
+    else:
+        scales = unpack_scale_tile(scale_tiles)  # [pages,H,ch,8]
     return dequantize_last_axis(nib, scales).permute(0, 3, 1, 2)
 
 
@@ -454,8 +483,8 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
     has_sink = has_tail and seqused_sink is not None
     for row in range(rows):
         fp4_tokens = int(seqused_fp4[row])
-        pages = fp4_tokens // PAGE
-        ids = page_table[row, :pages].long()
+        pages = fp4_tokens // PAGE  # 128-token steps of the walk, whatever the cache page size
+        ids = page_table[row, :fp4_tokens // key_codes.shape[1]].long()
         slot = int(tail_slot_ids[row]) if has_tail else -1
         tail_tokens = int(seqused_residual[row]) if has_tail and slot >= 0 else 0
         sink_tokens = int(seqused_sink[row]) if has_sink and slot >= 0 else 0
