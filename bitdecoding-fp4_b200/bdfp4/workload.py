@@ -32,7 +32,9 @@ def carve_cache(blocks: torch.Tensor, heads: int, page_tokens: int = PAGE):
     pitch = blocks.stride(0)
     base, origin = blocks, blocks.storage_offset()
     codes, scales = page_tokens * 64 * heads, page_tokens * 8 * heads  # bytes of one region
-    key_codes = base.as_strided((num_blocks, page_tokens, heads, 64), (pitch, heads * 64, 64, 1), origin)
+    # 128-token pages are token-major [tok][H][64]; a 64-token page is head-major [H][tok][64]
+    key_strides = (pitch, heads * 64, 64, 1) if page_tokens == PAGE else (pitch, 64, page_tokens * 64, 1)
+    key_codes = base.as_strided((num_blocks, page_tokens, heads, 64), key_strides, origin)
     value_codes = base.as_strided(
         (num_blocks, heads, HEAD_DIM, page_tokens // 2), (pitch, HEAD_DIM * page_tokens // 2, page_tokens // 2, 1),
         origin + codes + scales,

@@ -52,6 +52,9 @@ struct DecodeParams {
   const uint8_t* k_scales;
   const uint8_t* v_scales;
   int64_t k_scales_pitch, v_scales_pitch;
+  const uint8_t* k_codes;  // 64-token pages are fetched with bulk copies, not through the tensor maps
+  const uint8_t* v_codes;
+  int64_t k_codes_pitch, v_codes_pitch;
   int pages;
   const int32_t* page_table;
   int64_t page_table_stride;
@@ -89,6 +92,7 @@ struct DecodeSmem {
   float red[2][4][GP];
   float sum_red[4][GP];
   uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  uint64_t ksf_full[kStages];  // K scale blocks of 64-token pages, which arrive ahead of the codes
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -422,6 +426,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       tc::mbar_init(&sm.k_empty[s], 1);
       tc::mbar_init(&sm.v_full[s], 1);
       tc::mbar_init(&sm.v_empty[s], 1);
+      tc::mbar_init(&sm.ksf_full[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       tc::mbar_init(&sm.s_full[s], 1);
@@ -476,19 +481,24 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   // page-table read and the first copies.
   auto request_key = [&](int i, int page, int page_b) {  // one thread
     const int s = i % KS;
-    tc::mbar_expect_tx(&sm.k_full[s], kStageBytes);
     if constexpr (PT == 128) {
+      tc::mbar_expect_tx(&sm.k_full[s], kStageBytes);
       tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
       tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 1024, 1024,
                     &sm.k_full[s]);
     } else {
-      // tokens 0-63 of the step come from the first entry, 64-127 from the second; the two 512-byte
-      // scale blocks land side by side and are interleaved into atoms by the MMA warp
-      tc::tma_load_4d(sm.k_stage[s], &k_map, &sm.k_full[s], 0, kv_head, 0, page);
-      tc::tma_load_4d(sm.k_stage[s] + 4096, &k_map, &sm.k_full[s], 0, kv_head, 0, page_b);
+      tc::mbar_expect_tx(&sm.ksf_full[s], 1024);
+      tc::mbar_expect_tx(&sm.k_full[s], 8192);
+      // tokens 0-63 of the step come from the first entry, 64-127 from the second, each stored as
+      // its 4 KB swizzled shared-memory image. The two 512-byte scale blocks land side by side on
+      // a barrier of their own: the MMA warp interleaves them into atoms while the codes are
+      // still in flight.
       tc::bulk_load(sm.k_stage[s] + 8192, p.k_scales + (int64_t)page * p.k_scales_pitch + kv_head * 512, 512,
-                    &sm.k_full[s]);
+                    &sm.ksf_full[s]);
       tc::bulk_load(sm.k_stage[s] + 8192 + 512, p.k_scales + (int64_t)page_b * p.k_scales_pitch + kv_head * 512, 512,
+                    &sm.ksf_full[s]);
+      tc::bulk_load(sm.k_stage[s], p.k_codes + (int64_t)page * p.k_codes_pitch + kv_head * 4096, 4096, &sm.k_full[s]);
+      tc::bulk_load(sm.k_stage[s] + 4096, p.k_codes + (int64_t)page_b * p.k_codes_pitch + kv_head * 4096, 4096,
                     &sm.k_full[s]);
     }
   };
@@ -501,8 +511,9 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
                     &sm.v_full[s]);
     } else {
       // one [128 ch][32 B] tile and one scale atom per entry: the two K = 64 steps of the PV MMA
-      tc::tma_load_3d(sm.v_stage[s], &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page);
-      tc::tma_load_3d(sm.v_stage[s] + 4096, &v_map, &sm.v_full[s], 0, kv_head * kHeadDim, page_b);
+      tc::bulk_load(sm.v_stage[s], p.v_codes + (int64_t)page * p.v_codes_pitch + kv_head * 4096, 4096, &sm.v_full[s]);
+      tc::bulk_load(sm.v_stage[s] + 4096, p.v_codes + (int64_t)page_b * p.v_codes_pitch + kv_head * 4096, 4096,
+                    &sm.v_full[s]);
       tc::bulk_load(sm.v_stage[s] + 8192, p.v_scales + (int64_t)page * p.v_scales_pitch + kv_head * 512, 512,
                     &sm.v_full[s]);
       tc::bulk_load(sm.v_stage[s] + 8192 + 512, p.v_scales + (int64_t)page_b * p.v_scales_pitch + kv_head * 512, 512,
@@ -602,6 +613,9 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         const uint32_t parity = (i / KS) & 1;
         while (!tc::mbar_try_wait(&sm.k_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
         }
+        while (PT == 64 && !tc::mbar_try_wait(&sm.ksf_full[s], parity) &&
+               tc::global_timer_ns() - start < tc::kWaitLimitNs) {
+        }
         while (!tc::mbar_try_wait(&sm.v_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
         }
       }
@@ -655,8 +669,8 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       for (int i = 0; i < num_pages && ok; ++i) {
         const int s = i % KS;
         const int b = i & 1;
-        ok = tc::mbar_wait(&sm.k_full[s], (i / KS) & 1, abort_flag);
         if constexpr (PT == 64) {
+          ok = tc::mbar_wait(&sm.ksf_full[s], (i / KS) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           // K scales arrived as [page][atom][32 rows][8 B]; an atom row is 16 bytes, tokens 0-63
@@ -673,9 +687,11 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
           tc::fence_proxy_async_smem();
           __syncwarp();
         } else {
+          ok = tc::mbar_wait(&sm.k_full[s], (i / KS) & 1, abort_flag);
           if (!ok) break;
         }
-        if (issuer) {
+        if (issuer && PT == 64) ok = tc::mbar_wait(&sm.k_full[s], (i / KS) & 1, abort_flag);
+        if (issuer && ok) {
           tc::fence_after_sync();
           const uint32_t k_addr = tc::smem_u32(sm.k_stage[s]);
           tc::cp_sf_atom(tmem + kColSFK + 8 * b, tc::sf_atom_desc(k_addr + 8192));
@@ -694,6 +710,8 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
             }
             tc::commit(&sm.s_full[b]);
             tc::commit(&sm.k_empty[s]);
+            // PV of the previous step right behind QK of this one: the producer requests K and V
+            // in step order, so a later PV would hold back the next K request as well
             if (i > 0) ok = issue_pv(i - 1);
           }
         }
@@ -1142,7 +1160,8 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
 
   CUtensorMap k_map, v_map;
   {
-    // K codes: [pages][page_tokens][H][64 B]; one box = one head of one page, rows of 64 bytes
+    // K codes of 128-token pages: [pages][128 tok][H][64 B]; one box = one head of one page, rows of
+    // 64 bytes. (64-token pages are fetched with bulk copies; their maps are encoded but unused.)
     const cuuint64_t dims[4] = {64, (cuuint64_t)a->heads_kv, (cuuint64_t)page_tokens, (cuuint64_t)a->pages};
     const cuuint64_t strides[3] = {64, (cuuint64_t)a->heads_kv * 64, (cuuint64_t)a->key_codes_pitch};
     const cuuint32_t box[4] = {64, 1, (cuuint32_t)page_tokens, 1};
@@ -1180,6 +1199,10 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   p.v_scales = static_cast<const uint8_t*>(a->value_scales);
   p.k_scales_pitch = a->key_scales_pitch;
   p.v_scales_pitch = a->value_scales_pitch;
+  p.k_codes = static_cast<const uint8_t*>(a->key_codes);
+  p.v_codes = static_cast<const uint8_t*>(a->value_codes);
+  p.k_codes_pitch = a->key_codes_pitch;
+  p.v_codes_pitch = a->value_codes_pitch;
   p.pages = a->pages;
   p.page_table = a->page_table;
   p.page_table_stride = a->page_table_stride;

@@ -72,6 +72,10 @@ __device__ __forceinline__ void cache_basis16(float* v, int group, const void* s
   if (ROTATE || SHIFT_TYPE != BDFP4_SHIFT_NONE) round_to_bf16(v);
 }
 
+// 64-token pages are stored as the decode kernel's shared-memory images, one contiguous block per
+// (page, head), so that the kernel fetches them with plain bulk copies:
+//   K codes [H][64 tok][64 B]   16-byte chunk j of token t at position j ^ ((t >> 1) & 3)
+//   V codes [H][128 ch][32 B]   16-byte chunk j of channel c at position j ^ ((c >> 2) & 1)
 // Byte of (token, channel group) inside a 64-token page's 512-byte K scale block: two half
 // atoms [group / 4][token % 32][token / 32][group % 4]. The decode kernel interleaves the halves
 // of two such pages into the 128-row atoms its MMA reads.
@@ -107,7 +111,14 @@ __global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
     cache_basis16<SHIFT_TYPE, ROTATE>(v, group, p.key_shift,
                                       ((int64_t)layer * p.heads + head) * kHeadDim + group * kGroup);
     const GroupCodes q = quantize_group16(v, p.key_cand);
-    *reinterpret_cast<uint2*>(codes + ((int64_t)token * p.heads + head) * 64 + group * 8) = make_uint2(q.lo, q.hi);
+    if constexpr (PT == 128) {
+      *reinterpret_cast<uint2*>(codes + ((int64_t)token * p.heads + head) * 64 + group * 8) = make_uint2(q.lo, q.hi);
+    } else {
+      // head-major rows whose 16-byte chunks sit where the 64-byte shared-memory swizzle wants them
+      const int chunk = (group >> 1) ^ ((token >> 1) & 3);
+      *reinterpret_cast<uint2*>(codes + (int64_t)head * (PT * 64) + token * 64 + chunk * 16 + (group & 1) * 8) =
+          make_uint2(q.lo, q.hi);
+    }
     scale_tile[PT == 128 ? scale_tile_offset(token, group) : key_scale_offset64(token, group)] =
         (uint8_t)cvt_e4m3(q.scale);
   }
@@ -175,7 +186,10 @@ __global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) 
     const int index = it * 256 + threadIdx.x;  // 8-byte chunk of the code tile
     const int channel = index / (T::kCodeBytes / 8);
     const int chunk = index % (T::kCodeBytes / 8);
-    reinterpret_cast<uint2*>(codes)[index] =
+    // a 64-token page stores each 32-byte row with its 16-byte halves placed as the 32-byte
+    // shared-memory swizzle wants them
+    const int dst = PT == 128 ? index : channel * 4 + ((((chunk >> 1) ^ ((channel >> 2) & 1)) << 1) | (chunk & 1));
+    reinterpret_cast<uint2*>(codes)[dst] =
         *reinterpret_cast<const uint2*>(code_tile + channel * T::kCodePitch + chunk * 8);
   }
   if (threadIdx.x < T::kScaleBytes / 4)

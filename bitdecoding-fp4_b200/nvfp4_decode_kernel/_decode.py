@@ -157,7 +157,8 @@ def _validate(
     ):
         raise ValueError(f"value_pages_fp4 must be packed FP4 with shape [pages, heads_kv, 128, {cache_page // 2}]")
     for tensor, name, inner in (
-        (key_pages_fp4, "key_pages_fp4", (heads_kv * 64, 64, 1)),
+        # 128-token pages are token-major; a 64-token page is head-major in memory ([H][64][64])
+        (key_pages_fp4, "key_pages_fp4", (heads_kv * 64, 64, 1) if cache_page == PAGE_SIZE else (64, 64 * 64, 1)),
         (value_pages_fp4, "value_pages_fp4", (HEAD_DIM * cache_page // 2, cache_page // 2, 1)),
     ):
         if tensor.stride()[1:] != inner or tensor.stride(0) % 16 or tensor.data_ptr() % 16:

@@ -42,13 +42,13 @@ def _dense_strides(shape: tuple) -> tuple:
 
 
 def _validate_destination(pages_fp4, scales, *, heads: int, inner_shape: tuple, rest_k: int,
-                          half_atoms: bool = False) -> None:
+                          half_atoms: bool = False, inner_strides: tuple | None = None) -> None:
     """Only the page pitch of a destination is free; its interior is the decode kernel's layout."""
     if (
         pages_fp4.dtype is not torch.uint8
         or not pages_fp4.is_cuda
         or tuple(pages_fp4.shape[1:]) != inner_shape
-        or pages_fp4.stride()[1:] != _dense_strides(inner_shape)
+        or pages_fp4.stride()[1:] != (inner_strides or _dense_strides(inner_shape))
         or pages_fp4.stride(0) % 16
     ):
         raise ValueError(
@@ -200,6 +200,8 @@ class KVCacheWriter:
                 key_pages_fp4, key_scales, heads=self.heads,
                 inner_shape=(self.page_size, self.heads, HEAD_DIM // 2),
                 rest_k=scale_atoms(HEAD_DIM, self.key_scale_mode), half_atoms=self.page_size == 64,
+                # a 64-token K page is head-major in memory: [H][64 tok][64 B] seen as (tok, H, 64)
+                inner_strides=(64, 64 * 64, 1) if self.page_size == 64 else None,
             )
         if value_pages_fp4 is not None:
             _validate_destination(
@@ -328,11 +330,13 @@ def quantize_key_pages(key_pages: torch.Tensor, scale_mode: str = DEFAULT_SCALE_
     (``[pages,64,H,128]`` -> ``[pages,64,H,64]`` for 64-token pages)."""
     page_count, heads, page_size = _validate_pages(key_pages, "key_pages")
     rest_k = scale_atoms(HEAD_DIM, scale_mode)
-    key_pages_fp4 = torch.empty(page_count, page_size, heads, HEAD_DIM // 2, dtype=torch.uint8,
-                                device=key_pages.device)
     if page_size == PAGE_SIZE:
+        key_pages_fp4 = torch.empty(page_count, page_size, heads, HEAD_DIM // 2, dtype=torch.uint8,
+                                    device=key_pages.device)
         _, key_scales = _allocate_scales(page_count, heads, 1, rest_k, key_pages.device)
     else:
+        key_pages_fp4 = torch.empty(page_count, heads, page_size, HEAD_DIM // 2, dtype=torch.uint8,
+                                    device=key_pages.device).permute(0, 2, 1, 3)
         storage = torch.empty(page_count * heads * rest_k * 256, dtype=torch.uint8, device=key_pages.device)
         key_scales = storage.as_strided(
             (page_count, 32, 2, 1, 4, rest_k, heads),

@@ -79,9 +79,11 @@ int bdfp4_check_device(void);
  * 64-token pages (page_tokens = 64; the reference has none, src/nvfp4_decode_kernel/_decode.py:23 pins 128).
  * A sequence still moves to FP4 in 128-token steps (seqused_fp4 stays a multiple of 128), each step
  * filling two entries of the row's page table, older 64 tokens first; codes and scale values are
- * those of the 128-token page holding the same tokens, only the byte placement differs:
- *   K codes  u8 [64 tok][H][64]
- *   V codes  u8 [H][128 ch][32]           byte = tokens (2b, 2b+1)
+ * those of the 128-token page holding the same tokens, only the byte placement differs. A page's
+ * codes are stored per head as the shared-memory image the decode kernel's MMA reads (rows with
+ * their 16-byte chunks at the swizzled position), so the kernel fetches them as they lie:
+ *   K codes  u8 [H][64 tok][64]           chunk j of token t at position j ^ ((t >> 1) & 3)
+ *   V codes  u8 [H][128 ch][32]           byte = tokens (2b, 2b+1); chunk j of channel c at j ^ ((c >> 2) & 1)
  *   K scales u8 [H][2][32][2][4]          byte of (token t, group g, head h) =
  *            h*512 + (g/4)*256 + (t%32)*8 + (t/32)*4 + g%4   (two half atoms; the decode kernel
  *            interleaves the halves of a step's two pages into the 128-row atoms of its MMA)

@@ -221,18 +221,37 @@ def key_scale_offsets64() -> torch.Tensor:
     return (g // 4) * 256 + (t % 32) * 8 + (t // 32) * 4 + (g % 4)
 
 
+def _place_chunks(packed: torch.Tensor, row_key: torch.Tensor) -> torch.Tensor:
+    """Move the 16-byte chunks of each row (last axis) to position ``chunk ^ row_key``; ``row_key``
+    broadcasts against ``packed.shape[:-1]``. The move is its own inverse. 64-token pages store
+    their code rows this way: the placement of the 64- or 32-byte shared-memory swizzle the decode
+    kernel's MMA reads, so that a page is fetched as it lies."""
+    chunks = packed.reshape(*packed.shape[:-1], packed.shape[-1] // 16, 16)
+    position = torch.arange(chunks.shape[-2]) ^ row_key.expand(packed.shape[:-1])[..., None]
+    return torch.gather(chunks, -2, position[..., None].expand_as(chunks)).reshape(packed.shape)
+
+
+def _key_chunk_key() -> torch.Tensor:
+    return ((torch.arange(64) >> 1) & 3)[:, None]  # [tokens, 1] against [pages, tokens, H]
+
+
+def _value_chunk_key() -> torch.Tensor:
+    return (torch.arange(128) >> 2) & 1  # [channels] against [pages, H, channels]
+
+
 def quantize_key_pages(key_pages: torch.Tensor, scale_mode: str = "amax6", *, rotate: bool = False,
                        shift: torch.Tensor | None = None):
     """``[pages, 128, H, 128]`` BF16 -> (codes u8 ``[pages,128,H,64]``, scales u8 ``[pages,H,1024]``).
     Groups run along channels (src/nvfp4_decode_kernel/quantize_kv_kernel.py:165-221).
-    A 64-token page ``[pages, 64, H, 128]`` gives codes ``[pages,64,H,64]`` and scales ``[pages,H,512]``."""
+    A 64-token page ``[pages, 64, H, 128]`` gives codes ``[pages,64,H,64]`` (chunk j of token t at
+    position ``j ^ ((t >> 1) & 3)``; in memory the page is head-major) and scales ``[pages,H,512]``."""
     basis = key_cache_basis(key_pages, rotate=rotate, shift=shift)
     codes, scales = quantize_last_axis(basis, scale_mode)  # scales [pages,tok,H,8]
     if key_pages.shape[1] == 64:
         by_head = e4m3_bytes(scales).permute(0, 2, 1, 3)  # [pages,H,64,8]
         block = torch.zeros(*by_head.shape[:2], 512, dtype=torch.uint8)
         block[..., key_scale_offsets64().reshape(-1)] = by_head.reshape(*by_head.shape[:2], 512)
-        return pack_nibbles(codes), block
+        return _place_chunks(pack_nibbles(codes), _key_chunk_key()), block
     return pack_nibbles(codes), pack_scale_tile(scales.permute(0, 2, 1, 3))
 
 
@@ -240,18 +259,21 @@ def quantize_value_pages(value_pages: torch.Tensor, scale_mode: str = "amax6"):
     """``[pages, 128, H, 128]`` BF16 -> (codes u8 ``[pages,H,128,64]``, scales u8 ``[pages,H,1024]``).
     Groups run along the page's tokens (src/nvfp4_decode_kernel/quantize_kv_kernel.py:224-255,
     src/nvfp4_decode_kernel/reference.py:479-525). A 64-token page gives codes ``[pages,H,128,32]``
-    and scales ``[pages,H,512]``: the first atom of the 128-token tile (token groups 0-3)."""
+    (chunk j of channel c at position ``j ^ ((c >> 2) & 1)``) and scales ``[pages,H,512]``: the
+    first atom of the 128-token tile (token groups 0-3)."""
     by_channel = value_pages.permute(0, 2, 3, 1)  # [pages,H,ch,tok]
     codes, scales = quantize_last_axis(by_channel, scale_mode)  # scales [pages,H,ch,tok/16]
     if value_pages.shape[1] == 64:
         padded = torch.cat([scales, torch.zeros_like(scales)], dim=-1)
-        return pack_nibbles(codes), pack_scale_tile(padded)[..., :512].contiguous()
+        return _place_chunks(pack_nibbles(codes), _value_chunk_key()), pack_scale_tile(padded)[..., :512].contiguous()
     return pack_nibbles(codes), pack_scale_tile(scales)
 
 
 def dequantize_key_pages(codes: torch.Tensor, scale_tiles: torch.Tensor) -> torch.Tensor:
     """Inverse layout walk: -> FP32 ``[pages, tokens, H, 128]`` (tokens = 128, or 64 from the
     64-token layout, told apart by the code tensor's shape)."""
+    if codes.shape[1] == 64:
+        codes = _place_chunks(codes, _key_chunk_key())
     nib = unpack_nibbles(codes)  # [pages,tok,H,128]
     if codes.shape[1] == 64:
         picked = scale_tiles[..., key_scale_offsets64().reshape(-1)]
@@ -262,6 +284,8 @@ def dequantize_key_pages(codes: torch.Tensor, scale_tiles: torch.Tensor) -> torc
 
 
 def dequantize_value_pages(codes: torch.Tensor, scale_tiles: torch.Tensor) -> torch.Tensor:
+    if codes.shape[-1] == 32:
+        codes = _place_chunks(codes, _value_chunk_key())
     nib = unpack_nibbles(codes)  # [pages,H,ch,tok]
     if codes.shape[-1] == 32:
         padded = torch.cat([scale_tiles, torch.zeros_like(scale_tiles)], dim=-1)

@@ -62,7 +62,7 @@ def test_value_pages(mode, heads):
 
 def _cpu_cache(w):
     blocks, h = w.blocks.cpu(), w.heads_kv
-    key_codes = blocks[:, :4096 * h].reshape(-1, 64, h, 64)
+    key_codes = blocks[:, :4096 * h].reshape(-1, h, 64, 64).permute(0, 2, 1, 3)
     key_scales = blocks[:, 4096 * h:4608 * h].reshape(-1, h, 512)
     value_codes = blocks[:, 4608 * h:8704 * h].reshape(-1, h, 128, 32)
     value_scales = blocks[:, 8704 * h:9216 * h].reshape(-1, h, 512)

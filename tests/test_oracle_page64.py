@@ -21,7 +21,11 @@ def test_key_pages_hold_the_128_token_values():
     codes, scales = oracle.quantize_key_pages(k, "four_six", rotate=True, shift=shift)
     codes64, scales64 = oracle.quantize_key_pages(k.reshape(6, 64, 2, 128), "four_six", rotate=True, shift=shift)
     assert tuple(codes64.shape) == (6, 64, 2, 64) and tuple(scales64.shape) == (6, 2, 512)
-    assert torch.equal(codes64.reshape(3, 128, 2, 64), codes)
+    # code bytes: those of the 128-token page with each token's 16-byte chunks moved to j ^ ((t >> 1) & 3)
+    plain = codes.reshape(6, 64, 2, 4, 16)
+    for t in (0, 1, 2, 5, 63):
+        for j in range(4):
+            assert torch.equal(codes64.reshape(6, 64, 2, 4, 16)[:, t, :, j ^ ((t >> 1) & 3)], plain[:, t, :, j])
     # scale bytes: token t of the step, group g
     tile = scales.reshape(3, 2, 1024)
     for t in (0, 31, 32, 63, 64, 100, 127):
@@ -50,8 +54,12 @@ def test_value_pages_hold_the_128_token_values():
     codes, scales = oracle.quantize_value_pages(v, "four_six")
     codes64, scales64 = oracle.quantize_value_pages(v.reshape(6, 64, 2, 128), "four_six")
     assert tuple(codes64.shape) == (6, 2, 128, 32) and tuple(scales64.shape) == (6, 2, 512)
-    both = codes64.reshape(3, 2, 2, 128, 32)
-    assert torch.equal(torch.cat([both[:, 0], both[:, 1]], dim=-1), codes)
+    both = codes64.reshape(3, 2, 2, 128, 2, 16)
+    plain = codes.reshape(3, 2, 128, 2, 2, 16)  # [.., channel, half page, chunk, 16]
+    for c in (0, 3, 4, 7, 127):
+        for j in range(2):
+            for half in range(2):
+                assert torch.equal(both[:, half, :, c, j ^ ((c >> 2) & 1)], plain[:, :, c, half, j])
     # a page's 512 scale bytes are one atom: the first (tokens 0-63) or second (64-127) of the tile
     tile = scales.reshape(3, 2, 2, 512)
     assert torch.equal(scales64.reshape(3, 2, 2, 512).permute(0, 2, 1, 3), tile)
