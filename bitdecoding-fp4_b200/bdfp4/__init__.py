@@ -34,6 +34,8 @@ EXPORTS = (
     "bdfp4_control_step",
     "bdfp4_work_table",
     "bdfp4_tail_reset",
+    "bdfp4_key_channel_sums",
+    "bdfp4_probability_statistics",
 )
 
 
@@ -159,6 +161,11 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_tail_reset.restype = c_int32
     lib.bdfp4_tail_reset.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int64, c_void_p, c_void_p,
                                      c_void_p, c_int32, c_void_p]
+    lib.bdfp4_key_channel_sums.restype = c_int32
+    lib.bdfp4_key_channel_sums.argtypes = [c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p]
+    lib.bdfp4_probability_statistics.restype = c_int32
+    lib.bdfp4_probability_statistics.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int32, c_float, c_int32,
+                                                 c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.bdfp4_decode_split_static.restype = c_int32
     lib.bdfp4_decode_split_static.argtypes = [POINTER(DecodeArgs), c_void_p]
     _lib = lib
@@ -253,3 +260,23 @@ def tail_reset(tail_key, tail_value, query_start_loc, seq_lens, row_to_slot, num
                                    tokens * heads * head_dim, ptr(query_start_loc), ptr(seq_lens), ptr(row_to_slot),
                                    num_reqs, stream),
     )
+
+
+def key_channel_sums(key, sums, stream: int) -> None:
+    """``sums[h][c] += sum_t key[t][h][c]`` in FP64; ``key`` BF16 ``[tokens, H, 128]``, ``sums`` FP64 ``[H, 128]``."""
+    tokens, heads, _ = key.shape
+    check("bdfp4_key_channel_sums",
+          library().bdfp4_key_channel_sums(ptr(key), key.stride(0), tokens, heads, ptr(sums), stream))
+
+
+def probability_statistics(scores, *, fp4_tokens: int, softmax_scale: float, sink_tokens: int, multiplier: float,
+                           page_max_scratch, group_counts, winner_counts, error_sums, oracle_sums,
+                           stream: int) -> None:
+    """Adds one query position's probability-scale statistics (FP32 ``scores [heads, tokens]``) to the
+    per-E4M3-code accumulators; see ``bdfp4_probability_statistics`` in ``include/bdfp4.h``."""
+    heads, tokens = scores.shape
+    check("bdfp4_probability_statistics",
+          library().bdfp4_probability_statistics(
+              ptr(scores), scores.stride(0), heads, tokens, fp4_tokens, softmax_scale, sink_tokens, multiplier,
+              ptr(page_max_scratch), ptr(group_counts), ptr(winner_counts), ptr(error_sums), ptr(oracle_sums),
+              stream))

@@ -21,16 +21,18 @@ def build_llm(model, **kwargs):
 
 
 def calibrate_key_smoothing(llm, **kwargs):
-    """Measuring the key-smoothing mean needs a served model; this build only consumes the sidecar
-    (``NVFP4_KEY_SHIFT`` → ``runtime.load_key_shift``)."""
-    raise NotImplementedError(
-        "key-smoothing calibration is not built; point NVFP4_KEY_SHIFT at an existing sidecar"
-    )
+    """Calibrate static key smoothing, optionally fitting the probability threshold
+    (:func:`nvfp4_vllm.calibrate.calibrate_key_shift`)."""
+    from .calibrate import calibrate_key_shift as _calibrate
+
+    return _calibrate(llm, **kwargs)
 
 
 def set_key_smoothing_enabled(llm, enabled: bool):
-    """Enable or disable an engine's loaded key shift between requests."""
-    return llm.collective_rpc("nvfp4_set_key_shift_enabled", args=(bool(enabled),))
+    """Enable or disable an engine's calibrated static key smoothing between requests."""
+    from .calibrate import set_key_shift_enabled as _set
+
+    return _set(llm, enabled)
 
 
 __all__ = ["register", "build_llm", "calibrate_key_smoothing", "set_key_smoothing_enabled"]

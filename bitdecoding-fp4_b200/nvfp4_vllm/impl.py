@@ -122,6 +122,7 @@ class NVFP4Impl(FlashAttentionImpl):
             reset_new_request_tails(tail_key=runtime.tail_key, tail_value=runtime.tail_value,
                                     query_start_loc=metadata.query_start_loc, seq_lens=metadata.seq_lens,
                                     row_to_slot=metadata.row_to_slot)
+        runtime.measure_keys(self.layer_index, key, metadata.num_actual_tokens)  # only while calibrating
         key, _, _ = runtime.key_write(self.layer_index, key)
         writer, regions = runtime.writer_for(self.layer_index, kv_cache)
         decode_rows = metadata.decode_prefix_rows

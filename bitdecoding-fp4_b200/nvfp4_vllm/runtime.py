@@ -4,7 +4,7 @@ query and split scratch, the key-shift sidecar and the writers built on them.
 
 Created during the profile run, before the KV cache exists, so that the engine subtracts this
 memory from the cache budget. Only the rotations the kernels fuse are built (``none`` and the
-Sylvester ``hadamard``); ``block_hadamard_64`` and the calibration measurement hooks are not.
+Sylvester ``hadamard``); ``block_hadamard_64`` is not.
 """
 
 from __future__ import annotations
@@ -65,7 +65,12 @@ def load_key_shift(num_layers: int, num_kv_heads: int, head_dim: int, device, dt
             f"{path} holds a key_shift of {tuple(shift.shape)}, this model "
             f"needs {expected} (rank-local) or {global_shape} (full-model)"
         )
-    shift = shift.to(device)
+    return active_shift(shift.to(device), rotation, dtype)
+
+
+def active_shift(shift: torch.Tensor, rotation: torch.Tensor | None, dtype: torch.dtype) -> torch.Tensor:
+    """An original-basis mean in the form the write path subtracts: ``c R^T`` under a rotation,
+    computed in float64, rounded once into ``dtype`` (src/nvfp4_vllm/runtime.py:117-126)."""
     if rotation is None:
         return shift.to(dtype)
     return torch.matmul(shift.double(), rotation.to(device=shift.device).double().T).to(dtype).contiguous()
@@ -105,6 +110,9 @@ class LayerRuntime:
         self.key_shift = load_key_shift(
             num_layers, num_kv_heads, head_dim, device, self.key_shift_dtype, rotation=self.rotation,
             tensor_parallel_size=tensor_parallel_size, tensor_parallel_rank=tensor_parallel_rank)
+        # FP64 per-(layer, head, channel) sums of the keys seen while a key-smoothing measurement runs
+        self.key_shift_sum: torch.Tensor | None = None
+        self.key_shift_tokens = 0
         # query scratch, zeroed once (the quantizer rewrites only part of the padded query and of
         # the scale tiles) and shared by every layer
         self.query_padded = torch.zeros(num_slots, RESIDUAL_ROW_TILE, num_heads, head_dim, dtype=torch.bfloat16,
@@ -156,6 +164,47 @@ class LayerRuntime:
         if enabled and self.key_shift is None:
             raise ValueError("no shift has been loaded or measured, so there is nothing to enable")
         self.key_shift_enabled = enabled
+
+    def begin_key_shift_measurement(self) -> None:
+        """Measure the mean of K instead of removing it, until ``finish_key_shift_measurement``.
+        A shift in force is dropped first: measured against a shifted K the result would be the
+        residual mean, close to zero (src/nvfp4_vllm/runtime.py:485-501)."""
+        self.key_shift = None
+        self.key_shift_sum = torch.zeros(self.num_layers, self.num_kv_heads, self.head_dim, dtype=torch.float64,
+                                         device=self.tail_key.device)
+        self.key_shift_tokens = 0
+
+    def measure_keys(self, layer_index: int, key: torch.Tensor, tokens: int) -> None:
+        """Add this step's post-RoPE keys ``key[:tokens]`` of one layer to the running FP64 sums
+        (what src/nvfp4_vllm/impl.py:209-216 does with ``key.double().sum``); layer 0 counts the
+        tokens for the model, because every layer sees the same ones."""
+        if self.key_shift_sum is None or tokens <= 0:
+            return
+        import bdfp4
+
+        rows = key[:tokens].view(tokens, self.num_kv_heads, self.head_dim)
+        bdfp4.key_channel_sums(rows, self.key_shift_sum[layer_index], bdfp4.current_stream(rows.device))
+        if layer_index == 0:
+            self.key_shift_tokens += tokens
+
+    def finish_key_shift_measurement(self) -> torch.Tensor:
+        """Freeze the measured mean and start subtracting it. Returns the mean rounded once into the
+        cache dtype, in the original basis (the sidecar's contract); the active value is the same
+        mean rotated in float64 and rounded once into ``key_shift_dtype``
+        (src/nvfp4_vllm/runtime.py:503-527)."""
+        if self.key_shift_sum is None or self.key_shift_tokens == 0:
+            raise ValueError(
+                "no tokens were measured, so there is no mean to subtract; "
+                "begin_key_shift_measurement must precede a forward pass"
+            )
+        mean = self.key_shift_sum / self.key_shift_tokens
+        measured = mean.to(self.tail_key.dtype)
+        self.key_shift = active_shift(measured if self.rotation is None else mean, self.rotation,
+                                      self.key_shift_dtype)
+        self.key_shift_enabled = True
+        self.key_shift_sum = None
+        self.key_shift_tokens = 0
+        return measured
 
     def transform_query(self, query: torch.Tensor) -> torch.Tensor:
         """The part of Q's basis change the quantizer does not do itself: none in this build."""

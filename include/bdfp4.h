@@ -364,6 +364,32 @@ int bdfp4_tail_reset(void* tail_key, void* tail_value, int64_t layer_stride, int
 #define BDFP4_STATIC_SCRATCH_BYTES (8u << 20)
 int bdfp4_decode_split_static(const bdfp4_decode_args* args, void* stream);
 
+/*
+ * Calibration producers (run once before serving, over one long prefill).
+ *
+ * bdfp4_key_channel_sums: sums[h][c] += sum over `tokens` of key[t][h][c], in FP64; the mean of
+ * the post-RoPE keys is what static key smoothing subtracts. `key` is BF16 [tokens][H][128] with
+ * `token_pitch` elements between tokens, `sums` FP64 [H][128] (caller-zeroed at the start of a
+ * measurement). Replaces the accumulation of src/nvfp4_vllm/impl.py:209-216.
+ *
+ * bdfp4_probability_statistics: per-E4M3-code statistics of the FP4 probability operand, from
+ * FP32 attention scores [heads][tokens] (row_stride floats between heads) of one query position.
+ * Pages are walked newest first as decode does; each 16-token group of the FP4 prefix
+ * (fp4_tokens, a multiple of 128; the first sink_tokens positions of page 0 masked) is formed
+ * against the running maximum held at its page, multiplied by `multiplier`, and priced under the
+ * scale divisors 6, 4, 3, 2 (in that order). Bucketed by the E4M3 code of the group maximum and
+ * ADDED to the outputs: group_counts u64 [256], winner_counts u64 [256][4] (lowest error, first
+ * wins), error_sums f64 [256][4], oracle_sums f64 [256] (error of the winner).
+ * page_max_scratch: FP32 [heads][fp4_tokens/128 + 1]. Replaces online_probability_scale_statistics
+ * (src/nvfp4_decode_kernel/reference.py:758-871).
+ */
+int bdfp4_key_channel_sums(const void* key, int64_t token_pitch, int64_t tokens, int32_t heads, double* sums,
+                           void* stream);
+int bdfp4_probability_statistics(const float* scores, int64_t row_stride, int32_t heads, int32_t tokens,
+                                 int32_t fp4_tokens, float softmax_scale, int32_t sink_tokens, float multiplier,
+                                 float* page_max_scratch, uint64_t* group_counts, uint64_t* winner_counts,
+                                 double* error_sums, double* oracle_sums, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

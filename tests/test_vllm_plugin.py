@@ -109,8 +109,16 @@ def test_engine_kwargs():
     assert kwargs["max_num_seqs"] == 32 and kwargs["max_num_batched_tokens"] == 65536
     with pytest.raises(ValueError):
         engine.engine_kwargs("m", enable_prefix_caching=True)
-    with pytest.raises(NotImplementedError):
-        engine.engine_kwargs("m", additional_config={"nvfp4_key_smoothing": "auto"})
+    # smoothing defaults to calibration at start-up, which needs the plugin's worker extension
+    from nvfp4_vllm.calibrate import WORKER_EXTENSION_CLS
+
+    assert kwargs["additional_config"]["nvfp4_key_smoothing"] == "auto"
+    assert kwargs["worker_extension_cls"] == WORKER_EXTENSION_CLS
+    with pytest.raises(ValueError):
+        engine.engine_kwargs("m", worker_extension_cls="other.Extension")
+    sidecar = engine.engine_kwargs("m", additional_config={"nvfp4_key_smoothing": "/tmp/shift.safetensors"},
+                                   worker_extension_cls="other.Extension")
+    assert sidecar["worker_extension_cls"] == "other.Extension"
 
 
 def test_split_policies_match_reference_values(golden):
