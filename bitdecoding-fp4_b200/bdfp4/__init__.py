@@ -108,6 +108,7 @@ class DecodeArgs(Structure):
         ("error_word", c_void_p),
         ("bf16_page_cost", c_int32),
         ("page_tokens", c_int32),
+        ("merge_counters", c_void_p),
     ]
 
 

@@ -76,6 +76,9 @@ struct DecodeParams {
   float* partial_out;
   float* partial_lse;
   int32_t* error_word;
+  // fused merge: the last part of a (row, KV head) tile to finish writes the BF16 output
+  int32_t* merge_counters;
+  __nv_bfloat16* merged_out;
 };
 
 template <int GP, int STAGES>
@@ -97,6 +100,7 @@ struct DecodeSmem {
   int page_ids[2][32];  // physical pages of the producer's current batch of steps
   uint32_t tmem_base;
   int abort_flag;
+  int merge_last;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -1039,20 +1043,54 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     const bool skip = p.num_splits > 1 && part == p.num_splits && p.tail_key == nullptr;
 #pragma unroll
     for (int j = 0; j < GP; ++j) {
-      if (j < G && !skip) {
-        const bool empty = total[j] == 0.0f || total[j] != total[j];
+      if (j < G) {
+        const bool empty = skip || total[j] == 0.0f || total[j] != total[j];
         const float value = empty ? 0.0f : st.o_acc[j] * (1.0f / total[j]);
         const int head = kv_head * G + j;
         if (p.out != nullptr) {
           p.out[(int64_t)row * p.out_row_stride + head * kHeadDim + t] = __float2bfloat16_rn(value);
         } else {
-          p.partial_out[(((int64_t)part * p.rows + row) * p.heads_q + head) * kHeadDim + t] = value;
+          if (!skip) p.partial_out[(((int64_t)part * p.rows + row) * p.heads_q + head) * kHeadDim + t] = value;
           if (t == j) {
             const float safe = st.row_max[j] == -INFINITY ? 0.0f : st.row_max[j];
             const float lse = empty ? -INFINITY
                                     : (safe * p.scale_log2 + log2f(total[j]) - shift) * 0.6931471805599453f;
             p.partial_lse[((int64_t)part * p.rows + row) * p.heads_q + head] = lse;
           }
+        }
+      }
+    }
+    if (p.merge_counters != nullptr) {
+      // Fused split merge: every part publishes its partials, then takes a ticket on the tile's
+      // counter; the part that draws the last ticket reads all of them back (from L2) and writes
+      // the BF16 output exactly as the separate merge kernel would, in part order, and leaves the
+      // counter at zero for the next launch (src/nvfp4_decode_kernel/split_k_combine.py:47-83).
+      __threadfence();
+      softmax_barrier();
+      const int tile = row * p.heads_kv + kv_head;
+      if (t == 0) sm.merge_last = atomicAdd(&p.merge_counters[tile], 1) == p.parts - 1;
+      softmax_barrier();
+      if (sm.merge_last) {
+        __threadfence();
+        if (t == 0) p.merge_counters[tile] = 0;
+        constexpr float kLog2e = 1.4426950408889634f;
+        const int64_t lse_stride = (int64_t)p.rows * p.heads_q;
+        for (int j = 0; j < G; ++j) {
+          const int head = kv_head * G + j;
+          const float* lse = p.partial_lse + (int64_t)row * p.heads_q + head;
+          const float* values = p.partial_out + ((int64_t)row * p.heads_q + head) * kHeadDim + t;
+          float lse_max = -INFINITY;
+          for (int s = 0; s < p.parts; ++s) lse_max = fmaxf(lse_max, __ldcg(lse + s * lse_stride));
+          if (lse_max == -INFINITY) lse_max = 0.0f;
+          float weight_sum = 0.0f;
+          for (int s = 0; s < p.parts; ++s) weight_sum += exp2f(__ldcg(lse + s * lse_stride) * kLog2e - lse_max * kLog2e);
+          const float inverse = (weight_sum == 0.0f || weight_sum != weight_sum) ? 0.0f : 1.0f / weight_sum;
+          float acc = 0.0f;
+          for (int s = 0; s < p.parts; ++s) {
+            const float scale = exp2f(__ldcg(lse + s * lse_stride) * kLog2e - lse_max * kLog2e) * inverse;
+            if (scale > 0.0f) acc = acc + scale * __ldcg(values + s * lse_stride * kHeadDim);
+          }
+          p.merged_out[(int64_t)row * p.out_row_stride + head * kHeadDim + t] = __float2bfloat16_rn(acc);
         }
       }
     }
@@ -1243,6 +1281,11 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   p.partial_out = a->partial_out;
   p.partial_lse = a->partial_lse;
   p.error_word = a->error_word;
+  // With a counter array and an output, a split launch merges its own partials.
+  const bool merges = !writes_out && a->merge_counters != nullptr && a->out != nullptr;
+  if (merges && a->out_row_stride < (int64_t)a->heads_q * kHeadDim) return BDFP4_E_ARG;
+  p.merge_counters = merges ? a->merge_counters : nullptr;
+  p.merged_out = merges ? static_cast<__nv_bfloat16*>(a->out) : nullptr;
 
   const bool two = a->query_codes_second != nullptr;
   cudaError_t e;

@@ -399,10 +399,13 @@ def decode_fp4_split(
     query_padded_bf16=None, residual_key_pages_bf16=None, residual_value_pages_bf16=None,
     residual_page_ids=None, seqused_residual=None, seqused_sink=None, has_bf16=None, out=None,
     split_partial_scratch=None, split_lse_scratch=None, scale_format: str = "nvfp4",
+    split_merge_counters=None,
 ):
     """Split-KV decode: ``num_splits`` CTAs per (row, KV head) write FP32 partials and LSEs,
-    then one combine launch produces the BF16 output. Arguments are assumed validated by
-    ``decode_fp4(validate_only=True)``. Supplied scratch makes the call allocation-free."""
+    then one combine launch produces the BF16 output, or, given ``split_merge_counters`` (INT32,
+    at least ``rows * heads_kv`` zeros), the last CTA of each (row, KV head) merges them itself.
+    Arguments are assumed validated by ``decode_fp4(validate_only=True)``. Supplied scratch makes
+    the call allocation-free."""
     device = query_fp4.device
     rows, _, heads_q, _ = query_fp4.shape
     page_count, _, heads_kv, _ = key_pages_fp4.shape
@@ -451,6 +454,20 @@ def decode_fp4_split(
     a.bf16_page_cost = BF16_BLOCK_PAGE_COST if has_residual and parts == num_splits else 0
     a.partial_out, a.partial_lse = partial.data_ptr(), lse.data_ptr()
     stream = bdfp4.current_stream(device)
+    if split_merge_counters is not None:
+        if (
+            split_merge_counters.dtype is not torch.int32
+            or split_merge_counters.device != device
+            or not split_merge_counters.is_contiguous()
+            or split_merge_counters.numel() < rows * heads_kv
+        ):
+            raise ValueError(
+                f"split_merge_counters must be a contiguous INT32 buffer of at least {rows * heads_kv} zeros"
+            )
+        a.out, a.out_row_stride = out.data_ptr(), out.stride(0)
+        a.merge_counters = split_merge_counters.data_ptr()
+        bdfp4.decode(a, stream)
+        return out[:rows]
     bdfp4.decode(a, stream)
     bdfp4.combine(partial, lse, parts, rows, heads_q, out, out.stride(0), stream)
     return out[:rows]

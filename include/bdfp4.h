@@ -255,6 +255,13 @@ typedef struct bdfp4_decode_args {
   int32_t bf16_page_cost;
   /* Tokens per cache page: 0 or 128 (the reference's only size), or 64 (see "64-token pages"). */
   int32_t page_tokens;
+  /* Fused split merge, no reference counterpart (the reference always launches SplitKCombine,
+   * src/nvfp4_decode_kernel/split_k_combine.py:86-133). With num_splits > 1, `out` set and this
+   * pointer non-NULL, the part of each (row, KV head) that finishes last merges the partials into
+   * `out` itself, with the arithmetic and part order of bdfp4_combine; no merge launch is needed.
+   * int32 [rows * heads_kv], zero before the first launch; every launch leaves it zero. Launches
+   * that share the array must not overlap on the GPU. */
+  int32_t* merge_counters;
 } bdfp4_decode_args;
 
 int bdfp4_decode(const bdfp4_decode_args* args, void* stream);

@@ -190,6 +190,26 @@ def test_decode_split_kv_shared_bf16_split(cost, monkeypatch):
     _check(out, want, f"shared bf16 split, cost {cost}")
 
 
+@pytest.mark.parametrize("rows,num_splits,page_tokens", [(3, 4, 128), (80, 2, 128), (5, 3, 64)])
+def test_decode_fused_split_merge(rows, num_splits, page_tokens):
+    """With a counter array the split launch merges its own partials: bit-identical to the separate
+    merge kernel (same arithmetic, same part order), counters back at zero, repeatable."""
+    from bdfp4.workload import build_workload
+
+    lengths = [150 + 211 * (i % 9) + (1900 if i % 5 == 0 else 0) for i in range(rows)]
+    w = build_workload(rows=rows, heads_q=8, heads_kv=2, seq_lens=lengths, sink_tokens=16, seed=rows,
+                       page_tokens=page_tokens)
+    want = _decode(w, terms=2, num_splits=num_splits).clone()
+    counters = torch.zeros(rows * 2 + 7, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        out = torch.full((rows, 8, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        got = _decode(w, terms=2, num_splits=num_splits, split_merge_counters=counters, out=out)
+        assert torch.equal(got, want)
+        assert int(counters.abs().sum()) == 0
+    with pytest.raises(ValueError):
+        _decode(w, terms=2, num_splits=num_splits, split_merge_counters=counters[:rows])
+
+
 def test_decode_caller_buffers_and_error_word():
     """Caller-owned output and scratch; nothing else is written."""
     from bdfp4.workload import build_workload
