@@ -251,11 +251,12 @@ def run_ours(args) -> None:
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    if HEADS_KV % world:
-        raise SystemExit(f"{HEADS_KV} KV heads do not partition over {world} ranks")
-    heads_kv = HEADS_KV // world
+    total_heads_kv = args.heads_kv or HEADS_KV
+    if total_heads_kv % world or HEADS_Q % total_heads_kv:
+        raise SystemExit(f"{total_heads_kv} KV heads do not partition over {world} ranks / {HEADS_Q} query heads")
+    heads_kv = total_heads_kv // world
     heads_q = HEADS_Q // world
-    rows, context = BATCH, args.context
+    rows, context = args.batch or BATCH, args.context
 
     w = build_workload(rows=rows, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[context] * rows,
                        sink_tokens=SINK_ROWS, seed=1000 + rank, device=device, key_scale_mode="four_six",
@@ -481,8 +482,9 @@ def run_ours(args) -> None:
             "data": "synthetic",
             "config": {
                 "workload": WORKLOAD_NAME.format(page=page_tokens) + (
-                    "" if context == CONTEXT else f" [context overridden: {context}]"),
-                "partition": f"{heads_kv} of {HEADS_KV} KV heads per rank, no collective",
+                    "" if (context, rows, total_heads_kv) == (CONTEXT, BATCH, HEADS_KV)
+                    else f" [shape overridden: batch {rows}, {total_heads_kv} KV heads, context {context}]"),
+                "partition": f"{heads_kv} of {total_heads_kv} KV heads per rank, no collective",
                 "sink_tokens": SINK_USED, "recent_tokens": 128, "num_splits": splits,
                 "query": "two NVFP4 terms, Hadamard", "key_scale_mode": "four_six", "p_scale_mode": "amax2_or_amax6_c8",
                 "l2": "inputs (4.8 GB per step over all ranks) exceed the 126 MB L2; no flush needed",
@@ -514,6 +516,8 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--context", type=int, default=CONTEXT, help="override the context length (profiling only)")
+    parser.add_argument("--batch", type=int, default=0, help="override the batch (profiling only)")
+    parser.add_argument("--heads-kv", type=int, default=0, help="override the KV head count (profiling only)")
     parser.add_argument("--splits", type=int, default=0, help="override the split-KV count")
     parser.add_argument("--bf16-cost", type=int, default=-1,
                         help="pages split 0 is charged for the tail and sink (default: the library's)")
