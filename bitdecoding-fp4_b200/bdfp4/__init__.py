@@ -109,6 +109,7 @@ class DecodeArgs(Structure):
         ("bf16_page_cost", c_int32),
         ("page_tokens", c_int32),
         ("merge_counters", c_void_p),
+        ("row_order", c_void_p),
     ]
 
 

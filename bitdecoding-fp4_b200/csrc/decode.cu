@@ -79,6 +79,7 @@ struct DecodeParams {
   // fused merge: the last part of a (row, KV head) tile to finish writes the BF16 output
   int32_t* merge_counters;
   __nv_bfloat16* merged_out;
+  const int32_t* row_order;  // launch position -> row (longest rows first), or null
 };
 
 template <int GP, int STAGES>
@@ -379,7 +380,10 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   int part = blockIdx.x / tiles;
   if (p.bf16_split) part = (part + p.num_splits) % p.parts;
   const int kv_head = (blockIdx.x % tiles) % p.heads_kv;
-  const int row = (blockIdx.x % tiles) / p.heads_kv;
+  const int launch_row = (blockIdx.x % tiles) / p.heads_kv;
+  // CTAs are handed to SMs in launch order; with a ragged batch the caller lists the rows
+  // longest first, so that the longest walks start first and the short ones fill the gaps
+  const int row = p.row_order ? min(max(p.row_order[launch_row], 0), p.rows - 1) : launch_row;
   const int G = p.ratio;
   // A "page" below is one 128-token step of the walk: one cache page, or with 64-token pages
   // (PT = 64) two consecutive entries of the row's page table.
@@ -1286,6 +1290,7 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   if (merges && a->out_row_stride < (int64_t)a->heads_q * kHeadDim) return BDFP4_E_ARG;
   p.merge_counters = merges ? a->merge_counters : nullptr;
   p.merged_out = merges ? static_cast<__nv_bfloat16*>(a->out) : nullptr;
+  p.row_order = a->row_order;
 
   const bool two = a->query_codes_second != nullptr;
   cudaError_t e;

@@ -106,7 +106,7 @@ def _validate(
     *, query_fp4, query_scales, query_fp4_second, query_scales_second, query_padded_bf16,
     key_pages_fp4, key_scales, value_pages_fp4, value_scales, fp4_page_table, seqused_fp4,
     residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids, seqused_residual,
-    seqused_sink, has_bf16, softmax_scale, out, out_indices, trusted_metadata, scale_format,
+    seqused_sink, has_bf16, softmax_scale, out, out_indices, trusted_metadata, scale_format, row_order=None,
 ):
     """Every host-side contract check of the decode entry; returns the derived geometry."""
     if scale_format != "nvfp4":
@@ -319,6 +319,13 @@ def _validate(
             raise ValueError("out must be BF16 [>= rows, heads_q, 128], dense within a row")
     if out_indices is not None:
         raise NotImplementedError("out_indices (scattered output rows) is not built")
+    if row_order is not None:
+        _require_cuda_tensor(row_order, "row_order", device=device)
+        if row_order.dtype is not torch.int32 or tuple(row_order.shape) != (rows,) or not row_order.is_contiguous():
+            raise ValueError("row_order must be contiguous INT32 with shape [rows]")
+        if not trusted_metadata:
+            _check_device_values(torch.sort(row_order).values != torch.arange(rows, device=device),
+                                 "row_order must be a permutation of the rows")
     return device, rows, heads_q, heads_kv, page_count, has_residual
 
 
@@ -326,7 +333,7 @@ def _fill_args(
     a: "bdfp4.DecodeArgs", *, rows, heads_q, heads_kv, page_count, query_fp4, query_scales, query_fp4_second,
     query_scales_second, query_padded_bf16, key_pages_fp4, key_scales, value_pages_fp4, value_scales,
     fp4_page_table, seqused_fp4, residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids,
-    seqused_residual, seqused_sink, softmax_scale,
+    seqused_residual, seqused_sink, softmax_scale, row_order=None,
 ) -> None:
     a.rows, a.heads_q, a.heads_kv = rows, heads_q, heads_kv
     a.query_codes, a.query_scales = query_fp4.data_ptr(), query_scales.data_ptr()
@@ -351,6 +358,7 @@ def _fill_args(
         a.seqused_sink = bdfp4.ptr(seqused_sink)
     a.softmax_scale = float(softmax_scale)
     a.p_scale_mode, a.p_scale_tau = _p_scale_arguments()
+    a.row_order = bdfp4.ptr(row_order)
 
 
 def decode_fp4(
@@ -359,7 +367,7 @@ def decode_fp4(
     residual_key_pages_bf16=None, residual_value_pages_bf16=None, residual_page_ids=None,
     seqused_residual=None, seqused_sink=None, has_bf16=None, softmax_scale: float, out=None,
     out_indices=None, trusted_metadata: bool = False, validate_only: bool = False,
-    scale_format: str = "nvfp4",
+    scale_format: str = "nvfp4", row_order=None,
 ):
     """Validate and launch the unsplit decode; returns BF16 ``[rows, heads_q, 128]`` (a view of
     ``out[:rows]`` when given), or None under ``validate_only``."""
@@ -371,7 +379,7 @@ def decode_fp4(
         residual_key_pages_bf16=residual_key_pages_bf16, residual_value_pages_bf16=residual_value_pages_bf16,
         residual_page_ids=residual_page_ids, seqused_residual=seqused_residual, seqused_sink=seqused_sink,
         has_bf16=has_bf16, softmax_scale=softmax_scale, out=out, out_indices=out_indices,
-        trusted_metadata=trusted_metadata, scale_format=scale_format,
+        trusted_metadata=trusted_metadata, scale_format=scale_format, row_order=row_order,
     )
     if validate_only:
         return None
@@ -386,6 +394,7 @@ def decode_fp4(
         seqused_fp4=seqused_fp4, residual_key_pages_bf16=residual_key_pages_bf16,
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, seqused_sink=seqused_sink, softmax_scale=softmax_scale,
+        row_order=row_order,
     )
     a.out, a.out_row_stride = out.data_ptr(), out.stride(0)
     a.num_splits = 1
@@ -399,7 +408,7 @@ def decode_fp4_split(
     query_padded_bf16=None, residual_key_pages_bf16=None, residual_value_pages_bf16=None,
     residual_page_ids=None, seqused_residual=None, seqused_sink=None, has_bf16=None, out=None,
     split_partial_scratch=None, split_lse_scratch=None, scale_format: str = "nvfp4",
-    split_merge_counters=None,
+    split_merge_counters=None, row_order=None,
 ):
     """Split-KV decode: ``num_splits`` CTAs per (row, KV head) write FP32 partials and LSEs,
     then one combine launch produces the BF16 output, or, given ``split_merge_counters`` (INT32,
@@ -448,6 +457,7 @@ def decode_fp4_split(
         seqused_fp4=seqused_fp4, residual_key_pages_bf16=residual_key_pages_bf16,
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, seqused_sink=seqused_sink, softmax_scale=softmax_scale,
+        row_order=row_order,
     )
     a.num_splits = num_splits
     a.bf16_split = int(parts > num_splits)

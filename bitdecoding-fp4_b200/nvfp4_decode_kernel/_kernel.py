@@ -60,7 +60,7 @@ def fp4_decode_impl(
     query_fp4_scratch=None, query_scales_scratch=None, query_fp4_second_scratch=None,
     query_scales_second_scratch=None, split_partial_scratch=None, split_lse_scratch=None, query_terms=1,
     scale_mode=DEFAULT_SCALE_MODE, query_rotation="none", tail_write: DecodeTailWrite | None = None,
-    split_merge_counters=None,
+    split_merge_counters=None, row_order=None,
 ):
     from ._decode import decode_fp4, decode_fp4_split
     from ._quantize import quantize_query
@@ -156,7 +156,7 @@ def fp4_decode_impl(
         value_scales=value_scales, fp4_page_table=fp4_page_table, seqused_fp4=seqused_fp4,
         residual_key_pages_bf16=residual_key_pages_bf16, residual_value_pages_bf16=residual_value_pages_bf16,
         residual_page_ids=residual_page_ids, seqused_residual=seqused_residual, seqused_sink=seqused_sink,
-        has_bf16=has_bf16, softmax_scale=softmax_scale, out=out, scale_format=fmt,
+        has_bf16=has_bf16, softmax_scale=softmax_scale, out=out, scale_format=fmt, row_order=row_order,
     )
     if num_splits > 1:
         decode_fp4(**common, out_indices=out_indices, trusted_metadata=trusted_metadata, validate_only=True)

@@ -123,8 +123,14 @@ class NVFP4MetadataBuilder(FlashAttentionMetadataBuilder):
         if decode_tokens:
             query_start_loc = query_start_loc[decode_rows:] - decode_tokens
         _, max_fp4, _ = split_sequence_length(common_attn_metadata.max_seq_len)
+        splits = decode_num_splits(decode_rows, self.num_kv_heads, self.sms)
+        # A decode batch wider than the GPU holds at once (four CTAs per SM) is launched longest
+        # row first; a resident one starts every CTA at once and needs no order.
+        row_order = None
+        if decode_rows * self.num_kv_heads * (splits + 1) > 4 * self.sms:
+            row_order = torch.argsort(outputs.seqused_fp4[:decode_rows], descending=True).to(torch.int32)
         return NVFP4Metadata.from_flash(
             base, outputs, source_tokens=source_tokens, destination_pages=destination_pages,
             decode_prefix_rows=decode_rows, decode_prefix_tokens=decode_tokens,
             prefill_query_start_loc=query_start_loc, decode_page_columns=max(1, max_fp4 // PAGE_SIZE),
-            decode_num_splits=decode_num_splits(decode_rows, self.num_kv_heads, self.sms))
+            decode_num_splits=splits, decode_row_order=row_order)

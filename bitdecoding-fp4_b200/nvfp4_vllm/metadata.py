@@ -31,11 +31,15 @@ class NVFP4Metadata(FlashAttentionMetadata):
     decode_num_splits: int  # split-KV count, chosen from the decode row count alone
     source_tokens: torch.Tensor  # [work] int32: first token of each full page to quantize
     destination_pages: torch.Tensor  # [work] int32: its block, -1 where the grid slot has no work
+    # [decode rows] int32, the decode rows longest first (launch order of a batch too wide to be
+    # resident at once), or None; not a field of the reference's metadata
+    decode_row_order: torch.Tensor | None = None
 
     @classmethod
     def from_flash(cls, base: FlashAttentionMetadata, outputs: ControlOutputs, *, source_tokens, destination_pages,
                    decode_prefix_rows: int, decode_prefix_tokens: int, prefill_query_start_loc,
-                   decode_page_columns: int, decode_num_splits: int) -> "NVFP4Metadata":
+                   decode_page_columns: int, decode_num_splits: int,
+                   decode_row_order: torch.Tensor | None = None) -> "NVFP4Metadata":
         """Copy every FlashAttention field (the base object is shared by every layer) and append
         the slot fields."""
         return cls(
@@ -47,4 +51,5 @@ class NVFP4Metadata(FlashAttentionMetadata):
             decode_prefix_rows=decode_prefix_rows, decode_prefix_tokens=decode_prefix_tokens,
             prefill_query_start_loc=prefill_query_start_loc, decode_page_columns=decode_page_columns,
             decode_num_splits=decode_num_splits, source_tokens=source_tokens, destination_pages=destination_pages,
+            decode_row_order=decode_row_order,
         )

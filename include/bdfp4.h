@@ -262,6 +262,12 @@ typedef struct bdfp4_decode_args {
    * int32 [rows * heads_kv], zero before the first launch; every launch leaves it zero. Launches
    * that share the array must not overlap on the GPU. */
   int32_t* merge_counters;
+  /* Launch order of the rows, no reference counterpart: int32 [rows], a permutation of 0..rows-1
+   * (device memory); position i of the launch serves row row_order[i]. A caller with a ragged batch
+   * lists the rows longest first: CTAs reach the SMs in launch order, so the longest walks start
+   * first and the short ones fill in behind them. NULL: rows in index order. The result does not
+   * depend on it. */
+  const int32_t* row_order;
 } bdfp4_decode_args;
 
 int bdfp4_decode(const bdfp4_decode_args* args, void* stream);

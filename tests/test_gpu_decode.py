@@ -210,6 +210,23 @@ def test_decode_fused_split_merge(rows, num_splits, page_tokens):
         _decode(w, terms=2, num_splits=num_splits, split_merge_counters=counters[:rows])
 
 
+def test_decode_row_order_changes_nothing():
+    """A launch order (longest rows first) never changes the result; a non-permutation is refused
+    unless the metadata is trusted."""
+    from bdfp4.workload import build_workload
+
+    lengths = [200, 3000, 129, 1500, 64, 2600, 900]
+    w = build_workload(rows=len(lengths), heads_q=8, heads_kv=2, seq_lens=lengths, sink_tokens=16, seed=23)
+    want = _decode(w, terms=2)
+    order = torch.argsort(w.seqused_fp4, descending=True).to(torch.int32)
+    assert torch.equal(_decode(w, terms=2, row_order=order), want)
+    assert torch.equal(_decode(w, terms=2, num_splits=3, row_order=order), _decode(w, terms=2, num_splits=3))
+    with pytest.raises(ValueError):
+        _decode(w, terms=2, row_order=torch.zeros_like(order))
+    with pytest.raises(ValueError):
+        _decode(w, terms=2, row_order=order[:-1].contiguous())
+
+
 def test_decode_caller_buffers_and_error_word():
     """Caller-owned output and scratch; nothing else is written."""
     from bdfp4.workload import build_workload
