@@ -251,11 +251,11 @@ def run_ours(args) -> None:
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    total_heads_kv = args.heads_kv or HEADS_KV
-    if total_heads_kv % world or HEADS_Q % total_heads_kv:
-        raise SystemExit(f"{total_heads_kv} KV heads do not partition over {world} ranks / {HEADS_Q} query heads")
+    total_heads_kv, total_heads_q = args.heads_kv or HEADS_KV, args.heads_q or HEADS_Q
+    if total_heads_kv % world or total_heads_q % total_heads_kv:
+        raise SystemExit(f"{total_heads_kv} KV heads do not partition over {world} ranks / {total_heads_q} query heads")
     heads_kv = total_heads_kv // world
-    heads_q = HEADS_Q // world
+    heads_q = total_heads_q // world
     rows, context = args.batch or BATCH, args.context
 
     w = build_workload(rows=rows, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[context] * rows,
@@ -482,8 +482,8 @@ def run_ours(args) -> None:
             "data": "synthetic",
             "config": {
                 "workload": WORKLOAD_NAME.format(page=page_tokens) + (
-                    "" if (context, rows, total_heads_kv) == (CONTEXT, BATCH, HEADS_KV)
-                    else f" [shape overridden: batch {rows}, {total_heads_kv} KV heads, context {context}]"),
+                    "" if (context, rows, total_heads_kv, total_heads_q) == (CONTEXT, BATCH, HEADS_KV, HEADS_Q)
+                    else f" [shape overridden: batch {rows}, {total_heads_q}q/{total_heads_kv}kv heads, context {context}]"),
                 "partition": f"{heads_kv} of {total_heads_kv} KV heads per rank, no collective",
                 "sink_tokens": SINK_USED, "recent_tokens": 128, "num_splits": splits,
                 "query": "two NVFP4 terms, Hadamard", "key_scale_mode": "four_six", "p_scale_mode": "amax2_or_amax6_c8",
@@ -518,6 +518,7 @@ def main() -> None:
     parser.add_argument("--context", type=int, default=CONTEXT, help="override the context length (profiling only)")
     parser.add_argument("--batch", type=int, default=0, help="override the batch (profiling only)")
     parser.add_argument("--heads-kv", type=int, default=0, help="override the KV head count (profiling only)")
+    parser.add_argument("--heads-q", type=int, default=0, help="override the query head count (profiling only)")
     parser.add_argument("--splits", type=int, default=0, help="override the split-KV count")
     parser.add_argument("--bf16-cost", type=int, default=-1,
                         help="pages split 0 is charged for the tail and sink (default: the library's)")

@@ -285,6 +285,14 @@ __device__ __forceinline__ void hadamard_butterflies(float* v, int group) {
 
 constexpr float kInvSqrt128 = 0.08838834764831845f;  // fl32(1/sqrt(128))
 
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute
+// may start while the kernel before it in the stream is still running, once that kernel has called
+// dependents_may_launch() in every CTA (or finished); what it reads or writes of that kernel's
+// data must come after wait_for_prior_kernels(), which returns when the earlier kernels have
+// completed and their writes are visible. Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_prior_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Byte offset of (row, group) inside one head's 1024-byte scale tile.
 __host__ __device__ __forceinline__ int scale_tile_offset(int row, int group) {
   return (group >> 2) * 512 + (row & 31) * 16 + (row >> 5) * 4 + (group & 3);

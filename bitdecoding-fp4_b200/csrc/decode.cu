@@ -451,34 +451,6 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     tc::prefetch_tensormap(&k_map);
     tc::prefetch_tensormap(&v_map);
   }
-  // Warps 1-5 fetch the query operands into registers first, so that their load latency overlaps
-  // the zero fill, the barrier and warp 0's page-table read: one 16-byte chunk of query codes,
-  // one word of query scales and up to two 16-byte chunks of the BF16 query per thread.
-  const int qt = tid - 32;
-  const bool loads_codes = qt >= 0 && qt < TERMS * G * 4;
-  const bool loads_scales = qt >= 0 && qt < TERMS * G * 2;
-  uint4 code_chunk = make_uint4(0, 0, 0, 0);
-  uint32_t scale_word = 0;
-  uint4 bf16_chunk[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-  if (loads_codes) {
-    const int g = (qt >> 2) % G, term = (qt >> 2) / G;
-    code_chunk = __ldg(reinterpret_cast<const uint4*>(p.q_codes[term] +
-                                                      ((int64_t)row * p.heads_q + kv_head * G + g) * 64) + (qt & 3));
-  }
-  if (loads_scales) {
-    const int g = (qt >> 1) % G, term = (qt >> 1) / G;
-    scale_word = __ldg(reinterpret_cast<const uint32_t*>(
-        p.q_scales[term] + ((int64_t)row * p.heads_q + kv_head) * 1024 + (qt & 1) * 512 + g * 16));
-  }
-  if (with_bf16 && qt >= 0) {
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int i = qt + 160 * k;  // 16-byte chunk: head i / 16, channels 8 * (i % 16) ...
-      if (i < G * 16)
-        bf16_chunk[k] = __ldg(reinterpret_cast<const uint4*>(
-            p.q_padded + (((int64_t)row * kPage) * p.heads_q + kv_head * G + (i >> 4)) * kHeadDim + (i & 15) * 8));
-    }
-  }
   // zero the Q tiles, P tiles, both scale-atom buffers (contiguous 1 KB blocks) and the BF16 query
   {
     uint4* blocks[4] = {reinterpret_cast<uint4*>(sm.q_tile), reinterpret_cast<uint4*>(sm.p_tile),
@@ -549,6 +521,39 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         request_key(j, page, page_b);
         request_value(j, page, page_b);
       }
+    }
+  }
+  // Everything up to here reads only the cache and the batch's metadata. The query operands and
+  // the BF16 tail come from the launch before this one (the query quantizer): with programmatic
+  // dependent launch this kernel may have started while that one was still running, so wait for
+  // it here, then let the launch after this one start its own preamble.
+  wait_for_prior_kernels();
+  dependents_may_launch();
+  // Warps 1-5 fetch the query operands: one 16-byte chunk of query codes, one word of query
+  // scales and up to two 16-byte chunks of the BF16 query per thread.
+  const int qt = tid - 32;
+  const bool loads_codes = qt >= 0 && qt < TERMS * G * 4;
+  const bool loads_scales = qt >= 0 && qt < TERMS * G * 2;
+  uint4 code_chunk = make_uint4(0, 0, 0, 0);
+  uint32_t scale_word = 0;
+  uint4 bf16_chunk[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  if (loads_codes) {
+    const int g = (qt >> 2) % G, term = (qt >> 2) / G;
+    code_chunk = __ldg(reinterpret_cast<const uint4*>(p.q_codes[term] +
+                                                      ((int64_t)row * p.heads_q + kv_head * G + g) * 64) + (qt & 3));
+  }
+  if (loads_scales) {
+    const int g = (qt >> 1) % G, term = (qt >> 1) / G;
+    scale_word = __ldg(reinterpret_cast<const uint32_t*>(
+        p.q_scales[term] + ((int64_t)row * p.heads_q + kv_head) * 1024 + (qt & 1) * 512 + g * 16));
+  }
+  if (with_bf16 && qt >= 0) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = qt + 160 * k;  // 16-byte chunk: head i / 16, channels 8 * (i % 16) ...
+      if (i < G * 16)
+        bf16_chunk[k] = __ldg(reinterpret_cast<const uint4*>(
+            p.q_padded + (((int64_t)row * kPage) * p.heads_q + kv_head * G + (i >> 4)) * kHeadDim + (i & 15) * 8));
     }
   }
   if (loads_codes) {
@@ -1141,8 +1146,20 @@ static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensor
     configured = true;
   }
   const int grid = p.rows * p.heads_kv * p.parts;
-  decode_kernel<GP, TERMS, STAGES, PT><<<grid, 192, smem, stream>>>(k_map, v_map, p);
-  return cudaGetLastError();
+  // Programmatic stream serialization: after the query quantizer (which signals early) the CTAs
+  // come up, set up and request their first cache pages while it still runs; after any other kernel
+  // the launch starts when that kernel has finished, as an ordinary launch would.
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(192);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, decode_kernel<GP, TERMS, STAGES, PT>, k_map, v_map, p);
 }
 
 // Ring depth follows the grid: a launch with more than two CTAs per SM is given two K and two V

@@ -396,6 +396,13 @@ template <bool ROTATE, bool SECOND, bool TAIL, bool ROTATE_KEY, bool SHIFT_KEY>
 __global__ void __launch_bounds__(128) quantize_query_kernel(const QueryParams p) {
   const int row = blockIdx.x;
   const int chunk = blockIdx.y;
+  // First the kernels before this one must be over (their results visible): the buffers written
+  // here may still be read by the previous decode launch, and whatever starts early behind this
+  // kernel reads the cache those kernels may have written. Then the decode launch that follows may
+  // bring its CTAs up and request its first cache pages while this kernel runs; it waits for this
+  // kernel's end before it reads the query or the tail.
+  wait_for_prior_kernels();
+  dependents_may_launch();
   if (TAIL && chunk >= p.query_chunks) {
     const int position = p.seq_lens[row] - 1;
     write_tail_token<SHIFT_KEY ? BDFP4_SHIFT_F32 : BDFP4_SHIFT_NONE, ROTATE_KEY>(
@@ -431,21 +438,33 @@ __global__ void __launch_bounds__(128) quantize_query_kernel(const QueryParams p
   }
 }
 
+// Launched with programmatic stream serialization: after a decode launch of this library (which
+// signals early) its CTAs are resident by the time that kernel ends; after anything else it starts
+// when that kernel has finished, as an ordinary launch would.
+template <typename Kernel>
+static cudaError_t launch_overlapped(Kernel kernel, dim3 grid, const QueryParams& p, cudaStream_t stream) {
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = dim3(128);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, p);
+}
+
 template <bool ROTATE, bool SECOND>
 static cudaError_t launch_query(const QueryParams& p, dim3 grid, bool tail, bool rotate_key, bool shift_key,
                                 cudaStream_t stream) {
-  if (!tail) {
-    quantize_query_kernel<ROTATE, SECOND, false, false, false><<<grid, 128, 0, stream>>>(p);
-  } else if (rotate_key && shift_key) {
-    quantize_query_kernel<ROTATE, SECOND, true, true, true><<<grid, 128, 0, stream>>>(p);
-  } else if (rotate_key) {
-    quantize_query_kernel<ROTATE, SECOND, true, true, false><<<grid, 128, 0, stream>>>(p);
-  } else if (shift_key) {
-    quantize_query_kernel<ROTATE, SECOND, true, false, true><<<grid, 128, 0, stream>>>(p);
-  } else {
-    quantize_query_kernel<ROTATE, SECOND, true, false, false><<<grid, 128, 0, stream>>>(p);
-  }
-  return cudaGetLastError();
+  if (!tail) return launch_overlapped(quantize_query_kernel<ROTATE, SECOND, false, false, false>, grid, p, stream);
+  if (rotate_key && shift_key)
+    return launch_overlapped(quantize_query_kernel<ROTATE, SECOND, true, true, true>, grid, p, stream);
+  if (rotate_key) return launch_overlapped(quantize_query_kernel<ROTATE, SECOND, true, true, false>, grid, p, stream);
+  if (shift_key) return launch_overlapped(quantize_query_kernel<ROTATE, SECOND, true, false, true>, grid, p, stream);
+  return launch_overlapped(quantize_query_kernel<ROTATE, SECOND, true, false, false>, grid, p, stream);
 }
 
 }  // namespace bdfp4
