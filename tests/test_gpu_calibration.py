@@ -124,3 +124,47 @@ def test_runtime_measures_the_key_mean(rotation):
         assert runtime.active_key_shift.dtype is torch.float32
     assert runtime.key_shift_sum is None and runtime.key_shift_enabled
     runtime.measure_keys(0, key, 1)  # a no-op once the measurement is over
+
+
+def test_probability_calibration_collector_end_to_end():
+    """The collector's hook on a stand-in attention layer: BF16 Q/K of one unchunked prefill in,
+    per-position per-code error sums out, and a threshold fitted from them. The scores go through
+    the CUDA statistic; the oracle gives the same fit."""
+    pytest.importorskip("vllm")
+    import types
+
+    from nvfp4_vllm.probability_calibration import ProbabilityCalibration, fit_probability_threshold
+
+    tokens, heads, kv_heads, dim = 640, 8, 2, 128
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    query = (2.5 * torch.randn(tokens + 7, heads * dim, generator=gen, device="cuda")).to(torch.bfloat16)
+    key = (2.5 * torch.randn(tokens + 7, kv_heads * dim, generator=gen, device="cuda")).to(torch.bfloat16)
+    module = types.SimpleNamespace(num_heads=heads, num_kv_heads=kv_heads, head_size=dim)
+    collector = ProbabilityCalibration(tokens, 8.0, samples=3)
+    collector.expected_layers = 1
+    collector.observe(module, (query, key), {})
+    with pytest.raises(RuntimeError):
+        collector.observe(module, (query, key), {})  # one prefill per layer
+    samples = collector.finish()
+    assert [s["position"] for s in samples] == collector.positions == [128, 383, 639]
+    for sample in samples:
+        groups = heads * (sample["position"] // 128) * 128 // 16
+        assert sum(bucket["groups"] for bucket in sample["codes"].values()) == groups
+    report = fit_probability_threshold([samples], 8.0)
+
+    # the same samples from the CPU oracle
+    q = query[:tokens].float().cpu().reshape(tokens, kv_heads, heads // kv_heads, dim)
+    k = key[:tokens].float().cpu().reshape(tokens, kv_heads, dim)
+    want = []
+    for position in collector.positions:
+        scores = torch.einsum("hrd,thd->hrt", q[position], k[:position + 1]).reshape(heads, position + 1)
+        stats = calibration_oracle.probability_scale_statistics(scores, fp4_tokens=(position // 128) * 128, head_dim=dim,
+                                                                probability_multiplier=8.0)
+        want.append({"position": position, "codes": {
+            code: {"groups": b["groups"], "error_sum": {"6": b["error_sum"][0], "2": b["error_sum"][3]}}
+            for code, b in stats.items()}})
+    expected = fit_probability_threshold([want], 8.0)
+    assert report["tau"] == expected["tau"] and report["groups"] == expected["groups"]
+    assert math.isclose(report["squared_error"], expected["squared_error"], rel_tol=1e-3)
+    with pytest.raises(ValueError):
+        ProbabilityCalibration(tokens, 8.0, samples=3).observe(module, (query[:100], key[:100]), {})

@@ -273,3 +273,66 @@ def test_plain_attention_distance_reported():
         errs.append(((out[0, 4 * h:4 * h + 4] - want).abs().mean() / want.abs().mean()).item())
     print(f"mean-rel distance to plain dequantise-then-attend: {max(errs):.3e}")
     assert max(errs) < 0.3
+
+
+def test_decode_is_cuda_graph_capturable():
+    """With caller-owned scratch the whole call (query quantizer, decode, split merge) allocates
+    and synchronises nothing, so it captures into a CUDA graph; a replay follows changed inputs."""
+    from bdfp4.workload import build_workload
+    from nvfp4_decode_kernel import DecodeTailWrite, fp4_decode, split_partial_count
+
+    rows, hq, hkv = 4, 8, 2
+    w = build_workload(rows=rows, heads_q=hq, heads_kv=hkv, seq_lens=[700, 129, 2048, 400], sink_tokens=16, seed=31,
+                       key_scale_mode="four_six", rotate=True, page_tokens=64)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    parts = split_partial_count(rows, hkv, 3, residual=True, sms=sms)
+    scratch = dict(
+        query_padded_scratch=torch.zeros(rows, 128, hq, 128, dtype=torch.bfloat16, device="cuda"),
+        query_fp4_scratch=torch.zeros(rows, 1, hq, 64, dtype=torch.uint8, device="cuda"),
+        query_scales_scratch=torch.zeros(rows, 1, hq, 2, 32, 4, 4, dtype=torch.uint8, device="cuda"),
+        query_fp4_second_scratch=torch.zeros(rows, 1, hq, 64, dtype=torch.uint8, device="cuda"),
+        query_scales_second_scratch=torch.zeros(rows, 1, hq, 2, 32, 4, 4, dtype=torch.uint8, device="cuda"),
+        split_partial_scratch=torch.empty(parts * rows * hq * 128, device="cuda"),
+        split_lse_scratch=torch.empty(parts * rows * hq, device="cuda"),
+        split_merge_counters=torch.zeros(rows * hkv, dtype=torch.int32, device="cuda"),
+    )
+    query = w.query.clone()
+    new_key = torch.zeros(rows, hkv, 128, dtype=torch.bfloat16, device="cuda")
+    new_value = torch.zeros_like(new_key)
+    seq_lens = torch.tensor(w.seq_lens, dtype=torch.int32, device="cuda")
+    out = torch.empty(rows, hq, 128, dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        tail = DecodeTailWrite(new_key, new_value, w.tail_key[0], w.tail_value[0], w.slot_ids, seq_lens, w.seqused_fp4,
+                               True, None, 16)
+        return fp4_decode(
+            query, *w.regions, w.page_table, w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
+            residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
+            seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, out=out, trusted_metadata=True,
+            num_splits=3, query_terms=2, query_rotation="hadamard", tail_write=tail, **scratch)
+
+    gen = torch.Generator(device="cuda").manual_seed(1)
+
+    def fresh_inputs():
+        query.copy_(torch.randn(rows, hq, 128, generator=gen, device="cuda").to(torch.bfloat16))
+        new_key.copy_(torch.randn(rows, hkv, 128, generator=gen, device="cuda").to(torch.bfloat16))
+        new_value.copy_(torch.randn(rows, hkv, 128, generator=gen, device="cuda").to(torch.bfloat16))
+
+    fresh_inputs()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()  # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(2):
+        fresh_inputs()
+        graph.replay()
+        replayed = out.clone()
+        eager = step().clone()
+        assert torch.equal(replayed, eager)
+    assert torch.cuda.memory_allocated() - before < (1 << 20)  # the capture held no sizeable allocation
