@@ -95,6 +95,10 @@ struct DecodeSmem {
   float p_bf16[GP][128];  // BF16-rounded probabilities of a tail/sink block
   float red[2][4][GP];
   float sum_red[4][GP];
+  // the rows' running maxima and the two values derived from them: identical in every softmax
+  // thread, so with eight or more rows per thread they live here instead of in registers
+  float stat_row_max[GP], stat_threshold[GP], stat_max_scaled[GP];
+  float stat_acc[2][GP];  // rescale factors of the last two steps that moved a maximum
   uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   uint64_t ksf_full[kStages];  // K scale blocks of 64-token pages, which arrive ahead of the codes
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2];
@@ -773,9 +777,13 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       bf16_block<GP, STAGES>(st, sm, p, t, warp_q, lane, tail_k, tail_v, mask_below, tail_len, shift, red_buf);
     }
 
+    // factor the sums accumulated before the previous step are multiplied by when its O^T is folded
+    // in: 1 unless that step moved a maximum. Parked in shared memory with the other per-row values
+    // when a thread carries eight or more rows; `grew_prev` then says whether to read it at all.
     float acc_prev[GP];
 #pragma unroll
     for (int j = 0; j < GP; ++j) acc_prev[j] = 1.0f;
+    bool grew_prev = false;
     // Which row's group maximum this lane ends up holding after the reduce-scatter below: step i
     // hands the upper half of the rows still held to the lanes whose bit i is set.
     constexpr int LOG = GP == 4 ? 2 : (GP == 8 ? 3 : 4);
@@ -792,12 +800,26 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       threshold[j] = 0.0f;
     }
     float own_max_scaled = 0.0f;
+    // With eight or more rows per thread the three per-row arrays (24+ registers of values every
+    // thread holds identically) are parked in shared memory for the page loop and read back as
+    // broadcasts; they change only when a running maximum moves.
+    constexpr bool kStatsInSmem = GP >= 8;
     auto refresh_thresholds = [&]() {
       own_max_scaled = max_scaled[0];
 #pragma unroll
       for (int j = 0; j < GP; ++j) {
         threshold[j] = st.row_max[j] + headroom;
         own_max_scaled = own_row == j ? max_scaled[j] : own_max_scaled;
+      }
+      if constexpr (kStatsInSmem) {
+        // every thread writes the same values; the barrier orders them before the next reads
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          sm.stat_row_max[j] = st.row_max[j];
+          sm.stat_threshold[j] = threshold[j];
+          sm.stat_max_scaled[j] = max_scaled[j];
+        }
+        softmax_barrier();
       }
     };
     refresh_thresholds();
@@ -842,7 +864,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       if (!st.first) {
         bool own = *abort_flag != 0;
 #pragma unroll
-        for (int j = 0; j < GP; ++j) own = own || s[j] > threshold[j];
+        for (int j = 0; j < GP; ++j) own = own || s[j] > (kStatsInSmem ? sm.stat_threshold[j] : threshold[j]);
         grows = softmax_vote_any(own);
       }
       float acc[GP];
@@ -902,7 +924,15 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
           block_max[j] = fmaxf(fmaxf(sm.red[red_buf][0][j], sm.red[red_buf][1][j]),
                                fmaxf(sm.red[red_buf][2][j], sm.red[red_buf][3][j]));
         red_buf ^= 1;
+        if constexpr (kStatsInSmem) {
+#pragma unroll
+          for (int j = 0; j < GP; ++j) st.row_max[j] = sm.stat_row_max[j];
+        }
         update_max<GP>(st, block_max, p.scale_log2, shift, acc, max_scaled);
+        if constexpr (kStatsInSmem) {
+#pragma unroll
+          for (int j = 0; j < GP; ++j) sm.stat_acc[i & 1][j] = acc[j];
+        }
         refresh_thresholds();
         stop = *abort_flag != 0;  // uniform: every thread reads it after the same barrier
 #pragma unroll
@@ -915,7 +945,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       float prob[GP];
 #pragma unroll
       for (int j = 0; j < GP; ++j) {
-        prob[j] = ex2_approx(fmaf(s[j], p.scale_log2, -max_scaled[j]));
+        prob[j] = ex2_approx(fmaf(s[j], p.scale_log2, -(kStatsInSmem ? sm.stat_max_scaled[j] : max_scaled[j])));
         st.row_sum[j] += prob[j];
       }
       if constexpr (GP <= 8) {
@@ -977,7 +1007,8 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         float group_scale[GP];
 #pragma unroll
         for (int j = 0; j < GP; ++j) {
-          const float maximum = ex2_approx(fmaf(group_max[j], p.scale_log2, -max_scaled[j]));
+          const float maximum =
+              ex2_approx(fmaf(group_max[j], p.scale_log2, -(kStatsInSmem ? sm.stat_max_scaled[j] : max_scaled[j])));
           const float scale = probability_scale(maximum, p.p_mode, p.tau);
           group_scale[j] = scale;
           const float q = prob[j] * rcp_approx(fmaxf(scale, 1e-20f));
@@ -1008,11 +1039,29 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         tc::tmem_wait_ld();
         tc::fence_before_sync();
         tc::mbar_arrive(&sm.o_empty[pb]);
+        if constexpr (kStatsInSmem) {
+          if (grew_prev) {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
+            for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], sm.stat_acc[(i - 1) & 1][j], o[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < GP; ++j) st.o_acc[j] += o[j];  // == fma(o_acc, 1, o)
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
+        }
       }
+      if constexpr (kStatsInSmem) {
+        grew_prev = grows;
+      } else {
 #pragma unroll
-      for (int j = 0; j < GP; ++j) acc_prev[j] = acc[j];
+        for (int j = 0; j < GP; ++j) acc_prev[j] = acc[j];
+      }
+    }
+    if constexpr (kStatsInSmem) {
+#pragma unroll
+      for (int j = 0; j < GP; ++j) st.row_max[j] = sm.stat_row_max[j];
     }
     if (num_pages > 0) {
       const int pb = (num_pages - 1) & 1;
@@ -1023,7 +1072,10 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       tc::tmem_wait_ld();
       tc::fence_before_sync();
 #pragma unroll
-      for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
+      for (int j = 0; j < GP; ++j) {
+        const float factor = kStatsInSmem ? (grew_prev ? sm.stat_acc[(num_pages - 1) & 1][j] : 1.0f) : acc_prev[j];
+        st.o_acc[j] = fmaf(st.o_acc[j], factor, o[j]);
+      }
     }
     if (with_bf16 && p.seqused_sink) {
       bf16_block<GP, STAGES>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,
