@@ -462,10 +462,10 @@ def run_ours(args) -> None:
     achieved = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
     clocks = sampler.summary()
     # DRAM traffic per launch from the ncu capture of the same kernel on the 8,192-token case
-    # (dram__bytes_read + dram__bytes_write: 639.7 MB for 630.3 MB of algorithmic bytes with 64-token
+    # (dram__bytes_read + dram__bytes_write: 638.7 MB for 630.3 MB of algorithmic bytes with 64-token
     # pages, 637.9 MB for 630.2 MB with 128-token pages), scaled by the bytes this launch processes;
     # traffic grows in proportion to the pages walked.
-    traffic = algorithmic_bytes * ((639.7 / 630.3) if page_tokens == 64 else (637.9 / 630.2))
+    traffic = algorithmic_bytes * ((638.7 / 630.3) if page_tokens == 64 else (637.9 / 630.2))
     if rank == 0:
         line = {
             "metric": "decode_attn_us_per_step",
