@@ -288,7 +288,8 @@ def run_ours(args) -> None:
     if splits > 1:
         scratch["split_partial_scratch"] = torch.empty(parts * rows * heads_q * 128, device=device)
         scratch["split_lse_scratch"] = torch.empty(parts * rows * heads_q, device=device)
-        scratch["split_merge_counters"] = torch.zeros(rows * heads_kv, dtype=torch.int32, device=device)
+        if args.fused_merge:
+            scratch["split_merge_counters"] = torch.zeros(rows * heads_kv, dtype=torch.int32, device=device)
     out = torch.empty(rows, heads_q, 128, dtype=torch.bfloat16, device=device)
 
     def step(query, key_token, value_token):
@@ -345,10 +346,12 @@ def run_ours(args) -> None:
     kernel_args.num_splits = splits
     kernel_args.bf16_split = int(parts > splits)
     kernel_args.bf16_page_cost = args.bf16_cost if args.bf16_cost >= 0 else decode_module.BF16_BLOCK_PAGE_COST
-    kernel_args.out, kernel_args.out_row_stride = out.data_ptr(), out.stride(0)
-    if splits > 1:  # the split launch merges its own partials (fused merge)
+    if splits > 1:
         kernel_args.partial_out = scratch["split_partial_scratch"].data_ptr()
         kernel_args.partial_lse = scratch["split_lse_scratch"].data_ptr()
+    if splits == 1 or args.fused_merge:
+        kernel_args.out, kernel_args.out_row_stride = out.data_ptr(), out.stride(0)
+    if splits > 1 and args.fused_merge:  # the split launch merges its own partials
         kernel_args.merge_counters = scratch["split_merge_counters"].data_ptr()
     stream = bdfp4.current_stream(device)
 
@@ -359,6 +362,9 @@ def run_ours(args) -> None:
         bdfp4.decode(kernel_args, stream)
         if events:
             events[1].record()
+        if splits > 1 and not args.fused_merge:
+            bdfp4.combine(scratch["split_partial_scratch"], scratch["split_lse_scratch"], parts, rows, heads_q, out,
+                          out.stride(0), stream)
 
     for _ in range(args.warmup):
         device_step()
@@ -499,7 +505,7 @@ def run_ours(args) -> None:
                 "kernel": "decode_kernel", "algorithmic_bytes_per_launch": algorithmic_bytes,
             },
             "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * 2,
+            "gpu_launches": args.steps * (3 if splits > 1 and not args.fused_merge else 2),
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -525,6 +531,9 @@ def main() -> None:
     parser.add_argument("--page-tokens", type=int, default=64, choices=[64, 128],
                         help="tokens per cache page: 64 as the benchmark configuration names it, or the "
                              "reference's 128")
+    parser.add_argument("--fused-merge", action="store_true",
+                        help="merge split-KV partials inside the decode kernel instead of launching the merge "
+                             "kernel (measured no faster)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     if args.warmup < 3:

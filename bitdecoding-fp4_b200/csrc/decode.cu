@@ -1190,12 +1190,13 @@ template <int GP, int TERMS, int STAGES, int PT>
 static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
                                         cudaStream_t stream) {
   const int smem = (int)sizeof(DecodeSmem<GP, STAGES>) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  const int slot = current_device_slot();
+  if (slot < 0 || !configured.done[slot]) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS, STAGES, PT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (slot >= 0) configured.done[slot] = true;
   }
   const int grid = p.rows * p.heads_kv * p.parts;
   // Programmatic stream serialization: after the query quantizer (which signals early) the CTAs
@@ -1220,11 +1221,14 @@ static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensor
 template <int GP, int TERMS, int PT>
 static cudaError_t launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
                                  cudaStream_t stream) {
-  static int sms = 0;
+  static int sm_counts[kDeviceSlots] = {};
+  const int slot = current_device_slot();
+  int sms = slot >= 0 ? sm_counts[slot] : 0;
   if (sms == 0) {
     int device = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (slot >= 0) sm_counts[slot] = sms;
   }
   const int grid = p.rows * p.heads_kv * p.parts;
   if constexpr (GP <= 8) {

@@ -302,11 +302,12 @@ __global__ void __launch_bounds__(128) tail_token_kernel(const KvWriteParams p) 
 template <int PT>
 static cudaError_t launch_value_pages(const KvWriteParams& p, int page_items, cudaStream_t stream) {
   const int smem = ValueTile<PT>::kSmem;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  const int slot = current_device_slot();
+  if (slot < 0 || !configured.done[slot]) {
     cudaError_t e = cudaFuncSetAttribute(value_page_kernel<PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (slot >= 0) configured.done[slot] = true;
   }
   value_page_kernel<PT><<<dim3(page_items, 1, p.layers), 256, smem, stream>>>(p);
   return cudaGetLastError();

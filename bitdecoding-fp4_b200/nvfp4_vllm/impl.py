@@ -182,7 +182,7 @@ class NVFP4Impl(FlashAttentionImpl):
             query_scales_scratch=runtime.query_scales, query_fp4_second_scratch=runtime.query_fp4_second,
             query_scales_second_scratch=runtime.query_scales_second, num_splits=attn_metadata.decode_num_splits,
             split_partial_scratch=runtime.split_partial, split_lse_scratch=runtime.split_lse,
-            split_merge_counters=runtime.split_counters, row_order=attn_metadata.decode_row_order,
+            row_order=attn_metadata.decode_row_order,
             query_terms=runtime.query_terms, scale_mode=self.scale_modes.query,
             query_rotation=runtime.query_rotation, out=output[:rows], tail_write=tail_write)
 

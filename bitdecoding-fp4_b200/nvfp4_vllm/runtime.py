@@ -136,9 +136,6 @@ class LayerRuntime:
                               if split_rows else None)
         self.split_lse = (torch.empty(split_rows * num_heads, dtype=torch.float32, device=device)
                           if split_rows else None)
-        # tickets of the decode kernel's fused split merge: zero here, left zero by every launch
-        self.split_counters = (torch.zeros(num_slots * num_kv_heads, dtype=torch.int32, device=device)
-                               if split_rows else None)
         self._views: dict[int, tuple] = {}
         self._by_layer: dict[int, tuple] = {}
         self._bases: torch.Tensor | None = None
