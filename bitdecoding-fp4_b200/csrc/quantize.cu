@@ -85,11 +85,8 @@ __host__ __device__ __forceinline__ int key_scale_offset64(int token, int group)
 
 // One CTA = one head of one K page of PT tokens: 8 * PT scale groups, PT / 32 per thread.
 template <int SHIFT_TYPE, bool ROTATE, int PT>
-__global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
+__device__ __forceinline__ void key_page_body(const KvWriteParams& p, int item, int grid_layer, uint8_t* scale_tile) {
   constexpr int kScaleBytes = PT * 8;
-  __shared__ __align__(16) uint8_t scale_tile[kScaleBytes];
-  const int item = blockIdx.x;
-  const int grid_layer = blockIdx.z;
   const int layer = p.bases ? grid_layer : p.layer;
   const int head = item % p.heads;
   const int work = item / p.heads;
@@ -127,6 +124,12 @@ __global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
     reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
 }
 
+template <int SHIFT_TYPE, bool ROTATE, int PT>
+__global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
+  __shared__ __align__(16) uint8_t scale_tile[PT * 8];
+  key_page_body<SHIFT_TYPE, ROTATE, PT>(p, blockIdx.x, blockIdx.z, scale_tile);
+}
+
 // One CTA = one head of one V page of PT tokens. Scale groups run along the page's tokens, so the
 // [token][channel] tile is staged in shared memory and read back by columns. A channel's codes
 // are PT / 2 bytes; its PT / 16 scales sit at the 128-token layout's offsets (one atom per 64 tokens).
@@ -139,14 +142,11 @@ struct ValueTile {
 };
 
 template <int PT>
-__global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) {
+__device__ __forceinline__ void value_page_body(const KvWriteParams& p, int item, int grid_layer, uint8_t* smem) {
   using T = ValueTile<PT>;
-  extern __shared__ __align__(16) uint8_t smem[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [PT][128]
   uint8_t* code_tile = smem + PT * kHeadDim * 2;                 // [128][kCodePitch]
   uint8_t* scale_tile = code_tile + kHeadDim * T::kCodePitch;    // [kScaleBytes]
-  const int item = blockIdx.x;
-  const int grid_layer = blockIdx.z;
   const int layer = p.bases ? grid_layer : p.layer;
   const int head = item % p.heads;
   const int work = item / p.heads;
@@ -194,6 +194,26 @@ __global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) 
   }
   if (threadIdx.x < T::kScaleBytes / 4)
     reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
+}
+
+template <int PT>
+__global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  value_page_body<PT>(p, blockIdx.x, blockIdx.z, smem);
+}
+
+// K and V pages in one launch: even CTAs quantize a K page head, odd CTAs the V page head of the
+// same work item. The K role is bound by arithmetic and the V role by its loads and the staging
+// tile, so CTAs of both kinds resident on one SM overlap instead of running back to back.
+// (Five CTAs per SM measured faster for 64-token pages, four for 128-token pages.)
+template <int SHIFT_TYPE, bool ROTATE, int PT>
+__global__ void __launch_bounds__(256, PT == 64 ? 5 : 4) kv_page_kernel(const KvWriteParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int item = blockIdx.x >> 1;
+  if (blockIdx.x & 1)
+    value_page_body<PT>(p, item, blockIdx.z, smem);
+  else
+    key_page_body<SHIFT_TYPE, ROTATE, PT>(p, item, blockIdx.z, smem);
 }
 
 // One 16-element group of one token's new K or V into the BF16 tail: at `offset` of the rolling
@@ -313,18 +333,38 @@ static cudaError_t launch_value_pages(const KvWriteParams& p, int page_items, cu
   return cudaGetLastError();
 }
 
+template <int SHIFT_TYPE, bool ROTATE, int PT>
+static cudaError_t launch_kv_pages(const KvWriteParams& p, int page_items, cudaStream_t stream) {
+  const int smem = ValueTile<PT>::kSmem;
+  static PerDeviceOnce configured;
+  const int slot = current_device_slot();
+  if (slot < 0 || !configured.done[slot]) {
+    cudaError_t e = cudaFuncSetAttribute(kv_page_kernel<SHIFT_TYPE, ROTATE, PT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    if (slot >= 0) configured.done[slot] = true;
+  }
+  kv_page_kernel<SHIFT_TYPE, ROTATE, PT><<<dim3(2 * page_items, 1, p.layers), 256, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
 template <int SHIFT_TYPE, bool ROTATE>
 static cudaError_t launch_kv_write(const KvWriteParams& p, int page_tokens, cudaStream_t stream) {
   const int page_items = p.heads * p.work_items;
-  if (p.key && (p.region[0] || p.bases) && page_items > 0) {
+  const bool key_pages = p.key && (p.region[0] || p.bases) && page_items > 0;
+  const bool value_pages = p.value && (p.region[2] || p.bases) && page_items > 0;
+  if (key_pages && value_pages) {
+    cudaError_t e = page_tokens == 64 ? launch_kv_pages<SHIFT_TYPE, ROTATE, 64>(p, page_items, stream)
+                                      : launch_kv_pages<SHIFT_TYPE, ROTATE, 128>(p, page_items, stream);
+    if (e != cudaSuccess) return e;
+  } else if (key_pages) {
     if (page_tokens == 64)
       key_page_kernel<SHIFT_TYPE, ROTATE, 64><<<dim3(page_items, 1, p.layers), 256, 0, stream>>>(p);
     else
       key_page_kernel<SHIFT_TYPE, ROTATE, 128><<<dim3(page_items, 1, p.layers), 256, 0, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-  }
-  if (p.value && (p.region[2] || p.bases) && page_items > 0) {
+  } else if (value_pages) {
     cudaError_t e = page_tokens == 64 ? launch_value_pages<64>(p, page_items, stream)
                                       : launch_value_pages<128>(p, page_items, stream);
     if (e != cudaSuccess) return e;
