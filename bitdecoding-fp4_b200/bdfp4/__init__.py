@@ -36,6 +36,10 @@ EXPORTS = (
     "bdfp4_tail_reset",
     "bdfp4_key_channel_sums",
     "bdfp4_probability_statistics",
+    "bdfp4_mla_quantize_query",
+    "bdfp4_mla_write_rope",
+    "bdfp4_mla_decode",
+    "bdfp4_mla_combine",
 )
 
 
@@ -113,6 +117,26 @@ class DecodeArgs(Structure):
     ]
 
 
+class MlaDecodeArgs(Structure):
+    _fields_ = [
+        ("rows", c_int32), ("heads_q", c_int32),
+        ("query_codes", c_void_p), ("query_scales", c_void_p), ("query_rope", c_void_p),
+        ("key_codes", c_void_p), ("key_scales", c_void_p),
+        ("value_codes", c_void_p), ("value_scales", c_void_p),
+        ("key_codes_pitch", c_int64), ("key_scales_pitch", c_int64),
+        ("value_codes_pitch", c_int64), ("value_scales_pitch", c_int64),
+        ("rope_pages", c_void_p), ("rope_pitch", c_int64),
+        ("pages", c_int32),
+        ("page_table", c_void_p), ("page_table_stride", c_int64),
+        ("seq_lens", c_void_p),
+        ("softmax_scale", c_float), ("p_scale_mode", c_int32), ("p_scale_tau", c_float),
+        ("out", c_void_p),
+        ("num_splits", c_int32),
+        ("partial_out", c_void_p), ("partial_lse", c_void_p),
+        ("error_word", c_void_p),
+    ]
+
+
 class ControlArgs(Structure):
     _fields_ = [
         ("block_table", c_void_p), ("block_table_stride", c_int64), ("block_table_columns", c_int32),
@@ -168,6 +192,14 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_probability_statistics.restype = c_int32
     lib.bdfp4_probability_statistics.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int32, c_float, c_int32,
                                                  c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.bdfp4_mla_quantize_query.restype = c_int32
+    lib.bdfp4_mla_quantize_query.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
+    lib.bdfp4_mla_write_rope.restype = c_int32
+    lib.bdfp4_mla_write_rope.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p]
+    lib.bdfp4_mla_decode.restype = c_int32
+    lib.bdfp4_mla_decode.argtypes = [POINTER(MlaDecodeArgs), c_void_p]
+    lib.bdfp4_mla_combine.restype = c_int32
+    lib.bdfp4_mla_combine.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p]
     lib.bdfp4_decode_split_static.restype = c_int32
     lib.bdfp4_decode_split_static.argtypes = [POINTER(DecodeArgs), c_void_p]
     _lib = lib
@@ -238,6 +270,30 @@ def decode_split_static(args: DecodeArgs, stream: int) -> None:
     Raises :class:`KernelError` with ``E_TOO_LARGE`` when the partials would not fit. Calls share
     the array, so run them on one stream; make the first call on a device outside stream capture."""
     check("bdfp4_decode_split_static", library().bdfp4_decode_split_static(ctypes.byref(args), stream))
+
+
+def mla_quantize_query(query, scale_mode: int, codes, scales, stream: int) -> None:
+    """BF16 ``query [rows, heads, 512]`` -> ``codes [rows, heads, 256]`` u8, ``scales [rows, heads, 32]`` u8."""
+    rows, heads, _ = query.shape
+    check("bdfp4_mla_quantize_query",
+          library().bdfp4_mla_quantize_query(ptr(query), query.stride(0), rows, heads, scale_mode, ptr(codes),
+                                             ptr(scales), stream))
+
+
+def mla_write_rope(rope, source_tokens, destination_pages, rope_pages, stream: int) -> None:
+    """BF16 ``rope [tokens, 64]``: 64 tokens per work item into the swizzled 8 KB block of its page."""
+    check("bdfp4_mla_write_rope",
+          library().bdfp4_mla_write_rope(ptr(rope), rope.stride(0), ptr(source_tokens), ptr(destination_pages),
+                                         source_tokens.numel(), ptr(rope_pages), rope_pages.stride(0) * 2, stream))
+
+
+def mla_decode(args: MlaDecodeArgs, stream: int) -> None:
+    check("bdfp4_mla_decode", library().bdfp4_mla_decode(ctypes.byref(args), stream))
+
+
+def mla_combine(partial_out, partial_lse, parts: int, rows: int, heads_q: int, out, stream: int) -> None:
+    check("bdfp4_mla_combine",
+          library().bdfp4_mla_combine(ptr(partial_out), ptr(partial_lse), parts, rows, heads_q, ptr(out), stream))
 
 
 def control_step(args: ControlArgs, stream: int) -> None:

@@ -1,0 +1,757 @@
+// MLA latent-cache decode attention for sm_100a, and the writers around it.
+//
+// A token is a 512-channel latent (cached in NVFP4) plus a 64-channel BF16 rope key; every query
+// head attends over the same cache:
+//   score[h, t] = q_latent[h] . latent[t] + q_rope[h] . rope[t]       out[h] = sum_t p[h, t] latent[t]
+// The latent is cached twice, as four 128-channel pseudo heads of 64-token pages: once with scales
+// along channels (the K-side regions of the paged cache) and once with scales along tokens (the
+// V-side regions), because a block-scaled MMA wants its scales along the contraction axis.
+//
+// One CTA serves (row, 64 query heads[, split]) and walks the row's pages two at a time (128
+// tokens per step). Transposed as in the GQA kernel, a softmax thread owns one token:
+//   S^T[token, head]  = sum over 4 chunks  K_chunk[token, :] . Q_chunk[head, :]   8 x mxf4nvf4 (K = 64)
+//                     + rope[token, :] . q_rope[head, :]                           4 x kind::f16 (K = 16)
+//   O^T_chunk[chan, head] += V_chunk^T[chan, :] . P[head, :]                      8 x mxf4nvf4
+// all with M = 128, N = 64. O^T (4 x 64 columns) stays in tensor memory for the whole walk; when a
+// running maximum moves (rarely: the stale-maximum rule tolerates 2^8) the softmax threads rescale
+// it in place between two PV products. Tensor memory: S^T 64 + O^T 256 + scale factors 176 columns.
+//
+// Warp roles as in the GQA kernel: warp 0 issues the bulk copies (lane 0 the K side, lane 1 the V
+// side), warp 1 interleaves the two pages' K scale blocks into MMA atoms and issues every tcgen05
+// operation, warps 2-5 are the softmax. Every mbarrier wait is bounded.
+#include <cmath>
+#include <type_traits>
+
+#include "common.cuh"
+#include "host.h"
+#include "tcgen05.cuh"
+
+namespace bdfp4 {
+namespace mla {
+
+constexpr int kHeads = 64;    // query heads per CTA: N of every MMA
+constexpr int kChunks = 4;    // 128-channel chunks of the latent
+constexpr int kLatent = 512;
+constexpr int kRope = 64;
+constexpr int kStep = 128;    // tokens per step (two 64-token pages)
+constexpr int kStages = 2;
+constexpr float kRescaleThreshold = 8.0f;
+
+constexpr int kColS = 0;       // 64 columns
+constexpr int kColO = 64;      // 4 chunks x 64
+constexpr int kColSFQ = 320;   // 8 atoms x 4
+constexpr int kColSFK = 352;   // 2 buffers x 8 atoms x 4
+constexpr int kColSFV = 416;   // 2 buffers x 8 atoms x 4
+constexpr int kColSFP = 480;   // 2 buffers x 2 atoms x 4
+constexpr int kTmemColumns = 512;
+
+constexpr uint32_t kKeyBytes = kChunks * 8192 + 2 * 8192;  // codes of four chunks + two rope blocks
+constexpr uint32_t kKeyScaleBytes = 4096;
+constexpr uint32_t kValueBytes = 2 * 16384 + 2 * 2048;
+
+struct Params {
+  int rows, heads_q, groups;
+  const uint8_t* q_codes;
+  const uint8_t* q_scales;
+  const __nv_bfloat16* q_rope;
+  const uint8_t* k_codes;
+  const uint8_t* k_scales;
+  const uint8_t* v_codes;
+  const uint8_t* v_scales;
+  const uint8_t* rope;
+  int64_t k_codes_pitch, k_scales_pitch, v_codes_pitch, v_scales_pitch, rope_pitch;
+  int pages;
+  const int32_t* page_table;
+  int64_t page_table_stride;
+  const int32_t* seq_lens;
+  float scale_log2;
+  int p_mode;
+  float tau;
+  __nv_bfloat16* out;
+  int num_splits;
+  float* partial_out;
+  float* partial_lse;
+  int32_t* error_word;
+};
+
+struct Smem {
+  alignas(1024) uint8_t k_codes[kStages][kChunks][8192];     // [chunk][page a | page b], 64 B rows, 64 B swizzle
+  alignas(1024) uint8_t rope[kStages][16384];                // 128 tokens x 128 B, 128 B swizzle
+  alignas(1024) uint8_t v_codes[kStages][2][kChunks][4096];  // [page][chunk][128 ch x 32 B], 32 B swizzle
+  alignas(1024) uint8_t k_sf[kStages][4096];                 // two pages' blocks, merged in place into 8 atoms
+  alignas(1024) uint8_t v_sf[kStages][2][kChunks][512];      // [page][chunk] atoms
+  alignas(1024) uint8_t q_tile[kChunks][kHeads * 64];
+  alignas(1024) uint8_t q_rope[kHeads * 128];
+  alignas(1024) uint8_t q_sf[kChunks * 2][512];
+  alignas(1024) uint8_t p_tile[2][kHeads * 64];
+  alignas(1024) uint8_t p_sf[2][2][512];
+  float red[4][kHeads];
+  float stat_row_max[kHeads], stat_threshold[kHeads], stat_max_scaled[kHeads], stat_acc[kHeads];
+  float stat_inverse[kHeads];
+  uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  uint64_t s_full, s_empty, o_done, p_full[2], p_empty[2];
+  int page_ids[2][32];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+static_assert(sizeof(Smem) + 1024 <= 232448, "one CTA's shared memory (227 KB opt-in limit)");
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ bool softmax_vote_any(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+// A bounded wait that leaves its own number in the abort flag when it is the one that ran out of
+// time; the kernel reports it in bits [8,16) of the error word, so a lost arrival can be located.
+__device__ __forceinline__ bool wait_at(int site, uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (tc::mbar_try_wait(bar, parity)) return true;
+  uint64_t start = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = tc::global_timer_ns();
+      if (start == 0) start = now;
+      if (now - start > tc::kWaitLimitNs) {
+        atomicCAS(const_cast<int*>(abort_flag), 0, site);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ int swizzle64(int offset) { return offset ^ (((offset >> 7) & 3) << 4); }
+
+// Scale of one group of sixteen probabilities from its maximum (the rule of the GQA kernel).
+__device__ __forceinline__ float probability_scale(float maximum, int p_mode, float tau) {
+  float scale = __fmul_rn(maximum, (float)(1.0 / 6.0));
+  if (p_mode != BDFP4_P_AMAX6 && maximum <= tau) scale = __fmul_rn(maximum, 0.5f);
+  return scale;
+}
+
+__global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- which work ---------------------------------------------------------------------------
+  const int group = blockIdx.x % p.groups;
+  const int row = (blockIdx.x / p.groups) % p.rows;
+  const int part = blockIdx.x / (p.groups * p.rows);
+  const int head0 = group * kHeads;
+  const int seq_len = max(p.seq_lens[row], 0);
+  const int entries = (seq_len + 63) / 64;
+  const int total_steps = (seq_len + kStep - 1) / kStep;
+  const int chunk = (total_steps + p.num_splits - 1) / p.num_splits;
+  const int first_step = min(part * chunk, total_steps);
+  const int last_step = min(first_step + chunk, total_steps);
+  const int num_steps = last_step - first_step;
+
+  // ---- set-up -------------------------------------------------------------------------------
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&sm.k_full[s], 1);
+      tc::mbar_init(&sm.ksf_full[s], 1);
+      tc::mbar_init(&sm.k_empty[s], 1);
+      tc::mbar_init(&sm.v_full[s], 1);
+      tc::mbar_init(&sm.v_empty[s], 1);
+    }
+    tc::mbar_init(&sm.s_full, 1);
+    tc::mbar_init(&sm.s_empty, 128);
+    tc::mbar_init(&sm.o_done, 1);
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&sm.p_full[b], 128);
+      tc::mbar_init(&sm.p_empty[b], 1);
+    }
+    sm.abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  // zero the scale-atom buffers the kernel writes only in part
+  for (int i = tid; i < (int)(sizeof(sm.q_sf) / 16); i += 192) reinterpret_cast<uint4*>(sm.q_sf)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < (int)(sizeof(sm.p_sf) / 16); i += 192) reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  // query operands: codes (16 chunks of 16 bytes per head), scales (8 words per head), rope (8 chunks)
+  {
+    const int64_t head_base = (int64_t)row * p.heads_q + head0;
+    for (int i = tid; i < kHeads * 16; i += 192) {
+      const int h = i >> 4, c = i & 15;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q_codes + (head_base + h) * 256) + c);
+      *reinterpret_cast<uint4*>(sm.q_tile[c >> 2] + swizzle64(h * 64 + (c & 3) * 16)) = v;
+    }
+    for (int i = tid; i < kHeads * 8; i += 192) {
+      const int h = i >> 3, a = i & 7;
+      const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(p.q_scales + (head_base + h) * 32) + a);
+      *reinterpret_cast<uint32_t*>(sm.q_sf[a] + (h & 31) * 16 + (h >> 5) * 4) = v;
+    }
+    for (int i = tid; i < kHeads * 8; i += 192) {
+      const int h = i >> 3, c = i & 7;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q_rope + (head_base + h) * kRope) + c);
+      *reinterpret_cast<uint4*>(sm.q_rope + h * 128 + ((c ^ (h & 7)) << 4)) = v;
+    }
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(&sm.tmem_base, kTmemColumns);
+    tc::tmem_relinquish();
+  }
+  tc::fence_proxy_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  auto page_of = [&](int i, int which) {  // page of the i-th step this CTA walks (newest first)
+    const int step = last_step - 1 - i;
+    int entry = 2 * step + which;
+    if (entry >= entries) entry = 2 * step;  // an odd page count: the second half is masked anyway
+    int page = p.page_table[(int64_t)row * p.page_table_stride + entry];
+    if (page < 0 || page >= p.pages) {
+      if (p.error_word) atomicOr(p.error_word, (int)BDFP4_DEV_BAD_PAGE);
+      page = min(max(page, 0), p.pages - 1);
+    }
+    return page;
+  };
+
+  if (warp == 0) {
+    // ---- copy producer ----------------------------------------------------------------------
+    int issued = 0;
+    bool ok = true;
+    for (int base = 0; base < num_steps && ok; base += 32) {
+      const int count = min(32, num_steps - base);
+      if (lane < count) {
+        sm.page_ids[0][lane] = page_of(base + lane, 0);
+        sm.page_ids[1][lane] = page_of(base + lane, 1);
+      }
+      __syncwarp();
+      if (lane < 2) {
+        for (int j = 0; j < count && ok; ++j) {
+          const int i = base + j;
+          const int s = i % kStages;
+          const uint32_t parity = ((i / kStages) & 1) ^ 1;
+          const int page[2] = {sm.page_ids[0][j], sm.page_ids[1][j]};
+          if (lane == 0) {
+            ok = wait_at(1, &sm.k_empty[s], parity, abort_flag);
+            if (ok) {
+              tc::mbar_expect_tx(&sm.ksf_full[s], kKeyScaleBytes);
+              tc::mbar_expect_tx(&sm.k_full[s], kKeyBytes);
+#pragma unroll
+              for (int e = 0; e < 2; ++e)
+                tc::bulk_load(sm.k_sf[s] + e * 2048, p.k_scales + (int64_t)page[e] * p.k_scales_pitch, 2048,
+                              &sm.ksf_full[s]);
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c)
+                  tc::bulk_load(sm.k_codes[s][c] + e * 4096, p.k_codes + (int64_t)page[e] * p.k_codes_pitch + c * 4096,
+                                4096, &sm.k_full[s]);
+                tc::bulk_load(sm.rope[s] + e * 8192, p.rope + (int64_t)page[e] * p.rope_pitch, 8192, &sm.k_full[s]);
+              }
+            }
+          } else {
+            ok = wait_at(2, &sm.v_empty[s], parity, abort_flag);
+            if (ok) {
+              tc::mbar_expect_tx(&sm.v_full[s], kValueBytes);
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                tc::bulk_load(sm.v_codes[s][e], p.v_codes + (int64_t)page[e] * p.v_codes_pitch, 16384, &sm.v_full[s]);
+                tc::bulk_load(sm.v_sf[s][e], p.v_scales + (int64_t)page[e] * p.v_scales_pitch, 2048, &sm.v_full[s]);
+              }
+            }
+          }
+          if (ok) issued = i + 1;
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    // After a give-up, wait (bounded) until every copy already in flight has landed, so that no
+    // bulk copy can write into this CTA's shared memory after it exits.
+    if (lane < 2 && *abort_flag) {
+      const uint64_t start = tc::global_timer_ns();
+      for (int i = max(0, issued - kStages); i < issued; ++i) {
+        const int s = i % kStages;
+        const uint32_t parity = (i / kStages) & 1;
+        if (lane == 0) {
+          while (!tc::mbar_try_wait(&sm.k_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
+          }
+          while (!tc::mbar_try_wait(&sm.ksf_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
+          }
+        } else {
+          while (!tc::mbar_try_wait(&sm.v_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ---------------------------------------------------------------------------
+    const bool issuer = lane == 0;
+    constexpr uint32_t idesc_fp4 = tc::nvf4_idesc(128, kHeads);
+    constexpr uint32_t idesc_bf16 = tc::bf16_idesc(128, kHeads);
+    if (num_steps > 0) {
+      if (issuer) {
+#pragma unroll
+        for (int a = 0; a < kChunks * 2; ++a)
+          tc::cp_sf_atom(tmem + kColSFQ + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[a])));
+      }
+      auto issue_pv = [&](int m) -> bool {  // issuer only
+        const int s = m % kStages;
+        const int b = m & 1;
+        if (!wait_at(3, &sm.v_full[s], (m / kStages) & 1, abort_flag)) return false;
+        if (!wait_at(4, &sm.p_full[b], (m >> 1) & 1, abort_flag)) return false;
+        tc::fence_after_sync();
+#pragma unroll
+        for (int a = 0; a < 2 * kChunks; ++a)
+          tc::cp_sf_atom(tmem + kColSFV + 32 * b + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.v_sf[s][0][0]) + a * 512));
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          tc::cp_sf_atom(tmem + kColSFP + 8 * b + 4 * e, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b][e])));
+        const uint32_t p_addr = tc::smem_u32(sm.p_tile[b]);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e)
+            tc::mma_nvf4(tmem + kColO + kHeads * c, tc::fp4_half_tile_desc(tc::smem_u32(sm.v_codes[s][e][c])),
+                         tc::fp4_tile_desc(p_addr, e), idesc_fp4, tmem + kColSFV + 32 * b + 4 * (e * kChunks + c),
+                         tmem + kColSFP + 8 * b + 4 * e, m > 0 || e > 0);
+        }
+        tc::commit(&sm.o_done);
+        tc::commit(&sm.v_empty[s]);
+        tc::commit(&sm.p_empty[b]);
+        return true;
+      };
+      bool ok = true;
+      for (int i = 0; i < num_steps && ok; ++i) {
+        const int s = i % kStages;
+        const int b = i & 1;
+        ok = wait_at(5, &sm.ksf_full[s], (i / kStages) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        {
+          // The two pages' scale blocks arrived as [page][chunk][K block][32 rows][8 B]; an atom row
+          // is 16 bytes, tokens 0-63 (first page) in its low half, 64-127 in its high half. Every
+          // lane reads all its pieces before any lane writes, so the exchange is done in place.
+          uint8_t* sf = sm.k_sf[s];
+          uint2 first[8], second[8];
+#pragma unroll
+          for (int a = 0; a < 8; ++a) {
+            first[a] = *reinterpret_cast<const uint2*>(sf + a * 256 + lane * 8);
+            second[a] = *reinterpret_cast<const uint2*>(sf + 2048 + a * 256 + lane * 8);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int a = 0; a < 8; ++a)
+            *reinterpret_cast<uint4*>(sf + a * 512 + lane * 16) = make_uint4(first[a].x, first[a].y, second[a].x, second[a].y);
+          tc::fence_proxy_async_smem();
+          __syncwarp();
+        }
+        if (issuer) {
+          ok = wait_at(6, &sm.k_full[s], (i / kStages) & 1, abort_flag);
+          if (ok) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int a = 0; a < 2 * kChunks; ++a)
+              tc::cp_sf_atom(tmem + kColSFK + 32 * b + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.k_sf[s]) + a * 512));
+            ok = wait_at(7, &sm.s_empty, (i & 1) ^ 1, abort_flag);
+          }
+          if (ok) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+              for (int k = 0; k < 2; ++k)
+                tc::mma_nvf4(tmem + kColS, tc::fp4_tile_desc(tc::smem_u32(sm.k_codes[s][c]), k),
+                             tc::fp4_tile_desc(tc::smem_u32(sm.q_tile[c]), k), idesc_fp4,
+                             tmem + kColSFK + 32 * b + 4 * (2 * c + k), tmem + kColSFQ + 4 * (2 * c + k), (c | k) != 0);
+            }
+#pragma unroll
+            for (int k = 0; k < kRope / 16; ++k)
+              tc::mma_bf16(tmem + kColS, tc::bf16_tile_desc(tc::smem_u32(sm.rope[s]), k),
+                           tc::bf16_tile_desc(tc::smem_u32(sm.q_rope), k), idesc_bf16, true);
+            tc::commit(&sm.s_full);
+            tc::commit(&sm.k_empty[s]);
+            if (i > 0) ok = issue_pv(i - 1);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      }
+      if (issuer && ok) issue_pv(num_steps - 1);
+    }
+  } else {
+    // ---- softmax --------------------------------------------------------------------------------
+    const int warp_q = warp & 3;
+    const int t = warp_q * 32 + lane;  // token (S^T lane) and channel (O^T lane) of this thread
+    const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
+    const float shift = p.p_mode == BDFP4_P_AMAX2_OR_AMAX6_C8 ? 3.0f : 0.0f;
+    const float headroom = kRescaleThreshold / p.scale_log2;
+    float row_sum[kHeads];
+#pragma unroll
+    for (int j = 0; j < kHeads; ++j) row_sum[j] = 0.0f;
+    if (t < kHeads) {
+      sm.stat_row_max[t] = -INFINITY;
+      sm.stat_threshold[t] = -INFINITY;
+      sm.stat_max_scaled[t] = 0.0f;
+      sm.stat_acc[t] = 1.0f;
+    }
+    softmax_barrier();
+    const int token_group = t >> 4;
+    const int sf_base = (token_group >> 2) * 512 + (token_group & 3);
+
+    for (int i = 0; i < num_steps; ++i) {
+      const int b = i & 1;
+      const int step = last_step - 1 - i;
+      wait_at(8, &sm.s_full, i & 1, abort_flag);
+      tc::fence_after_sync();
+      float s[kHeads];
+#pragma unroll
+      for (int q = 0; q < kHeads / 16; ++q) tc::tmem_ld16(lane_base + kColS + 16 * q, s + 16 * q);
+      tc::tmem_wait_ld();
+      tc::fence_before_sync();
+      tc::mbar_arrive(&sm.s_empty);
+      if (step * kStep + t >= seq_len) {
+#pragma unroll
+        for (int j = 0; j < kHeads; ++j) s[j] = -INFINITY;
+      }
+      // does any head's maximum have to move? one predicate per thread, one barrier-wide OR
+      bool own = i == 0 || *abort_flag != 0;
+#pragma unroll
+      for (int j = 0; j < kHeads; ++j) own = own || s[j] > sm.stat_threshold[j];
+      const bool grows = softmax_vote_any(own);
+      if (grows) {
+#pragma unroll
+        for (int j = 0; j < kHeads; ++j) {
+          float m = s[j];
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+          if (lane == (j & 31)) sm.red[warp_q][j] = m;
+        }
+        softmax_barrier();
+        if (t < kHeads) {
+          const float block_max = fmaxf(fmaxf(sm.red[0][t], sm.red[1][t]), fmaxf(sm.red[2][t], sm.red[3][t]));
+          float new_max, safe, acc;
+          if (i == 0) {
+            new_max = block_max;
+            safe = new_max == -INFINITY ? 0.0f : new_max;
+            acc = 0.0f;
+          } else {
+            const float old_max = sm.stat_row_max[t];
+            new_max = fmaxf(old_max, block_max);
+            safe = new_max == -INFINITY ? 0.0f : new_max;
+            const float growth = (old_max - safe) * p.scale_log2;
+            if (growth >= -kRescaleThreshold) {
+              new_max = old_max;
+              safe = old_max;
+              acc = 1.0f;
+            } else {
+              acc = ex2_approx(growth);
+            }
+          }
+          sm.stat_row_max[t] = new_max;
+          sm.stat_max_scaled[t] = safe * p.scale_log2 - shift;
+          sm.stat_threshold[t] = new_max + headroom;
+          sm.stat_acc[t] = acc;
+        }
+        softmax_barrier();
+        if (i > 0) {
+          // O^T so far is rescaled in tensor memory. Every earlier PV product has completed once
+          // the previous step's has, and the next one is not issued before this step's P arrives.
+          wait_at(9, &sm.o_done, (i - 1) & 1, abort_flag);
+          tc::fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+            for (int q = 0; q < kHeads / 16; ++q) {
+              float o[16];
+              tc::tmem_ld16(lane_base + kColO + kHeads * c + 16 * q, o);
+              tc::tmem_wait_ld();
+#pragma unroll
+              for (int k = 0; k < 16; ++k) o[k] *= sm.stat_acc[16 * q + k];
+              tc::tmem_st16(lane_base + kColO + kHeads * c + 16 * q, o);
+            }
+          }
+          tc::tmem_wait_st();
+          tc::fence_before_sync();
+#pragma unroll
+          for (int j = 0; j < kHeads; ++j) row_sum[j] *= sm.stat_acc[j];
+        }
+      }
+      // the PV product of two steps ago must be done with this P buffer
+      wait_at(10, &sm.p_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
+#pragma unroll
+      for (int j = 0; j < kHeads; ++j) {
+        const float prob = ex2_approx(fmaf(s[j], p.scale_log2, -sm.stat_max_scaled[j]));
+        row_sum[j] += prob;
+        float maximum = prob;
+#pragma unroll
+        for (int d = 1; d < 16; d <<= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
+        const float scale = probability_scale(maximum, p.p_mode, p.tau);
+        const float q = prob * rcp_approx(fmaxf(scale, 1e-20f));
+        uint32_t word = (cvt_e2m1x2(q, 0.0f) & 0xfu) << (4 * (lane & 7));
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+        word |= __shfl_xor_sync(0xffffffffu, word, 4);
+        if ((lane & 7) == (j & 7)) *reinterpret_cast<uint32_t*>(sm.p_tile[b] + swizzle64(j * 64 + (t >> 3) * 4)) = word;
+        if ((lane & 15) == (j & 15)) sm.p_sf[b][0][sf_base + (j & 31) * 16 + (j >> 5) * 4] = (uint8_t)cvt_e4m3(scale);
+      }
+      tc::fence_proxy_async_smem();
+      // Every PV product's completion is observed in turn (a parity wait can only tell the current
+      // phase from the one before it): the previous step's here, unless the rescale above already did.
+      if (i > 0 && !grows) wait_at(11, &sm.o_done, (i - 1) & 1, abort_flag);
+      tc::mbar_arrive(&sm.p_full[b]);
+    }
+
+    // ---- normalise and write ------------------------------------------------------------------
+#pragma unroll
+    for (int j = 0; j < kHeads; ++j) {
+      float v = row_sum[j];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+      if (lane == (j & 31)) sm.red[warp_q][j] = v;
+    }
+    softmax_barrier();
+    if (t < kHeads) {
+      const float total = (sm.red[0][t] + sm.red[1][t]) + (sm.red[2][t] + sm.red[3][t]);
+      const bool empty = num_steps == 0 || total == 0.0f || total != total;
+      sm.stat_inverse[t] = empty ? 0.0f : 1.0f / total;
+      if (p.out == nullptr) {
+        const float row_max = sm.stat_row_max[t];
+        const float safe = row_max == -INFINITY ? 0.0f : row_max;
+        p.partial_lse[((int64_t)part * p.rows + row) * p.heads_q + head0 + t] =
+            empty ? -INFINITY : (safe * p.scale_log2 + log2f(total) - shift) * 0.6931471805599453f;
+      }
+    }
+    softmax_barrier();
+    if (num_steps > 0) {
+      wait_at(12, &sm.o_done, (num_steps - 1) & 1, abort_flag);
+      tc::fence_after_sync();
+    }
+#pragma unroll 1
+    for (int c = 0; c < kChunks; ++c) {
+#pragma unroll 1
+      for (int q = 0; q < kHeads / 16; ++q) {
+        float o[16];
+        if (num_steps > 0) {
+          tc::tmem_ld16(lane_base + kColO + kHeads * c + 16 * q, o);
+          tc::tmem_wait_ld();
+        }
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const float inverse = sm.stat_inverse[16 * q + k];
+          const float value = inverse == 0.0f ? 0.0f : o[k] * inverse;
+          const int64_t head = (int64_t)row * p.heads_q + head0 + 16 * q + k;
+          if (p.out != nullptr)
+            p.out[head * kLatent + c * 128 + t] = __float2bfloat16_rn(value);
+          else
+            p.partial_out[((int64_t)part * p.rows * p.heads_q + head) * kLatent + c * 128 + t] = value;
+        }
+      }
+    }
+    tc::fence_before_sync();
+  }
+
+  // ---- teardown -------------------------------------------------------------------------------
+  tc::fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && sm.abort_flag && p.error_word)
+    atomicOr(p.error_word, (int)BDFP4_DEV_WAIT_TIMEOUT | ((sm.abort_flag & 0xff) << 8));
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, kTmemColumns);
+  }
+}
+
+// ---- writers ------------------------------------------------------------------------------------
+
+// One thread per 16-channel group of the absorbed query: codes at [row][head][256], scale byte at
+// [row][head][32].
+__global__ void __launch_bounds__(256) quantize_query_kernel(const __nv_bfloat16* query, int64_t row_pitch, int rows,
+                                                             int heads_q, ScaleCandidates cand, uint8_t* codes,
+                                                             uint8_t* scales) {
+  const int64_t index = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  const int64_t total = (int64_t)rows * heads_q * 32;
+  if (index >= total) return;
+  const int group = (int)(index & 31);
+  const int64_t head = index >> 5;
+  const int64_t row = head / heads_q;
+  const int h = (int)(head % heads_q);
+  float v[16];
+  load_bf16x16(query + row * row_pitch + (int64_t)h * kLatent + group * 16, v);
+  const GroupCodes q = quantize_group16(v, cand);
+  *reinterpret_cast<uint2*>(codes + head * 256 + group * 8) = make_uint2(q.lo, q.hi);
+  scales[head * 32 + group] = (uint8_t)cvt_e4m3(q.scale);
+}
+
+// One CTA per work item: 64 tokens x 128 bytes into the page's swizzled block.
+__global__ void __launch_bounds__(256) rope_page_kernel(const __nv_bfloat16* rope, int64_t token_pitch,
+                                                        const int32_t* source_tokens, const int32_t* destination_pages,
+                                                        uint8_t* pages, int64_t rope_pitch) {
+  const int page = destination_pages[blockIdx.x];
+  if (page < 0) return;
+  const int64_t source = source_tokens[blockIdx.x];
+  for (int i = threadIdx.x; i < 64 * 8; i += 256) {
+    const int token = i >> 3, c = i & 7;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(rope + (source + token) * token_pitch) + c);
+    *reinterpret_cast<uint4*>(pages + (int64_t)page * rope_pitch + token * 128 + ((c ^ (token & 7)) << 4)) = v;
+  }
+}
+
+// Merge of split partials: one CTA per (row, head), one thread per 4 channels.
+__global__ void __launch_bounds__(128) combine_kernel(const float* partial_out, const float* partial_lse, int parts,
+                                                      int64_t part_stride_heads, __nv_bfloat16* out) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  const int64_t head = blockIdx.x;
+  float lse_max = -INFINITY;
+  for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, partial_lse[s * part_stride_heads + head]);
+  if (lse_max == -INFINITY) lse_max = 0.0f;
+  float weight_sum = 0.0f;
+  for (int s = 0; s < parts; ++s) weight_sum += exp2f(partial_lse[s * part_stride_heads + head] * kLog2e - lse_max * kLog2e);
+  const float inverse = (weight_sum == 0.0f || weight_sum != weight_sum) ? 0.0f : 1.0f / weight_sum;
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int s = 0; s < parts; ++s) {
+    const float scale = exp2f(partial_lse[s * part_stride_heads + head] * kLog2e - lse_max * kLog2e) * inverse;
+    if (scale > 0.0f) {
+      const float4 v = *reinterpret_cast<const float4*>(partial_out + (s * part_stride_heads + head) * kLatent +
+                                                        threadIdx.x * 4);
+      acc.x = acc.x + scale * v.x;
+      acc.y = acc.y + scale * v.y;
+      acc.z = acc.z + scale * v.z;
+      acc.w = acc.w + scale * v.w;
+    }
+  }
+  __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + head * kLatent + threadIdx.x * 4);
+  dst[0] = __floats2bfloat162_rn(acc.x, acc.y);
+  dst[1] = __floats2bfloat162_rn(acc.z, acc.w);
+}
+
+}  // namespace mla
+}  // namespace bdfp4
+
+using namespace bdfp4;
+
+extern "C" int bdfp4_mla_quantize_query(const void* query, int64_t row_pitch, int32_t rows, int32_t heads_q,
+                                        int32_t scale_mode, void* codes, void* scales, void* stream) {
+  if (!query || !codes || !scales || rows < 1 || heads_q < 1) return BDFP4_E_ARG;
+  if (scale_mode < 0 || scale_mode > 2) return BDFP4_E_ARG;
+  if (row_pitch < (int64_t)heads_q * mla::kLatent || row_pitch % 8) return BDFP4_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(query) & 15) || (reinterpret_cast<uintptr_t>(codes) & 7)) return BDFP4_E_ARG;
+  const int64_t groups = (int64_t)rows * heads_q * 32;
+  mla::quantize_query_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(query), row_pitch, rows, heads_q, scale_candidates(scale_mode),
+      static_cast<uint8_t*>(codes), static_cast<uint8_t*>(scales));
+  return bdfp4::cuda_status(cudaGetLastError());
+}
+
+extern "C" int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const int32_t* source_tokens,
+                                    const int32_t* destination_pages, int32_t work_items, void* rope_pages,
+                                    int64_t rope_pitch, void* stream) {
+  if (!rope || !source_tokens || !destination_pages || !rope_pages || work_items < 0) return BDFP4_E_ARG;
+  if (token_pitch < mla::kRope || token_pitch % 8 || rope_pitch < 8192 || rope_pitch % 16) return BDFP4_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(rope) & 15) || (reinterpret_cast<uintptr_t>(rope_pages) & 15)) return BDFP4_E_ARG;
+  if (work_items == 0) return BDFP4_OK;
+  mla::rope_page_kernel<<<work_items, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(rope), token_pitch, source_tokens, destination_pages,
+      static_cast<uint8_t*>(rope_pages), rope_pitch);
+  return bdfp4::cuda_status(cudaGetLastError());
+}
+
+extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_handle) {
+  if (!a) return BDFP4_E_ARG;
+  if (a->rows < 1 || a->heads_q < 1) return BDFP4_E_ARG;
+  if (a->heads_q % mla::kHeads) return BDFP4_E_UNSUPPORTED;
+  if (!a->query_codes || !a->query_scales || !a->query_rope) return BDFP4_E_ARG;
+  if (!a->key_codes || !a->key_scales || !a->value_codes || !a->value_scales || !a->rope_pages) return BDFP4_E_ARG;
+  if (a->pages < 1 || !a->page_table || !a->seq_lens || a->page_table_stride < 1) return BDFP4_E_ARG;
+  auto misaligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
+  if (misaligned(a->query_codes) || misaligned(a->query_scales) || misaligned(a->query_rope) ||
+      misaligned(a->key_codes) || misaligned(a->key_scales) || misaligned(a->value_codes) ||
+      misaligned(a->value_scales) || misaligned(a->rope_pages))
+    return BDFP4_E_ARG;
+  if (a->key_codes_pitch % 16 || a->key_scales_pitch % 16 || a->value_codes_pitch % 16 ||
+      a->value_scales_pitch % 16 || a->rope_pitch % 16)
+    return BDFP4_E_ARG;
+  if (a->key_codes_pitch < 16384 || a->value_codes_pitch < 16384 || a->key_scales_pitch < 2048 ||
+      a->value_scales_pitch < 2048 || a->rope_pitch < 8192)
+    return BDFP4_E_ARG;
+  if (!(a->softmax_scale > 0.0f) || !isfinite(a->softmax_scale)) return BDFP4_E_ARG;
+  if (a->p_scale_mode < 0 || a->p_scale_mode > 2 || a->num_splits < 1) return BDFP4_E_ARG;
+  const bool writes_out = a->num_splits == 1 && a->out != nullptr;
+  if (!writes_out && (!a->partial_out || !a->partial_lse)) return BDFP4_E_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+
+  mla::Params p{};
+  p.rows = a->rows;
+  p.heads_q = a->heads_q;
+  p.groups = a->heads_q / mla::kHeads;
+  p.q_codes = static_cast<const uint8_t*>(a->query_codes);
+  p.q_scales = static_cast<const uint8_t*>(a->query_scales);
+  p.q_rope = static_cast<const __nv_bfloat16*>(a->query_rope);
+  p.k_codes = static_cast<const uint8_t*>(a->key_codes);
+  p.k_scales = static_cast<const uint8_t*>(a->key_scales);
+  p.v_codes = static_cast<const uint8_t*>(a->value_codes);
+  p.v_scales = static_cast<const uint8_t*>(a->value_scales);
+  p.rope = static_cast<const uint8_t*>(a->rope_pages);
+  p.k_codes_pitch = a->key_codes_pitch;
+  p.k_scales_pitch = a->key_scales_pitch;
+  p.v_codes_pitch = a->value_codes_pitch;
+  p.v_scales_pitch = a->value_scales_pitch;
+  p.rope_pitch = a->rope_pitch;
+  p.pages = a->pages;
+  p.page_table = a->page_table;
+  p.page_table_stride = a->page_table_stride;
+  p.seq_lens = a->seq_lens;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.p_mode = a->p_scale_mode;
+  p.tau = a->p_scale_tau;
+  p.out = writes_out ? static_cast<__nv_bfloat16*>(a->out) : nullptr;
+  p.num_splits = a->num_splits;
+  p.partial_out = a->partial_out;
+  p.partial_lse = a->partial_lse;
+  p.error_word = a->error_word;
+
+  const int smem = (int)sizeof(mla::Smem) + 1024;
+  static PerDeviceOnce configured;
+  const int slot = current_device_slot();
+  if (slot < 0 || !configured.done[slot]) {
+    cudaError_t e = cudaFuncSetAttribute(mla::decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return bdfp4::cuda_status(e);
+    if (slot >= 0) configured.done[slot] = true;
+  }
+  const int64_t grid = (int64_t)a->rows * p.groups * a->num_splits;
+  if (grid > 0x7fffffff) return BDFP4_E_TOO_LARGE;
+  mla::decode_kernel<<<(unsigned)grid, 192, smem, stream>>>(p);
+  return bdfp4::cuda_status(cudaGetLastError());
+}
+
+extern "C" int bdfp4_mla_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
+                                 int32_t heads_q, void* out, void* stream) {
+  if (!partial_out || !partial_lse || !out || parts < 1 || rows < 1 || heads_q < 1) return BDFP4_E_ARG;
+  const int64_t heads = (int64_t)rows * heads_q;
+  if (heads > 0x7fffffff) return BDFP4_E_TOO_LARGE;
+  mla::combine_kernel<<<(unsigned)heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      partial_out, partial_lse, parts, heads, static_cast<__nv_bfloat16*>(out));
+  return bdfp4::cuda_status(cudaGetLastError());
+}

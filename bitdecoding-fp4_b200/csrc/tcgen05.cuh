@@ -170,6 +170,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t address, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Sixteen columns of this thread's lane back into tensor memory.
+__device__ __forceinline__ void tmem_st16(uint32_t address, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16};" ::"r"(address),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+      "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+      "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 template <int N>
 __device__ __forceinline__ void tmem_ld(uint32_t address, float* v) {
   static_assert(N == 4 || N == 8 || N == 16, "supported tcgen05.ld widths");
@@ -183,7 +197,7 @@ __device__ __forceinline__ void tmem_ld(uint32_t address, float* v) {
 // Shared-memory matrix descriptor (64-bit): start address >> 4 in [0,14), leading byte offset >> 4
 // in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48), swizzle mode in
 // [61,64) (0 none, 2 128B, 4 64B, 6 32B).
-constexpr uint64_t kSwizzleNone = 0, kSwizzle64B = 4, kSwizzle32B = 6;
+constexpr uint64_t kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6;
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_address, uint64_t swizzle, uint32_t stride_bytes,
                                               uint32_t leading_bytes) {
@@ -207,6 +221,12 @@ __device__ __forceinline__ uint64_t fp4_half_tile_desc(uint32_t smem_address) {
   return smem_desc(smem_address, kSwizzle32B, 256, 16);
 }
 
+// K-major BF16 operand tile: rows of 128 bytes (64 values), 128-byte swizzle, eight-row groups
+// 1024 bytes apart. `k_step` selects the 16-value slice one kind::f16 MMA consumes (32 bytes).
+__device__ __forceinline__ uint64_t bf16_tile_desc(uint32_t smem_address, int k_step) {
+  return smem_desc(smem_address + k_step * 32, kSwizzle128B, 1024, 16);
+}
+
 // One 512-byte scale-factor atom (32 rows x 16 bytes) as the source of tcgen05.cp 32x128b.
 __device__ __forceinline__ uint64_t sf_atom_desc(uint32_t smem_address) {
   return smem_desc(smem_address, kSwizzleNone, 128, 0);
@@ -220,7 +240,23 @@ __host__ __device__ constexpr uint32_t nvf4_idesc(int m, int n) {
   return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Instruction descriptor of kind::f16 with BF16 operands, FP32 accumulate, both K-major:
+// D format F32 = 1 at [4,6), A/B format BF16 = 1 at [7,10)/[10,13), N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t bf16_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
 // ---- tcgen05 issue (one thread) ---------------------------------------------------------------
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
 
 __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t sfa_tmem, uint32_t sfb_tmem, bool accumulate) {

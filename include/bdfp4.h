@@ -403,6 +403,69 @@ int bdfp4_probability_statistics(const float* scores, int64_t row_stride, int32_
                                  float* page_max_scratch, uint64_t* group_counts, uint64_t* winner_counts,
                                  double* error_sums, double* oracle_sums, void* stream);
 
+/*
+ * MLA latent-cache decode (one compressed KV shared by all query heads). The reference has no
+ * code for it (src/nvfp4_vllm/backend.py:102 only forwards `use_mla`; head_dim is pinned to 128
+ * at backend.py:112-117), so this layout is this library's own:
+ *
+ * A token is a 512-channel latent plus a 64-channel BF16 rope key. The latent is cached twice in
+ * NVFP4, as four 128-channel pseudo heads of 64-token pages written by bdfp4_kv_write with
+ * heads = 4, page_tokens = 64 and the latent given as both `key` and `value`:
+ *   key regions   (scales along channels)  feed the score product  q_latent . latent
+ *   value regions (scales along tokens)    feed the output product P . latent
+ * (a block-scaled MMA needs its scales along the contraction axis, which is the channel axis for
+ * the first product and the token axis for the second). Rope keys are cached in BF16 by
+ * bdfp4_mla_write_rope, one 8 KB block per page: token t's 128 bytes with 16-byte chunk j stored
+ * at position j ^ (t & 7), the shared-memory image the decode kernel's BF16 MMA reads.
+ * Bytes per token: 2 x (256 + 32) + 128 = 704.
+ *
+ * bdfp4_mla_quantize_query: BF16 absorbed query [rows][heads_q][512] (row pitch in elements)
+ *   -> codes [rows][heads_q][256] and E4M3 scales [rows][heads_q][32], scale_mode as the K/V modes.
+ * bdfp4_mla_decode: out[r][h][:] = softmax_t(scale * (q_latent.latent_t + q_rope.rope_t)) . latent,
+ *   BF16 [rows][heads_q][512]; probabilities are quantized per 16 tokens exactly as bdfp4_decode
+ *   does (same stale-maximum rule and p_scale_mode). heads_q must be a multiple of 64. The row's
+ *   page table lists its 64-token pages oldest first; every listed page must have been written in
+ *   full; positions at or past seq_lens[r] are masked. With num_splits > 1 the parts leave FP32
+ *   partials [parts][rows][heads_q][512] and natural-log LSEs [parts][rows][heads_q] for
+ *   bdfp4_mla_combine.
+ */
+typedef struct bdfp4_mla_decode_args {
+  int32_t rows, heads_q;
+  const void* query_codes;  /* u8 [rows][heads_q][256] */
+  const void* query_scales; /* u8 [rows][heads_q][32] */
+  const void* query_rope;   /* BF16 [rows][heads_q][64] */
+  const void* key_codes;    /* the four cache regions of bdfp4_kv_write (heads = 4, page_tokens = 64) */
+  const void* key_scales;
+  const void* value_codes;
+  const void* value_scales;
+  int64_t key_codes_pitch, key_scales_pitch, value_codes_pitch, value_scales_pitch; /* bytes per page */
+  const void* rope_pages;   /* BF16, 8192 bytes per page at rope_pitch bytes */
+  int64_t rope_pitch;
+  int32_t pages;
+  const int32_t* page_table; /* [rows][page_table_stride] 64-token pages, oldest first */
+  int64_t page_table_stride;
+  const int32_t* seq_lens;   /* [rows] tokens */
+  float softmax_scale;
+  int32_t p_scale_mode;      /* BDFP4_P_* */
+  float p_scale_tau;
+  void* out;                 /* BF16 [rows][heads_q][512]; used when num_splits == 1 */
+  int32_t num_splits;
+  float* partial_out;
+  float* partial_lse;
+  int32_t* error_word;
+} bdfp4_mla_decode_args;
+
+int bdfp4_mla_quantize_query(const void* query, int64_t row_pitch, int32_t rows, int32_t heads_q, int32_t scale_mode,
+                             void* codes, void* scales, void* stream);
+/* rope: BF16 [tokens][64] with token_pitch elements between tokens; work item i copies tokens
+ * source_tokens[i] .. +63 into page destination_pages[i] (negative: skipped). */
+int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const int32_t* source_tokens,
+                         const int32_t* destination_pages, int32_t work_items, void* rope_pages, int64_t rope_pitch,
+                         void* stream);
+int bdfp4_mla_decode(const bdfp4_mla_decode_args* args, void* stream);
+int bdfp4_mla_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
+                      int32_t heads_q, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

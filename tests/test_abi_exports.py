@@ -73,8 +73,9 @@ def test_struct_sizes_match_the_header(lib):
 
     import bdfp4
 
-    source = '#include <stdio.h>\n#include "bdfp4.h"\nint main(void){printf("%zu %zu %zu\\n", ' \
-             "sizeof(bdfp4_kv_write_args), sizeof(bdfp4_quantize_query_args), sizeof(bdfp4_decode_args));return 0;}\n"
+    source = '#include <stdio.h>\n#include "bdfp4.h"\nint main(void){printf("%zu %zu %zu %zu\\n", ' \
+             "sizeof(bdfp4_kv_write_args), sizeof(bdfp4_quantize_query_args), sizeof(bdfp4_decode_args), " \
+             "sizeof(bdfp4_mla_decode_args));return 0;}\n"
     with tempfile.TemporaryDirectory() as tmp:
         src = Path(tmp) / "sizes.c"
         src.write_text(source)
@@ -82,4 +83,4 @@ def test_struct_sizes_match_the_header(lib):
         subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
         sizes = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     assert sizes == [ctypes.sizeof(bdfp4.KvWriteArgs), ctypes.sizeof(bdfp4.QuantizeQueryArgs),
-                     ctypes.sizeof(bdfp4.DecodeArgs)]
+                     ctypes.sizeof(bdfp4.DecodeArgs), ctypes.sizeof(bdfp4.MlaDecodeArgs)]
