@@ -7,14 +7,19 @@
 // along channels (the K-side regions of the paged cache) and once with scales along tokens (the
 // V-side regions), because a block-scaled MMA wants its scales along the contraction axis.
 //
-// One CTA serves (row, 64 query heads[, split]) and walks the row's pages two at a time (128
-// tokens per step). Transposed as in the GQA kernel, a softmax thread owns one token:
-//   S^T[token, head]  = sum over 4 chunks  K_chunk[token, :] . Q_chunk[head, :]   8 x mxf4nvf4 (K = 64)
-//                     + rope[token, :] . q_rope[head, :]                           4 x kind::f16 (K = 16)
-//   O^T_chunk[chan, head] += V_chunk^T[chan, :] . P[head, :]                      8 x mxf4nvf4
-// all with M = 128, N = 64. O^T (4 x 64 columns) stays in tensor memory for the whole walk; when a
-// running maximum moves (rarely: the stale-maximum rule tolerates 2^8) the softmax threads rescale
-// it in place between two PV products. Tensor memory: S^T 64 + O^T 256 + scale factors 176 columns.
+// A pair of CTAs serves (row, 128 query heads[, split]); each walks the row's pages two at a time
+// (128 tokens per step), computes all the scores, and accumulates one half of the 512 output
+// channels (128 heads x 512 FP32 is the whole of an SM's tensor memory, and the scores need room
+// too). Query heads are the M rows of every MMA, so a softmax thread owns one head:
+//   S[head, token]  = sum over 4 chunks  Q_chunk[head, :] . K_chunk[token, :]   8 x mxf4nvf4 (N = 128, K = 64)
+//                   + q_rope[head, :] . rope[token, :]                           4 x kind::f16  (N = 128, K = 16)
+//   O[head, chan]  += P[head, :] . V^T[chan, :]                                  2 x mxf4nvf4 (N = 256, K = 64)
+// The thread reads its 128 scores from tensor memory, keeps its own running maximum and sum (no
+// reduction between threads, no barrier), and quantizes its row of probabilities sixteen tokens at
+// a time straight into the shared-memory A operand of the PV product. O (256 columns) stays in
+// tensor memory for the whole walk; when a thread's maximum moves (rarely: the stale-maximum rule
+// tolerates 2^8) its warp rescales its rows in place between two PV products.
+// Tensor memory: S 128 + O 256 + scale factors 112 columns.
 //
 // Warp roles as in the GQA kernel: warp 0 issues the bulk copies (lane 0 the K side, lane 1 the V
 // side), warp 1 interleaves the two pages' K scale blocks into MMA atoms and issues every tcgen05
@@ -29,28 +34,29 @@
 namespace bdfp4 {
 namespace mla {
 
-constexpr int kHeads = 64;    // query heads per CTA: N of every MMA
+constexpr int kHeads = 128;   // query heads per CTA pair: M of every MMA
 constexpr int kChunks = 4;    // 128-channel chunks of the latent
 constexpr int kLatent = 512;
+constexpr int kHalf = 256;    // output channels per CTA
 constexpr int kRope = 64;
 constexpr int kStep = 128;    // tokens per step (two 64-token pages)
 constexpr int kStages = 2;
 constexpr float kRescaleThreshold = 8.0f;
 
-constexpr int kColS = 0;       // 64 columns
-constexpr int kColO = 64;      // 4 chunks x 64
-constexpr int kColSFQ = 320;   // 8 atoms x 4
-constexpr int kColSFK = 352;   // 2 buffers x 8 atoms x 4
-constexpr int kColSFV = 416;   // 2 buffers x 8 atoms x 4
+constexpr int kColS = 0;       // 128 columns
+constexpr int kColO = 128;     // 256 columns
+constexpr int kColSFQ = 384;   // 8 atoms x 4
+constexpr int kColSFK = 416;   // 8 atoms x 4
+constexpr int kColSFV = 448;   // 2 buffers x 2 pages x 2 atoms x 4
 constexpr int kColSFP = 480;   // 2 buffers x 2 atoms x 4
 constexpr int kTmemColumns = 512;
 
 constexpr uint32_t kKeyBytes = kChunks * 8192 + 2 * 8192;  // codes of four chunks + two rope blocks
 constexpr uint32_t kKeyScaleBytes = 4096;
-constexpr uint32_t kValueBytes = 2 * 16384 + 2 * 2048;
+constexpr uint32_t kValueBytes = 2 * (8192 + 1024);        // this CTA's two chunks of two pages
 
 struct Params {
-  int rows, heads_q, groups;
+  int rows, heads_q, head_blocks;
   const uint8_t* q_codes;
   const uint8_t* q_scales;
   const __nv_bfloat16* q_rope;
@@ -75,19 +81,16 @@ struct Params {
 };
 
 struct Smem {
-  alignas(1024) uint8_t k_codes[kStages][kChunks][8192];     // [chunk][page a | page b], 64 B rows, 64 B swizzle
-  alignas(1024) uint8_t rope[kStages][16384];                // 128 tokens x 128 B, 128 B swizzle
-  alignas(1024) uint8_t v_codes[kStages][2][kChunks][4096];  // [page][chunk][128 ch x 32 B], 32 B swizzle
-  alignas(1024) uint8_t k_sf[kStages][4096];                 // two pages' blocks, merged in place into 8 atoms
-  alignas(1024) uint8_t v_sf[kStages][2][kChunks][512];      // [page][chunk] atoms
+  alignas(1024) uint8_t k_codes[kStages][kChunks][8192];  // [chunk][page a | page b], 64 B rows, 64 B swizzle
+  alignas(1024) uint8_t rope[kStages][16384];             // 128 tokens x 128 B, 128 B swizzle
+  alignas(1024) uint8_t v_codes[kStages][2][8192];        // [page][256 ch x 32 B], 32 B swizzle
+  alignas(1024) uint8_t k_sf[kStages][4096];              // two pages' blocks, merged in place into 8 atoms
+  alignas(1024) uint8_t v_sf[kStages][2][1024];           // [page][2 atoms]
   alignas(1024) uint8_t q_tile[kChunks][kHeads * 64];
   alignas(1024) uint8_t q_rope[kHeads * 128];
   alignas(1024) uint8_t q_sf[kChunks * 2][512];
   alignas(1024) uint8_t p_tile[2][kHeads * 64];
   alignas(1024) uint8_t p_sf[2][2][512];
-  float red[4][kHeads];
-  float stat_row_max[kHeads], stat_threshold[kHeads], stat_max_scaled[kHeads], stat_acc[kHeads];
-  float stat_inverse[kHeads];
   uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   uint64_t s_full, s_empty, o_done, p_full[2], p_empty[2];
   int page_ids[2][32];
@@ -107,21 +110,6 @@ __device__ __forceinline__ float rcp_approx(float x) {
   float y;
   asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ bool softmax_vote_any(bool pred) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 p, %1, 0;\n\t"
-      "bar.red.or.pred q, 1, 128, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(out)
-      : "r"((uint32_t)pred)
-      : "memory");
-  return out != 0;
 }
 
 // A bounded wait that leaves its own number in the abort flag when it is the one that ran out of
@@ -161,10 +149,14 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
   const int lane = tid & 31;
 
   // ---- which work ---------------------------------------------------------------------------
-  const int group = blockIdx.x % p.groups;
-  const int row = (blockIdx.x / p.groups) % p.rows;
-  const int part = blockIdx.x / (p.groups * p.rows);
-  const int head0 = group * kHeads;
+  // The two CTAs of a pair are neighbours in the grid, so that they run at the same time and the
+  // second finds in L2 what the first fetched.
+  const int half = blockIdx.x & 1;
+  const int head_block = (blockIdx.x >> 1) % p.head_blocks;
+  const int row = ((blockIdx.x >> 1) / p.head_blocks) % p.rows;
+  const int part = (blockIdx.x >> 1) / (p.head_blocks * p.rows);
+  const int head0 = head_block * kHeads;
+  const int valid_heads = min(kHeads, p.heads_q - head0);
   const int seq_len = max(p.seq_lens[row], 0);
   const int entries = (seq_len + 63) / 64;
   const int total_steps = (seq_len + kStep - 1) / kStep;
@@ -192,26 +184,26 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
     sm.abort_flag = 0;
     tc::fence_barrier_init();
   }
-  // zero the scale-atom buffers the kernel writes only in part
-  for (int i = tid; i < (int)(sizeof(sm.q_sf) / 16); i += 192) reinterpret_cast<uint4*>(sm.q_sf)[i] = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < (int)(sizeof(sm.p_sf) / 16); i += 192) reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
-  __syncthreads();
-  // query operands: codes (16 chunks of 16 bytes per head), scales (8 words per head), rope (8 chunks)
+  // query operands: codes (16 chunks of 16 bytes per head), scales (8 words per head), rope (8
+  // chunks); rows past the last head stay zero
   {
     const int64_t head_base = (int64_t)row * p.heads_q + head0;
     for (int i = tid; i < kHeads * 16; i += 192) {
       const int h = i >> 4, c = i & 15;
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q_codes + (head_base + h) * 256) + c);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h < valid_heads) v = __ldg(reinterpret_cast<const uint4*>(p.q_codes + (head_base + h) * 256) + c);
       *reinterpret_cast<uint4*>(sm.q_tile[c >> 2] + swizzle64(h * 64 + (c & 3) * 16)) = v;
     }
     for (int i = tid; i < kHeads * 8; i += 192) {
       const int h = i >> 3, a = i & 7;
-      const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(p.q_scales + (head_base + h) * 32) + a);
+      uint32_t v = 0;
+      if (h < valid_heads) v = __ldg(reinterpret_cast<const uint32_t*>(p.q_scales + (head_base + h) * 32) + a);
       *reinterpret_cast<uint32_t*>(sm.q_sf[a] + (h & 31) * 16 + (h >> 5) * 4) = v;
     }
     for (int i = tid; i < kHeads * 8; i += 192) {
       const int h = i >> 3, c = i & 7;
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q_rope + (head_base + h) * kRope) + c);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h < valid_heads) v = __ldg(reinterpret_cast<const uint4*>(p.q_rope + (head_base + h) * kRope) + c);
       *reinterpret_cast<uint4*>(sm.q_rope + h * 128 + ((c ^ (h & 7)) << 4)) = v;
     }
   }
@@ -279,8 +271,10 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
               tc::mbar_expect_tx(&sm.v_full[s], kValueBytes);
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
-                tc::bulk_load(sm.v_codes[s][e], p.v_codes + (int64_t)page[e] * p.v_codes_pitch, 16384, &sm.v_full[s]);
-                tc::bulk_load(sm.v_sf[s][e], p.v_scales + (int64_t)page[e] * p.v_scales_pitch, 2048, &sm.v_full[s]);
+                tc::bulk_load(sm.v_codes[s][e], p.v_codes + (int64_t)page[e] * p.v_codes_pitch + half * 8192, 8192,
+                              &sm.v_full[s]);
+                tc::bulk_load(sm.v_sf[s][e], p.v_scales + (int64_t)page[e] * p.v_scales_pitch + half * 1024, 1024,
+                              &sm.v_full[s]);
               }
             }
           }
@@ -310,8 +304,9 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
   } else if (warp == 1) {
     // ---- MMA issuer ---------------------------------------------------------------------------
     const bool issuer = lane == 0;
-    constexpr uint32_t idesc_fp4 = tc::nvf4_idesc(128, kHeads);
-    constexpr uint32_t idesc_bf16 = tc::bf16_idesc(128, kHeads);
+    constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, kStep);
+    constexpr uint32_t idesc_rope = tc::bf16_idesc(128, kStep);
+    constexpr uint32_t idesc_pv = tc::nvf4_idesc(128, kHalf);
     if (num_steps > 0) {
       if (issuer) {
 #pragma unroll
@@ -325,20 +320,16 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
         if (!wait_at(4, &sm.p_full[b], (m >> 1) & 1, abort_flag)) return false;
         tc::fence_after_sync();
 #pragma unroll
-        for (int a = 0; a < 2 * kChunks; ++a)
-          tc::cp_sf_atom(tmem + kColSFV + 32 * b + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.v_sf[s][0][0]) + a * 512));
+        for (int a = 0; a < 4; ++a)  // [page][atom of chunk 0, atom of chunk 1]
+          tc::cp_sf_atom(tmem + kColSFV + 16 * b + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.v_sf[s][0]) + a * 512));
 #pragma unroll
         for (int e = 0; e < 2; ++e)
           tc::cp_sf_atom(tmem + kColSFP + 8 * b + 4 * e, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b][e])));
         const uint32_t p_addr = tc::smem_u32(sm.p_tile[b]);
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e)
-            tc::mma_nvf4(tmem + kColO + kHeads * c, tc::fp4_half_tile_desc(tc::smem_u32(sm.v_codes[s][e][c])),
-                         tc::fp4_tile_desc(p_addr, e), idesc_fp4, tmem + kColSFV + 32 * b + 4 * (e * kChunks + c),
-                         tmem + kColSFP + 8 * b + 4 * e, m > 0 || e > 0);
-        }
+        for (int e = 0; e < 2; ++e)
+          tc::mma_nvf4(tmem + kColO, tc::fp4_tile_desc(p_addr, e), tc::fp4_half_tile_desc(tc::smem_u32(sm.v_codes[s][e])),
+                       idesc_pv, tmem + kColSFP + 8 * b + 4 * e, tmem + kColSFV + 16 * b + 8 * e, m > 0 || e > 0);
         tc::commit(&sm.o_done);
         tc::commit(&sm.v_empty[s]);
         tc::commit(&sm.p_empty[b]);
@@ -347,7 +338,6 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
       bool ok = true;
       for (int i = 0; i < num_steps && ok; ++i) {
         const int s = i % kStages;
-        const int b = i & 1;
         ok = wait_at(5, &sm.ksf_full[s], (i / kStages) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -371,27 +361,25 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
         }
         if (issuer) {
           ok = wait_at(6, &sm.k_full[s], (i / kStages) & 1, abort_flag);
+          // the scores of the previous step have been read: S and the K scale columns are free
+          if (ok) ok = wait_at(7, &sm.s_empty, (i & 1) ^ 1, abort_flag);
           if (ok) {
             tc::fence_after_sync();
 #pragma unroll
             for (int a = 0; a < 2 * kChunks; ++a)
-              tc::cp_sf_atom(tmem + kColSFK + 32 * b + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.k_sf[s]) + a * 512));
-            ok = wait_at(7, &sm.s_empty, (i & 1) ^ 1, abort_flag);
-          }
-          if (ok) {
-            tc::fence_after_sync();
+              tc::cp_sf_atom(tmem + kColSFK + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.k_sf[s]) + a * 512));
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
               for (int k = 0; k < 2; ++k)
-                tc::mma_nvf4(tmem + kColS, tc::fp4_tile_desc(tc::smem_u32(sm.k_codes[s][c]), k),
-                             tc::fp4_tile_desc(tc::smem_u32(sm.q_tile[c]), k), idesc_fp4,
-                             tmem + kColSFK + 32 * b + 4 * (2 * c + k), tmem + kColSFQ + 4 * (2 * c + k), (c | k) != 0);
+                tc::mma_nvf4(tmem + kColS, tc::fp4_tile_desc(tc::smem_u32(sm.q_tile[c]), k),
+                             tc::fp4_tile_desc(tc::smem_u32(sm.k_codes[s][c]), k), idesc_qk,
+                             tmem + kColSFQ + 4 * (2 * c + k), tmem + kColSFK + 4 * (2 * c + k), (c | k) != 0);
             }
 #pragma unroll
             for (int k = 0; k < kRope / 16; ++k)
-              tc::mma_bf16(tmem + kColS, tc::bf16_tile_desc(tc::smem_u32(sm.rope[s]), k),
-                           tc::bf16_tile_desc(tc::smem_u32(sm.q_rope), k), idesc_bf16, true);
+              tc::mma_bf16(tmem + kColS, tc::bf16_tile_desc(tc::smem_u32(sm.q_rope), k),
+                           tc::bf16_tile_desc(tc::smem_u32(sm.rope[s]), k), idesc_rope, true);
             tc::commit(&sm.s_full);
             tc::commit(&sm.k_empty[s]);
             if (i > 0) ok = issue_pv(i - 1);
@@ -402,171 +390,140 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
       if (issuer && ok) issue_pv(num_steps - 1);
     }
   } else {
-    // ---- softmax --------------------------------------------------------------------------------
+    // ---- softmax: one thread per query head ---------------------------------------------------
     const int warp_q = warp & 3;
-    const int t = warp_q * 32 + lane;  // token (S^T lane) and channel (O^T lane) of this thread
+    const int h = warp_q * 32 + lane;  // head = TMEM lane of S and O
     const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
     const float shift = p.p_mode == BDFP4_P_AMAX2_OR_AMAX6_C8 ? 3.0f : 0.0f;
     const float headroom = kRescaleThreshold / p.scale_log2;
-    float row_sum[kHeads];
-#pragma unroll
-    for (int j = 0; j < kHeads; ++j) row_sum[j] = 0.0f;
-    if (t < kHeads) {
-      sm.stat_row_max[t] = -INFINITY;
-      sm.stat_threshold[t] = -INFINITY;
-      sm.stat_max_scaled[t] = 0.0f;
-      sm.stat_acc[t] = 1.0f;
-    }
-    softmax_barrier();
-    const int token_group = t >> 4;
-    const int sf_base = (token_group >> 2) * 512 + (token_group & 3);
+    float row_max = -INFINITY, row_sum = 0.0f, max_scaled = 0.0f;
+    const int p_row = h * 64;
+    const int sf_row = (h & 31) * 16 + (h >> 5) * 4;
 
     for (int i = 0; i < num_steps; ++i) {
       const int b = i & 1;
       const int step = last_step - 1 - i;
       wait_at(8, &sm.s_full, i & 1, abort_flag);
       tc::fence_after_sync();
-      float s[kHeads];
+      float s[kStep];
 #pragma unroll
-      for (int q = 0; q < kHeads / 16; ++q) tc::tmem_ld16(lane_base + kColS + 16 * q, s + 16 * q);
+      for (int q = 0; q < kStep / 16; ++q) tc::tmem_ld16(lane_base + kColS + 16 * q, s + 16 * q);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       tc::mbar_arrive(&sm.s_empty);
-      if (step * kStep + t >= seq_len) {
+      const int valid = seq_len - step * kStep;  // only the row's last step can be short
+      if (valid < kStep) {
 #pragma unroll
-        for (int j = 0; j < kHeads; ++j) s[j] = -INFINITY;
+        for (int k = 0; k < kStep; ++k) s[k] = k < valid ? s[k] : -INFINITY;
       }
-      // does any head's maximum have to move? one predicate per thread, one barrier-wide OR
-      bool own = i == 0 || *abort_flag != 0;
+      float block_max = s[0];
 #pragma unroll
-      for (int j = 0; j < kHeads; ++j) own = own || s[j] > sm.stat_threshold[j];
-      const bool grows = softmax_vote_any(own);
-      if (grows) {
-#pragma unroll
-        for (int j = 0; j < kHeads; ++j) {
-          float m = s[j];
-#pragma unroll
-          for (int d = 1; d < 32; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-          if (lane == (j & 31)) sm.red[warp_q][j] = m;
+      for (int k = 1; k < kStep; ++k) block_max = fmaxf(block_max, s[k]);
+      // the stale-maximum rule, per head
+      float acc = 1.0f;
+      if (i == 0) {
+        row_max = block_max;
+        acc = 0.0f;
+      } else if (block_max > row_max) {
+        const float safe = block_max == -INFINITY ? 0.0f : block_max;
+        const float growth = (row_max - safe) * p.scale_log2;
+        if (growth < -kRescaleThreshold) {
+          acc = ex2_approx(growth);
+          row_max = block_max;
         }
-        softmax_barrier();
-        if (t < kHeads) {
-          const float block_max = fmaxf(fmaxf(sm.red[0][t], sm.red[1][t]), fmaxf(sm.red[2][t], sm.red[3][t]));
-          float new_max, safe, acc;
-          if (i == 0) {
-            new_max = block_max;
-            safe = new_max == -INFINITY ? 0.0f : new_max;
-            acc = 0.0f;
-          } else {
-            const float old_max = sm.stat_row_max[t];
-            new_max = fmaxf(old_max, block_max);
-            safe = new_max == -INFINITY ? 0.0f : new_max;
-            const float growth = (old_max - safe) * p.scale_log2;
-            if (growth >= -kRescaleThreshold) {
-              new_max = old_max;
-              safe = old_max;
-              acc = 1.0f;
-            } else {
-              acc = ex2_approx(growth);
-            }
-          }
-          sm.stat_row_max[t] = new_max;
-          sm.stat_max_scaled[t] = safe * p.scale_log2 - shift;
-          sm.stat_threshold[t] = new_max + headroom;
-          sm.stat_acc[t] = acc;
-        }
-        softmax_barrier();
-        if (i > 0) {
-          // O^T so far is rescaled in tensor memory. Every earlier PV product has completed once
-          // the previous step's has, and the next one is not issued before this step's P arrives.
-          wait_at(9, &sm.o_done, (i - 1) & 1, abort_flag);
-          tc::fence_after_sync();
+      }
+      max_scaled = (row_max == -INFINITY ? 0.0f : row_max) * p.scale_log2 - shift;
+      // Every PV product's completion is observed in turn (a parity wait can only tell the current
+      // phase from the one before it): here when a row of this warp has to be rescaled, else below.
+      const bool rescale = i > 0 && __any_sync(0xffffffffu, acc != 1.0f);
+      if (rescale) {
+        // O so far is rescaled in tensor memory. Every earlier PV product has completed once the
+        // previous step's has, and the next one is not issued before this step's P arrives.
+        wait_at(9, &sm.o_done, (i - 1) & 1, abort_flag);
+        tc::fence_after_sync();
 #pragma unroll 1
-          for (int c = 0; c < kChunks; ++c) {
+        for (int q = 0; q < kHalf / 16; ++q) {
+          float o[16];
+          tc::tmem_ld16(lane_base + kColO + 16 * q, o);
+          tc::tmem_wait_ld();
 #pragma unroll
-            for (int q = 0; q < kHeads / 16; ++q) {
-              float o[16];
-              tc::tmem_ld16(lane_base + kColO + kHeads * c + 16 * q, o);
-              tc::tmem_wait_ld();
-#pragma unroll
-              for (int k = 0; k < 16; ++k) o[k] *= sm.stat_acc[16 * q + k];
-              tc::tmem_st16(lane_base + kColO + kHeads * c + 16 * q, o);
-            }
-          }
-          tc::tmem_wait_st();
-          tc::fence_before_sync();
-#pragma unroll
-          for (int j = 0; j < kHeads; ++j) row_sum[j] *= sm.stat_acc[j];
+          for (int k = 0; k < 16; ++k) o[k] *= acc;
+          tc::tmem_st16(lane_base + kColO + 16 * q, o);
         }
+        tc::tmem_wait_st();
+        tc::fence_before_sync();
       }
+      row_sum *= acc;
       // the PV product of two steps ago must be done with this P buffer
       wait_at(10, &sm.p_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
+      uint32_t scale_words[2] = {0, 0};
 #pragma unroll
-      for (int j = 0; j < kHeads; ++j) {
-        const float prob = ex2_approx(fmaf(s[j], p.scale_log2, -sm.stat_max_scaled[j]));
-        row_sum[j] += prob;
-        float maximum = prob;
+      for (int g = 0; g < kStep / 16; ++g) {
+        float prob[16];
+        float maximum = 0.0f;
 #pragma unroll
-        for (int d = 1; d < 16; d <<= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
+        for (int k = 0; k < 16; ++k) {
+          prob[k] = ex2_approx(fmaf(s[16 * g + k], p.scale_log2, -max_scaled));
+          row_sum += prob[k];
+          maximum = fmaxf(maximum, prob[k]);
+        }
         const float scale = probability_scale(maximum, p.p_mode, p.tau);
-        const float q = prob * rcp_approx(fmaxf(scale, 1e-20f));
-        uint32_t word = (cvt_e2m1x2(q, 0.0f) & 0xfu) << (4 * (lane & 7));
-        word |= __shfl_xor_sync(0xffffffffu, word, 1);
-        word |= __shfl_xor_sync(0xffffffffu, word, 2);
-        word |= __shfl_xor_sync(0xffffffffu, word, 4);
-        if ((lane & 7) == (j & 7)) *reinterpret_cast<uint32_t*>(sm.p_tile[b] + swizzle64(j * 64 + (t >> 3) * 4)) = word;
-        if ((lane & 15) == (j & 15)) sm.p_sf[b][0][sf_base + (j & 31) * 16 + (j >> 5) * 4] = (uint8_t)cvt_e4m3(scale);
+        const float inverse = rcp_approx(fmaxf(scale, 1e-20f));
+        uint32_t words[2] = {0, 0};
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          words[k >> 2] |= cvt_e2m1x2(prob[2 * k] * inverse, prob[2 * k + 1] * inverse) << (8 * (k & 3));
+        *reinterpret_cast<uint2*>(sm.p_tile[b] + swizzle64(p_row + g * 8)) = make_uint2(words[0], words[1]);
+        scale_words[g >> 2] |= cvt_e4m3(scale) << (8 * (g & 3));
       }
+      *reinterpret_cast<uint32_t*>(sm.p_sf[b][0] + sf_row) = scale_words[0];
+      *reinterpret_cast<uint32_t*>(sm.p_sf[b][1] + sf_row) = scale_words[1];
       tc::fence_proxy_async_smem();
-      // Every PV product's completion is observed in turn (a parity wait can only tell the current
-      // phase from the one before it): the previous step's here, unless the rescale above already did.
-      if (i > 0 && !grows) wait_at(11, &sm.o_done, (i - 1) & 1, abort_flag);
+      if (i > 0 && !rescale) wait_at(11, &sm.o_done, (i - 1) & 1, abort_flag);
       tc::mbar_arrive(&sm.p_full[b]);
     }
 
     // ---- normalise and write ------------------------------------------------------------------
-#pragma unroll
-    for (int j = 0; j < kHeads; ++j) {
-      float v = row_sum[j];
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-      if (lane == (j & 31)) sm.red[warp_q][j] = v;
+    const bool empty = num_steps == 0 || row_sum == 0.0f || row_sum != row_sum;
+    const float inverse = empty ? 0.0f : 1.0f / row_sum;
+    const int64_t head = (int64_t)row * p.heads_q + head0 + h;
+    if (p.out == nullptr && half == 0 && h < valid_heads) {
+      const float safe = row_max == -INFINITY ? 0.0f : row_max;
+      p.partial_lse[(int64_t)part * p.rows * p.heads_q + head] =
+          empty ? -INFINITY : (safe * p.scale_log2 + log2f(row_sum) - shift) * 0.6931471805599453f;
     }
-    softmax_barrier();
-    if (t < kHeads) {
-      const float total = (sm.red[0][t] + sm.red[1][t]) + (sm.red[2][t] + sm.red[3][t]);
-      const bool empty = num_steps == 0 || total == 0.0f || total != total;
-      sm.stat_inverse[t] = empty ? 0.0f : 1.0f / total;
-      if (p.out == nullptr) {
-        const float row_max = sm.stat_row_max[t];
-        const float safe = row_max == -INFINITY ? 0.0f : row_max;
-        p.partial_lse[((int64_t)part * p.rows + row) * p.heads_q + head0 + t] =
-            empty ? -INFINITY : (safe * p.scale_log2 + log2f(total) - shift) * 0.6931471805599453f;
-      }
-    }
-    softmax_barrier();
     if (num_steps > 0) {
       wait_at(12, &sm.o_done, (num_steps - 1) & 1, abort_flag);
       tc::fence_after_sync();
     }
 #pragma unroll 1
-    for (int c = 0; c < kChunks; ++c) {
-#pragma unroll 1
-      for (int q = 0; q < kHeads / 16; ++q) {
-        float o[16];
-        if (num_steps > 0) {
-          tc::tmem_ld16(lane_base + kColO + kHeads * c + 16 * q, o);
-          tc::tmem_wait_ld();
-        }
+    for (int q = 0; q < kHalf / 16; ++q) {
+      float o[16];
+      if (num_steps > 0) {
+        tc::tmem_ld16(lane_base + kColO + 16 * q, o);
+        tc::tmem_wait_ld();
+      }
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const float inverse = sm.stat_inverse[16 * q + k];
-          const float value = inverse == 0.0f ? 0.0f : o[k] * inverse;
-          const int64_t head = (int64_t)row * p.heads_q + head0 + 16 * q + k;
-          if (p.out != nullptr)
-            p.out[head * kLatent + c * 128 + t] = __float2bfloat16_rn(value);
-          else
-            p.partial_out[((int64_t)part * p.rows * p.heads_q + head) * kLatent + c * 128 + t] = value;
+      for (int k = 0; k < 16; ++k) o[k] = empty ? 0.0f : o[k] * inverse;
+      if (h < valid_heads) {
+        if (p.out != nullptr) {
+          uint4 lo, hi;
+          lo.x = pack_bf16x2(o[0], o[1]);
+          lo.y = pack_bf16x2(o[2], o[3]);
+          lo.z = pack_bf16x2(o[4], o[5]);
+          lo.w = pack_bf16x2(o[6], o[7]);
+          hi.x = pack_bf16x2(o[8], o[9]);
+          hi.y = pack_bf16x2(o[10], o[11]);
+          hi.z = pack_bf16x2(o[12], o[13]);
+          hi.w = pack_bf16x2(o[14], o[15]);
+          uint4* dst = reinterpret_cast<uint4*>(p.out + head * kLatent + half * kHalf + 16 * q);
+          dst[0] = lo;
+          dst[1] = hi;
+        } else {
+          float4* dst = reinterpret_cast<float4*>(p.partial_out + ((int64_t)part * p.rows * p.heads_q + head) * kLatent +
+                                                  half * kHalf + 16 * q);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) dst[k] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
         }
       }
     }
@@ -681,7 +638,7 @@ extern "C" int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const
 extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_handle) {
   if (!a) return BDFP4_E_ARG;
   if (a->rows < 1 || a->heads_q < 1) return BDFP4_E_ARG;
-  if (a->heads_q % mla::kHeads) return BDFP4_E_UNSUPPORTED;
+  if (a->heads_q % 64) return BDFP4_E_UNSUPPORTED;
   if (!a->query_codes || !a->query_scales || !a->query_rope) return BDFP4_E_ARG;
   if (!a->key_codes || !a->key_scales || !a->value_codes || !a->value_scales || !a->rope_pages) return BDFP4_E_ARG;
   if (a->pages < 1 || !a->page_table || !a->seq_lens || a->page_table_stride < 1) return BDFP4_E_ARG;
@@ -705,7 +662,7 @@ extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_han
   mla::Params p{};
   p.rows = a->rows;
   p.heads_q = a->heads_q;
-  p.groups = a->heads_q / mla::kHeads;
+  p.head_blocks = (a->heads_q + mla::kHeads - 1) / mla::kHeads;
   p.q_codes = static_cast<const uint8_t*>(a->query_codes);
   p.q_scales = static_cast<const uint8_t*>(a->query_scales);
   p.q_rope = static_cast<const __nv_bfloat16*>(a->query_rope);
@@ -740,7 +697,7 @@ extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_han
     if (e != cudaSuccess) return bdfp4::cuda_status(e);
     if (slot >= 0) configured.done[slot] = true;
   }
-  const int64_t grid = (int64_t)a->rows * p.groups * a->num_splits;
+  const int64_t grid = (int64_t)a->rows * p.head_blocks * a->num_splits * 2;
   if (grid > 0x7fffffff) return BDFP4_E_TOO_LARGE;
   mla::decode_kernel<<<(unsigned)grid, 192, smem, stream>>>(p);
   return bdfp4::cuda_status(cudaGetLastError());
