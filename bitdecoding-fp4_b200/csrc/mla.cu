@@ -41,6 +41,11 @@ constexpr int kHalf = 256;    // output channels per CTA
 constexpr int kRope = 64;
 constexpr int kStep = 128;    // tokens per step (two 64-token pages)
 constexpr int kStages = 2;
+constexpr int kSoftmaxGroups = 4;                   // softmax threads per head
+constexpr int kRun = kStep / kSoftmaxGroups;        // tokens of a step one softmax thread owns
+constexpr int kShare = kHalf / kSoftmaxGroups;      // output columns one softmax thread rescales and writes
+constexpr int kSoftmaxThreads = 128 * kSoftmaxGroups;
+constexpr int kThreads = 64 + kSoftmaxThreads;
 constexpr float kRescaleThreshold = 8.0f;
 
 constexpr int kColS = 0;       // 128 columns
@@ -91,6 +96,7 @@ struct Smem {
   alignas(1024) uint8_t q_sf[kChunks * 2][512];
   alignas(1024) uint8_t p_tile[2][kHeads * 64];
   alignas(1024) uint8_t p_sf[2][2][512];
+  float red[2][kSoftmaxGroups][kHeads];  // per-head values exchanged between a head's softmax threads
   uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   uint64_t s_full, s_empty, o_done, p_full[2], p_empty[2];
   int page_ids[2][32];
@@ -102,13 +108,13 @@ static_assert(sizeof(Smem) + 1024 <= 232448, "one CTA's shared memory (227 KB op
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
 __device__ __forceinline__ float rcp_approx(float x) {
   float y;
-  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
@@ -132,6 +138,23 @@ __device__ __forceinline__ bool wait_at(int site, uint64_t* bar, uint32_t parity
   }
 }
 
+__device__ __forceinline__ void softmax_barrier() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+}
+
+__device__ __forceinline__ bool softmax_vote_any(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"((uint32_t)pred), "n"(kSoftmaxThreads)
+      : "memory");
+  return out != 0;
+}
+
 __device__ __forceinline__ int swizzle64(int offset) { return offset ^ (((offset >> 7) & 3) << 4); }
 
 // Scale of one group of sixteen probabilities from its maximum (the rule of the GQA kernel).
@@ -141,7 +164,7 @@ __device__ __forceinline__ float probability_scale(float maximum, int p_mode, fl
   return scale;
 }
 
-__global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x;
@@ -175,10 +198,10 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
       tc::mbar_init(&sm.v_empty[s], 1);
     }
     tc::mbar_init(&sm.s_full, 1);
-    tc::mbar_init(&sm.s_empty, 128);
+    tc::mbar_init(&sm.s_empty, kSoftmaxThreads);
     tc::mbar_init(&sm.o_done, 1);
     for (int b = 0; b < 2; ++b) {
-      tc::mbar_init(&sm.p_full[b], 128);
+      tc::mbar_init(&sm.p_full[b], kSoftmaxThreads);
       tc::mbar_init(&sm.p_empty[b], 1);
     }
     sm.abort_flag = 0;
@@ -188,19 +211,19 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
   // chunks); rows past the last head stay zero
   {
     const int64_t head_base = (int64_t)row * p.heads_q + head0;
-    for (int i = tid; i < kHeads * 16; i += 192) {
+    for (int i = tid; i < kHeads * 16; i += kThreads) {
       const int h = i >> 4, c = i & 15;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (h < valid_heads) v = __ldg(reinterpret_cast<const uint4*>(p.q_codes + (head_base + h) * 256) + c);
       *reinterpret_cast<uint4*>(sm.q_tile[c >> 2] + swizzle64(h * 64 + (c & 3) * 16)) = v;
     }
-    for (int i = tid; i < kHeads * 8; i += 192) {
+    for (int i = tid; i < kHeads * 8; i += kThreads) {
       const int h = i >> 3, a = i & 7;
       uint32_t v = 0;
       if (h < valid_heads) v = __ldg(reinterpret_cast<const uint32_t*>(p.q_scales + (head_base + h) * 32) + a);
       *reinterpret_cast<uint32_t*>(sm.q_sf[a] + (h & 31) * 16 + (h >> 5) * 4) = v;
     }
-    for (int i = tid; i < kHeads * 8; i += 192) {
+    for (int i = tid; i < kHeads * 8; i += kThreads) {
       const int h = i >> 3, c = i & 7;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (h < valid_heads) v = __ldg(reinterpret_cast<const uint4*>(p.q_rope + (head_base + h) * kRope) + c);
@@ -390,122 +413,166 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
       if (issuer && ok) issue_pv(num_steps - 1);
     }
   } else {
-    // ---- softmax: one thread per query head ---------------------------------------------------
-    const int warp_q = warp & 3;
-    const int h = warp_q * 32 + lane;  // head = TMEM lane of S and O
+    // ---- softmax: kSoftmaxGroups threads per query head, each owning a run of the step's tokens ---
+    const int warp_q = warp & 3;            // TMEM lane quarter this warp may read
+    const int wg = (warp - 2) >> 2;         // which run of kRun tokens of every step
+    const int h = warp_q * 32 + lane;       // head = TMEM lane of S and O
     const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
     const float shift = p.p_mode == BDFP4_P_AMAX2_OR_AMAX6_C8 ? 3.0f : 0.0f;
-    const float headroom = kRescaleThreshold / p.scale_log2;
+    // A probability this large against the stale maximum means the maximum may have to move; the
+    // trigger is a little below the rule's 2^8 so that the rule itself is only ever applied to the
+    // exact scores (the slow path), never to an approximate exponential.
+    const float trigger_above = exp2f(kRescaleThreshold - 0.25f + shift);
     float row_max = -INFINITY, row_sum = 0.0f, max_scaled = 0.0f;
     const int p_row = h * 64;
     const int sf_row = (h & 31) * 16 + (h >> 5) * 4;
+    constexpr int kRunGroups = kRun / 16;
 
     for (int i = 0; i < num_steps; ++i) {
       const int b = i & 1;
       const int step = last_step - 1 - i;
       wait_at(8, &sm.s_full, i & 1, abort_flag);
       tc::fence_after_sync();
-      float s[kStep];
+      float s[kRun];
 #pragma unroll
-      for (int q = 0; q < kStep / 16; ++q) tc::tmem_ld16(lane_base + kColS + 16 * q, s + 16 * q);
+      for (int q = 0; q < kRunGroups; ++q) tc::tmem_ld16(lane_base + kColS + wg * kRun + 16 * q, s + 16 * q);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       tc::mbar_arrive(&sm.s_empty);
-      const int valid = seq_len - step * kStep;  // only the row's last step can be short
-      if (valid < kStep) {
+      const int valid = seq_len - step * kStep - wg * kRun;  // only the row's last step can be short
+      if (valid < kRun) {
 #pragma unroll
-        for (int k = 0; k < kStep; ++k) s[k] = k < valid ? s[k] : -INFINITY;
+        for (int k = 0; k < kRun; ++k) s[k] = k < valid ? s[k] : -INFINITY;
       }
-      float block_max = s[0];
+      float prob[kRun], group_sum[kRunGroups], group_max[kRunGroups];
+      auto form_probabilities = [&]() {
 #pragma unroll
-      for (int k = 1; k < kStep; ++k) block_max = fmaxf(block_max, s[k]);
-      // the stale-maximum rule, per head
-      float acc = 1.0f;
-      if (i == 0) {
-        row_max = block_max;
-        acc = 0.0f;
-      } else if (block_max > row_max) {
-        const float safe = block_max == -INFINITY ? 0.0f : block_max;
-        const float growth = (row_max - safe) * p.scale_log2;
-        if (growth < -kRescaleThreshold) {
-          acc = ex2_approx(growth);
+        for (int g = 0; g < kRunGroups; ++g) {
+          float* pg = prob + 16 * g;
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pg[k] = ex2_approx(fmaf(s[16 * g + k], p.scale_log2, -max_scaled));
+          // sums and maxima as trees: few warps share a scheduler, so a serial chain is paid in full
+          float sum4[4], max4[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            sum4[k] = (pg[k] + pg[k + 4]) + (pg[k + 8] + pg[k + 12]);
+            max4[k] = fmaxf(fmaxf(pg[k], pg[k + 4]), fmaxf(pg[k + 8], pg[k + 12]));
+          }
+          group_sum[g] = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+          group_max[g] = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
+        }
+      };
+      form_probabilities();  // against the stale maximum: almost always the final ones
+      bool trigger = i == 0 || *abort_flag != 0;
+#pragma unroll
+      for (int g = 0; g < kRunGroups; ++g) trigger = trigger || group_max[g] > trigger_above;
+      bool observed = false;  // whether this step has already waited for the previous PV product
+      if (softmax_vote_any(trigger)) {
+        // the stale-maximum rule on the exact scores, identically in every thread of a head
+        float run_max = s[0];
+#pragma unroll
+        for (int k = 1; k < kRun; ++k) run_max = fmaxf(run_max, s[k]);
+        sm.red[i & 1][wg][h] = run_max;
+        softmax_barrier();
+        float block_max = sm.red[i & 1][0][h];
+#pragma unroll
+        for (int w = 1; w < kSoftmaxGroups; ++w) block_max = fmaxf(block_max, sm.red[i & 1][w][h]);
+        float acc = 1.0f;
+        if (i == 0) {
           row_max = block_max;
+          acc = 0.0f;
+        } else if (block_max > row_max) {
+          const float safe = block_max == -INFINITY ? 0.0f : block_max;
+          const float growth = (row_max - safe) * p.scale_log2;
+          if (growth < -kRescaleThreshold) {
+            acc = ex2_approx(growth);
+            row_max = block_max;
+          }
         }
-      }
-      max_scaled = (row_max == -INFINITY ? 0.0f : row_max) * p.scale_log2 - shift;
-      // Every PV product's completion is observed in turn (a parity wait can only tell the current
-      // phase from the one before it): here when a row of this warp has to be rescaled, else below.
-      const bool rescale = i > 0 && __any_sync(0xffffffffu, acc != 1.0f);
-      if (rescale) {
-        // O so far is rescaled in tensor memory. Every earlier PV product has completed once the
-        // previous step's has, and the next one is not issued before this step's P arrives.
-        wait_at(9, &sm.o_done, (i - 1) & 1, abort_flag);
-        tc::fence_after_sync();
+        max_scaled = (row_max == -INFINITY ? 0.0f : row_max) * p.scale_log2 - shift;
+        if (i > 0 && __any_sync(0xffffffffu, acc != 1.0f)) {
+          // O so far is rescaled in tensor memory, each thread of a head taking its share of the
+          // columns. Every earlier PV product has completed once the previous step's has, and the
+          // next one is not issued before this step's P has arrived from every thread.
+          wait_at(9, &sm.o_done, (i - 1) & 1, abort_flag);
+          observed = true;
+          tc::fence_after_sync();
 #pragma unroll 1
-        for (int q = 0; q < kHalf / 16; ++q) {
-          float o[16];
-          tc::tmem_ld16(lane_base + kColO + 16 * q, o);
-          tc::tmem_wait_ld();
+          for (int q = 0; q < kShare / 16; ++q) {
+            float o[16];
+            tc::tmem_ld16(lane_base + kColO + wg * kShare + 16 * q, o);
+            tc::tmem_wait_ld();
 #pragma unroll
-          for (int k = 0; k < 16; ++k) o[k] *= acc;
-          tc::tmem_st16(lane_base + kColO + 16 * q, o);
+            for (int k = 0; k < 16; ++k) o[k] *= acc;
+            tc::tmem_st16(lane_base + kColO + wg * kShare + 16 * q, o);
+          }
+          tc::tmem_wait_st();
+          tc::fence_before_sync();
         }
-        tc::tmem_wait_st();
-        tc::fence_before_sync();
+        row_sum *= acc;
+        form_probabilities();
       }
-      row_sum *= acc;
+#pragma unroll
+      for (int g = 0; g < kRunGroups; ++g) row_sum += group_sum[g];
       // the PV product of two steps ago must be done with this P buffer
       wait_at(10, &sm.p_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
-      uint32_t scale_words[2] = {0, 0};
+      uint32_t scale_bytes = 0;
 #pragma unroll
-      for (int g = 0; g < kStep / 16; ++g) {
-        float prob[16];
-        float maximum = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          prob[k] = ex2_approx(fmaf(s[16 * g + k], p.scale_log2, -max_scaled));
-          row_sum += prob[k];
-          maximum = fmaxf(maximum, prob[k]);
-        }
-        const float scale = probability_scale(maximum, p.p_mode, p.tau);
+      for (int g = 0; g < kRunGroups; ++g) {
+        const float scale = probability_scale(group_max[g], p.p_mode, p.tau);
         const float inverse = rcp_approx(fmaxf(scale, 1e-20f));
         uint32_t words[2] = {0, 0};
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          words[k >> 2] |= cvt_e2m1x2(prob[2 * k] * inverse, prob[2 * k + 1] * inverse) << (8 * (k & 3));
-        *reinterpret_cast<uint2*>(sm.p_tile[b] + swizzle64(p_row + g * 8)) = make_uint2(words[0], words[1]);
-        scale_words[g >> 2] |= cvt_e4m3(scale) << (8 * (g & 3));
+          words[k >> 2] |= cvt_e2m1x2(prob[16 * g + 2 * k] * inverse, prob[16 * g + 2 * k + 1] * inverse) << (8 * (k & 3));
+        *reinterpret_cast<uint2*>(sm.p_tile[b] + swizzle64(p_row + (wg * kRunGroups + g) * 8)) = make_uint2(words[0], words[1]);
+        scale_bytes |= cvt_e4m3(scale) << (8 * g);
       }
-      *reinterpret_cast<uint32_t*>(sm.p_sf[b][0] + sf_row) = scale_words[0];
-      *reinterpret_cast<uint32_t*>(sm.p_sf[b][1] + sf_row) = scale_words[1];
+      {
+        // this thread's scale bytes: groups wg * kRunGroups ... of the step's eight, four per K block
+        const int first_group = wg * kRunGroups;
+        uint8_t* dst = sm.p_sf[b][first_group >> 2] + sf_row + (first_group & 3);
+        if constexpr (kRunGroups == 1) *dst = (uint8_t)scale_bytes;
+        if constexpr (kRunGroups == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)scale_bytes;
+        if constexpr (kRunGroups == 4) *reinterpret_cast<uint32_t*>(dst) = scale_bytes;
+      }
       tc::fence_proxy_async_smem();
-      if (i > 0 && !rescale) wait_at(11, &sm.o_done, (i - 1) & 1, abort_flag);
+      // Every PV product's completion is observed in turn (a parity wait can only tell the current
+      // phase from the one before it): the previous step's here, unless the rescale above already did.
+      if (i > 0 && !observed) wait_at(11, &sm.o_done, (i - 1) & 1, abort_flag);
       tc::mbar_arrive(&sm.p_full[b]);
     }
 
     // ---- normalise and write ------------------------------------------------------------------
-    const bool empty = num_steps == 0 || row_sum == 0.0f || row_sum != row_sum;
-    const float inverse = empty ? 0.0f : 1.0f / row_sum;
+    softmax_barrier();  // the last slow step's exchange has been read by every thread
+    sm.red[0][wg][h] = row_sum;
+    softmax_barrier();
+    float total = sm.red[0][0][h];
+#pragma unroll
+    for (int w = 1; w < kSoftmaxGroups; ++w) total += sm.red[0][w][h];
+    const bool empty = num_steps == 0 || total == 0.0f || total != total;
+    const float inverse = empty ? 0.0f : 1.0f / total;
     const int64_t head = (int64_t)row * p.heads_q + head0 + h;
-    if (p.out == nullptr && half == 0 && h < valid_heads) {
+    if (p.out == nullptr && half == 0 && wg == 0 && h < valid_heads) {
       const float safe = row_max == -INFINITY ? 0.0f : row_max;
       p.partial_lse[(int64_t)part * p.rows * p.heads_q + head] =
-          empty ? -INFINITY : (safe * p.scale_log2 + log2f(row_sum) - shift) * 0.6931471805599453f;
+          empty ? -INFINITY : (safe * p.scale_log2 + log2f(total) - shift) * 0.6931471805599453f;
     }
     if (num_steps > 0) {
       wait_at(12, &sm.o_done, (num_steps - 1) & 1, abort_flag);
       tc::fence_after_sync();
     }
 #pragma unroll 1
-    for (int q = 0; q < kHalf / 16; ++q) {
+    for (int q = 0; q < kShare / 16; ++q) {
       float o[16];
       if (num_steps > 0) {
-        tc::tmem_ld16(lane_base + kColO + 16 * q, o);
+        tc::tmem_ld16(lane_base + kColO + wg * kShare + 16 * q, o);
         tc::tmem_wait_ld();
       }
 #pragma unroll
       for (int k = 0; k < 16; ++k) o[k] = empty ? 0.0f : o[k] * inverse;
       if (h < valid_heads) {
+        const int channel = half * kHalf + wg * kShare + 16 * q;
         if (p.out != nullptr) {
           uint4 lo, hi;
           lo.x = pack_bf16x2(o[0], o[1]);
@@ -516,12 +583,12 @@ __global__ void __launch_bounds__(192, 1) decode_kernel(const Params p) {
           hi.y = pack_bf16x2(o[10], o[11]);
           hi.z = pack_bf16x2(o[12], o[13]);
           hi.w = pack_bf16x2(o[14], o[15]);
-          uint4* dst = reinterpret_cast<uint4*>(p.out + head * kLatent + half * kHalf + 16 * q);
+          uint4* dst = reinterpret_cast<uint4*>(p.out + head * kLatent + channel);
           dst[0] = lo;
           dst[1] = hi;
         } else {
           float4* dst = reinterpret_cast<float4*>(p.partial_out + ((int64_t)part * p.rows * p.heads_q + head) * kLatent +
-                                                  half * kHalf + 16 * q);
+                                                  channel);
 #pragma unroll
           for (int k = 0; k < 4; ++k) dst[k] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
         }
@@ -699,7 +766,7 @@ extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_han
   }
   const int64_t grid = (int64_t)a->rows * p.head_blocks * a->num_splits * 2;
   if (grid > 0x7fffffff) return BDFP4_E_TOO_LARGE;
-  mla::decode_kernel<<<(unsigned)grid, 192, smem, stream>>>(p);
+  mla::decode_kernel<<<(unsigned)grid, mla::kThreads, smem, stream>>>(p);
   return bdfp4::cuda_status(cudaGetLastError());
 }
 
