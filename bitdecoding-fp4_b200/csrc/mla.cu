@@ -198,10 +198,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       tc::mbar_init(&sm.v_empty[s], 1);
     }
     tc::mbar_init(&sm.s_full, 1);
-    tc::mbar_init(&sm.s_empty, kSoftmaxThreads);
+    tc::mbar_init(&sm.s_empty, kSoftmaxThreads / 32);  // one arrival per softmax warp
     tc::mbar_init(&sm.o_done, 1);
     for (int b = 0; b < 2; ++b) {
-      tc::mbar_init(&sm.p_full[b], kSoftmaxThreads);
+      tc::mbar_init(&sm.p_full[b], kSoftmaxThreads / 32);
       tc::mbar_init(&sm.p_empty[b], 1);
     }
     sm.abort_flag = 0;
@@ -438,7 +438,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       for (int q = 0; q < kRunGroups; ++q) tc::tmem_ld16(lane_base + kColS + wg * kRun + 16 * q, s + 16 * q);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
-      tc::mbar_arrive(&sm.s_empty);
+      // one lane arrives for the warp: hundreds of per-thread arrivals on one barrier serialise
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&sm.s_empty);
       const int valid = seq_len - step * kStep - wg * kRun;  // only the row's last step can be short
       if (valid < kRun) {
 #pragma unroll
@@ -540,7 +542,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       // Every PV product's completion is observed in turn (a parity wait can only tell the current
       // phase from the one before it): the previous step's here, unless the rescale above already did.
       if (i > 0 && !observed) wait_at(11, &sm.o_done, (i - 1) & 1, abort_flag);
-      tc::mbar_arrive(&sm.p_full[b]);
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&sm.p_full[b]);
     }
 
     // ---- normalise and write ------------------------------------------------------------------
