@@ -45,7 +45,7 @@ constexpr int kSoftmaxGroups = 4;                   // softmax threads per head
 constexpr int kRun = kStep / kSoftmaxGroups;        // tokens of a step one softmax thread owns
 constexpr int kShare = kHalf / kSoftmaxGroups;      // output columns one softmax thread rescales and writes
 constexpr int kSoftmaxThreads = 128 * kSoftmaxGroups;
-constexpr int kThreads = 64 + kSoftmaxThreads;
+constexpr int kThreads = 128 + kSoftmaxThreads;  // producer, QK, PV and K-scale warps, then the softmax warps
 constexpr float kRescaleThreshold = 8.0f;
 
 constexpr int kColS = 0;       // 128 columns
@@ -98,7 +98,7 @@ struct Smem {
   alignas(1024) uint8_t p_sf[2][2][512];
   float red[2][kSoftmaxGroups][kHeads];  // per-head values exchanged between a head's softmax threads
   uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-  uint64_t s_full, s_empty, o_done, p_full[2], p_empty[2];
+  uint64_t s_full, s_empty, o_done, sfk_ready, p_full[2], p_empty[2];
   int page_ids[2][32];
   uint32_t tmem_base;
   int abort_flag;
@@ -200,6 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     tc::mbar_init(&sm.s_full, 1);
     tc::mbar_init(&sm.s_empty, kSoftmaxThreads / 32);  // one arrival per softmax warp
     tc::mbar_init(&sm.o_done, 1);
+    tc::mbar_init(&sm.sfk_ready, 1);
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&sm.p_full[b], kSoftmaxThreads / 32);
       tc::mbar_init(&sm.p_empty[b], 1);
@@ -325,22 +326,53 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer ---------------------------------------------------------------------------
-    const bool issuer = lane == 0;
-    constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, kStep);
-    constexpr uint32_t idesc_rope = tc::bf16_idesc(128, kStep);
-    constexpr uint32_t idesc_pv = tc::nvf4_idesc(128, kHalf);
-    if (num_steps > 0) {
-      if (issuer) {
+    // ---- score products: one thread ---------------------------------------------------------------
+    // Issuing is what bounds a step (a tcgen05.cp holds its thread for about 50 ns, an MMA for 40),
+    // so the three strands of tensor work are issued by three threads: QK here, PV in warp 2, the K
+    // scale atoms in warp 3. The tensor pipe runs what they issue in arrival order; the strands
+    // touch different accumulators and hand over through mbarriers fed by tcgen05.commit.
+    if (lane == 0 && num_steps > 0) {
+      constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, kStep);
+      constexpr uint32_t idesc_rope = tc::bf16_idesc(128, kStep);
 #pragma unroll
-        for (int a = 0; a < kChunks * 2; ++a)
-          tc::cp_sf_atom(tmem + kColSFQ + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[a])));
+      for (int a = 0; a < kChunks * 2; ++a)
+        tc::cp_sf_atom(tmem + kColSFQ + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[a])));
+      bool ok = true;
+      for (int i = 0; i < num_steps && ok; ++i) {
+        const int s = i % kStages;
+        ok = wait_at(6, &sm.k_full[s], (i / kStages) & 1, abort_flag);
+        if (ok) ok = wait_at(14, &sm.sfk_ready, i & 1, abort_flag);
+        // the scores of the previous step have been read
+        if (ok) ok = wait_at(7, &sm.s_empty, (i & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+            tc::mma_nvf4(tmem + kColS, tc::fp4_tile_desc(tc::smem_u32(sm.q_tile[c]), k),
+                         tc::fp4_tile_desc(tc::smem_u32(sm.k_codes[s][c]), k), idesc_qk,
+                         tmem + kColSFQ + 4 * (2 * c + k), tmem + kColSFK + 4 * (2 * c + k), (c | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < kRope / 16; ++k)
+          tc::mma_bf16(tmem + kColS, tc::bf16_tile_desc(tc::smem_u32(sm.q_rope), k),
+                       tc::bf16_tile_desc(tc::smem_u32(sm.rope[s]), k), idesc_rope, true);
+        tc::commit(&sm.s_full);
+        tc::commit(&sm.k_empty[s]);
       }
-      auto issue_pv = [&](int m) -> bool {  // issuer only
+    }
+  } else if (warp == 2) {
+    // ---- output products: one thread --------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = tc::nvf4_idesc(128, kHalf);
+      bool ok = true;
+      for (int m = 0; m < num_steps && ok; ++m) {
         const int s = m % kStages;
         const int b = m & 1;
-        if (!wait_at(3, &sm.v_full[s], (m / kStages) & 1, abort_flag)) return false;
-        if (!wait_at(4, &sm.p_full[b], (m >> 1) & 1, abort_flag)) return false;
+        ok = wait_at(3, &sm.v_full[s], (m / kStages) & 1, abort_flag);
+        if (ok) ok = wait_at(4, &sm.p_full[b], (m >> 1) & 1, abort_flag);
+        if (!ok) break;
         tc::fence_after_sync();
 #pragma unroll
         for (int a = 0; a < 4; ++a)  // [page][atom of chunk 0, atom of chunk 1]
@@ -356,66 +388,51 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
         tc::commit(&sm.o_done);
         tc::commit(&sm.v_empty[s]);
         tc::commit(&sm.p_empty[b]);
-        return true;
-      };
-      bool ok = true;
-      for (int i = 0; i < num_steps && ok; ++i) {
-        const int s = i % kStages;
-        ok = wait_at(5, &sm.ksf_full[s], (i / kStages) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        {
-          // The two pages' scale blocks arrived as [page][chunk][K block][32 rows][8 B]; an atom row
-          // is 16 bytes, tokens 0-63 (first page) in its low half, 64-127 in its high half. Every
-          // lane reads all its pieces before any lane writes, so the exchange is done in place.
-          uint8_t* sf = sm.k_sf[s];
-          uint2 first[8], second[8];
-#pragma unroll
-          for (int a = 0; a < 8; ++a) {
-            first[a] = *reinterpret_cast<const uint2*>(sf + a * 256 + lane * 8);
-            second[a] = *reinterpret_cast<const uint2*>(sf + 2048 + a * 256 + lane * 8);
-          }
-          __syncwarp();
-#pragma unroll
-          for (int a = 0; a < 8; ++a)
-            *reinterpret_cast<uint4*>(sf + a * 512 + lane * 16) = make_uint4(first[a].x, first[a].y, second[a].x, second[a].y);
-          tc::fence_proxy_async_smem();
-          __syncwarp();
-        }
-        if (issuer) {
-          ok = wait_at(6, &sm.k_full[s], (i / kStages) & 1, abort_flag);
-          // the scores of the previous step have been read: S and the K scale columns are free
-          if (ok) ok = wait_at(7, &sm.s_empty, (i & 1) ^ 1, abort_flag);
-          if (ok) {
-            tc::fence_after_sync();
-#pragma unroll
-            for (int a = 0; a < 2 * kChunks; ++a)
-              tc::cp_sf_atom(tmem + kColSFK + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.k_sf[s]) + a * 512));
-#pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-              for (int k = 0; k < 2; ++k)
-                tc::mma_nvf4(tmem + kColS, tc::fp4_tile_desc(tc::smem_u32(sm.q_tile[c]), k),
-                             tc::fp4_tile_desc(tc::smem_u32(sm.k_codes[s][c]), k), idesc_qk,
-                             tmem + kColSFQ + 4 * (2 * c + k), tmem + kColSFK + 4 * (2 * c + k), (c | k) != 0);
-            }
-#pragma unroll
-            for (int k = 0; k < kRope / 16; ++k)
-              tc::mma_bf16(tmem + kColS, tc::bf16_tile_desc(tc::smem_u32(sm.q_rope), k),
-                           tc::bf16_tile_desc(tc::smem_u32(sm.rope[s]), k), idesc_rope, true);
-            tc::commit(&sm.s_full);
-            tc::commit(&sm.k_empty[s]);
-            if (i > 0) ok = issue_pv(i - 1);
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       }
-      if (issuer && ok) issue_pv(num_steps - 1);
+    }
+  } else if (warp == 3) {
+    // ---- K scale atoms: the warp interleaves, one thread copies to tensor memory -------------------
+    bool ok = true;
+    for (int i = 0; i < num_steps && ok; ++i) {
+      const int s = i % kStages;
+      ok = wait_at(5, &sm.ksf_full[s], (i / kStages) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      {
+        // The two pages' scale blocks arrived as [page][chunk][K block][32 rows][8 B]; an atom row
+        // is 16 bytes, tokens 0-63 (first page) in its low half, 64-127 in its high half. Every
+        // lane reads all its pieces before any lane writes, so the exchange is done in place.
+        uint8_t* sf = sm.k_sf[s];
+        uint2 first[8], second[8];
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+          first[a] = *reinterpret_cast<const uint2*>(sf + a * 256 + lane * 8);
+          second[a] = *reinterpret_cast<const uint2*>(sf + 2048 + a * 256 + lane * 8);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int a = 0; a < 8; ++a)
+          *reinterpret_cast<uint4*>(sf + a * 512 + lane * 16) = make_uint4(first[a].x, first[a].y, second[a].x, second[a].y);
+        tc::fence_proxy_async_smem();
+        __syncwarp();
+      }
+      if (lane == 0) {
+        // the K scale columns are free once the previous step's score product has completed
+        if (i > 0) ok = wait_at(15, &sm.s_full, (i - 1) & 1, abort_flag);
+        if (ok) {
+          tc::fence_after_sync();
+#pragma unroll
+          for (int a = 0; a < 2 * kChunks; ++a)
+            tc::cp_sf_atom(tmem + kColSFK + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.k_sf[s]) + a * 512));
+          tc::commit(&sm.sfk_ready);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
     }
   } else {
     // ---- softmax: kSoftmaxGroups threads per query head, each owning a run of the step's tokens ---
     const int warp_q = warp & 3;            // TMEM lane quarter this warp may read
-    const int wg = (warp - 2) >> 2;         // which run of kRun tokens of every step
+    const int wg = (warp - 4) >> 2;         // which run of kRun tokens of every step
     const int h = warp_q * 32 + lane;       // head = TMEM lane of S and O
     const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
     const float shift = p.p_mode == BDFP4_P_AMAX2_OR_AMAX6_C8 ? 3.0f : 0.0f;
