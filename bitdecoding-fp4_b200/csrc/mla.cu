@@ -98,7 +98,7 @@ struct Smem {
   alignas(1024) uint8_t p_sf[2][2][512];
   float red[2][kSoftmaxGroups][kHeads];  // per-head values exchanged between a head's softmax threads
   uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-  uint64_t s_full, s_empty, o_done, sfk_ready, p_full[2], p_empty[2];
+  uint64_t s_full, s_empty, o_done, sfk_ready, p_full[2];
   int page_ids[2][32];
   uint32_t tmem_base;
   int abort_flag;
@@ -203,7 +203,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     tc::mbar_init(&sm.sfk_ready, 1);
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&sm.p_full[b], kSoftmaxThreads / 32);
-      tc::mbar_init(&sm.p_empty[b], 1);
     }
     sm.abort_flag = 0;
     tc::fence_barrier_init();
@@ -387,7 +386,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
                        idesc_pv, tmem + kColSFP + 8 * b + 4 * e, tmem + kColSFV + 16 * b + 8 * e, m > 0 || e > 0);
         tc::commit(&sm.o_done);
         tc::commit(&sm.v_empty[s]);
-        tc::commit(&sm.p_empty[b]);
       }
     }
   } else if (warp == 3) {
@@ -533,8 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       }
 #pragma unroll
       for (int g = 0; g < kRunGroups; ++g) row_sum += group_sum[g];
-      // the PV product of two steps ago must be done with this P buffer
-      wait_at(10, &sm.p_empty[b], ((i >> 1) & 1) ^ 1, abort_flag);
+      // (the PV product of two steps ago is done with this P buffer: its completion was observed
+      // at the end of the previous step)
       uint32_t scale_bytes = 0;
 #pragma unroll
       for (int g = 0; g < kRunGroups; ++g) {
