@@ -461,28 +461,50 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
 #pragma unroll
         for (int k = 0; k < kRun; ++k) s[k] = k < valid ? s[k] : -INFINITY;
       }
-      float prob[kRun], group_sum[kRunGroups], group_max[kRunGroups];
-      auto form_probabilities = [&]() {
+      // Probabilities of this thread's run against `max_scaled`, quantized sixteen at a time and
+      // stored as the PV product's A operand with their scale bytes. Forming and quantizing are one
+      // loop so that the exponentials of one group overlap the conversions of the one before.
+      // Returns the run's sum; `largest` is its largest probability. (The PV product of two steps ago
+      // is done with this P buffer: its completion was observed at the end of the previous step.)
+      float largest = 0.0f;
+      auto form_and_store = [&]() -> float {
+        float run_sum = 0.0f;
+        uint32_t scale_bytes = 0;
+        largest = 0.0f;
 #pragma unroll
         for (int g = 0; g < kRunGroups; ++g) {
-          float* pg = prob + 16 * g;
+          float prob[16];
 #pragma unroll
-          for (int k = 0; k < 16; ++k) pg[k] = ex2_approx(fmaf(s[16 * g + k], p.scale_log2, -max_scaled));
+          for (int k = 0; k < 16; ++k) prob[k] = ex2_approx(fmaf(s[16 * g + k], p.scale_log2, -max_scaled));
           // sums and maxima as trees: few warps share a scheduler, so a serial chain is paid in full
           float sum4[4], max4[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            sum4[k] = (pg[k] + pg[k + 4]) + (pg[k + 8] + pg[k + 12]);
-            max4[k] = fmaxf(fmaxf(pg[k], pg[k + 4]), fmaxf(pg[k + 8], pg[k + 12]));
+            sum4[k] = (prob[k] + prob[k + 4]) + (prob[k + 8] + prob[k + 12]);
+            max4[k] = fmaxf(fmaxf(prob[k], prob[k + 4]), fmaxf(prob[k + 8], prob[k + 12]));
           }
-          group_sum[g] = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-          group_max[g] = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
-        }
-      };
-      form_probabilities();  // against the stale maximum: almost always the final ones
-      bool trigger = i == 0 || *abort_flag != 0;
+          run_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+          const float group_max = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
+          largest = fmaxf(largest, group_max);
+          const float scale = probability_scale(group_max, p.p_mode, p.tau);
+          const float inverse = rcp_approx(fmaxf(scale, 1e-20f));
+          uint32_t words[2] = {0, 0};
 #pragma unroll
-      for (int g = 0; g < kRunGroups; ++g) trigger = trigger || group_max[g] > trigger_above;
+          for (int k = 0; k < 8; ++k)
+            words[k >> 2] |= cvt_e2m1x2(prob[2 * k] * inverse, prob[2 * k + 1] * inverse) << (8 * (k & 3));
+          *reinterpret_cast<uint2*>(sm.p_tile[b] + swizzle64(p_row + (wg * kRunGroups + g) * 8)) = make_uint2(words[0], words[1]);
+          scale_bytes |= cvt_e4m3(scale) << (8 * g);
+        }
+        // this thread's scale bytes: groups wg * kRunGroups ... of the step's eight, four per K block
+        const int first_group = wg * kRunGroups;
+        uint8_t* dst = sm.p_sf[b][first_group >> 2] + sf_row + (first_group & 3);
+        if constexpr (kRunGroups == 1) *dst = (uint8_t)scale_bytes;
+        if constexpr (kRunGroups == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)scale_bytes;
+        if constexpr (kRunGroups == 4) *reinterpret_cast<uint32_t*>(dst) = scale_bytes;
+        return run_sum;
+      };
+      float run_sum = form_and_store();  // against the stale maximum: almost always final
+      const bool trigger = i == 0 || *abort_flag != 0 || largest > trigger_above;
       bool observed = false;  // whether this step has already waited for the previous PV product
       if (softmax_vote_any(trigger)) {
         // the stale-maximum rule on the exact scores, identically in every thread of a head
@@ -527,32 +549,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
           tc::fence_before_sync();
         }
         row_sum *= acc;
-        form_probabilities();
+        run_sum = form_and_store();  // again, against the maximum now in force
       }
-#pragma unroll
-      for (int g = 0; g < kRunGroups; ++g) row_sum += group_sum[g];
-      // (the PV product of two steps ago is done with this P buffer: its completion was observed
-      // at the end of the previous step)
-      uint32_t scale_bytes = 0;
-#pragma unroll
-      for (int g = 0; g < kRunGroups; ++g) {
-        const float scale = probability_scale(group_max[g], p.p_mode, p.tau);
-        const float inverse = rcp_approx(fmaxf(scale, 1e-20f));
-        uint32_t words[2] = {0, 0};
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          words[k >> 2] |= cvt_e2m1x2(prob[16 * g + 2 * k] * inverse, prob[16 * g + 2 * k + 1] * inverse) << (8 * (k & 3));
-        *reinterpret_cast<uint2*>(sm.p_tile[b] + swizzle64(p_row + (wg * kRunGroups + g) * 8)) = make_uint2(words[0], words[1]);
-        scale_bytes |= cvt_e4m3(scale) << (8 * g);
-      }
-      {
-        // this thread's scale bytes: groups wg * kRunGroups ... of the step's eight, four per K block
-        const int first_group = wg * kRunGroups;
-        uint8_t* dst = sm.p_sf[b][first_group >> 2] + sf_row + (first_group & 3);
-        if constexpr (kRunGroups == 1) *dst = (uint8_t)scale_bytes;
-        if constexpr (kRunGroups == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)scale_bytes;
-        if constexpr (kRunGroups == 4) *reinterpret_cast<uint32_t*>(dst) = scale_bytes;
-      }
+      row_sum += run_sum;
       tc::fence_proxy_async_smem();
       // Every PV product's completion is observed in turn (a parity wait can only tell the current
       // phase from the one before it): the previous step's here, unless the rescale above already did.
