@@ -10,20 +10,23 @@
 // A pair of CTAs serves (row, 128 query heads[, split]); each walks the row's pages two at a time
 // (128 tokens per step), computes all the scores, and accumulates one half of the 512 output
 // channels (128 heads x 512 FP32 is the whole of an SM's tensor memory, and the scores need room
-// too). Query heads are the M rows of every MMA, so a softmax thread owns one head:
+// too). Query heads are the M rows of every MMA, so a head is a lane of tensor memory:
 //   S[head, token]  = sum over 4 chunks  Q_chunk[head, :] . K_chunk[token, :]   8 x mxf4nvf4 (N = 128, K = 64)
 //                   + q_rope[head, :] . rope[token, :]                           4 x kind::f16  (N = 128, K = 16)
 //   O[head, chan]  += P[head, :] . V^T[chan, :]                                  2 x mxf4nvf4 (N = 256, K = 64)
-// The thread reads its 128 scores from tensor memory, keeps its own running maximum and sum (no
-// reduction between threads, no barrier), and quantizes its row of probabilities sixteen tokens at
-// a time straight into the shared-memory A operand of the PV product. O (256 columns) stays in
-// tensor memory for the whole walk; when a thread's maximum moves (rarely: the stale-maximum rule
-// tolerates 2^8) its warp rescales its rows in place between two PV products.
+// Each head has four softmax threads (32 tokens of a step each). A thread reads its scores from
+// tensor memory, forms the probabilities against the stale maximum, quantizes them sixteen at a time
+// (the groups are in its own registers: no shuffles) straight into the shared-memory A operand of the
+// PV product, and keeps a partial sum. A CTA-wide vote catches the rare step in which a maximum may
+// have to move (the stale-maximum rule tolerates 2^8); then the exact rule runs on the scores, the
+// head's threads rescale their share of O in place in tensor memory between two PV products, and the
+// probabilities are formed again. O (256 columns) stays in tensor memory for the whole walk.
 // Tensor memory: S 128 + O 256 + scale factors 112 columns.
 //
-// Warp roles as in the GQA kernel: warp 0 issues the bulk copies (lane 0 the K side, lane 1 the V
-// side), warp 1 interleaves the two pages' K scale blocks into MMA atoms and issues every tcgen05
-// operation, warps 2-5 are the softmax. Every mbarrier wait is bounded.
+// Warps: 0 issues the bulk copies (lane 0 the K side, lane 1 the V side); 1, 2 and 3 issue the tensor
+// work, one thread each for QK, for PV, and for the K scale atoms (whose two half blocks per step the
+// whole of warp 3 first interleaves); 4-19 are the softmax. Every mbarrier wait is bounded and
+// reports its site in bits [8,16) of the error word.
 #include <cmath>
 #include <type_traits>
 
