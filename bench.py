@@ -647,9 +647,12 @@ def run_mla(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    scratch = mla.MLAScratch(rows, MLA_HEADS, splits, device)
+    result = torch.empty(rows, MLA_HEADS, 512, dtype=torch.bfloat16, device=device)
+
     def decode(ql, qr):
         return mla.mla_decode(ql, qr, cache, table, seq_lens, softmax_scale=MLA_SCALE, num_splits=splits,
-                              error_word=error)
+                              error_word=error, out=result, scratch=scratch)
 
     # ---- device-resident step: query quantize + decode (+ merge), kernel timed by events around it
     stream = torch.cuda.current_stream(device)

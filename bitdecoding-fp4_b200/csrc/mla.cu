@@ -210,6 +210,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     sm.abort_flag = 0;
     tc::fence_barrier_init();
   }
+  // Everything up to here reads only the batch's metadata. The query operands come from the launch
+  // before this one (the query quantizer): with programmatic dependent launch this kernel may have
+  // started while that one was still running, so wait for it here, then let the launch after this
+  // one (the merge, or the next step's quantizer) start its own preamble.
+  wait_for_prior_kernels();
+  dependents_may_launch();
   // query operands: codes (16 chunks of 16 bytes per head), scales (8 words per head), rope (8
   // chunks); rows past the last head stay zero
   {
@@ -635,6 +641,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
 __global__ void __launch_bounds__(256) quantize_query_kernel(const __nv_bfloat16* query, int64_t row_pitch, int rows,
                                                              int heads_q, ScaleCandidates cand, uint8_t* codes,
                                                              uint8_t* scales) {
+  wait_for_prior_kernels();  // the buffers written here may still be read by the launch before
+  dependents_may_launch();
   const int64_t index = (int64_t)blockIdx.x * 256 + threadIdx.x;
   const int64_t total = (int64_t)rows * heads_q * 32;
   if (index >= total) return;
@@ -668,6 +676,8 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* partial_out, 
                                                       int64_t part_stride_heads, __nv_bfloat16* out) {
   constexpr float kLog2e = 1.4426950408889634f;
   const int64_t head = blockIdx.x;
+  wait_for_prior_kernels();
+  dependents_may_launch();
   float lse_max = -INFINITY;
   for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, partial_lse[s * part_stride_heads + head]);
   if (lse_max == -INFINITY) lse_max = 0.0f;
@@ -691,6 +701,24 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* partial_out, 
   dst[1] = __floats2bfloat162_rn(acc.z, acc.w);
 }
 
+// Launch with programmatic stream serialization: after a kernel that signals early the CTAs come
+// up and run their preamble while it still runs; after any other kernel this is an ordinary launch.
+template <typename... Params, typename... Args>
+static cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 }  // namespace mla
 }  // namespace bdfp4
 
@@ -703,10 +731,10 @@ extern "C" int bdfp4_mla_quantize_query(const void* query, int64_t row_pitch, in
   if (row_pitch < (int64_t)heads_q * mla::kLatent || row_pitch % 8) return BDFP4_E_ARG;
   if ((reinterpret_cast<uintptr_t>(query) & 15) || (reinterpret_cast<uintptr_t>(codes) & 7)) return BDFP4_E_ARG;
   const int64_t groups = (int64_t)rows * heads_q * 32;
-  mla::quantize_query_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  return bdfp4::cuda_status(mla::launch_overlapped(
+      mla::quantize_query_kernel, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(query), row_pitch, rows, heads_q, scale_candidates(scale_mode),
-      static_cast<uint8_t*>(codes), static_cast<uint8_t*>(scales));
-  return bdfp4::cuda_status(cudaGetLastError());
+      static_cast<uint8_t*>(codes), static_cast<uint8_t*>(scales)));
 }
 
 extern "C" int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const int32_t* source_tokens,
@@ -786,8 +814,8 @@ extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_han
   }
   const int64_t grid = (int64_t)a->rows * p.head_blocks * a->num_splits * 2;
   if (grid > 0x7fffffff) return BDFP4_E_TOO_LARGE;
-  mla::decode_kernel<<<(unsigned)grid, mla::kThreads, smem, stream>>>(p);
-  return bdfp4::cuda_status(cudaGetLastError());
+  return bdfp4::cuda_status(
+      mla::launch_overlapped(mla::decode_kernel, dim3((unsigned)grid), dim3(mla::kThreads), smem, stream, p));
 }
 
 extern "C" int bdfp4_mla_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
@@ -795,7 +823,7 @@ extern "C" int bdfp4_mla_combine(const float* partial_out, const float* partial_
   if (!partial_out || !partial_lse || !out || parts < 1 || rows < 1 || heads_q < 1) return BDFP4_E_ARG;
   const int64_t heads = (int64_t)rows * heads_q;
   if (heads > 0x7fffffff) return BDFP4_E_TOO_LARGE;
-  mla::combine_kernel<<<(unsigned)heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial_out, partial_lse, parts, heads, static_cast<__nv_bfloat16*>(out));
-  return bdfp4::cuda_status(cudaGetLastError());
+  return bdfp4::cuda_status(mla::launch_overlapped(mla::combine_kernel, dim3((unsigned)heads), dim3(128), 0,
+                                                   static_cast<cudaStream_t>(stream), partial_out, partial_lse,
+                                                   (int)parts, (int64_t)heads, static_cast<__nv_bfloat16*>(out)));
 }

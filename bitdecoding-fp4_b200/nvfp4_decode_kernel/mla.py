@@ -108,14 +108,32 @@ def write_pages(cache: MLACache, latent: torch.Tensor, rope: torch.Tensor, sourc
                                                cache.rope.data_ptr(), cache.pitch, stream))
 
 
-def quantize_query(q_latent: torch.Tensor, scale_mode: str = "amax6"):
+class MLAScratch:
+    """Buffers a decode call would otherwise allocate: query codes and scales, and the split partials.
+    Build once per (rows, heads, num_splits) and pass as ``scratch=``; a serving loop then allocates
+    nothing per step (and stays capturable in a CUDA graph)."""
+
+    def __init__(self, rows: int, heads: int, num_splits: int, device) -> None:
+        self.shape = (rows, heads, num_splits)
+        self.codes = torch.empty(rows, heads, LATENT // 2, dtype=torch.uint8, device=device)
+        self.scales = torch.empty(rows, heads, LATENT // 16, dtype=torch.uint8, device=device)
+        self.partial_out = self.partial_lse = None
+        if num_splits > 1:
+            self.partial_out = torch.empty(num_splits, rows, heads, LATENT, dtype=torch.float32, device=device)
+            self.partial_lse = torch.empty(num_splits, rows, heads, dtype=torch.float32, device=device)
+
+
+def quantize_query(q_latent: torch.Tensor, scale_mode: str = "amax6", *, out: tuple | None = None):
     """BF16 ``[rows, heads, 512]`` -> ``(codes u8 [rows, heads, 256], scales u8 [rows, heads, 32])``."""
     if q_latent.dtype is not torch.bfloat16 or not q_latent.is_cuda or q_latent.ndim != 3 \
             or q_latent.shape[2] != LATENT or q_latent.stride()[1:] != (LATENT, 1):
         raise ValueError("q_latent must be BF16 CUDA [rows, heads, 512], dense within a row")
     rows, heads, _ = q_latent.shape
-    codes = torch.empty(rows, heads, LATENT // 2, dtype=torch.uint8, device=q_latent.device)
-    scales = torch.empty(rows, heads, LATENT // 16, dtype=torch.uint8, device=q_latent.device)
+    if out is not None:
+        codes, scales = out
+    else:
+        codes = torch.empty(rows, heads, LATENT // 2, dtype=torch.uint8, device=q_latent.device)
+        scales = torch.empty(rows, heads, LATENT // 16, dtype=torch.uint8, device=q_latent.device)
     bdfp4.mla_quantize_query(q_latent, mode_id(scale_mode), codes, scales, bdfp4.current_stream(q_latent.device))
     return codes, scales
 
@@ -124,12 +142,13 @@ def mla_decode(q_latent: torch.Tensor, q_rope: torch.Tensor, cache: MLACache, pa
                seq_lens: torch.Tensor, *, softmax_scale: float, num_splits: int = 1,
                p_scale_mode: str = DEFAULT_P_SCALE_MODE, p_scale_tau: float = P_SMALL_GROUP_AMAX,
                query_scale_mode: str = "amax6", error_word: torch.Tensor | None = None,
-               return_partials: bool = False):
+               return_partials: bool = False, out: torch.Tensor | None = None, scratch: MLAScratch | None = None):
     """Decode attention of ``q_latent [rows, heads, 512]`` + ``q_rope [rows, heads, 64]`` (BF16; the
     query with the key up-projection absorbed) over the paged latent cache. ``page_table``
     ``[rows, max_pages]`` INT32 lists each row's 64-token pages oldest first, ``seq_lens`` ``[rows]``
     INT32 its tokens. Returns BF16 ``[rows, heads, 512]`` (the value up-projection is the
-    caller's), or with ``return_partials`` the FP32 partials and LSEs of the ``num_splits`` parts."""
+    caller's), or with ``return_partials`` the FP32 partials and LSEs of the ``num_splits`` parts.
+    ``out`` and ``scratch`` (:class:`MLAScratch`) take the place of the per-call allocations."""
     rows, heads, _ = q_latent.shape
     if heads % HEADS_PER_CTA:
         raise NotImplementedError(f"the MLA kernel serves query heads in groups of {HEADS_PER_CTA}")
@@ -143,7 +162,10 @@ def mla_decode(q_latent: torch.Tensor, q_rope: torch.Tensor, cache: MLACache, pa
     if num_splits < 1:
         raise ValueError("num_splits must be at least 1")
     device = q_latent.device
-    codes, scales = quantize_query(q_latent, query_scale_mode)
+    if scratch is not None and scratch.shape != (rows, heads, num_splits):
+        raise ValueError(f"scratch was built for (rows, heads, splits) = {scratch.shape}")
+    codes, scales = quantize_query(q_latent, query_scale_mode,
+                                   out=None if scratch is None else (scratch.codes, scratch.scales))
     a = bdfp4.MlaDecodeArgs()
     a.rows, a.heads_q = rows, heads
     a.query_codes, a.query_scales, a.query_rope = codes.data_ptr(), scales.data_ptr(), q_rope.data_ptr()
@@ -160,13 +182,19 @@ def mla_decode(q_latent: torch.Tensor, q_rope: torch.Tensor, cache: MLACache, pa
     a.num_splits = int(num_splits)
     a.error_word = bdfp4.ptr(error_word)
     stream = bdfp4.current_stream(device)
-    out = torch.empty(rows, heads, LATENT, dtype=torch.bfloat16, device=device)
+    if out is None:
+        out = torch.empty(rows, heads, LATENT, dtype=torch.bfloat16, device=device)
+    elif out.dtype is not torch.bfloat16 or out.shape != (rows, heads, LATENT) or not out.is_contiguous():
+        raise ValueError("out must be contiguous BF16 [rows, heads, 512]")
     if num_splits == 1 and not return_partials:
         a.out = out.data_ptr()
         bdfp4.mla_decode(a, stream)
         return out
-    partial_out = torch.empty(num_splits, rows, heads, LATENT, dtype=torch.float32, device=device)
-    partial_lse = torch.empty(num_splits, rows, heads, dtype=torch.float32, device=device)
+    if scratch is not None and scratch.partial_out is not None:
+        partial_out, partial_lse = scratch.partial_out, scratch.partial_lse
+    else:
+        partial_out = torch.empty(num_splits, rows, heads, LATENT, dtype=torch.float32, device=device)
+        partial_lse = torch.empty(num_splits, rows, heads, dtype=torch.float32, device=device)
     a.partial_out, a.partial_lse = partial_out.data_ptr(), partial_lse.data_ptr()
     bdfp4.mla_decode(a, stream)
     if return_partials:
