@@ -14,7 +14,7 @@
 //   S[head, token]  = sum over 4 chunks  Q_chunk[head, :] . K_chunk[token, :]   8 x mxf4nvf4 (N = 128, K = 64)
 //                   + q_rope[head, :] . rope[token, :]                           4 x kind::f16  (N = 128, K = 16)
 //   O[head, chan]  += P[head, :] . V^T[chan, :]                                  2 x mxf4nvf4 (N = 256, K = 64)
-// Each head has four softmax threads (32 tokens of a step each). A thread reads its scores from
+// Each head has two softmax threads (64 tokens of a step each). A thread reads its scores from
 // tensor memory, forms the probabilities against the stale maximum, quantizes them sixteen at a time
 // (the groups are in its own registers: no shuffles) straight into the shared-memory A operand of the
 // PV product, and keeps a partial sum. A CTA-wide vote catches the rare step in which a maximum may
@@ -25,7 +25,7 @@
 //
 // Warps: 0 issues the bulk copies (lane 0 the K side, lane 1 the V side); 1, 2 and 3 issue the tensor
 // work, one thread each for QK, for PV, and for the K scale atoms (whose two half blocks per step the
-// whole of warp 3 first interleaves); 4-19 are the softmax. Every mbarrier wait is bounded and
+// whole of warp 3 first interleaves); 4-11 are the softmax. Every mbarrier wait is bounded and
 // reports its site in bits [8,16) of the error word.
 #include <cmath>
 #include <type_traits>
@@ -44,7 +44,7 @@ constexpr int kHalf = 256;    // output channels per CTA
 constexpr int kRope = 64;
 constexpr int kStep = 128;    // tokens per step (two 64-token pages)
 constexpr int kStages = 2;
-constexpr int kSoftmaxGroups = 4;                   // softmax threads per head
+constexpr int kSoftmaxGroups = 2;                   // softmax threads per head (2 measured faster than 1 or 4)
 constexpr int kRun = kStep / kSoftmaxGroups;        // tokens of a step one softmax thread owns
 constexpr int kShare = kHalf / kSoftmaxGroups;      // output columns one softmax thread rescales and writes
 constexpr int kSoftmaxThreads = 128 * kSoftmaxGroups;
@@ -478,7 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       float largest = 0.0f;
       auto form_and_store = [&]() -> float {
         float run_sum = 0.0f;
-        uint32_t scale_bytes = 0;
+        uint64_t scale_bytes = 0;
         largest = 0.0f;
 #pragma unroll
         for (int g = 0; g < kRunGroups; ++g) {
@@ -502,14 +502,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
           for (int k = 0; k < 8; ++k)
             words[k >> 2] |= cvt_e2m1x2(prob[2 * k] * inverse, prob[2 * k + 1] * inverse) << (8 * (k & 3));
           *reinterpret_cast<uint2*>(sm.p_tile[b] + swizzle64(p_row + (wg * kRunGroups + g) * 8)) = make_uint2(words[0], words[1]);
-          scale_bytes |= cvt_e4m3(scale) << (8 * g);
+          scale_bytes |= (uint64_t)cvt_e4m3(scale) << (8 * g);
         }
         // this thread's scale bytes: groups wg * kRunGroups ... of the step's eight, four per K block
         const int first_group = wg * kRunGroups;
         uint8_t* dst = sm.p_sf[b][first_group >> 2] + sf_row + (first_group & 3);
         if constexpr (kRunGroups == 1) *dst = (uint8_t)scale_bytes;
         if constexpr (kRunGroups == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)scale_bytes;
-        if constexpr (kRunGroups == 4) *reinterpret_cast<uint32_t*>(dst) = scale_bytes;
+        if constexpr (kRunGroups == 4) *reinterpret_cast<uint32_t*>(dst) = (uint32_t)scale_bytes;
+        if constexpr (kRunGroups == 8) {  // both K blocks of the step
+          *reinterpret_cast<uint32_t*>(dst) = (uint32_t)scale_bytes;
+          *reinterpret_cast<uint32_t*>(dst + 512) = (uint32_t)(scale_bytes >> 32);
+        }
         return run_sum;
       };
       float run_sum = form_and_store();  // against the stale maximum: almost always final
