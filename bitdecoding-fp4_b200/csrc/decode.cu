@@ -1221,9 +1221,9 @@ static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensor
 template <int GP, int TERMS, int PT>
 static cudaError_t launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
                                  cudaStream_t stream) {
-  static int sm_counts[kDeviceSlots] = {};
+  static std::atomic<int> sm_counts[kDeviceSlots] = {};
   const int slot = current_device_slot();
-  int sms = slot >= 0 ? sm_counts[slot] : 0;
+  int sms = slot >= 0 ? sm_counts[slot].load() : 0;
   if (sms == 0) {
     int device = 0;
     cudaGetDevice(&device);

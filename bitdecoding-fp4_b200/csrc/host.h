@@ -3,6 +3,8 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "../../include/bdfp4.h"
 
 namespace bdfp4 {
@@ -11,10 +13,11 @@ namespace bdfp4 {
 int cuda_status(cudaError_t error);
 
 // Per-device once-flags for settings CUDA keeps per device (a kernel's dynamic shared-memory limit):
-// `done` is indexed by the current device, since a process may drive several GPUs.
+// `done` is indexed by the current device, since a process may drive several GPUs. Two threads
+// racing on a slot both set the attribute, which is harmless; the flag itself is atomic.
 constexpr int kDeviceSlots = 64;
 struct PerDeviceOnce {
-  bool done[kDeviceSlots] = {};
+  std::atomic<bool> done[kDeviceSlots] = {};
 };
 // Index of the current device, or -1 when it cannot be read or is past kDeviceSlots (the caller
 // then sets the attribute on every call).
