@@ -177,3 +177,30 @@ def test_empty_row_and_argument_checks():
     with pytest.raises(NotImplementedError):
         mla.mla_decode(w["q_latent"][:, :32].contiguous().cuda(), w["q_rope"][:, :32].contiguous().cuda(), w["cache"],
                        w["table"].cuda(), w["seq_lens"].cuda(), softmax_scale=SCALE)
+
+
+@pytest.mark.parametrize("num_splits", [1, 3])
+def test_decode_with_scratch_is_capturable_and_identical(num_splits):
+    """Preallocated scratch and output: the same bytes as the allocating call, also when the whole
+    step (query quantize, decode, merge; programmatic dependent launches) is replayed from a CUDA graph."""
+    from nvfp4_decode_kernel import mla
+
+    w = _build([640, 200], 128, 31)
+    args = (w["q_latent"].cuda(), w["q_rope"].cuda(), w["cache"], w["table"].cuda(), w["seq_lens"].cuda())
+    plain = mla.mla_decode(*args, softmax_scale=SCALE, num_splits=num_splits)
+    scratch = mla.MLAScratch(2, 128, num_splits, "cuda")
+    out = torch.zeros(2, 128, 512, dtype=torch.bfloat16, device="cuda")
+    same = mla.mla_decode(*args, softmax_scale=SCALE, num_splits=num_splits, scratch=scratch, out=out)
+    assert same is out and torch.equal(out, plain)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        mla.mla_decode(*args, softmax_scale=SCALE, num_splits=num_splits, scratch=scratch, out=out)  # warm
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            mla.mla_decode(*args, softmax_scale=SCALE, num_splits=num_splits, scratch=scratch, out=out)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, plain)
+    with pytest.raises(ValueError):
+        mla.mla_decode(*args, softmax_scale=SCALE, num_splits=num_splits + 1, scratch=scratch)
