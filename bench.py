@@ -624,13 +624,23 @@ def run_mla(args) -> None:
     outliers = torch.randperm(512, generator=gen, device=device)[:8]
     factor = torch.exp(1.5 * torch.randn(8, generator=gen, device=device))
     source = torch.arange(pages_per_row, dtype=torch.int32, device=device) * 64
+    # every step appends one token per row (quantize-on-write) before it attends: the rows sit one
+    # token short of the context, their last page open in the appender's BF16 staging buffers
+    appender = mla.MLAAppender(rows, device)
+    open_latent = torch.zeros(rows, 64, 512, dtype=torch.bfloat16, device=device)
+    open_rope = torch.zeros(rows, 64, 64, dtype=torch.bfloat16, device=device)
     for row in range(rows):
         latent = torch.randn(context, 512, generator=gen, device=device)
         latent[:, outliers] *= factor
-        rope = torch.randn(context, 64, generator=gen, device=device)
-        mla.write_pages(cache, latent.to(torch.bfloat16), rope.to(torch.bfloat16), source, table[row].contiguous())
-    del latent, rope
+        latent = latent.to(torch.bfloat16)
+        rope = torch.randn(context, 64, generator=gen, device=device).to(torch.bfloat16)
+        mla.write_pages(cache, latent, rope, source, table[row].contiguous())
+        open_latent[row, :63], open_rope[row, :63] = latent[-64:-1], rope[-64:-1]
+    appender.load_open_pages(open_latent, open_rope)
+    new_latent, new_rope = latent[-1:].expand(rows, 512).contiguous(), rope[-1:].expand(rows, 64).contiguous()
+    del latent, rope, open_latent, open_rope
     seq_lens = torch.full((rows,), context, dtype=torch.int32, device=device)
+    lens_before = seq_lens - 1
     q_latent = torch.randn(rows, MLA_HEADS, 512, generator=gen, device=device).to(torch.bfloat16)
     q_rope = torch.randn(rows, MLA_HEADS, 64, generator=gen, device=device).to(torch.bfloat16)
     error = torch.zeros(1, dtype=torch.int32, device=device)
@@ -651,10 +661,11 @@ def run_mla(args) -> None:
     result = torch.empty(rows, MLA_HEADS, 512, dtype=torch.bfloat16, device=device)
 
     def decode(ql, qr):
+        appender.append(cache, new_latent, new_rope, lens_before, table, error_word=error)
         return mla.mla_decode(ql, qr, cache, table, seq_lens, softmax_scale=MLA_SCALE, num_splits=splits,
                               error_word=error, out=result, scratch=scratch)
 
-    # ---- device-resident step: query quantize + decode (+ merge), kernel timed by events around it
+    # ---- device-resident step: one-token append (3 launches), query quantize, decode (+ merge)
     stream = torch.cuda.current_stream(device)
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(args.warmup):
@@ -746,7 +757,8 @@ def run_mla(args) -> None:
                                             else f" [shape overridden: batch {total_rows}, context {context}]"),
                 "partition": f"{rows} of {total_rows} rows per rank, no collective", "num_splits": splits,
                 "l2": "inputs (1.5 GB per step over all ranks) exceed the 126 MB L2; no flush needed",
-                "e2e": "every step: H2D of the pinned query, query quantize, decode (+ merge), D2H of the output into pinned memory, synchronise",
+                "step": "append one token per row (stage, re-quantize the open page, rope block), query quantize, decode (+ merge)",
+                "e2e": "every step: H2D of the pinned query, the step, D2H of the output into pinned memory, synchronise",
             },
             "decode_kernel_us": kernel_ms * 1e3,
             "cache_read_gb_s": cache_bytes / (kernel_ms * 1e-3) / 1e9,
@@ -760,7 +772,7 @@ def run_mla(args) -> None:
             },
             "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": host_q.numel() * 2,
                     "d2h_bytes_per_step": host_out.numel() * 2},
-            "gpu_launches": args.steps * (2 if splits == 1 else 3),
+            "gpu_launches": args.steps * (5 if splits == 1 else 6),
             "clocks": sampler.summary(),
             "device_errors": int(error.item()),
         }

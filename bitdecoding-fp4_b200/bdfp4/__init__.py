@@ -38,6 +38,7 @@ EXPORTS = (
     "bdfp4_probability_statistics",
     "bdfp4_mla_quantize_query",
     "bdfp4_mla_write_rope",
+    "bdfp4_mla_append",
     "bdfp4_mla_decode",
     "bdfp4_mla_combine",
 )
@@ -196,6 +197,9 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_mla_quantize_query.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
     lib.bdfp4_mla_write_rope.restype = c_int32
     lib.bdfp4_mla_write_rope.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p]
+    lib.bdfp4_mla_append.restype = c_int32
+    lib.bdfp4_mla_append.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
+                                     c_int32, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.bdfp4_mla_decode.restype = c_int32
     lib.bdfp4_mla_decode.argtypes = [POINTER(MlaDecodeArgs), c_void_p]
     lib.bdfp4_mla_combine.restype = c_int32

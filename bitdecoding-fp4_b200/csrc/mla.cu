@@ -675,6 +675,40 @@ __global__ void __launch_bounds__(256) rope_page_kernel(const __nv_bfloat16* rop
   }
 }
 
+// One CTA per row: the row's new token into its open page of the staging buffers, and the row's
+// entry of the page writers' work table.
+__global__ void __launch_bounds__(128) append_kernel(const __nv_bfloat16* new_latent, const __nv_bfloat16* new_rope,
+                                                     __nv_bfloat16* staging_latent, __nv_bfloat16* staging_rope,
+                                                     const int32_t* seq_lens, const int32_t* page_table,
+                                                     int64_t page_table_stride, int pages, int32_t* source_tokens,
+                                                     int32_t* destination_pages, int32_t* error_word) {
+  wait_for_prior_kernels();
+  dependents_may_launch();
+  const int row = blockIdx.x;
+  const int length = max(seq_lens[row], 0);
+  const int position = length & 63;
+  uint4* latent = reinterpret_cast<uint4*>(staging_latent + (int64_t)row * 64 * kLatent);  // 64 chunks per token
+  uint4* rope = reinterpret_cast<uint4*>(staging_rope + (int64_t)row * 64 * kRope);        // 8 chunks per token
+  const int t = threadIdx.x;
+  if (position == 0) {  // a page starts: nothing of the previous one may remain
+    for (int i = t; i < 64 * 64; i += 128) latent[i] = make_uint4(0, 0, 0, 0);
+    for (int i = t; i < 64 * 8; i += 128) rope[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+  }
+  if (t < 64) latent[position * 64 + t] = __ldg(reinterpret_cast<const uint4*>(new_latent + (int64_t)row * kLatent) + t);
+  if (t >= 64 && t < 72)
+    rope[position * 8 + (t - 64)] = __ldg(reinterpret_cast<const uint4*>(new_rope + (int64_t)row * kRope) + (t - 64));
+  if (t == 0) {
+    int page = page_table[(int64_t)row * page_table_stride + (length >> 6)];
+    if (page < 0 || page >= pages) {
+      if (error_word) atomicOr(error_word, (int)BDFP4_DEV_BAD_PAGE);
+      page = -1;
+    }
+    source_tokens[row] = row * 64;
+    destination_pages[row] = page;
+  }
+}
+
 // Merge of split partials: one CTA per (row, head), one thread per 4 channels.
 __global__ void __launch_bounds__(128) combine_kernel(const float* partial_out, const float* partial_lse, int parts,
                                                       int64_t part_stride_heads, __nv_bfloat16* out) {
@@ -752,6 +786,24 @@ extern "C" int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const
       static_cast<const __nv_bfloat16*>(rope), token_pitch, source_tokens, destination_pages,
       static_cast<uint8_t*>(rope_pages), rope_pitch);
   return bdfp4::cuda_status(cudaGetLastError());
+}
+
+extern "C" int bdfp4_mla_append(const void* new_latent, const void* new_rope, void* staging_latent, void* staging_rope,
+                                const int32_t* seq_lens, const int32_t* page_table, int64_t page_table_stride,
+                                int32_t rows, int32_t pages, int32_t* source_tokens, int32_t* destination_pages,
+                                int32_t* error_word, void* stream) {
+  if (!new_latent || !new_rope || !staging_latent || !staging_rope || !seq_lens || !page_table || !source_tokens ||
+      !destination_pages)
+    return BDFP4_E_ARG;
+  if (rows < 1 || pages < 1 || page_table_stride < 1) return BDFP4_E_ARG;
+  auto misaligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
+  if (misaligned(new_latent) || misaligned(new_rope) || misaligned(staging_latent) || misaligned(staging_rope))
+    return BDFP4_E_ARG;
+  return bdfp4::cuda_status(mla::launch_overlapped(
+      mla::append_kernel, dim3((unsigned)rows), dim3(128), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const __nv_bfloat16*>(new_latent), static_cast<const __nv_bfloat16*>(new_rope),
+      static_cast<__nv_bfloat16*>(staging_latent), static_cast<__nv_bfloat16*>(staging_rope), seq_lens, page_table,
+      page_table_stride, (int)pages, source_tokens, destination_pages, error_word));
 }
 
 extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_handle) {

@@ -108,6 +108,45 @@ def write_pages(cache: MLACache, latent: torch.Tensor, rope: torch.Tensor, sourc
                                                cache.rope.data_ptr(), cache.pitch, stream))
 
 
+class MLAAppender:
+    """Quantize-on-write of one token per row and step. The rows' open pages (the last, partly filled
+    page of each sequence) are kept in BF16 staging buffers; a step puts every row's new token into
+    its open page and re-quantizes that page into the cache, so the cache always holds every token in
+    NVFP4 (there is no BF16 window in the MLA path). Three launches, no allocation, no host read."""
+
+    def __init__(self, rows: int, device, *, key_scale_mode: str = "amax6", value_scale_mode: str = "amax6") -> None:
+        self.rows = rows
+        self.latent = torch.zeros(rows * PAGE_TOKENS, LATENT, dtype=torch.bfloat16, device=device)
+        self.rope = torch.zeros(rows * PAGE_TOKENS, ROPE, dtype=torch.bfloat16, device=device)
+        self.source_tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.destination_pages = torch.full((rows,), -1, dtype=torch.int32, device=device)
+        self.key_scale_mode, self.value_scale_mode = key_scale_mode, value_scale_mode
+
+    def load_open_pages(self, latent: torch.Tensor, rope: torch.Tensor) -> None:
+        """Seed the staging buffers (``[rows, 64, 512]`` / ``[rows, 64, 64]`` BF16, zero past each row's
+        length) when sequences enter with a partly filled last page, e.g. after prefill."""
+        self.latent.copy_(latent.reshape(self.rows * PAGE_TOKENS, LATENT))
+        self.rope.copy_(rope.reshape(self.rows * PAGE_TOKENS, ROPE))
+
+    def append(self, cache: MLACache, new_latent: torch.Tensor, new_rope: torch.Tensor, seq_lens: torch.Tensor,
+               page_table: torch.Tensor, error_word: torch.Tensor | None = None) -> None:
+        """``new_latent [rows, 512]``, ``new_rope [rows, 64]`` BF16 become token ``seq_lens[r]`` of row
+        ``r`` (``seq_lens`` = the lengths before this step; the caller advances them afterwards)."""
+        if new_latent.dtype is not torch.bfloat16 or new_latent.shape != (self.rows, LATENT) or not new_latent.is_contiguous() \
+                or new_rope.dtype is not torch.bfloat16 or new_rope.shape != (self.rows, ROPE) or not new_rope.is_contiguous():
+            raise ValueError("new_latent is contiguous BF16 [rows, 512], new_rope contiguous BF16 [rows, 64]")
+        if seq_lens.dtype is not torch.int32 or seq_lens.shape != (self.rows,) or page_table.dtype is not torch.int32 \
+                or page_table.ndim != 2 or page_table.shape[0] != self.rows or page_table.stride(1) != 1:
+            raise ValueError("seq_lens is INT32 [rows], page_table INT32 [rows, max_pages]")
+        stream = bdfp4.current_stream(new_latent.device)
+        bdfp4.check("bdfp4_mla_append", bdfp4.library().bdfp4_mla_append(
+            new_latent.data_ptr(), new_rope.data_ptr(), self.latent.data_ptr(), self.rope.data_ptr(),
+            seq_lens.data_ptr(), page_table.data_ptr(), page_table.stride(0), self.rows, cache.pages,
+            self.source_tokens.data_ptr(), self.destination_pages.data_ptr(), bdfp4.ptr(error_word), stream))
+        write_pages(cache, self.latent, self.rope, self.source_tokens, self.destination_pages,
+                    key_scale_mode=self.key_scale_mode, value_scale_mode=self.value_scale_mode)
+
+
 class MLAScratch:
     """Buffers a decode call would otherwise allocate: query codes and scales, and the split partials.
     Build once per (rows, heads, num_splits) and pass as ``scratch=``; a serving loop then allocates

@@ -462,6 +462,17 @@ int bdfp4_mla_quantize_query(const void* query, int64_t row_pitch, int32_t rows,
 int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const int32_t* source_tokens,
                          const int32_t* destination_pages, int32_t work_items, void* rope_pages, int64_t rope_pitch,
                          void* stream);
+/* One new token per row: row r's token number seq_lens[r] (its length before the call) goes to
+ * position seq_lens[r] % 64 of the row's open page in the BF16 staging buffers (latent
+ * [rows][64][512], rope [rows][64][64]; a page that starts here has its other positions zeroed), and
+ * the work table of the page writers is filled: source_tokens[r] = 64 r (a token index into the
+ * staging buffers), destination_pages[r] = page_table[r][seq_lens[r] / 64] (-1 and BDFP4_DEV_BAD_PAGE
+ * when that is not a page of the cache). bdfp4_kv_write and bdfp4_mla_write_rope over that table
+ * then re-quantize every row's open page, so the cache always holds all tokens in NVFP4. */
+int bdfp4_mla_append(const void* new_latent, const void* new_rope, void* staging_latent, void* staging_rope,
+                     const int32_t* seq_lens, const int32_t* page_table, int64_t page_table_stride, int32_t rows,
+                     int32_t pages, int32_t* source_tokens, int32_t* destination_pages, int32_t* error_word,
+                     void* stream);
 int bdfp4_mla_decode(const bdfp4_mla_decode_args* args, void* stream);
 int bdfp4_mla_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
                       int32_t heads_q, void* out, void* stream);

@@ -204,3 +204,79 @@ def test_decode_with_scratch_is_capturable_and_identical(num_splits):
     assert torch.equal(out, plain)
     with pytest.raises(ValueError):
         mla.mla_decode(*args, softmax_scale=SCALE, num_splits=num_splits + 1, scratch=scratch)
+
+
+def test_append_requantizes_the_open_page():
+    """One token per row and step: after every append the cache holds exactly the oracle's
+    quantization of the row's tokens so far (the open page zero past the last token), across page
+    boundaries, and decode over it meets the gate."""
+    from nvfp4_decode_kernel import mla
+
+    starts, steps, heads = [0, 70, 127], 70, 128
+    rows = len(starts)
+    streams = [_tokens(((s + steps + 63) // 64) * 64, 900 + r) for r, s in enumerate(starts)]
+    max_pages = max(t[0].shape[0] // 64 for t in streams)
+    gen = torch.Generator().manual_seed(41)
+    table = torch.randperm(rows * max_pages + 1, generator=gen)[:rows * max_pages].to(torch.int32).reshape(rows, max_pages)
+    cache = mla.MLACache.allocate(rows * max_pages + 1, "cuda")
+    appender = mla.MLAAppender(rows, "cuda")
+    open_latent = torch.zeros(rows, 64, 512, dtype=torch.bfloat16)
+    open_rope = torch.zeros(rows, 64, 64, dtype=torch.bfloat16)
+    for r, start in enumerate(starts):  # what a prefill would have left: whole pages in the cache, the rest staged
+        latent, rope = streams[r]
+        whole = start // 64
+        if whole:
+            mla.write_pages(cache, latent[:whole * 64].cuda(), rope[:whole * 64].cuda(),
+                            (torch.arange(whole, dtype=torch.int32) * 64).cuda(), table[r, :whole].contiguous().cuda())
+        open_latent[r, :start - whole * 64] = latent[whole * 64:start]
+        open_rope[r, :start - whole * 64] = rope[whole * 64:start]
+    appender.load_open_pages(open_latent.cuda(), open_rope.cuda())
+    seq_lens = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    table_gpu = table.cuda()
+    for step in range(steps):
+        new_latent = torch.stack([streams[r][0][starts[r] + step] for r in range(rows)]).cuda()
+        new_rope = torch.stack([streams[r][1][starts[r] + step] for r in range(rows)]).cuda()
+        appender.append(cache, new_latent, new_rope, seq_lens, table_gpu, error_word=error)
+        seq_lens += 1
+    torch.cuda.synchronize()
+    assert int(error.item()) == 0
+    regions = {name: getattr(cache, name).cpu() for name in ("key_codes", "key_scales", "value_codes", "value_scales", "rope")}
+    for r, start in enumerate(starts):
+        length = start + steps
+        pages = -(-length // 64)
+        latent, rope = (t[:pages * 64].clone() for t in streams[r])
+        latent[length:] = 0
+        rope[length:] = 0
+        kc, ks, vc, vs = oracle.quantize_pages(latent.reshape(pages, 64, 512))
+        ids = table[r, :pages].long()
+        assert torch.equal(regions["key_codes"][ids], kc.permute(0, 2, 1, 3).reshape(pages, 16384)), r
+        assert torch.equal(regions["key_scales"][ids], ks.reshape(pages, 2048)), r
+        assert torch.equal(regions["value_codes"][ids], vc.reshape(pages, 16384)), r
+        assert torch.equal(regions["value_scales"][ids], vs.reshape(pages, 2048)), r
+        assert torch.equal(regions["rope"][ids], oracle.rope_page_bytes(rope.reshape(pages, 64, 64))), r
+    # decode over the appended cache against the oracle reading the same bytes
+    q_latent = torch.randn(rows, heads, 512, generator=gen).to(torch.bfloat16)
+    q_rope = torch.randn(rows, heads, 64, generator=gen).to(torch.bfloat16)
+    out = mla.mla_decode(q_latent.cuda(), q_rope.cuda(), cache, table_gpu, seq_lens, softmax_scale=SCALE)
+    total = cache.pages
+    _, _, q_values = oracle.quantize_query(q_latent)
+    want, _, _ = oracle.decode_reference(
+        q_values=q_values, q_rope=q_rope,
+        key_codes=regions["key_codes"].reshape(total, 4, 64, 64).permute(0, 2, 1, 3),
+        key_scales=regions["key_scales"].reshape(total, 4, 512), value_codes=regions["value_codes"].reshape(total, 4, 128, 32),
+        value_scales=regions["value_scales"].reshape(total, 4, 512),
+        rope=base_rope_from_bytes(regions["rope"]), page_table=table, seq_lens=seq_lens.cpu(),
+        softmax_scale=SCALE)
+    err = (out.float().cpu() - want.float()).abs()
+    assert float((err - MAX_ABS * want.float().abs().clamp_min(1.0)).max()) <= 0
+    assert float(err.mean() / want.float().abs().mean()) <= MEAN_REL
+
+
+def base_rope_from_bytes(blocks: torch.Tensor) -> torch.Tensor:
+    """u8 ``[pages, 8192]`` swizzled rope blocks -> BF16 ``[pages, 64, 64]`` (the placement is its own inverse)."""
+    from oracle import nvfp4_oracle as base
+
+    pages = blocks.shape[0]
+    raw = base._place_chunks(blocks.reshape(pages, 64, 128), (torch.arange(64) & 7)[None, :])
+    return raw.contiguous().view(torch.bfloat16).reshape(pages, 64, 64)
