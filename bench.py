@@ -716,6 +716,10 @@ def run_mla(args) -> None:
     host_q = torch.empty(rows, MLA_HEADS, 576, dtype=torch.bfloat16).pin_memory()
     host_q[..., :512].copy_(q_latent.cpu())
     host_q[..., 512:].copy_(q_rope.cpu())
+    host_new = torch.empty(rows, 576, dtype=torch.bfloat16).pin_memory()  # the step's new token per row
+    host_new[:, :512].copy_(new_latent.cpu())
+    host_new[:, 512:].copy_(new_rope.cpu())
+    device_new = torch.empty(rows, 576, dtype=torch.bfloat16, device=device)
     host_out = torch.empty(rows, MLA_HEADS, 512, dtype=torch.bfloat16).pin_memory()
     device_q = torch.empty(rows, MLA_HEADS, 576, dtype=torch.bfloat16, device=device)
     dense_latent = torch.empty(rows, MLA_HEADS, 512, dtype=torch.bfloat16, device=device)
@@ -723,6 +727,9 @@ def run_mla(args) -> None:
 
     def e2e_step():
         device_q.copy_(host_q, non_blocking=True)
+        device_new.copy_(host_new, non_blocking=True)
+        new_latent.copy_(device_new[:, :512])
+        new_rope.copy_(device_new[:, 512:])
         dense_latent.copy_(device_q[..., :512])
         dense_rope.copy_(device_q[..., 512:])
         host_out.copy_(decode(dense_latent, dense_rope), non_blocking=True)
@@ -758,7 +765,7 @@ def run_mla(args) -> None:
                 "partition": f"{rows} of {total_rows} rows per rank, no collective", "num_splits": splits,
                 "l2": "inputs (1.5 GB per step over all ranks) exceed the 126 MB L2; no flush needed",
                 "step": "append one token per row (stage, re-quantize the open page, rope block), query quantize, decode (+ merge)",
-                "e2e": "every step: H2D of the pinned query, the step, D2H of the output into pinned memory, synchronise",
+                "e2e": "every step: H2D of the pinned query and new token, the step, D2H of the output into pinned memory, synchronise",
             },
             "decode_kernel_us": kernel_ms * 1e3,
             "cache_read_gb_s": cache_bytes / (kernel_ms * 1e-3) / 1e9,
@@ -770,7 +777,7 @@ def run_mla(args) -> None:
                 "algorithmic_bytes_per_launch": algorithmic,
                 "note": "algorithmic bytes count one latent copy (416 B per token); this cache holds two (704 B)",
             },
-            "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": host_q.numel() * 2,
+            "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": (host_q.numel() + host_new.numel()) * 2,
                     "d2h_bytes_per_step": host_out.numel() * 2},
             "gpu_launches": args.steps * (5 if splits == 1 else 6),
             "clocks": sampler.summary(),
