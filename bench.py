@@ -791,6 +791,93 @@ def run_mla(args) -> None:
 
 
 
+# ---------------------------------------------------------------------------------------------
+# One very long sequence split along the KV axis over the ranks (`--workload longseq`): 1,048,576
+# tokens of the Qwen3-4B shape (32 query / 8 KV heads); the one path with a collective
+# ---------------------------------------------------------------------------------------------
+
+LONG_TOKENS = 1 << 20
+
+
+def run_longseq(args) -> None:
+    import torch.distributed as dist
+
+    from bdfp4.distributed import decode_kv_sharded
+    from bdfp4.workload import build_workload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run, one rank per GPU")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    total = args.context if args.context != CONTEXT else LONG_TOKENS
+    shard = total // world // 128 * 128
+    # every rank holds its shard as a cache of its own; the rolling tail (128 tokens here) and the sink
+    # exist on every rank's workload but only their owners pass them on
+    w = build_workload(rows=1, heads_q=HEADS_Q, heads_kv=HEADS_KV, seq_lens=[shard + 128], sink_tokens=SINK_ROWS,
+                       seed=7000 + rank, device=device, key_scale_mode="four_six", value_scale_mode="amax6",
+                       rotate=True, page_tokens=args.page_tokens)
+    w.seqused_sink.clamp_(max=SINK_USED)
+    zeros = torch.zeros_like(w.seqused_residual)
+    owner_tail, owner_sink = rank == world - 1, rank == 0
+    out = torch.empty(1, HEADS_Q, 128, dtype=torch.bfloat16, device=device)
+
+    def step():
+        return decode_kv_sharded(
+            w.query, *w.regions, w.page_table, w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
+            residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
+            seqused_residual=w.seqused_residual if owner_tail else zeros,
+            seqused_sink=w.seqused_sink if owner_sink else torch.zeros_like(w.seqused_sink), query_terms=2,
+            query_rotation="hadamard", out=out, num_splits=args.splits or None)
+
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    sampler.__enter__()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler.open_window()
+    begin.record()
+    for _ in range(args.steps):
+        step()
+    end.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sampler.close_window()
+    sampler.__exit__(None, None, None)
+    t = torch.tensor([begin.elapsed_time(end) / args.steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms = float(t.item())
+    shard_bytes = w.algorithmic_bytes()
+    peak, peak_kind = measured_peak_gbs()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "kv_sharded_decode_us_per_step", "value": step_ms * 1e3, "unit": "us/step", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"one sequence of {shard * world + 128:,} tokens, 32 query / 8 KV heads, {args.page_tokens}-token "
+                                   f"pages, split along the KV axis over {world} ranks; per step: query quantize, shard "
+                                   "decode (split again inside the rank), local merge, one all-gather of [O | LSE] "
+                                   "records, merge",
+                       "tokens_per_rank": shard},
+            "hbm_tb_s": shard_bytes * world / (step_ms * 1e-3) / 1e12,
+            "roofline": {"bound": "hbm", "achieved": shard_bytes / (step_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": shard_bytes / (step_ms * 1e-3) / 1e9 / peak, "traffic": None,
+                         "peak_kind": f"of {peak_kind}", "kernel": "whole step (per rank)",
+                         "algorithmic_bytes_per_launch": shard_bytes},
+            "clocks": sampler.summary(),
+        }))
+    dist.destroy_process_group()
+
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -811,12 +898,15 @@ def main() -> None:
                         help="merge split-KV partials inside the decode kernel instead of launching the merge "
                              "kernel (measured no faster)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--workload", default="gqa", choices=["gqa", "mla"],
-                        help="gqa: the headline Qwen3-4B-shaped step; mla: the MLA latent-cache decode configuration")
+    parser.add_argument("--workload", default="gqa", choices=["gqa", "mla", "longseq"],
+                        help="gqa: the headline Qwen3-4B-shaped step; mla: the MLA latent-cache decode configuration; "
+                             "longseq: one 1M-token sequence split along the KV axis over the ranks")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload == "mla":
+    if args.workload == "longseq":
+        run_longseq(args)
+    elif args.workload == "mla":
         run_mla_reference(args) if args.impl == "reference" else run_mla(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -30,6 +30,7 @@ EXPORTS = (
     "bdfp4_decode",
     "bdfp4_combine",
     "bdfp4_combine_strided",
+    "bdfp4_combine_record",
     "bdfp4_decode_split_static",
     "bdfp4_control_step",
     "bdfp4_work_table",
@@ -177,6 +178,8 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_decode.argtypes = [POINTER(DecodeArgs), c_void_p]
     lib.bdfp4_combine.restype = c_int32
     lib.bdfp4_combine.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]
+    lib.bdfp4_combine_record.restype = c_int32
+    lib.bdfp4_combine_record.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
     lib.bdfp4_combine_strided.restype = c_int32
     lib.bdfp4_combine_strided.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p,
                                           c_int64, c_void_p]
@@ -257,6 +260,14 @@ def combine(partial_out, partial_lse, parts: int, rows: int, heads_q: int, out, 
         library().bdfp4_combine(ptr(partial_out), ptr(partial_lse), parts, rows, heads_q, ptr(out),
                                 out_row_stride, stream),
     )
+
+
+def combine_record(partial_out, partial_lse, parts: int, rows: int, heads_q: int, record_out_ptr: int,
+                   record_lse_ptr: int, stream: int) -> None:
+    """Split-KV partials folded into one FP32 ``[O | LSE]`` partial (addresses given as integers)."""
+    check("bdfp4_combine_record",
+          library().bdfp4_combine_record(ptr(partial_out), ptr(partial_lse), parts, rows, heads_q, record_out_ptr,
+                                         record_lse_ptr, stream))
 
 
 def combine_strided(partial_out_ptr: int, out_part_stride: int, partial_lse_ptr: int, lse_part_stride: int,

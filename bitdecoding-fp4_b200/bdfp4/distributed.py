@@ -52,13 +52,18 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
                       residual_key_pages_bf16=None, residual_value_pages_bf16=None, residual_page_ids=None,
                       seqused_residual=None, seqused_sink=None, softmax_scale: float | None = None,
                       query_terms: int = 2, scale_mode: str = "amax6", query_rotation: str = "none",
-                      out: torch.Tensor | None = None) -> torch.Tensor:
+                      out: torch.Tensor | None = None, num_splits: int | None = None) -> torch.Tensor:
     """Decode attention over a sequence whose FP4 pages are sharded across the ranks of ``group``.
 
     Every rank passes the same ``query`` and its own shard: local cache regions, a local page table
     and ``seqused_fp4`` counting only its pages. Pass the BF16 residual arguments only on the rank
     that owns them (see the module docstring); with ``seqused_sink`` but ``seqused_residual`` zero a
     rank owns the sink alone. Returns the merged BF16 output on every rank.
+
+    A rank's shard of one long sequence is only ``rows * heads_kv`` independent walks, far fewer than
+    the GPU has SMs, so the shard is itself split along KV into ``num_splits`` parts (default: enough
+    to keep four CTAs per SM resident, from the batch width alone) whose partials the rank folds into
+    its one record before the exchange.
     """
     import torch.distributed as dist
 
@@ -89,11 +94,25 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
     record = record_floats(rows, heads_q)
     local = torch.empty(record, dtype=torch.float32, device=device)
     gathered = torch.empty(world * record, dtype=torch.float32, device=device)
-    args.num_splits = 1
-    args.partial_out = local.data_ptr()
-    args.partial_lse = local.data_ptr() + rows * heads_q * HEAD_DIM * 4
+    if num_splits is None:
+        num_splits = _decode.resident_num_splits(rows, heads_kv, sms=_decode._multiprocessor_count(device.index or 0))
     stream = bdfp4.current_stream(device)
-    bdfp4.decode(args, stream)
+    lse_offset = rows * heads_q * HEAD_DIM * 4
+    if num_splits <= 1:
+        args.num_splits = 1
+        args.partial_out = local.data_ptr()
+        args.partial_lse = local.data_ptr() + lse_offset
+        bdfp4.decode(args, stream)
+    else:
+        partial_out = torch.empty(num_splits, rows, heads_q, HEAD_DIM, dtype=torch.float32, device=device)
+        partial_lse = torch.empty(num_splits, rows, heads_q, dtype=torch.float32, device=device)
+        args.num_splits = num_splits
+        args.bf16_split = 0
+        args.out = None
+        args.partial_out, args.partial_lse = partial_out.data_ptr(), partial_lse.data_ptr()
+        bdfp4.decode(args, stream)
+        bdfp4.combine_record(partial_out, partial_lse, num_splits, rows, heads_q, local.data_ptr(),
+                             local.data_ptr() + lse_offset, stream)
     dist.all_gather_into_tensor(gathered, local, group=group)
     if out is None:
         out = torch.empty(rows, heads_q, head_dim, dtype=torch.bfloat16, device=device)

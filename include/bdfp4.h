@@ -287,6 +287,12 @@ int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t pa
  * all-gather: the KV-axis split of a single long sequence across GPUs. Merge math as above
  * (src/nvfp4_decode_kernel/split_k_combine.py:62-83); the reference has no multi-GPU merge.
  */
+/* Merge into another partial instead of the BF16 output: record_out FP32 [rows][Hq][128] normalised,
+ * record_lse FP32 [rows][Hq] = the natural-log LSE of all parts together (-inf when none
+ * contributed). A rank of a KV-axis shard folds its own split-KV parts with it into the one record
+ * it sends to the other ranks. */
+int bdfp4_combine_record(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
+                         int32_t heads_q, float* record_out, float* record_lse, void* stream);
 int bdfp4_combine_strided(const float* partial_out, int64_t out_part_stride, const float* partial_lse,
                           int64_t lse_part_stride, int32_t parts, int32_t rows, int32_t heads_q, void* out,
                           int64_t out_row_stride, void* stream);

@@ -32,7 +32,9 @@ def _shard_args(w, rank, world):
     return table, used, residual, sink, (first, last)
 
 
-def _oracle_sharded(w, world):
+def _oracle_sharded(w, world, splits=1):
+    """Every rank's shard decoded by the oracle (split again into ``splits`` parts inside the rank, as
+    the CUDA path is asked to), all partials merged at once: a two-level merge is the same sum."""
     from tests.test_gpu_decode import _cpu_cache
 
     kc, ks, vc, vs = _cpu_cache(w)
@@ -44,9 +46,10 @@ def _oracle_sharded(w, world):
             query_values=q["values"], query_padded=q["padded"], key_codes=kc, key_scales=ks, value_codes=vc,
             value_scales=vs, page_table=table.cpu(), seqused_fp4=used.cpu(), heads_kv=w.heads_kv,
             softmax_scale=128 ** -0.5, tail_key=w.tail_key[0].cpu(), tail_value=w.tail_value[0].cpu(),
-            tail_slot_ids=w.slot_ids.cpu(), seqused_residual=residual.cpu(), seqused_sink=sink.cpu())
-        outs.append(partial[0])
-        lses.append(lse[0])
+            tail_slot_ids=w.slot_ids.cpu(), seqused_residual=residual.cpu(), seqused_sink=sink.cpu(),
+            num_splits=splits)
+        outs.extend(partial)
+        lses.extend(lse)
     return oracle.combine_partials(torch.stack(outs), torch.stack(lses))
 
 
@@ -93,6 +96,50 @@ def test_shards_on_one_gpu(world):
     _check(out, _oracle_sharded(w, world))
 
 
+@pytest.mark.parametrize("splits", [3, 7])
+def test_shards_split_again_inside_a_rank(splits):
+    """A rank's shard is itself split along KV; its parts are folded into the rank's one record by
+    bdfp4_combine_record before the (here emulated) exchange."""
+    import bdfp4
+    from bdfp4.distributed import record_floats
+    from bdfp4.workload import build_workload
+    from nvfp4_decode_kernel import _decode
+    from nvfp4_decode_kernel._quantize import quantize_query
+
+    world = 2
+    w = build_workload(rows=1, heads_q=8, heads_kv=2, seq_lens=[4100], sink_tokens=16, seed=15 + splits)
+    rows, hq = w.rows, w.heads_q
+    padded = torch.zeros(rows, 128, hq, 128, dtype=torch.bfloat16, device="cuda")
+    quantized = quantize_query(w.query, query_padded_out=padded, heads_kv=w.heads_kv, query_terms=2)
+    record = record_floats(rows, hq)
+    gathered = torch.full((world * record,), float("nan"), device="cuda")
+    stream = bdfp4.current_stream(w.device)
+    for rank in range(world):
+        table, used, residual, sink, _ = _shard_args(w, rank, world)
+        partial_out = torch.full((splits, rows, hq, 128), float("nan"), device="cuda")
+        partial_lse = torch.full((splits, rows, hq), float("nan"), device="cuda")
+        a = bdfp4.DecodeArgs()
+        _decode._fill_args(
+            a, rows=rows, heads_q=hq, heads_kv=w.heads_kv, page_count=w.regions[0].shape[0],
+            query_fp4=quantized[0], query_scales=quantized[1], query_fp4_second=quantized[2],
+            query_scales_second=quantized[3], query_padded_bf16=padded, key_pages_fp4=w.regions[0],
+            key_scales=w.regions[1], value_pages_fp4=w.regions[2], value_scales=w.regions[3],
+            fp4_page_table=table, seqused_fp4=used, residual_key_pages_bf16=w.tail_key[0],
+            residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids, seqused_residual=residual,
+            seqused_sink=sink, softmax_scale=128 ** -0.5)
+        a.num_splits = splits
+        a.partial_out, a.partial_lse = partial_out.data_ptr(), partial_lse.data_ptr()
+        bdfp4.decode(a, stream)
+        slot = gathered.data_ptr() + rank * record * 4
+        bdfp4.combine_record(partial_out, partial_lse, splits, rows, hq, slot, slot + rows * hq * 128 * 4, stream)
+    out = torch.empty(rows, hq, 128, dtype=torch.bfloat16, device="cuda")
+    bdfp4.combine_strided(gathered.data_ptr(), record, gathered.data_ptr() + rows * hq * 128 * 4, record, world,
+                          rows, hq, out, out.stride(0), stream)
+    torch.cuda.synchronize()
+    assert not torch.isnan(gathered).any()
+    _check(out, _oracle_sharded(w, world, splits))
+
+
 def _nccl_worker(rank, world, port, result_dir):
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "bitdecoding-fp4_b200"))
@@ -111,11 +158,11 @@ def _nccl_worker(rank, world, port, result_dir):
     out = decode_kv_sharded(
         w.query, *w.regions, table, used, residual_key_pages_bf16=w.tail_key[0],
         residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids, seqused_residual=residual,
-        seqused_sink=sink, query_terms=2)
+        seqused_sink=sink, query_terms=2, num_splits=3)
     torch.cuda.synchronize()
     torch.save(out.cpu(), os.path.join(result_dir, f"out{rank}.pt"))
     if rank == 0:
-        torch.save(_oracle_sharded(w, world), os.path.join(result_dir, "want.pt"))
+        torch.save(_oracle_sharded(w, world, 3), os.path.join(result_dir, "want.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
