@@ -826,14 +826,16 @@ def run_longseq(args) -> None:
     zeros = torch.zeros_like(w.seqused_residual)
     owner_tail, owner_sink = rank == world - 1, rank == 0
     out = torch.empty(1, HEADS_Q, 128, dtype=torch.bfloat16, device=device)
+    workspace: dict = {}
+    no_sink = torch.zeros_like(w.seqused_sink)
 
     def step():
         return decode_kv_sharded(
             w.query, *w.regions, w.page_table, w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
             residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
             seqused_residual=w.seqused_residual if owner_tail else zeros,
-            seqused_sink=w.seqused_sink if owner_sink else torch.zeros_like(w.seqused_sink), query_terms=2,
-            query_rotation="hadamard", out=out, num_splits=args.splits or None)
+            seqused_sink=w.seqused_sink if owner_sink else no_sink, query_terms=2,
+            query_rotation="hadamard", out=out, num_splits=args.splits or None, workspace=workspace)
 
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(args.warmup):

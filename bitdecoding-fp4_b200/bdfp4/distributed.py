@@ -52,7 +52,8 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
                       residual_key_pages_bf16=None, residual_value_pages_bf16=None, residual_page_ids=None,
                       seqused_residual=None, seqused_sink=None, softmax_scale: float | None = None,
                       query_terms: int = 2, scale_mode: str = "amax6", query_rotation: str = "none",
-                      out: torch.Tensor | None = None, num_splits: int | None = None) -> torch.Tensor:
+                      out: torch.Tensor | None = None, num_splits: int | None = None,
+                      workspace: dict | None = None) -> torch.Tensor:
     """Decode attention over a sequence whose FP4 pages are sharded across the ranks of ``group``.
 
     Every rank passes the same ``query`` and its own shard: local cache regions, a local page table
@@ -63,7 +64,8 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
     A rank's shard of one long sequence is only ``rows * heads_kv`` independent walks, far fewer than
     the GPU has SMs, so the shard is itself split along KV into ``num_splits`` parts (default: enough
     to keep four CTAs per SM resident, from the batch width alone) whose partials the rank folds into
-    its one record before the exchange.
+    its one record before the exchange. ``workspace`` (a dict the caller keeps between steps) holds
+    the buffers a call would otherwise allocate; it is tied to the shapes of its first call.
     """
     import torch.distributed as dist
 
@@ -76,8 +78,23 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
     heads_kv = key_pages_fp4.shape[2]
     device = query.device
     has_residual = residual_key_pages_bf16 is not None
-    padded = (torch.zeros(rows, 128, heads_q, head_dim, dtype=torch.bfloat16, device=device)
-              if has_residual else None)
+    if num_splits is None:
+        num_splits = _decode.resident_num_splits(rows, heads_kv, sms=_decode._multiprocessor_count(device.index or 0))
+    record = record_floats(rows, heads_q)
+    ws = workspace if workspace is not None else {}
+    key = (rows, heads_q, world, num_splits, has_residual, device)
+    if ws.get("key") != key:
+        ws.clear()
+        ws["key"] = key
+        # rows past the first of each padded query tile stay zero: written once, here
+        ws["padded"] = (torch.zeros(rows, 128, heads_q, head_dim, dtype=torch.bfloat16, device=device)
+                        if has_residual else None)
+        ws["local"] = torch.empty(record, dtype=torch.float32, device=device)
+        ws["gathered"] = torch.empty(world * record, dtype=torch.float32, device=device)
+        if num_splits > 1:
+            ws["partial_out"] = torch.empty(num_splits, rows, heads_q, HEAD_DIM, dtype=torch.float32, device=device)
+            ws["partial_lse"] = torch.empty(num_splits, rows, heads_q, dtype=torch.float32, device=device)
+    padded = ws["padded"]
     quantized = quantize_query(query, query_padded_out=padded, heads_kv=heads_kv, query_terms=query_terms,
                                scale_mode=scale_mode, rotation=query_rotation)
     second = (quantized[2], quantized[3]) if query_terms == 2 else (None, None)
@@ -91,11 +108,7 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
         residual_key_pages_bf16=residual_key_pages_bf16, residual_value_pages_bf16=residual_value_pages_bf16,
         residual_page_ids=residual_page_ids, seqused_residual=seqused_residual, seqused_sink=seqused_sink,
         softmax_scale=softmax_scale if softmax_scale is not None else head_dim ** -0.5)
-    record = record_floats(rows, heads_q)
-    local = torch.empty(record, dtype=torch.float32, device=device)
-    gathered = torch.empty(world * record, dtype=torch.float32, device=device)
-    if num_splits is None:
-        num_splits = _decode.resident_num_splits(rows, heads_kv, sms=_decode._multiprocessor_count(device.index or 0))
+    local, gathered = ws["local"], ws["gathered"]
     stream = bdfp4.current_stream(device)
     lse_offset = rows * heads_q * HEAD_DIM * 4
     if num_splits <= 1:
@@ -104,8 +117,7 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
         args.partial_lse = local.data_ptr() + lse_offset
         bdfp4.decode(args, stream)
     else:
-        partial_out = torch.empty(num_splits, rows, heads_q, HEAD_DIM, dtype=torch.float32, device=device)
-        partial_lse = torch.empty(num_splits, rows, heads_q, dtype=torch.float32, device=device)
+        partial_out, partial_lse = ws["partial_out"], ws["partial_lse"]
         args.num_splits = num_splits
         args.bf16_split = 0
         args.out = None
