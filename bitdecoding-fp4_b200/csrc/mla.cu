@@ -183,7 +183,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
   const int part = (blockIdx.x >> 1) / (p.head_blocks * p.rows);
   const int head0 = head_block * kHeads;
   const int valid_heads = min(kHeads, p.heads_q - head0);
-  const int seq_len = max(p.seq_lens[row], 0);
+  // a length the row's page-table entries cannot cover is cut to what they cover
+  const int64_t covered = p.page_table_stride * 64;
+  const int seq_len = (int)min((int64_t)max(p.seq_lens[row], 0), covered);
   const int entries = (seq_len + 63) / 64;
   const int total_steps = (seq_len + kStep - 1) / kStep;
   const int chunk = (total_steps + p.num_splits - 1) / p.num_splits;

@@ -448,7 +448,8 @@ typedef struct bdfp4_mla_decode_args {
   const void* rope_pages;   /* BF16, 8192 bytes per page at rope_pitch bytes */
   int64_t rope_pitch;
   int32_t pages;
-  const int32_t* page_table; /* [rows][page_table_stride] 64-token pages, oldest first */
+  const int32_t* page_table; /* [rows][page_table_stride] 64-token pages, oldest first; a row's length is
+                                cut to the 64 * page_table_stride tokens its entries can cover */
   int64_t page_table_stride;
   const int32_t* seq_lens;   /* [rows] tokens */
   float softmax_scale;
