@@ -464,6 +464,21 @@ def run_ours(args) -> None:
         total_bytes = sum(gathered)
     else:
         total_bytes = algorithmic_bytes
+    # ---- parity at the benchmarked size, after and outside every timed region ------------------
+    verified = None
+    if args.verify and rank == 0:
+        from oracle import tile_check
+
+        torch.manual_seed(0)
+        tiles = [(int(torch.randint(rows, (1,))), int(torch.randint(heads_kv, (1,)))) for _ in range(args.verify)]
+        result = step(w.query, new_key, new_value)
+        torch.cuda.synchronize()
+        verified = tile_check.check_tiles(
+            w, result, tiles, terms=2, scale_mode="amax6", rotate=True, num_splits=splits, bf16_split=parts > splits,
+            bf16_page_cost=decode_module.BF16_BLOCK_PAGE_COST if parts == splits else 0)
+        verified["tolerance"] = {"max_abs": 1e-2, "mean_rel": 1e-3}
+        verified["against"] = "CPU oracle on sampled (row, KV head) tiles of this run's cache"
+
     peak, peak_kind = measured_peak_gbs()
     achieved = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
     clocks = sampler.summary()
@@ -508,6 +523,8 @@ def run_ours(args) -> None:
             "gpu_launches": args.steps * (3 if splits > 1 and not args.fused_merge else 2),
             "clocks": clocks,
         }
+        if verified is not None:
+            line["verified"] = verified
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(heads_kv, page_tokens=page_tokens)
         print(json.dumps(line))
@@ -900,6 +917,9 @@ def main() -> None:
                         help="merge split-KV partials inside the decode kernel instead of launching the merge "
                              "kernel (measured no faster)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--verify", type=int, default=4, metavar="TILES",
+                        help="after the timed regions, compare this many sampled (row, KV head) tiles of one decode "
+                             "with the CPU oracle and report the errors (0: skip)")
     parser.add_argument("--workload", default="gqa", choices=["gqa", "mla", "longseq"],
                         help="gqa: the headline Qwen3-4B-shaped step; mla: the MLA latent-cache decode configuration; "
                              "longseq: one 1M-token sequence split along the KV axis over the ranks")

@@ -16,7 +16,9 @@ LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libbdfp4.so"
 OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_TOO_LARGE = 0, -1, -2, -3, -4, -5
 STATIC_SCRATCH_BYTES = 8 << 20
 DEV_WAIT_TIMEOUT, DEV_BAD_PAGE = 1, 2
-SCALE_MODE_IDS = {"amax6": 0, "four_six": 1, "four_six_sixhalf": 2}
+SCALE_MODE_IDS = {"amax6": 0, "four_six": 1, "four_six_sixhalf": 2,
+                  "mxfp4_ocp": 3, "mxfp4_round_up": 4, "mxfp4_search": 5}
+FORMAT_NVFP4, FORMAT_MXFP4 = 0, 1
 P_MODE_IDS = {"amax6": 0, "amax2_or_amax6": 1, "amax2_or_amax6_c8": 2}
 SHIFT_NONE, SHIFT_F32, SHIFT_BF16 = 0, 1, 2
 
@@ -71,6 +73,8 @@ class KvWriteArgs(Structure):
         ("rows", c_int32), ("decode_rows", c_int32), ("first_row", c_int32),
         ("error_word", c_void_p),
         ("page_tokens", c_int32),
+        ("pages", c_int32),
+        ("key_tensor_scale", c_float), ("value_tensor_scale", c_float),
     ]
 
 
@@ -88,6 +92,7 @@ class QuantizeQueryArgs(Structure):
         ("tail_key", c_void_p), ("tail_value", c_void_p), ("tail_slot_stride", c_int64),
         ("row_to_slot", c_void_p), ("seq_lens", c_void_p), ("seqused_fp4", c_void_p),
         ("rotate_key", c_int32), ("key_shift", c_void_p), ("sink_tokens", c_int32),
+        ("tensor_scale", c_float),
     ]
 
 
@@ -116,6 +121,8 @@ class DecodeArgs(Structure):
         ("page_tokens", c_int32),
         ("merge_counters", c_void_p),
         ("row_order", c_void_p),
+        ("scale_format", c_int32),
+        ("key_tensor_scale", c_float), ("query_tensor_scale", c_float), ("value_tensor_scale", c_float),
     ]
 
 
@@ -202,7 +209,7 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_mla_write_rope.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p]
     lib.bdfp4_mla_append.restype = c_int32
     lib.bdfp4_mla_append.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
-                                     c_int32, c_void_p, c_void_p, c_void_p, c_void_p]
+                                     c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.bdfp4_mla_decode.restype = c_int32
     lib.bdfp4_mla_decode.argtypes = [POINTER(MlaDecodeArgs), c_void_p]
     lib.bdfp4_mla_combine.restype = c_int32

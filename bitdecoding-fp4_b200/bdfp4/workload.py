@@ -24,11 +24,13 @@ PAGE = 128
 HEAD_DIM = 128
 
 
-def carve_cache(blocks: torch.Tensor, heads: int, page_tokens: int = PAGE):
+def carve_cache(blocks: torch.Tensor, heads: int, page_tokens: int = PAGE, scale_format: str = "nvfp4"):
     """Four region views of a flat ``[num_blocks, 2*page_tokens*H*72]`` u8 cache: K codes, K scales,
-    V codes, V scales at byte offsets 0, 64, 72 and 136 times ``page_tokens * H``."""
+    V codes, V scales at byte offsets 0, 64, 72 and 136 times ``page_tokens * H``. An MXFP4 cache
+    (128-token pages) keeps those offsets and uses the first half of each scale region."""
     num_blocks, block_bytes = blocks.shape
     assert page_tokens in (128, 64) and block_bytes == 2 * page_tokens * heads * 72
+    assert scale_format == "nvfp4" or page_tokens == PAGE
     pitch = blocks.stride(0)
     base, origin = blocks, blocks.storage_offset()
     codes, scales = page_tokens * 64 * heads, page_tokens * 8 * heads  # bytes of one region
@@ -40,10 +42,10 @@ def carve_cache(blocks: torch.Tensor, heads: int, page_tokens: int = PAGE):
         origin + codes + scales,
     )
     if page_tokens == PAGE:
-        key_scales = base.as_strided((num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024),
-                                     origin + codes)
-        value_scales = base.as_strided((num_blocks, 32, 4, 1, 4, 2, heads), (pitch, 16, 4, 1024, 1, 512, 1024),
-                                       origin + 2 * codes + scales)
+        atoms = 1 if scale_format == "mxfp4" else 2
+        shape, strides = (num_blocks, 32, 4, 1, 4, atoms, heads), (pitch, 16, 4, atoms * 512, 1, 512, atoms * 512)
+        key_scales = base.as_strided(shape, strides, origin + codes)
+        value_scales = base.as_strided(shape, strides, origin + 2 * codes + scales)
     else:
         key_scales = base.as_strided((num_blocks, 32, 2, 1, 4, 2, heads), (pitch, 8, 4, 512, 1, 256, 512),
                                      origin + codes)
@@ -79,6 +81,8 @@ class Workload:
     key_shift: torch.Tensor | None = None
     rotate: bool = False
     page_tokens: int = PAGE
+    scale_format: str = "nvfp4"
+    tensor_scales: tuple = (1.0, 1.0, 1.0)  # key, query, value
     outlier_scale: torch.Tensor = None  # [H, 128] multiplicative factors applied to K
     kept: dict = field(default_factory=dict)  # raw BF16 K/V of each row when keep_source
 
@@ -96,22 +100,29 @@ def build_workload(
     *, rows: int, heads_q: int, heads_kv: int, seq_lens, sink_tokens: int = 16, seed: int = 0,
     device="cuda", key_scale_mode: str = "amax6", value_scale_mode: str = "amax6", rotate: bool = False,
     key_shift: bool = False, shuffle: bool = True, keep_source: bool = False, chunk_pages: int = 256,
-    page_tokens: int = PAGE,
+    page_tokens: int = PAGE, key_tensor_scale: float = 1.0, value_tensor_scale: float = 1.0,
+    loud_prefix: int = 0, loud_factor: float = 6.0,
 ) -> Workload:
     """Generate K/V, quantize them into a paged cache with ``KVCacheWriter`` and fill the BF16
-    tail and sink, sequence by sequence so that temporaries stay bounded."""
+    tail and sink, sequence by sequence so that temporaries stay bounded. An ``mxfp4_*`` key scale mode
+    builds an MXFP4 cache. ``loud_prefix`` multiplies the keys of every sequence's first tokens by
+    ``loud_factor``: the oldest pages and the sink, which the decode reaches last, then score far
+    above what came before them, so the running maximum has to move late in the walk."""
     from nvfp4_decode_kernel.quantize_kv_kernel import KVCacheWriter
+    from nvfp4_decode_kernel.scale_mode import scale_format as format_of
 
     device = torch.device(device)
     seq_lens = [int(n) for n in seq_lens]
     assert len(seq_lens) == rows
     gen = torch.Generator(device=device).manual_seed(seed)
-    w = Workload(rows, heads_q, heads_kv, seq_lens, sink_tokens, device, rotate=rotate, page_tokens=page_tokens)
+    w = Workload(rows, heads_q, heads_kv, seq_lens, sink_tokens, device, rotate=rotate, page_tokens=page_tokens,
+                 scale_format=format_of(key_scale_mode),
+                 tensor_scales=(float(key_tensor_scale), 1.0, float(value_tensor_scale)))
     pages_per_row = [split_lengths(n, sink_tokens)[1] // page_tokens for n in seq_lens]
     max_pages = max(1, max(pages_per_row))
     num_blocks = 1 + sum(pages_per_row)
     w.blocks = torch.zeros(num_blocks, 2 * page_tokens * heads_kv * 72, dtype=torch.uint8, device=device)
-    w.regions = carve_cache(w.blocks, heads_kv, page_tokens)
+    w.regions = carve_cache(w.blocks, heads_kv, page_tokens, w.scale_format)
     # the block order has a generator of its own, so the token values do not depend on the page size
     order_gen = torch.Generator(device=device).manual_seed(seed + 0x5EED)
     order = torch.randperm(num_blocks - 1, generator=order_gen, device=device) + 1 if shuffle else torch.arange(
@@ -131,7 +142,7 @@ def build_workload(
     writer = KVCacheWriter(
         regions=w.regions, key_scale_mode=key_scale_mode, value_scale_mode=value_scale_mode,
         rotate_key=rotate, key_shift=w.key_shift, tail_key=w.tail_key, tail_value=w.tail_value,
-        sink_tokens=sink_tokens,
+        sink_tokens=sink_tokens, key_tensor_scale=key_tensor_scale, value_tensor_scale=value_tensor_scale,
     )
     cursor = 0
     fp4_list, tail_list, sink_list = [], [], []
@@ -152,7 +163,10 @@ def build_workload(
             last = start == starts[-1]
             tokens_here = (n - start) if last else (stop - start)
             k = torch.randn(tokens_here, heads_kv, HEAD_DIM, generator=gen, device=device)
-            k = (k * w.outlier_scale).to(torch.bfloat16)
+            k = k * w.outlier_scale
+            if start < loud_prefix:
+                k[:loud_prefix - start] *= loud_factor
+            k = k.to(torch.bfloat16)
             v = torch.randn(tokens_here, heads_kv, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
             if keep_source:
                 kept_k.append(k)

@@ -18,6 +18,11 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ 
   const float* lse = partial_lse + (int64_t)row * heads_q + head;
   const float* values = partial_out + ((int64_t)row * heads_q + head) * kHeadDim + channel;
   constexpr float kLog2e = 1.4426950408889634f;
+  // Launched with programmatic stream serialization: the CTAs may be resident before the decode
+  // launch that writes the partials has finished, so its results are waited for here; the launch
+  // behind this one (the next step's query quantizer) may then bring its CTAs up in turn.
+  wait_for_prior_kernels();
+  dependents_may_launch();
 
   float lse_max = -INFINITY;
   for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, lse[s * lse_stride]);
@@ -48,6 +53,8 @@ __global__ void __launch_bounds__(128) combine_record_kernel(const float* __rest
   const float* lse = partial_lse + (int64_t)row * heads_q + head;
   const float* values = partial_out + ((int64_t)row * heads_q + head) * kHeadDim + channel;
   constexpr float kLog2e = 1.4426950408889634f;
+  wait_for_prior_kernels();
+  dependents_may_launch();
   float lse_max = -INFINITY;
   for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, lse[s * lse_stride]);
   const bool empty = lse_max == -INFINITY;
@@ -65,15 +72,32 @@ __global__ void __launch_bounds__(128) combine_record_kernel(const float* __rest
     record_lse[(int64_t)row * heads_q + head] = (empty || inverse == 0.0f) ? -INFINITY : lse_max + logf(weight_sum);
 }
 
+// After a decode launch of this library (which lets its dependents launch early) the merge's CTAs are
+// resident by the time the last partial is written; after anything else this is an ordinary launch.
+template <typename... Params, typename... Args>
+static cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, cudaStream_t stream, Args... args) {
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = dim3(128);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 }  // namespace bdfp4
 
 extern "C" int bdfp4_combine_record(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
                                     int32_t heads_q, float* record_out, float* record_lse, void* stream) {
   if (!partial_out || !partial_lse || !record_out || !record_lse || parts < 1 || rows < 1 || heads_q < 1)
     return BDFP4_E_ARG;
-  bdfp4::combine_record_kernel<<<dim3(heads_q, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial_out, partial_lse, parts, rows, heads_q, record_out, record_lse);
-  return bdfp4::cuda_status(cudaGetLastError());
+  return bdfp4::cuda_status(bdfp4::launch_overlapped(bdfp4::combine_record_kernel, dim3(heads_q, rows),
+                                                     static_cast<cudaStream_t>(stream), partial_out, partial_lse,
+                                                     (int)parts, (int)rows, (int)heads_q, record_out, record_lse));
 }
 
 extern "C" int bdfp4_combine_strided(const float* partial_out, int64_t out_part_stride, const float* partial_lse,
@@ -83,10 +107,10 @@ extern "C" int bdfp4_combine_strided(const float* partial_out, int64_t out_part_
   if (out_row_stride < (int64_t)heads_q * bdfp4::kHeadDim) return BDFP4_E_ARG;
   if (out_part_stride < (int64_t)rows * heads_q * bdfp4::kHeadDim || lse_part_stride < (int64_t)rows * heads_q)
     return BDFP4_E_ARG;
-  bdfp4::combine_kernel<<<dim3(heads_q, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial_out, partial_lse, parts, rows, heads_q, static_cast<__nv_bfloat16*>(out), out_row_stride,
-      out_part_stride, lse_part_stride);
-  return bdfp4::cuda_status(cudaGetLastError());
+  return bdfp4::cuda_status(bdfp4::launch_overlapped(
+      bdfp4::combine_kernel, dim3(heads_q, rows), static_cast<cudaStream_t>(stream), partial_out, partial_lse,
+      (int)parts, (int)rows, (int)heads_q, static_cast<__nv_bfloat16*>(out), out_row_stride, out_part_stride,
+      lse_part_stride));
 }
 
 extern "C" int bdfp4_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,

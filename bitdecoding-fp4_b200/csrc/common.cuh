@@ -25,19 +25,26 @@ constexpr int kGroup = 16;
 constexpr int kGroupsPerVec = kHeadDim / kGroup;  // 8
 constexpr int kMaxCandidates = 3;
 
+// MXFP4 exponent rules (src/nvfp4_decode_kernel/scale_mode.py:40-49); 0 = an NVFP4 mode
+constexpr int kMxNone = 0, kMxOcp = 1, kMxRoundUp = 2, kMxSearch = 3;
+
 struct ScaleCandidates {
   int count;
   float reciprocal[kMaxCandidates];  // fl32(1/divisor), tie-break order
+  int mx_rule;                       // kMx*: E8M0 scale per 32 values instead of the candidates above
 };
 
+// `mode` is a BDFP4_SCALE_* id: 0-2 NVFP4 candidate sets, 3-5 the MXFP4 rules.
 __host__ __device__ inline ScaleCandidates scale_candidates(int mode) {
   ScaleCandidates c;
   c.count = 1;
   c.reciprocal[0] = (float)(1.0 / 6.0);
   c.reciprocal[1] = (float)(1.0 / 4.0);
   c.reciprocal[2] = (float)(1.0 / 6.5);
+  c.mx_rule = kMxNone;
   if (mode == 1) c.count = 2;
   if (mode == 2) c.count = 3;
+  if (mode >= 3) c.mx_rule = mode - 2;
   return c;
 }
 
@@ -184,6 +191,95 @@ __device__ __forceinline__ GroupCodes quantize_group16(const float* x, const Sca
     }
   }
   return best;
+}
+
+// ---- MXFP4: E2M1 codes on a power-of-two scale shared by 32 values ---------------------------
+// (src/nvfp4_decode_kernel/_block_scale.py:384-546, CPU model src/nvfp4_decode_kernel/reference.py:262-328)
+
+// 2^e for an E8M0 exponent in [-127, 127]; 2^-127 is the one subnormal.
+__device__ __forceinline__ float mx_power_of_two(int e) {
+  return __uint_as_float(e < -126 ? (1u << 22) : ((uint32_t)(e + 127) << 23));
+}
+
+// floor(log2(amax)) - 2 clamped below at -127, read off the exponent field: a zero or subnormal
+// maximum lands on the clamp (_block_scale.py:418-427).
+__device__ __forceinline__ int mx_ocp_exponent(float amax) {
+  return max((int)((__float_as_uint(amax) >> 23) & 0xffu) - 129, -127);
+}
+
+// The smallest exponent whose scale keeps amax at or below six: one more than the OCP exponent
+// exactly when the mantissa is above 1.5, which is when adding 0x3FFFFF carries into the exponent
+// field (_block_scale.py:430-440).
+__device__ __forceinline__ int mx_round_up_exponent(float amax) {
+  return max((int)((__float_as_uint(amax) + 0x3FFFFFu) >> 23) - 129, -127);
+}
+
+// The stored byte of a power-of-two scale: its exponent field (0 for 2^-127).
+__device__ __forceinline__ uint32_t e8m0_byte(float scale) { return (__float_as_uint(scale) >> 23) & 0xffu; }
+
+// Sixteen values on the scale 2^e: their codes and the squared error of this half of the group.
+__device__ __forceinline__ void mx_encode16(const float* x, int e, uint32_t& lo, uint32_t& hi, float& error) {
+  const float scale = mx_power_of_two(e), inverse = mx_power_of_two(-e);
+  float scaled[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) scaled[i] = __fmul_rn(x[i], inverse);
+  lo = pack_e2m1x8(scaled);
+  hi = pack_e2m1x8(scaled + 8);
+  error = reconstruction_error16(x, scale, lo, hi);
+}
+
+// One lane's half of a 32-value group that it shares with the adjacent lane (lane ^ 1): the
+// maximum and, under the search rule, the two halves' errors are exchanged by shuffle; a half's
+// error is accumulated by FMA in element order and the group's is the one FP32 sum of the halves
+// (reference.py:113-118). Every lane of the warp must call it.
+__device__ __forceinline__ GroupCodes mx_quantize_pair16(const float* x, int rule) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  int e = rule == kMxRoundUp ? mx_round_up_exponent(amax) : mx_ocp_exponent(amax);
+  GroupCodes best;
+  float error;
+  mx_encode16(x, e, best.lo, best.hi, error);
+  if (rule == kMxSearch) {
+    const int above = min(e + 1, 127);
+    uint32_t lo, hi;
+    float error_above;
+    mx_encode16(x, above, lo, hi, error_above);
+    const float total = __fadd_rn(error, __shfl_xor_sync(0xffffffffu, error, 1));
+    const float total_above = __fadd_rn(error_above, __shfl_xor_sync(0xffffffffu, error_above, 1));
+    if (total_above < total) {
+      e = above;
+      best.lo = lo;
+      best.hi = hi;
+    }
+  }
+  best.scale = mx_power_of_two(e);
+  return best;
+}
+
+// A whole 32-value group held by one thread: `words` receives its 16 bytes of codes.
+__device__ __forceinline__ float mx_quantize32(const float* x, int rule, uint32_t* words) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  int e = rule == kMxRoundUp ? mx_round_up_exponent(amax) : mx_ocp_exponent(amax);
+  float error0, error1;
+  mx_encode16(x, e, words[0], words[1], error0);
+  mx_encode16(x + 16, e, words[2], words[3], error1);
+  if (rule == kMxSearch) {
+    const int above = min(e + 1, 127);
+    uint32_t other[4];
+    float above0, above1;
+    mx_encode16(x, above, other[0], other[1], above0);
+    mx_encode16(x + 16, above, other[2], other[3], above1);
+    if (__fadd_rn(above0, above1) < __fadd_rn(error0, error1)) {
+      e = above;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) words[i] = other[i];
+    }
+  }
+  return mx_power_of_two(e);
 }
 
 // x - decode(codes) * scale for one group, one rounding per element

@@ -682,8 +682,9 @@ __global__ void __launch_bounds__(256) rope_page_kernel(const __nv_bfloat16* rop
 __global__ void __launch_bounds__(128) append_kernel(const __nv_bfloat16* new_latent, const __nv_bfloat16* new_rope,
                                                      __nv_bfloat16* staging_latent, __nv_bfloat16* staging_rope,
                                                      const int32_t* seq_lens, const int32_t* page_table,
-                                                     int64_t page_table_stride, int pages, int32_t* source_tokens,
-                                                     int32_t* destination_pages, int32_t* error_word) {
+                                                     int64_t page_table_stride, int page_table_columns, int pages,
+                                                     int32_t* source_tokens, int32_t* destination_pages,
+                                                     int32_t* error_word) {
   wait_for_prior_kernels();
   dependents_may_launch();
   const int row = blockIdx.x;
@@ -701,7 +702,10 @@ __global__ void __launch_bounds__(128) append_kernel(const __nv_bfloat16* new_la
   if (t >= 64 && t < 72)
     rope[position * 8 + (t - 64)] = __ldg(reinterpret_cast<const uint4*>(new_rope + (int64_t)row * kRope) + (t - 64));
   if (t == 0) {
-    int page = page_table[(int64_t)row * page_table_stride + (length >> 6)];
+    // a row that has filled every column of its table has no open page: reading one column further
+    // would return the next row's first entry, a valid page of another sequence
+    const int column = length >> 6;
+    int page = column < page_table_columns ? page_table[(int64_t)row * page_table_stride + column] : -1;
     if (page < 0 || page >= pages) {
       if (error_word) atomicOr(error_word, (int)BDFP4_DEV_BAD_PAGE);
       page = -1;
@@ -792,12 +796,12 @@ extern "C" int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const
 
 extern "C" int bdfp4_mla_append(const void* new_latent, const void* new_rope, void* staging_latent, void* staging_rope,
                                 const int32_t* seq_lens, const int32_t* page_table, int64_t page_table_stride,
-                                int32_t rows, int32_t pages, int32_t* source_tokens, int32_t* destination_pages,
-                                int32_t* error_word, void* stream) {
+                                int32_t page_table_columns, int32_t rows, int32_t pages, int32_t* source_tokens,
+                                int32_t* destination_pages, int32_t* error_word, void* stream) {
   if (!new_latent || !new_rope || !staging_latent || !staging_rope || !seq_lens || !page_table || !source_tokens ||
       !destination_pages)
     return BDFP4_E_ARG;
-  if (rows < 1 || pages < 1 || page_table_stride < 1) return BDFP4_E_ARG;
+  if (rows < 1 || pages < 1 || page_table_columns < 1 || page_table_stride < page_table_columns) return BDFP4_E_ARG;
   auto misaligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
   if (misaligned(new_latent) || misaligned(new_rope) || misaligned(staging_latent) || misaligned(staging_rope))
     return BDFP4_E_ARG;
@@ -805,7 +809,7 @@ extern "C" int bdfp4_mla_append(const void* new_latent, const void* new_rope, vo
       mla::append_kernel, dim3((unsigned)rows), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(new_latent), static_cast<const __nv_bfloat16*>(new_rope),
       static_cast<__nv_bfloat16*>(staging_latent), static_cast<__nv_bfloat16*>(staging_rope), seq_lens, page_table,
-      page_table_stride, (int)pages, source_tokens, destination_pages, error_word));
+      page_table_stride, (int)page_table_columns, (int)pages, source_tokens, destination_pages, error_word));
 }
 
 extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_handle) {

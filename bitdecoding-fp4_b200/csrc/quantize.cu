@@ -2,6 +2,8 @@
 // query. One thread owns one 16-value scale group; a head vector is eight adjacent lanes, so
 // global loads are 256-byte coalesced runs and the Hadamard's upper three index bits are
 // warp shuffles. Scale bytes are staged in shared memory and leave as whole 1024-byte tiles.
+#include <cmath>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -33,7 +35,30 @@ struct KvWriteParams {
   const int32_t* seqused_fp4;
   const int32_t* row_to_slot;
   int rows, decode_rows, first_row;
+  int pages;              // pages in each destination region (0: unknown)
+  int32_t* error_word;
+  float key_inverse_scale, value_inverse_scale;  // fl32(1 / tensor scale); 1 when there is none
 };
+
+// A work item's destination page, or -1 when the item is to be skipped: a negative id by
+// convention, an id past the cache because a corrupt work table must not write outside it
+// (that one is reported).
+__device__ __forceinline__ int destination_page(const KvWriteParams& p, int work) {
+  const int page = p.destination_pages[work];
+  if (page >= 0 && p.pages > 0 && page >= p.pages) {
+    if (threadIdx.x == 0 && p.error_word) atomicOr(p.error_word, (int)BDFP4_DEV_BAD_PAGE);
+    return -1;
+  }
+  return page;
+}
+
+// The pages hold x / tensor_scale: a multiplication by the reciprocal, rounded once.
+__device__ __forceinline__ void apply_inverse_scale(float* v, float inverse, int n = 16) {
+  if (inverse != 1.0f) {
+#pragma unroll
+    for (int j = 0; j < n; ++j) v[j] = __fmul_rn(v[j], inverse);
+  }
+}
 
 template <int SHIFT_TYPE>
 __device__ __forceinline__ void load_shift16(const void* shift, int64_t offset, float* out) {
@@ -84,19 +109,21 @@ __host__ __device__ __forceinline__ int key_scale_offset64(int token, int group)
 }
 
 // One CTA = one head of one K page of PT tokens: 8 * PT scale groups, PT / 32 per thread.
-template <int SHIFT_TYPE, bool ROTATE, int PT>
+template <int SHIFT_TYPE, bool ROTATE, int PT, bool MX>
 __device__ __forceinline__ void key_page_body(const KvWriteParams& p, int item, int grid_layer, uint8_t* scale_tile) {
-  constexpr int kScaleBytes = PT * 8;
+  // MXFP4 (128-token pages only) stores one E8M0 byte per 32 channels: half the scale bytes
+  constexpr bool mx = MX;
+  constexpr int scale_bytes = mx ? PT * 4 : PT * 8;
   const int layer = p.bases ? grid_layer : p.layer;
   const int head = item % p.heads;
   const int work = item / p.heads;
-  const int page = p.destination_pages[work];
+  const int page = destination_page(p, work);
   if (page < 0) return;
   const int64_t source_token = (int64_t)p.source_tokens[work] + (int64_t)grid_layer * p.source_layer_stride;
   uint8_t* codes = p.bases ? reinterpret_cast<uint8_t*>(p.bases[0 * p.layers + layer]) : p.region[0];
   uint8_t* scales = p.bases ? reinterpret_cast<uint8_t*>(p.bases[1 * p.layers + layer]) : p.region[1];
   codes += (int64_t)page * p.pitch[0];
-  scales += (int64_t)page * p.pitch[1] + head * kScaleBytes;
+  scales += (int64_t)page * p.pitch[1] + head * scale_bytes;
 
 #pragma unroll 1
   for (int it = 0; it < PT / 32; ++it) {
@@ -107,7 +134,11 @@ __device__ __forceinline__ void key_page_body(const KvWriteParams& p, int item, 
     load_bf16x16(p.key + (source_token + token) * p.key_pitch + head * kHeadDim + group * kGroup, v);
     cache_basis16<SHIFT_TYPE, ROTATE>(v, group, p.key_shift,
                                       ((int64_t)layer * p.heads + head) * kHeadDim + group * kGroup);
-    const GroupCodes q = quantize_group16(v, p.key_cand);
+    apply_inverse_scale(v, p.key_inverse_scale);
+    // an MXFP4 group of 32 channels is shared by the lanes holding channel groups 2k and 2k + 1
+    GroupCodes q;
+    if constexpr (mx) q = mx_quantize_pair16(v, p.key_cand.mx_rule);
+    else q = quantize_group16(v, p.key_cand);
     if constexpr (PT == 128) {
       *reinterpret_cast<uint2*>(codes + ((int64_t)token * p.heads + head) * 64 + group * 8) = make_uint2(q.lo, q.hi);
     } else {
@@ -116,18 +147,23 @@ __device__ __forceinline__ void key_page_body(const KvWriteParams& p, int item, 
       *reinterpret_cast<uint2*>(codes + (int64_t)head * (PT * 64) + token * 64 + chunk * 16 + (group & 1) * 8) =
           make_uint2(q.lo, q.hi);
     }
-    scale_tile[PT == 128 ? scale_tile_offset(token, group) : key_scale_offset64(token, group)] =
-        (uint8_t)cvt_e4m3(q.scale);
+    if constexpr (mx) {
+      // one atom per head: (token, 32-channel group g) at (token % 32) * 16 + (token / 32) * 4 + g
+      if ((group & 1) == 0) scale_tile[scale_tile_offset(token, group >> 1)] = (uint8_t)e8m0_byte(q.scale);
+    } else {
+      scale_tile[PT == 128 ? scale_tile_offset(token, group) : key_scale_offset64(token, group)] =
+          (uint8_t)cvt_e4m3(q.scale);
+    }
   }
   __syncthreads();
-  if (threadIdx.x < kScaleBytes / 4)
+  if (threadIdx.x < scale_bytes / 4)
     reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
 }
 
-template <int SHIFT_TYPE, bool ROTATE, int PT>
+template <int SHIFT_TYPE, bool ROTATE, int PT, bool MX>
 __global__ void __launch_bounds__(256) key_page_kernel(const KvWriteParams p) {
   __shared__ __align__(16) uint8_t scale_tile[PT * 8];
-  key_page_body<SHIFT_TYPE, ROTATE, PT>(p, blockIdx.x, blockIdx.z, scale_tile);
+  key_page_body<SHIFT_TYPE, ROTATE, PT, MX>(p, blockIdx.x, blockIdx.z, scale_tile);
 }
 
 // One CTA = one head of one V page of PT tokens. Scale groups run along the page's tokens, so the
@@ -141,22 +177,24 @@ struct ValueTile {
   static constexpr int kSmem = PT * kHeadDim * 2 + kHeadDim * kCodePitch + kScaleBytes;
 };
 
-template <int PT>
+template <int PT, bool MX>
 __device__ __forceinline__ void value_page_body(const KvWriteParams& p, int item, int grid_layer, uint8_t* smem) {
   using T = ValueTile<PT>;
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [PT][128]
   uint8_t* code_tile = smem + PT * kHeadDim * 2;                 // [128][kCodePitch]
   uint8_t* scale_tile = code_tile + kHeadDim * T::kCodePitch;    // [kScaleBytes]
+  constexpr bool mx = MX;
+  constexpr int scale_bytes = mx ? T::kScaleBytes / 2 : T::kScaleBytes;
   const int layer = p.bases ? grid_layer : p.layer;
   const int head = item % p.heads;
   const int work = item / p.heads;
-  const int page = p.destination_pages[work];
+  const int page = destination_page(p, work);
   if (page < 0) return;
   const int64_t source_token = (int64_t)p.source_tokens[work] + (int64_t)grid_layer * p.source_layer_stride;
   uint8_t* codes = p.bases ? reinterpret_cast<uint8_t*>(p.bases[2 * p.layers + layer]) : p.region[2];
   uint8_t* scales = p.bases ? reinterpret_cast<uint8_t*>(p.bases[3 * p.layers + layer]) : p.region[3];
   codes += (int64_t)page * p.pitch[2] + (int64_t)head * (kHeadDim * T::kCodeBytes);
-  scales += (int64_t)page * p.pitch[3] + head * T::kScaleBytes;
+  scales += (int64_t)page * p.pitch[3] + head * scale_bytes;
 
 #pragma unroll
   for (int it = 0; it < PT / 16; ++it) {
@@ -168,17 +206,38 @@ __device__ __forceinline__ void value_page_body(const KvWriteParams& p, int item
     reinterpret_cast<uint4*>(tile)[index] = v;
   }
   __syncthreads();
+  if constexpr (mx) {
+    // MXFP4: a thread owns a whole group of 32 tokens of one channel; one atom of E8M0 bytes per head
 #pragma unroll 1
-  for (int it = 0; it < PT / 32; ++it) {
-    const int index = it * 256 + threadIdx.x;
-    const int channel = index & 127;
-    const int group = index >> 7;  // token group
-    float v[16];
+    for (int it = 0; it < PT / 64; ++it) {
+      const int index = it * 256 + threadIdx.x;
+      const int channel = index & 127;
+      const int group = index >> 7;  // 32-token group
+      float v[32];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(tile[(group * 16 + i) * kHeadDim + channel]);
-    const GroupCodes q = quantize_group16(v, p.value_cand);
-    *reinterpret_cast<uint2*>(code_tile + channel * T::kCodePitch + group * 8) = make_uint2(q.lo, q.hi);
-    scale_tile[scale_tile_offset(channel, group)] = (uint8_t)cvt_e4m3(q.scale);
+      for (int i = 0; i < 32; ++i) v[i] = __bfloat162float(tile[(group * 32 + i) * kHeadDim + channel]);
+      apply_inverse_scale(v, p.value_inverse_scale, 32);
+      uint32_t words[4];
+      const float scale = mx_quantize32(v, p.value_cand.mx_rule, words);
+      uint2* dst = reinterpret_cast<uint2*>(code_tile + channel * T::kCodePitch + group * 16);
+      dst[0] = make_uint2(words[0], words[1]);
+      dst[1] = make_uint2(words[2], words[3]);
+      scale_tile[scale_tile_offset(channel, group)] = (uint8_t)e8m0_byte(scale);
+    }
+  } else {
+#pragma unroll 1
+    for (int it = 0; it < PT / 32; ++it) {
+      const int index = it * 256 + threadIdx.x;
+      const int channel = index & 127;
+      const int group = index >> 7;  // token group
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(tile[(group * 16 + i) * kHeadDim + channel]);
+      apply_inverse_scale(v, p.value_inverse_scale);
+      const GroupCodes q = quantize_group16(v, p.value_cand);
+      *reinterpret_cast<uint2*>(code_tile + channel * T::kCodePitch + group * 8) = make_uint2(q.lo, q.hi);
+      scale_tile[scale_tile_offset(channel, group)] = (uint8_t)cvt_e4m3(q.scale);
+    }
   }
   __syncthreads();
 #pragma unroll
@@ -192,28 +251,28 @@ __device__ __forceinline__ void value_page_body(const KvWriteParams& p, int item
     reinterpret_cast<uint2*>(codes)[dst] =
         *reinterpret_cast<const uint2*>(code_tile + channel * T::kCodePitch + chunk * 8);
   }
-  if (threadIdx.x < T::kScaleBytes / 4)
+  if (threadIdx.x < scale_bytes / 4)
     reinterpret_cast<uint32_t*>(scales)[threadIdx.x] = reinterpret_cast<const uint32_t*>(scale_tile)[threadIdx.x];
 }
 
-template <int PT>
+template <int PT, bool MX>
 __global__ void __launch_bounds__(256) value_page_kernel(const KvWriteParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
-  value_page_body<PT>(p, blockIdx.x, blockIdx.z, smem);
+  value_page_body<PT, MX>(p, blockIdx.x, blockIdx.z, smem);
 }
 
 // K and V pages in one launch: even CTAs quantize a K page head, odd CTAs the V page head of the
 // same work item. The K role is bound by arithmetic and the V role by its loads and the staging
 // tile, so CTAs of both kinds resident on one SM overlap instead of running back to back.
 // (Five CTAs per SM measured faster for 64-token pages, four for 128-token pages.)
-template <int SHIFT_TYPE, bool ROTATE, int PT>
-__global__ void __launch_bounds__(256, PT == 64 ? 5 : 4) kv_page_kernel(const KvWriteParams p) {
+template <int SHIFT_TYPE, bool ROTATE, int PT, bool MX>
+__global__ void __launch_bounds__(256, MX ? 2 : (PT == 64 ? 5 : 4)) kv_page_kernel(const KvWriteParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int item = blockIdx.x >> 1;
   if (blockIdx.x & 1)
-    value_page_body<PT>(p, item, blockIdx.z, smem);
+    value_page_body<PT, MX>(p, item, blockIdx.z, smem);
   else
-    key_page_body<SHIFT_TYPE, ROTATE, PT>(p, item, blockIdx.z, smem);
+    key_page_body<SHIFT_TYPE, ROTATE, PT, MX>(p, item, blockIdx.z, smem);
 }
 
 // One 16-element group of one token's new K or V into the BF16 tail: at `offset` of the rolling
@@ -319,32 +378,32 @@ __global__ void __launch_bounds__(128) tail_token_kernel(const KvWriteParams p) 
   }
 }
 
-template <int PT>
+template <int PT, bool MX>
 static cudaError_t launch_value_pages(const KvWriteParams& p, int page_items, cudaStream_t stream) {
   const int smem = ValueTile<PT>::kSmem;
   static PerDeviceOnce configured;
   const int slot = current_device_slot();
   if (slot < 0 || !configured.done[slot]) {
-    cudaError_t e = cudaFuncSetAttribute(value_page_kernel<PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(value_page_kernel<PT, MX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     if (slot >= 0) configured.done[slot] = true;
   }
-  value_page_kernel<PT><<<dim3(page_items, 1, p.layers), 256, smem, stream>>>(p);
+  value_page_kernel<PT, MX><<<dim3(page_items, 1, p.layers), 256, smem, stream>>>(p);
   return cudaGetLastError();
 }
 
-template <int SHIFT_TYPE, bool ROTATE, int PT>
+template <int SHIFT_TYPE, bool ROTATE, int PT, bool MX>
 static cudaError_t launch_kv_pages(const KvWriteParams& p, int page_items, cudaStream_t stream) {
   const int smem = ValueTile<PT>::kSmem;
   static PerDeviceOnce configured;
   const int slot = current_device_slot();
   if (slot < 0 || !configured.done[slot]) {
-    cudaError_t e = cudaFuncSetAttribute(kv_page_kernel<SHIFT_TYPE, ROTATE, PT>,
+    cudaError_t e = cudaFuncSetAttribute(kv_page_kernel<SHIFT_TYPE, ROTATE, PT, MX>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     if (slot >= 0) configured.done[slot] = true;
   }
-  kv_page_kernel<SHIFT_TYPE, ROTATE, PT><<<dim3(2 * page_items, 1, p.layers), 256, smem, stream>>>(p);
+  kv_page_kernel<SHIFT_TYPE, ROTATE, PT, MX><<<dim3(2 * page_items, 1, p.layers), 256, smem, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -353,20 +412,30 @@ static cudaError_t launch_kv_write(const KvWriteParams& p, int page_tokens, cuda
   const int page_items = p.heads * p.work_items;
   const bool key_pages = p.key && (p.region[0] || p.bases) && page_items > 0;
   const bool value_pages = p.value && (p.region[2] || p.bases) && page_items > 0;
-  if (key_pages && value_pages) {
-    cudaError_t e = page_tokens == 64 ? launch_kv_pages<SHIFT_TYPE, ROTATE, 64>(p, page_items, stream)
-                                      : launch_kv_pages<SHIFT_TYPE, ROTATE, 128>(p, page_items, stream);
+  const bool mx_key = p.key_cand.mx_rule != kMxNone, mx_value = p.value_cand.mx_rule != kMxNone;
+  const dim3 grid(page_items, 1, p.layers);
+  // K and V pages of one scale format go in one launch; MXFP4 exists for 128-token pages only
+  const bool fused = key_pages && value_pages && mx_key == mx_value;
+  if (fused) {
+    cudaError_t e = mx_key             ? launch_kv_pages<SHIFT_TYPE, ROTATE, 128, true>(p, page_items, stream)
+                    : page_tokens == 64 ? launch_kv_pages<SHIFT_TYPE, ROTATE, 64, false>(p, page_items, stream)
+                                        : launch_kv_pages<SHIFT_TYPE, ROTATE, 128, false>(p, page_items, stream);
     if (e != cudaSuccess) return e;
-  } else if (key_pages) {
-    if (page_tokens == 64)
-      key_page_kernel<SHIFT_TYPE, ROTATE, 64><<<dim3(page_items, 1, p.layers), 256, 0, stream>>>(p);
+  }
+  if (key_pages && !fused) {
+    if (mx_key)
+      key_page_kernel<SHIFT_TYPE, ROTATE, 128, true><<<grid, 256, 0, stream>>>(p);
+    else if (page_tokens == 64)
+      key_page_kernel<SHIFT_TYPE, ROTATE, 64, false><<<grid, 256, 0, stream>>>(p);
     else
-      key_page_kernel<SHIFT_TYPE, ROTATE, 128><<<dim3(page_items, 1, p.layers), 256, 0, stream>>>(p);
+      key_page_kernel<SHIFT_TYPE, ROTATE, 128, false><<<grid, 256, 0, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-  } else if (value_pages) {
-    cudaError_t e = page_tokens == 64 ? launch_value_pages<64>(p, page_items, stream)
-                                      : launch_value_pages<128>(p, page_items, stream);
+  }
+  if (value_pages && !fused) {
+    cudaError_t e = mx_value           ? launch_value_pages<128, true>(p, page_items, stream)
+                    : page_tokens == 64 ? launch_value_pages<64, false>(p, page_items, stream)
+                                        : launch_value_pages<128, false>(p, page_items, stream);
     if (e != cudaSuccess) return e;
   }
   if (p.tail_key) {
@@ -407,6 +476,7 @@ struct QueryParams {
   const int32_t* seqused_fp4;
   const float* key_shift;
   int sink_tokens;
+  float inverse_scale;  // fl32(1 / tensor scale); 1 when there is none
 };
 
 // The atom's four E4M3 scale bytes as one word, gathered from its four adjacent lanes.
@@ -419,15 +489,29 @@ __device__ __forceinline__ uint32_t gather_scale_word(float scale, int slot) {
 
 __device__ __forceinline__ void store_query_term(const QueryParams& p, int term, const GroupCodes& q, int row,
                                                  int head, int group, bool active) {
-  const int slot = group & 3;
-  const uint32_t word = gather_scale_word(q.scale, slot);
+  const bool mx = p.cand.mx_rule != kMxNone;
+  uint32_t word;
+  if (mx) {
+    // the head's four E8M0 bytes sit in its even lanes (one per 32-channel group): gather them
+    word = (group & 1) ? 0u : e8m0_byte(q.scale) << ((group >> 1) * 8);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    word |= __shfl_xor_sync(0xffffffffu, word, 4);
+  } else {
+    word = gather_scale_word(q.scale, group & 3);
+  }
   if (!active) return;
   *reinterpret_cast<uint2*>(p.codes[term] + ((int64_t)row * p.heads_q + head) * 64 + group * 8) =
       make_uint2(q.lo, q.hi);
-  if (slot == 0) {
-    const int ratio = p.heads_q / p.heads_kv;
-    const int packed_row = head % ratio;
-    const int kv_head = head / ratio;
+  const int ratio = p.heads_q / p.heads_kv;
+  const int packed_row = head % ratio;
+  const int kv_head = head / ratio;
+  if (mx) {
+    // one 512-byte atom per (row, KV head) tile: the storage is [rows][1][Hq][1][32][4][4]
+    if (group == 0) {
+      uint8_t* tile = p.scales[term] + ((int64_t)row * p.heads_q + kv_head) * 512;
+      *reinterpret_cast<uint32_t*>(tile + (packed_row & 31) * 16 + (packed_row >> 5) * 4) = word;
+    }
+  } else if ((group & 3) == 0) {
     uint8_t* tile = p.scales[term] + ((int64_t)row * p.heads_q + kv_head) * 1024;
     *reinterpret_cast<uint32_t*>(tile + (group >> 2) * 512 + (packed_row & 31) * 16 + (packed_row >> 5) * 4) = word;
   }
@@ -469,12 +553,14 @@ __global__ void __launch_bounds__(128) quantize_query_kernel(const QueryParams p
   if (p.padded && active) {
     store_bf16x16(p.padded + (((int64_t)row * kPage) * p.heads_q + head) * kHeadDim + group * kGroup, v);
   }
-  const GroupCodes first = quantize_group16(v, p.cand);
+  apply_inverse_scale(v, p.inverse_scale);
+  const bool mx = p.cand.mx_rule != kMxNone;
+  const GroupCodes first = mx ? mx_quantize_pair16(v, p.cand.mx_rule) : quantize_group16(v, p.cand);
   store_query_term(p, 0, first, row, head, group, active);
   if (SECOND) {
     float residual[16];
     group_residual16(v, first, residual);
-    const GroupCodes second = quantize_group16(residual, p.cand);
+    const GroupCodes second = mx ? mx_quantize_pair16(residual, p.cand.mx_rule) : quantize_group16(residual, p.cand);
     store_query_term(p, 1, second, row, head, group, active);
   }
 }
@@ -520,8 +606,14 @@ extern "C" int bdfp4_kv_write(const bdfp4_kv_write_args* a, void* stream_handle)
   if (a->heads < 1 || a->work_items < 0) return BDFP4_E_ARG;
   const int page_tokens = a->page_tokens == 0 ? kPage : a->page_tokens;
   if (page_tokens != 128 && page_tokens != 64) return BDFP4_E_UNSUPPORTED;
-  if (a->key_scale_mode < 0 || a->key_scale_mode > 2 || a->value_scale_mode < 0 || a->value_scale_mode > 2)
+  if (a->key_scale_mode < 0 || a->key_scale_mode > BDFP4_SCALE_MXFP4_SEARCH || a->value_scale_mode < 0 ||
+      a->value_scale_mode > BDFP4_SCALE_MXFP4_SEARCH)
     return BDFP4_E_ARG;
+  const bool mx_key = a->key_scale_mode >= BDFP4_SCALE_MXFP4_OCP, mx_value = a->value_scale_mode >= BDFP4_SCALE_MXFP4_OCP;
+  if ((mx_key || mx_value) && page_tokens != 128) return BDFP4_E_UNSUPPORTED;
+  if (a->pages < 0) return BDFP4_E_ARG;
+  auto bad_scale = [](float s) { return s != 0.0f && !(s > 0.0f && isfinite(s)); };
+  if (bad_scale(a->key_tensor_scale) || bad_scale(a->value_tensor_scale)) return BDFP4_E_ARG;
   const bool per_layer = a->bases != nullptr;
   const bool write_key = a->key && (per_layer || a->key_codes);
   const bool write_value = a->value && (per_layer || a->value_codes);
@@ -597,6 +689,10 @@ extern "C" int bdfp4_kv_write(const bdfp4_kv_write_args* a, void* stream_handle)
   p.rows = a->rows;
   p.decode_rows = a->decode_rows;
   p.first_row = a->first_row;
+  p.pages = a->pages;
+  p.error_word = a->error_word;
+  p.key_inverse_scale = a->key_tensor_scale == 0.0f ? 1.0f : 1.0f / a->key_tensor_scale;
+  p.value_inverse_scale = a->value_tensor_scale == 0.0f ? 1.0f : 1.0f / a->value_tensor_scale;
   if (!write_key) p.key = write_tail ? p.key : nullptr;
   if (!write_value) p.value = write_tail ? p.value : nullptr;
 
@@ -622,7 +718,8 @@ extern "C" int bdfp4_quantize_query(const bdfp4_quantize_query_args* a, void* st
   if (!a) return BDFP4_E_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
   if (a->rows < 1 || a->heads_q < 1 || a->heads_kv < 1 || a->heads_q % a->heads_kv) return BDFP4_E_ARG;
-  if (a->scale_mode < 0 || a->scale_mode > 2) return BDFP4_E_ARG;
+  if (a->scale_mode < 0 || a->scale_mode > BDFP4_SCALE_MXFP4_SEARCH) return BDFP4_E_ARG;
+  if (a->tensor_scale != 0.0f && !(a->tensor_scale > 0.0f && isfinite(a->tensor_scale))) return BDFP4_E_ARG;
   if (!a->query || !aligned16(a->query) || a->query_row_stride % 8 || a->query_head_stride % 8) return BDFP4_E_ARG;
   if (!a->query_codes || !a->query_scales || !aligned16(a->query_codes) || !aligned16(a->query_scales))
     return BDFP4_E_ARG;
@@ -664,6 +761,7 @@ extern "C" int bdfp4_quantize_query(const bdfp4_quantize_query_args* a, void* st
   p.seqused_fp4 = a->seqused_fp4;
   p.key_shift = a->key_shift;
   p.sink_tokens = a->sink_tokens;
+  p.inverse_scale = a->tensor_scale == 0.0f ? 1.0f : 1.0f / a->tensor_scale;
   const int tail_chunks = tail ? tail_chunks_for(a->heads_kv) : 0;
   const dim3 grid(a->rows, p.query_chunks + tail_chunks, 1);
   const bool second = a->query_codes_second != nullptr;

@@ -240,6 +240,17 @@ __host__ __device__ constexpr uint32_t nvf4_idesc(int m, int n) {
   return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Instruction descriptor of kind::mxf4 (E2M1 x E2M1, UE8M0 scales per 32 values, scale_vec::2X): as
+// above with the scale format bit 23 set. One 32-bit TMEM column holds a row's scales of two 64-value
+// K slices, two bytes each; mxf4_sf_ids names the first byte (0 or 2) the instruction uses for B in
+// bits [4,6) and for A in bits [29,31).
+__host__ __device__ constexpr uint32_t mxf4_idesc(int m, int n) {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t mxf4_sf_ids(int a_id, int b_id) {
+  return ((uint32_t)b_id << 4) | ((uint32_t)a_id << 29);
+}
+
 // Instruction descriptor of kind::f16 with BF16 operands, FP32 accumulate, both K-major:
 // D format F32 = 1 at [4,6), A/B format BF16 = 1 at [7,10)/[10,13), N >> 3 at [17,23), M >> 4 at [24,29).
 __host__ __device__ constexpr uint32_t bf16_idesc(int m, int n) {
@@ -264,6 +275,16 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint6
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t sfa_tmem, uint32_t sfb_tmem, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }

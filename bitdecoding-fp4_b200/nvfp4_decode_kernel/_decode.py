@@ -19,6 +19,8 @@ from .interface import SINK_TOKENS, split_partial_count
 from .p_scale import BUILT_P_SCALE_MODES, resolve_p_scale_environment, resolve_p_scale_tau
 
 PAGE_SIZE = 128
+# values per scale: NVFP4 stores an E4M3 scale per 16, MXFP4 an E8M0 scale per 32
+SCALE_FORMATS = {"nvfp4": 16, "mxfp4": 32}
 # Cache page sizes this build serves. 128 is the reference's only size; with 64-token pages (no
 # reference counterpart) a sequence still moves to FP4 in 128-token steps, two page-table entries
 # each, and the page size is read off the shape of ``key_pages_fp4``.
@@ -93,7 +95,16 @@ def _check_device_values(bad: torch.Tensor, message: str) -> None:
         raise ValueError(message)
 
 
-def _p_scale_arguments() -> tuple[int, float]:
+def _p_scale_arguments(scale_format: str = "nvfp4") -> tuple[int, float]:
+    """The probability-scale rule and threshold of an NVFP4 launch. MXFP4 has one rule of its own, so
+    the NVFP4 overrides in the environment do not apply to it
+    (src/nvfp4_decode_kernel/_decode.py:172-180 of OpenBitSys/BitDecoding-FP4)."""
+    if scale_format == "mxfp4":
+        import os
+
+        if "NVFP4_P_SCALE_MODE" in os.environ or "NVFP4_P_SCALE_DIVISOR" in os.environ:
+            raise ValueError("the NVFP4 P-scale overrides do not apply to MXFP4")
+        return bdfp4.P_MODE_IDS["amax6"], resolve_p_scale_tau()
     mode, _, _ = resolve_p_scale_environment()
     if mode not in BUILT_P_SCALE_MODES:
         raise NotImplementedError(
@@ -109,8 +120,10 @@ def _validate(
     seqused_sink, has_bf16, softmax_scale, out, out_indices, trusted_metadata, scale_format, row_order=None,
 ):
     """Every host-side contract check of the decode entry; returns the derived geometry."""
-    if scale_format != "nvfp4":
-        raise NotImplementedError("only the NVFP4 (E4M3 per 16) scale format is built")
+    if scale_format not in SCALE_FORMATS:
+        raise ValueError(f"scale_format must be one of {list(SCALE_FORMATS)}, got {scale_format!r}")
+    # scale atoms (512 bytes: 128 rows x 4 groups) along the 128-value contraction axis
+    atoms = HEAD_DIM // (4 * SCALE_FORMATS[scale_format])
     if not torch.cuda.is_available():
         raise RuntimeError("decode_fp4 requires CUDA")
     if not math.isfinite(softmax_scale) or softmax_scale <= 0.0:
@@ -152,6 +165,8 @@ def _validate(
     ):
         raise ValueError("key_pages_fp4 must be packed FP4 with shape [pages, 128, heads_kv, 64]")
     page_count, cache_page, heads_kv, _ = key_pages_fp4.shape
+    if scale_format == "mxfp4" and cache_page != PAGE_SIZE:
+        raise NotImplementedError("MXFP4 is built for 128-token pages only")
     if value_pages_fp4.dtype not in packed_types or tuple(value_pages_fp4.shape) != (
         page_count, heads_kv, HEAD_DIM, cache_page // 2,
     ):
@@ -172,16 +187,16 @@ def _validate(
         raise NotImplementedError(
             f"this build serves at most {MAX_QUERY_HEADS_PER_KV_HEAD} query heads per KV head, got {ratio}"
         )
-    expected_query_sf = (32, 4, 1, 4, 2, heads_kv, rows)
+    expected_query_sf = (32, 4, 1, 4, atoms, heads_kv, rows)
     # scale regions as (pages, 32, 4, 1, 4, atoms, heads) views of [heads][atoms][32][4][4] bytes; a
     # 64-token K page holds two half atoms, (pages, 32, 2, 1, 4, 2, heads) over [heads][2][32][2][4]
     if cache_page == PAGE_SIZE:
-        expected_key_sf = expected_value_sf = (page_count, 32, 4, 1, 4, 2, heads_kv)
-        key_sf_strides = value_sf_strides = (16, 4, 1024, 1, 512, 1024)
+        expected_key_sf = expected_value_sf = (page_count, 32, 4, 1, 4, atoms, heads_kv)
+        key_sf_strides = value_sf_strides = (16, 4, atoms * 512, 1, 512, atoms * 512)
     else:
         expected_key_sf, key_sf_strides = (page_count, 32, 2, 1, 4, 2, heads_kv), (8, 4, 512, 1, 256, 512)
         expected_value_sf, value_sf_strides = (page_count, 32, 4, 1, 4, 1, heads_kv), (16, 4, 512, 1, 512, 512)
-    query_sf_strides = (16, 4, heads_q * 1024, 1, 512, 1024, heads_q * 1024)
+    query_sf_strides = (16, 4, heads_q * atoms * 512, 1, 512, atoms * 512, heads_q * atoms * 512)
     for scales, name in ((query_scales, "query_scales"), (query_scales_second, "query_scales_second")):
         if scales is None:
             continue
@@ -198,8 +213,8 @@ def _validate(
     ):
         if tuple(scales.shape) != expected_page_sf:
             raise ValueError(f"{name} must have shape {expected_page_sf}")
-        if scales.dtype not in (torch.uint8, torch.float8_e4m3fn):
-            raise ValueError(f"{name} must hold E4M3 scale bytes")
+        if scales.dtype not in (torch.uint8, torch.float8_e4m3fn if scale_format == "nvfp4" else torch.float8_e8m0fnu):
+            raise ValueError(f"{name} must hold the scale bytes of the {scale_format} format")
         if scales.stride()[1:] != sf_strides or scales.stride(0) % 512:
             raise ValueError(f"{name} must use the quantizer's scale layout with a 512-byte aligned page pitch")
     if (
@@ -333,7 +348,8 @@ def _fill_args(
     a: "bdfp4.DecodeArgs", *, rows, heads_q, heads_kv, page_count, query_fp4, query_scales, query_fp4_second,
     query_scales_second, query_padded_bf16, key_pages_fp4, key_scales, value_pages_fp4, value_scales,
     fp4_page_table, seqused_fp4, residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids,
-    seqused_residual, seqused_sink, softmax_scale, row_order=None,
+    seqused_residual, seqused_sink, softmax_scale, row_order=None, scale_format: str = "nvfp4",
+    tensor_scales=(1.0, 1.0, 1.0),
 ) -> None:
     a.rows, a.heads_q, a.heads_kv = rows, heads_q, heads_kv
     a.query_codes, a.query_scales = query_fp4.data_ptr(), query_scales.data_ptr()
@@ -357,8 +373,10 @@ def _fill_args(
         a.seqused_residual = seqused_residual.data_ptr()
         a.seqused_sink = bdfp4.ptr(seqused_sink)
     a.softmax_scale = float(softmax_scale)
-    a.p_scale_mode, a.p_scale_tau = _p_scale_arguments()
+    a.p_scale_mode, a.p_scale_tau = _p_scale_arguments(scale_format)
     a.row_order = bdfp4.ptr(row_order)
+    a.scale_format = bdfp4.FORMAT_MXFP4 if scale_format == "mxfp4" else bdfp4.FORMAT_NVFP4
+    a.key_tensor_scale, a.query_tensor_scale, a.value_tensor_scale = (float(x) for x in tensor_scales)
 
 
 def decode_fp4(
@@ -367,7 +385,7 @@ def decode_fp4(
     residual_key_pages_bf16=None, residual_value_pages_bf16=None, residual_page_ids=None,
     seqused_residual=None, seqused_sink=None, has_bf16=None, softmax_scale: float, out=None,
     out_indices=None, trusted_metadata: bool = False, validate_only: bool = False,
-    scale_format: str = "nvfp4", row_order=None,
+    scale_format: str = "nvfp4", row_order=None, tensor_scales=(1.0, 1.0, 1.0),
 ):
     """Validate and launch the unsplit decode; returns BF16 ``[rows, heads_q, 128]`` (a view of
     ``out[:rows]`` when given), or None under ``validate_only``."""
@@ -394,7 +412,7 @@ def decode_fp4(
         seqused_fp4=seqused_fp4, residual_key_pages_bf16=residual_key_pages_bf16,
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, seqused_sink=seqused_sink, softmax_scale=softmax_scale,
-        row_order=row_order,
+        row_order=row_order, scale_format=scale_format, tensor_scales=tensor_scales,
     )
     a.out, a.out_row_stride = out.data_ptr(), out.stride(0)
     a.num_splits = 1
@@ -408,7 +426,7 @@ def decode_fp4_split(
     query_padded_bf16=None, residual_key_pages_bf16=None, residual_value_pages_bf16=None,
     residual_page_ids=None, seqused_residual=None, seqused_sink=None, has_bf16=None, out=None,
     split_partial_scratch=None, split_lse_scratch=None, scale_format: str = "nvfp4",
-    split_merge_counters=None, row_order=None,
+    split_merge_counters=None, row_order=None, tensor_scales=(1.0, 1.0, 1.0),
 ):
     """Split-KV decode: ``num_splits`` CTAs per (row, KV head) write FP32 partials and LSEs,
     then one combine launch produces the BF16 output, or, given ``split_merge_counters`` (INT32,
@@ -457,7 +475,7 @@ def decode_fp4_split(
         seqused_fp4=seqused_fp4, residual_key_pages_bf16=residual_key_pages_bf16,
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, seqused_sink=seqused_sink, softmax_scale=softmax_scale,
-        row_order=row_order,
+        row_order=row_order, scale_format=scale_format, tensor_scales=tensor_scales,
     )
     a.num_splits = num_splits
     a.bf16_split = int(parts > num_splits)

@@ -42,13 +42,15 @@ def quantize_query(
     scale_mode: str = DEFAULT_SCALE_MODE,
     rotation: str = "none",
     tail_write: DecodeTailWrite | None = None,
+    tensor_scale: float = 1.0,
 ):
     """Quantize BF16 decode rows; returns ``(q, s)`` or, with two terms, ``(q0, s0, q1, s1)``.
 
     Outputs may come from the caller and may be wider than this batch; a supplied scale buffer
     must arrive zeroed, because only the ``heads // heads_kv`` scale rows of each KV-head tile
     that carry a query head are ever written, and it belongs to one ``(heads, heads_kv,
-    head_dim)`` geometry for its whole life.
+    head_dim)`` geometry for its whole life. ``tensor_scale`` (no reference counterpart) is an FP32
+    per-tensor scale: the terms then hold ``query / tensor_scale``.
     """
     if query_terms not in (1, 2):
         raise ValueError(f"query_terms must be 1 or 2, got {query_terms!r}")
@@ -94,7 +96,7 @@ def quantize_query(
         query, query_fp4, query_scales, query_padded_out,
         query_fp4_out_2=second[0], query_scales_out_2=second[1],
         row_indices=row_indices, heads_kv=heads_kv, scale_mode=scale_mode, rotation=rotation,
-        tail_write=tail_write,
+        tail_write=tail_write, tensor_scale=tensor_scale,
     )
     if query_terms == 2:
         return query_fp4, query_scales, second[0], second[1]

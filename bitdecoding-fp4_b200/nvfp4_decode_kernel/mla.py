@@ -100,6 +100,7 @@ def write_pages(cache: MLACache, latent: torch.Tensor, rope: torch.Tensor, sourc
     a.key_scale_mode, a.value_scale_mode = mode_id(key_scale_mode), mode_id(value_scale_mode)
     a.key_shift_type = bdfp4.SHIFT_NONE
     a.page_tokens = PAGE_TOKENS
+    a.pages = cache.pages
     bdfp4.kv_write(a, stream)
     check = bdfp4.check
     check("bdfp4_mla_write_rope",
@@ -141,7 +142,8 @@ class MLAAppender:
         stream = bdfp4.current_stream(new_latent.device)
         bdfp4.check("bdfp4_mla_append", bdfp4.library().bdfp4_mla_append(
             new_latent.data_ptr(), new_rope.data_ptr(), self.latent.data_ptr(), self.rope.data_ptr(),
-            seq_lens.data_ptr(), page_table.data_ptr(), page_table.stride(0), self.rows, cache.pages,
+            seq_lens.data_ptr(), page_table.data_ptr(), page_table.stride(0), page_table.shape[1], self.rows,
+            cache.pages,
             self.source_tokens.data_ptr(), self.destination_pages.data_ptr(), bdfp4.ptr(error_word), stream))
         write_pages(cache, self.latent, self.rope, self.source_tokens, self.destination_pages,
                     key_scale_mode=self.key_scale_mode, value_scale_mode=self.value_scale_mode)

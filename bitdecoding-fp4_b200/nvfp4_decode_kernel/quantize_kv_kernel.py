@@ -97,6 +97,9 @@ class KVCacheWriter:
         tail_value: torch.Tensor | None = None,
         sink_tokens: int = 0,
         destination_bases: torch.Tensor | None = None,
+        key_tensor_scale: float = 1.0,
+        value_tensor_scale: float = 1.0,
+        error_word: torch.Tensor | None = None,
     ) -> None:
         key_packed, key_scales, value_packed, value_scales = regions
         any_packed = key_packed if key_packed is not None else value_packed
@@ -117,8 +120,18 @@ class KVCacheWriter:
             )
         if "mxfp4" in formats and key_scale_geometry != "local":
             raise ValueError("MXFP4 pages support local scales only")
-        if "mxfp4" in formats:
-            raise NotImplementedError("MXFP4 page quantization is not built")
+        if "mxfp4" in formats and self.page_size != PAGE_SIZE:
+            raise NotImplementedError("MXFP4 pages are built for 128 tokens only")
+        for name, scale in (("key_tensor_scale", key_tensor_scale), ("value_tensor_scale", value_tensor_scale)):
+            if not (scale > 0.0 and scale < float("inf")):
+                raise ValueError(f"{name} must be finite and positive")
+        self.key_tensor_scale, self.value_tensor_scale = float(key_tensor_scale), float(value_tensor_scale)
+        if error_word is not None and (error_word.dtype is not torch.int32 or not error_word.is_cuda
+                                       or error_word.numel() < 1):
+            raise ValueError("error_word must be an INT32 CUDA tensor")
+        # optional INT32 [1]: a work item whose destination lies past the regions is skipped and
+        # BDFP4_DEV_BAD_PAGE is OR-ed in here (not in the reference's signature)
+        self._error_word = error_word
         if key_scale_geometry != "local":
             raise NotImplementedError("key_scale_geometry='gaussian_global' is not built")
         if key_packed is None and (key_shift is not None or rotate_key):
@@ -282,6 +295,10 @@ class KVCacheWriter:
         )
         a.layer = int(layer)
         a.page_tokens = self.page_size
+        # a destination at or past the regions' page count is skipped and reported, never written
+        a.pages = (key_packed if key_packed is not None else value_packed).shape[0]
+        a.key_tensor_scale, a.value_tensor_scale = self.key_tensor_scale, self.value_tensor_scale
+        a.error_word = bdfp4.ptr(self._error_word)
         if self.writes_tail:
             if any(t is None for t in (query_start_loc, seq_lens, seqused_fp4, row_to_slot)):
                 raise ValueError("a tail-writing call needs query_start_loc, seq_lens, seqused_fp4 and row_to_slot")

@@ -82,6 +82,7 @@ def quantize_decode_q_to_padded_fp4(
     scale_mode: str = DEFAULT_SCALE_MODE,
     rotation: str = "none",
     tail_write: Optional[DecodeTailWrite] = None,
+    tensor_scale: float = 1.0,
 ) -> None:
     """Quantize selected BF16 query rows into preallocated outputs.
 
@@ -90,8 +91,8 @@ def quantize_decode_q_to_padded_fp4(
     to BF16. ``tail_write`` also places each row's new K/V token in the BF16 tail from extra CTAs
     of the same launch.
     """
-    if sf_vec_size(scale_mode) != SF_VEC_SIZE:
-        raise NotImplementedError("MXFP4 query quantization is not built")
+    if not (tensor_scale > 0.0 and tensor_scale < float("inf")):
+        raise ValueError("tensor_scale must be finite and positive")
     if rotation not in QUERY_ROTATIONS:
         raise ValueError(f"rotation must be one of {QUERY_ROTATIONS}, got {rotation!r}")
     if query.dtype is not torch.bfloat16 or not query.is_cuda:
@@ -123,7 +124,7 @@ def quantize_decode_q_to_padded_fp4(
     ):
         raise ValueError("row_indices must be contiguous INT32 CUDA with shape [rows]")
 
-    rest_k = head_dim // (GROUPS_PER_ATOM * SF_VEC_SIZE)
+    rest_k = head_dim // (GROUPS_PER_ATOM * sf_vec_size(scale_mode))  # scale atoms per head: 2 (NVFP4) or 1 (MXFP4)
     expected_fp4_shape = (rows, 1, heads, head_dim // 2)
     expected_scales_shape = (32, 4, 1, 4, rest_k, heads_kv, rows)
     expected_scales_strides = (16, 4, heads * rest_k * 512, 1, 512, rest_k * 512, heads * rest_k * 512)
@@ -173,6 +174,7 @@ def quantize_decode_q_to_padded_fp4(
     a.row_indices = bdfp4.ptr(row_indices)
     a.rows, a.heads_q, a.heads_kv = rows, heads, heads_kv
     a.scale_mode = mode_id(scale_mode)
+    a.tensor_scale = float(tensor_scale)
     a.rotate = int(rotation == "hadamard")
     a.query_codes, a.query_scales = query_fp4_out.data_ptr(), query_scales_out.data_ptr()
     a.query_codes_second, a.query_scales_second = bdfp4.ptr(query_fp4_out_2), bdfp4.ptr(query_scales_out_2)

@@ -5,8 +5,7 @@ An NVFP4 mode is a tuple of divisors: a group of sixteen values stores
 earliest divisor winning ties, so ``amax6`` is the answer whenever nothing beats it and each
 longer tuple only ever improves on its prefix. Mirrors
 src/nvfp4_decode_kernel/scale_mode.py of OpenBitSys/BitDecoding-FP4 (same names and results).
-The MXFP4 modes (32 values per E8M0 scale) are recognised by name so that callers get a clear
-``NotImplementedError`` from the kernels rather than a ``ValueError`` here.
+The MXFP4 modes store one E8M0 power-of-two scale per 32 values, picked by an exponent rule.
 """
 
 from __future__ import annotations
@@ -67,7 +66,8 @@ def parse_scale_mode_spec(spec: str):
 
 
 def mode_id(scale_mode: str) -> int:
-    """Integer the C ABI uses for an NVFP4 mode; MXFP4 has no kernel in this build."""
+    """Integer the C ABI uses for a mode (``BDFP4_SCALE_*``): the NVFP4 candidate sets 0-2, then the
+    MXFP4 rules 3-5."""
     if scale_format(scale_mode) == "mxfp4":
-        raise NotImplementedError("MXFP4 scale modes are not built; use an NVFP4 mode")
+        return len(SCALE_MODES) + list(MX_SCALE_MODES).index(scale_mode)
     return list(SCALE_MODES).index(scale_mode)

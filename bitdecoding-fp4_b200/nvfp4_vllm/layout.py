@@ -4,6 +4,8 @@ OpenBitSys/BitDecoding-FP4).
 vLLM hands out one flat byte page per block. The four regions — K codes, K scales, V codes,
 V scales — sit one after another inside each block, so every region view has the block pitch as
 its page stride and a block stays the self-contained byte range the engine believes it is.
+An MXFP4 page has the same code regions and uses the first half of each scale region (one E8M0
+atom per head instead of two E4M3 atoms), so a block has the same size in either format.
 """
 
 from __future__ import annotations
@@ -25,15 +27,17 @@ def region_specs(num_kv_heads: int, head_dim: int, device: str = "cpu",
     (``include/bdfp4.h``)."""
     if head_dim != 128:
         raise ValueError(f"the NVFP4 page layout is defined for head_dim 128, got {head_dim}")
-    if scale_format(scale_mode) != "nvfp4":
-        raise NotImplementedError("MXFP4 pages are not built")
     h = num_kv_heads
-    scale_shape, scale_strides = (32, 4, 1, 4, 2, h), (16, 4, 1024, 1, 512, 1024)
+    if scale_format(scale_mode) == "mxfp4":
+        atoms, scale_type = 1, torch.float8_e8m0fnu
+    else:
+        atoms, scale_type = 2, torch.float8_e4m3fn
+    scale_shape, scale_strides = (32, 4, 1, 4, atoms, h), (16, 4, atoms * 512, 1, 512, atoms * 512)
     return (
         ((PAGE_SIZE, h, 64), (h * 64, 64, 1), torch.uint8, PAGE_SIZE * h * 64),
-        (scale_shape, scale_strides, torch.float8_e4m3fn, h * 1024),
+        (scale_shape, scale_strides, scale_type, h * 1024),
         ((h, head_dim, 64), (head_dim * 64, 64, 1), torch.uint8, h * head_dim * 64),
-        (scale_shape, scale_strides, torch.float8_e4m3fn, h * 1024),
+        (scale_shape, scale_strides, scale_type, h * 1024),
     )
 
 

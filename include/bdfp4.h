@@ -43,6 +43,15 @@ extern "C" {
 #define BDFP4_SCALE_AMAX6 0            /* (6) */
 #define BDFP4_SCALE_FOUR_SIX 1         /* (6, 4) */
 #define BDFP4_SCALE_FOUR_SIX_SIXHALF 2 /* (6, 4, 6.5) */
+/* MXFP4 exponent rules: one E8M0 power-of-two scale per 32 values
+ * (src/nvfp4_decode_kernel/scale_mode.py:40-49, src/nvfp4_decode_kernel/_block_scale.py:418-546) */
+#define BDFP4_SCALE_MXFP4_OCP 3      /* floor(log2(amax)) - 2 */
+#define BDFP4_SCALE_MXFP4_ROUND_UP 4 /* the smallest exponent that keeps amax at or below 6 */
+#define BDFP4_SCALE_MXFP4_SEARCH 5   /* ocp or ocp + 1, whichever has strictly less squared error */
+
+/* scale format of a cache / of the decode operands */
+#define BDFP4_FORMAT_NVFP4 0 /* E4M3 scale per 16 values */
+#define BDFP4_FORMAT_MXFP4 1 /* E8M0 scale per 32 values; 128-token pages only */
 
 /* softmax-probability scale rules (src/nvfp4_decode_kernel/p_scale.py:29-40) */
 #define BDFP4_P_AMAX6 0              /* amax/6 */
@@ -139,6 +148,19 @@ typedef struct bdfp4_kv_write_args {
   /* Tokens per cache page: 0 or 128 (the reference's only size), or 64 (see "64-token pages"):
    * a work item then reads 64 tokens. The BF16 tail keeps its 128 rolling rows either way. */
   int32_t page_tokens;
+  /* Pages in each destination region. A work item whose destination is at or past it is skipped
+   * and BDFP4_DEV_BAD_PAGE is OR-ed into *error_word, so a corrupt work table cannot write outside
+   * the cache. 0: unknown, only negative ids are skipped. */
+  int32_t pages;
+  /* FP32 per-tensor scales, no reference counterpart (the reference's scale is the E4M3 block
+   * scale alone, src/nvfp4_decode_kernel/_block_scale.py:272-289): the pages hold x / tensor_scale,
+   * i.e. x ~ code * block_scale * tensor_scale, which keeps block scales inside E4M3's range for
+   * tensors far from unit magnitude. The division is a multiplication by fl32(1 / tensor_scale)
+   * before the block-scale search (K: after the cache-basis transform and its BF16 rounding). The
+   * BF16 tail is not scaled. 0 or 1.0: none, and the bytes are those of the reference. The decode
+   * call must be given the same values. */
+  float key_tensor_scale;
+  float value_tensor_scale;
 } bdfp4_kv_write_args;
 
 int bdfp4_kv_write(const bdfp4_kv_write_args* args, void* stream);
@@ -185,6 +207,9 @@ typedef struct bdfp4_quantize_query_args {
   int32_t rotate_key;
   const float* key_shift; /* FP32 [H][128], already in the rotated basis; NULL: none */
   int32_t sink_tokens;
+  /* FP32 per-tensor scale of the query codes (see bdfp4_kv_write_args): the terms hold
+   * q / tensor_scale; the padded BF16 copy is not scaled. 0 or 1.0: none. */
+  float tensor_scale;
 } bdfp4_quantize_query_args;
 
 int bdfp4_quantize_query(const bdfp4_quantize_query_args* args, void* stream);
@@ -268,6 +293,19 @@ typedef struct bdfp4_decode_args {
    * first and the short ones fill in behind them. NULL: rows in index order. The result does not
    * depend on it. */
   const int32_t* row_order;
+  /* BDFP4_FORMAT_*: NVFP4 (0, default) or MXFP4. With MXFP4 the scale regions are E8M0 bytes, one
+   * 512-byte atom per (page, head) for K (128 tokens x 4 channel groups of 32) and for V (128
+   * channels x 4 token groups of 32), the query scales one atom per (row, KV head), the products
+   * are tcgen05.mma kind::mxf4 scale_vec::2X, and the probabilities are quantized per 32 tokens with
+   * the one MXFP4 rule (src/nvfp4_decode_kernel/reference.py:331-355); p_scale_mode is ignored.
+   * page_tokens must be 128. */
+  int32_t scale_format;
+  /* FP32 per-tensor scales the cache and the query were written with (0 or 1.0: none): FP4-page
+   * scores are multiplied by key_tensor_scale * query_tensor_scale, FP4-page outputs by
+   * value_tensor_scale; the BF16 tail and sink are not scaled. */
+  float key_tensor_scale;
+  float query_tensor_scale;
+  float value_tensor_scale;
 } bdfp4_decode_args;
 
 int bdfp4_decode(const bdfp4_decode_args* args, void* stream);
@@ -379,6 +417,9 @@ int bdfp4_tail_reset(void* tail_key, void* tail_value, int64_t layer_stride, int
  * start at zero: each part writes its log-sum-exp on every call (-inf when it had no work) and the
  * merge adds a partial only under a positive weight. Two calls that overlap on the GPU (different
  * streams, or different host threads) race on the array; serialise them on one stream.
+ * A fused merge is never used here: `merge_counters` of `args` is ignored. The array's address is
+ * remembered per device for the life of the process; after cudaDeviceReset it is stale, so a process
+ * that resets a device must not call this entry point on it again.
  */
 #define BDFP4_STATIC_SCRATCH_BYTES (8u << 20)
 int bdfp4_decode_split_static(const bdfp4_decode_args* args, void* stream);
@@ -474,12 +515,13 @@ int bdfp4_mla_write_rope(const void* rope, int64_t token_pitch, const int32_t* s
  * [rows][64][512], rope [rows][64][64]; a page that starts here has its other positions zeroed), and
  * the work table of the page writers is filled: source_tokens[r] = 64 r (a token index into the
  * staging buffers), destination_pages[r] = page_table[r][seq_lens[r] / 64] (-1 and BDFP4_DEV_BAD_PAGE
- * when that is not a page of the cache). bdfp4_kv_write and bdfp4_mla_write_rope over that table
+ * when that column is past page_table_columns, the row being full, or the entry is not a page of
+ * the cache; the token is then staged but written to no page). bdfp4_kv_write and bdfp4_mla_write_rope over that table
  * then re-quantize every row's open page, so the cache always holds all tokens in NVFP4. */
 int bdfp4_mla_append(const void* new_latent, const void* new_rope, void* staging_latent, void* staging_rope,
-                     const int32_t* seq_lens, const int32_t* page_table, int64_t page_table_stride, int32_t rows,
-                     int32_t pages, int32_t* source_tokens, int32_t* destination_pages, int32_t* error_word,
-                     void* stream);
+                     const int32_t* seq_lens, const int32_t* page_table, int64_t page_table_stride,
+                     int32_t page_table_columns, int32_t rows, int32_t pages, int32_t* source_tokens,
+                     int32_t* destination_pages, int32_t* error_word, void* stream);
 int bdfp4_mla_decode(const bdfp4_mla_decode_args* args, void* stream);
 int bdfp4_mla_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,
                       int32_t heads_q, void* out, void* stream);

@@ -239,13 +239,23 @@ def _value_chunk_key() -> torch.Tensor:
     return (torch.arange(128) >> 2) & 1  # [channels] against [pages, H, channels]
 
 
+def divide_by_tensor_scale(x: torch.Tensor, tensor_scale: float) -> torch.Tensor:
+    """``x / tensor_scale`` as the CUDA path forms it: FP32 values times fl32(1 / tensor_scale), one
+    rounding. The reference has no per-tensor scale (src/nvfp4_decode_kernel/_block_scale.py:272-289
+    stores the E4M3 block scale alone); 1.0 leaves ``x`` untouched, which is the pinned arithmetic."""
+    if tensor_scale == 1.0:
+        return x
+    inverse = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(tensor_scale, dtype=torch.float32)
+    return x.float() * inverse
+
+
 def quantize_key_pages(key_pages: torch.Tensor, scale_mode: str = "amax6", *, rotate: bool = False,
-                       shift: torch.Tensor | None = None):
+                       shift: torch.Tensor | None = None, tensor_scale: float = 1.0):
     """``[pages, 128, H, 128]`` BF16 -> (codes u8 ``[pages,128,H,64]``, scales u8 ``[pages,H,1024]``).
     Groups run along channels (src/nvfp4_decode_kernel/quantize_kv_kernel.py:165-221).
     A 64-token page ``[pages, 64, H, 128]`` gives codes ``[pages,64,H,64]`` (chunk j of token t at
     position ``j ^ ((t >> 1) & 3)``; in memory the page is head-major) and scales ``[pages,H,512]``."""
-    basis = key_cache_basis(key_pages, rotate=rotate, shift=shift)
+    basis = divide_by_tensor_scale(key_cache_basis(key_pages, rotate=rotate, shift=shift), tensor_scale)
     codes, scales = quantize_last_axis(basis, scale_mode)  # scales [pages,tok,H,8]
     if key_pages.shape[1] == 64:
         by_head = e4m3_bytes(scales).permute(0, 2, 1, 3)  # [pages,H,64,8]
@@ -255,13 +265,13 @@ def quantize_key_pages(key_pages: torch.Tensor, scale_mode: str = "amax6", *, ro
     return pack_nibbles(codes), pack_scale_tile(scales.permute(0, 2, 1, 3))
 
 
-def quantize_value_pages(value_pages: torch.Tensor, scale_mode: str = "amax6"):
+def quantize_value_pages(value_pages: torch.Tensor, scale_mode: str = "amax6", *, tensor_scale: float = 1.0):
     """``[pages, 128, H, 128]`` BF16 -> (codes u8 ``[pages,H,128,64]``, scales u8 ``[pages,H,1024]``).
     Groups run along the page's tokens (src/nvfp4_decode_kernel/quantize_kv_kernel.py:224-255,
     src/nvfp4_decode_kernel/reference.py:479-525). A 64-token page gives codes ``[pages,H,128,32]``
     (chunk j of channel c at position ``j ^ ((c >> 2) & 1)``) and scales ``[pages,H,512]``: the
     first atom of the 128-token tile (token groups 0-3)."""
-    by_channel = value_pages.permute(0, 2, 3, 1)  # [pages,H,ch,tok]
+    by_channel = divide_by_tensor_scale(value_pages.permute(0, 2, 3, 1), tensor_scale)  # [pages,H,ch,tok]
     codes, scales = quantize_last_axis(by_channel, scale_mode)  # scales [pages,H,ch,tok/16]
     if value_pages.shape[1] == 64:
         padded = torch.cat([scales, torch.zeros_like(scales)], dim=-1)
@@ -300,7 +310,7 @@ def dequantize_value_pages(codes: torch.Tensor, scale_tiles: torch.Tensor) -> to
 # --------------------------------------------------------------------------------------
 
 def quantize_query(query: torch.Tensor, heads_kv: int, *, scale_mode: str = "amax6", terms: int = 1,
-                   rotate: bool = False):
+                   rotate: bool = False, tensor_scale: float = 1.0):
     """``[rows, Hq, 128]`` BF16 -> dict with per-term codes ``[rows,1,Hq,64]`` u8, scale storage
     ``[rows,1,Hq,2,32,4,4]`` u8 (zero where nothing is written), the padded-copy values
     ``[rows,Hq,128]`` BF16, and per-term round-trip values FP32.
@@ -312,9 +322,9 @@ def quantize_query(query: torch.Tensor, heads_kv: int, *, scale_mode: str = "ama
     rows, heads_q, dim = query.shape
     ratio = heads_q // heads_kv
     values = hadamard_rotate(query) if rotate else query.float()
-    padded = values.to(torch.bfloat16)
+    padded = values.to(torch.bfloat16)  # the BF16 copy is never divided by the tensor scale
     out = {"padded": padded, "codes": [], "scales": [], "values": []}
-    current = values
+    current = divide_by_tensor_scale(values, tensor_scale)
     for _ in range(terms):
         codes, scales = quantize_last_axis(current, scale_mode)  # [rows,Hq,128], [rows,Hq,8]
         storage = torch.zeros(rows, heads_q, 1024, dtype=torch.uint8)
@@ -371,7 +381,8 @@ def probability_quantize(p: torch.Tensor, mode: str = "amax2_or_amax6_c8", tau: 
 # --------------------------------------------------------------------------------------
 
 def online_attention(blocks, *, softmax_scale: float, p_mode: str = "amax2_or_amax6_c8",
-                     tau: float = DEFAULT_P_TAU, rescale_threshold: float = RESCALE_THRESHOLD):
+                     tau: float = DEFAULT_P_TAU, rescale_threshold: float = RESCALE_THRESHOLD,
+                     p_quantizer=None):
     """Online softmax over ``blocks`` in the order given, for the query heads of one KV head.
 
     Each block is ``(scores [G, n], values [n, D], kind)``: raw (unscaled) QK products with masked
@@ -386,6 +397,10 @@ def online_attention(blocks, *, softmax_scale: float, p_mode: str = "amax2_or_am
     * the denominator sums the unquantised probabilities;
     * FP4 blocks quantise P per 16 positions (:func:`probability_quantize`), BF16 blocks round it
       to BF16.
+
+    ``p_quantizer`` replaces the NVFP4 rule for FP4 blocks (the MXFP4 operand: a callable from the
+    probabilities ``[G, n]`` to the values the PV product sees); ``p_mode`` then only decides the
+    ``_c8`` shift.
 
     Returns ``(out [G, D] FP32 normalised, lse [G] natural log)``; a row nothing contributed to
     has out 0 and lse -inf.
@@ -418,7 +433,12 @@ def online_attention(blocks, *, softmax_scale: float, p_mode: str = "amax2_or_am
         max_scaled = finite(new_max) * scale_log2 - shift
         p = torch.exp2(block_scores * scale_log2 - max_scaled[:, None])
         row_sum = row_sum * acc + p.sum(dim=-1)
-        used = probability_quantize(p, base_mode, tau) if kind == "fp4" else p.to(torch.bfloat16).float()
+        if kind != "fp4":
+            used = p.to(torch.bfloat16).float()
+        elif p_quantizer is not None:
+            used = p_quantizer(p)
+        else:
+            used = probability_quantize(p, base_mode, tau)
         out = out * acc[:, None] + used @ block_values.float()
         row_max = new_max
 
@@ -489,7 +509,8 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
                      tail_key=None, tail_value=None, tail_slot_ids=None, seqused_residual=None,
                      seqused_sink=None, p_mode: str = "amax2_or_amax6_c8", tau: float = DEFAULT_P_TAU,
                      num_splits: int = 1, bf16_split: bool = False, bf16_page_cost: int = 0,
-                     rescale_threshold: float = RESCALE_THRESHOLD):
+                     rescale_threshold: float = RESCALE_THRESHOLD, tensor_scales=(1.0, 1.0, 1.0),
+                     dequantize_pages=None, p_quantizer=None):
     """Whole-batch decode attention from the packed cache, as the CUDA path is asked to compute it.
 
     ``query_values`` is a list of one or two FP32 ``[rows, Hq, 128]`` reconstructions of the FP4
@@ -497,6 +518,11 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
     ``[rows, Hq, 128]`` BF16 scores the tail and the sink. Cache regions are the packed byte
     layouts of this module. Returns ``(out BF16 [rows,Hq,128], partial_out, partial_lse)`` where the
     partials are ``[parts, rows, Hq, 128]`` / ``[parts, rows, Hq]`` FP32 (parts = 1 when unsplit).
+
+    ``tensor_scales`` = (key, query, value) FP32 per-tensor scales (no reference counterpart; parity
+    unpinned away from 1.0): FP4-page scores are multiplied by fl32(key * query), FP4-page values by
+    the value scale. ``dequantize_pages`` = (key_fn, value_fn) and ``p_quantizer`` swap in another
+    scale format (MXFP4, ``oracle/mxfp4_oracle.py``) for the pages and the probability operand.
     """
     rows, heads_q, dim = query_values[0].shape
     ratio = heads_q // heads_kv
@@ -505,6 +531,9 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
     partial_lse = torch.full((parts, rows, heads_q), -torch.inf)
     has_tail = tail_key is not None
     has_sink = has_tail and seqused_sink is not None
+    key_fn, value_fn = dequantize_pages or (dequantize_key_pages, dequantize_value_pages)
+    score_scale = torch.tensor(tensor_scales[0], dtype=torch.float32) * torch.tensor(tensor_scales[1], dtype=torch.float32)
+    value_scale = torch.tensor(tensor_scales[2], dtype=torch.float32)
     for row in range(rows):
         fp4_tokens = int(seqused_fp4[row])
         pages = fp4_tokens // PAGE  # 128-token steps of the walk, whatever the cache page size
@@ -516,11 +545,11 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
         for kvh in range(heads_kv):
             heads = slice(kvh * ratio, (kvh + 1) * ratio)
             if pages:
-                k = dequantize_key_pages(key_codes[ids][:, :, kvh:kvh + 1], key_scales[ids][:, kvh:kvh + 1])
-                v = dequantize_value_pages(value_codes[ids][:, kvh:kvh + 1], value_scales[ids][:, kvh:kvh + 1])
+                k = key_fn(key_codes[ids][:, :, kvh:kvh + 1], key_scales[ids][:, kvh:kvh + 1])
+                v = value_fn(value_codes[ids][:, kvh:kvh + 1], value_scales[ids][:, kvh:kvh + 1])
                 k = k.reshape(fp4_tokens, dim)
-                v = v.reshape(fp4_tokens, dim)
-                scores_fp4 = sum(q[row, heads].float() @ k.T for q in query_values)
+                v = v.reshape(fp4_tokens, dim) * value_scale
+                scores_fp4 = sum(q[row, heads].float() @ k.T for q in query_values) * score_scale
             else:
                 scores_fp4, v = torch.zeros(ratio, 0), torch.zeros(0, dim)
             scores_tail = values_tail = scores_sink = values_sink = None
@@ -550,7 +579,7 @@ def decode_reference(*, query_values, query_padded, key_codes, key_scales, value
                 if bf16_split and num_splits > 1 and part == num_splits:
                     blocks = [b for b in blocks if b[2] == "bf16"]
                 o, lse = online_attention(blocks, softmax_scale=softmax_scale, p_mode=p_mode, tau=tau,
-                                          rescale_threshold=rescale_threshold)
+                                          rescale_threshold=rescale_threshold, p_quantizer=p_quantizer)
                 partial_out[part, row, heads] = o
                 partial_lse[part, row, heads] = lse
     if parts == 1:

@@ -1,9 +1,9 @@
 """Paged FP4 decode attention (through the package API and the C ABI) against the CPU oracle.
 
-Tolerance (BASELINE north_star): max |err| <= 1e-2 and mean relative error <= 1e-3, both in
-BF16, against the oracle that models the kernel's own operands (FP4 query terms, FP4
-probabilities, block order, stale-maximum rule). The kernel uses ex2.approx / rcp.approx, so
-agreement is statistical rather than bitwise.
+Tolerance: max |err| <= 1e-2 and mean relative error <= 1e-3, both in BF16, against the oracle
+that models the kernel's own operands (FP4 query terms, FP4 probabilities, block order,
+stale-maximum rule). The kernel uses ex2.approx / rcp.approx, so agreement is statistical rather
+than bitwise.
 """
 
 import math
@@ -34,9 +34,10 @@ def _cpu_cache(w):
 
 
 def _oracle_decode(w, *, terms, scale_mode, rotate, num_splits=1, bf16_split=False, with_tail=True,
-                   p_mode="amax2_or_amax6_c8", bf16_page_cost=0):
+                   p_mode="amax2_or_amax6_c8", bf16_page_cost=0, tau=oracle.DEFAULT_P_TAU, query_scale=1.0):
     kc, ks, vc, vs = _cpu_cache(w)
-    q = oracle.quantize_query(w.query.cpu(), w.heads_kv, scale_mode=scale_mode, terms=terms, rotate=rotate)
+    q = oracle.quantize_query(w.query.cpu(), w.heads_kv, scale_mode=scale_mode, terms=terms, rotate=rotate,
+                              tensor_scale=query_scale)
     kwargs = {}
     if with_tail:
         kwargs = dict(tail_key=w.tail_key[0].cpu(), tail_value=w.tail_value[0].cpu(),
@@ -45,8 +46,9 @@ def _oracle_decode(w, *, terms, scale_mode, rotate, num_splits=1, bf16_split=Fal
     return oracle.decode_reference(
         query_values=q["values"], query_padded=q["padded"], key_codes=kc, key_scales=ks, value_codes=vc,
         value_scales=vs, page_table=w.page_table.cpu(), seqused_fp4=w.seqused_fp4.cpu(), heads_kv=w.heads_kv,
-        softmax_scale=128 ** -0.5, p_mode=p_mode, num_splits=num_splits, bf16_split=bf16_split,
-        bf16_page_cost=bf16_page_cost, **kwargs)
+        softmax_scale=128 ** -0.5, p_mode=p_mode, tau=tau, num_splits=num_splits, bf16_split=bf16_split,
+        bf16_page_cost=bf16_page_cost, tensor_scales=(w.tensor_scales[0], query_scale, w.tensor_scales[2]),
+        **kwargs)
 
 
 def _check(got, want, label=""):
@@ -118,10 +120,9 @@ def test_decode_pages_only(heads_q, heads_kv, terms):
 
 
 @pytest.mark.parametrize("sink_tokens", [16, 4, 0])
-def test_decode_config1_shape(sink_tokens):
-    """BASELINE config 1: batch 4, 8 query / 2 KV heads, contexts uniform in [512, 2048], BF16 sink
-    and rolling tail, the recipe the reference serves with (two query terms, Hadamard, four_six K,
-    key shift)."""
+def test_decode_small_batch_with_the_serving_recipe(sink_tokens):
+    """Batch 4, 8 query / 2 KV heads, contexts uniform in [512, 2048], BF16 sink and rolling tail,
+    the recipe the reference serves with (two query terms, Hadamard, four_six K, key shift)."""
     from bdfp4.workload import build_workload
 
     gen = torch.Generator().manual_seed(0)
@@ -336,3 +337,92 @@ def test_decode_is_cuda_graph_capturable():
         eager = step().clone()
         assert torch.equal(replayed, eager)
     assert torch.cuda.memory_allocated() - before < (1 << 20)  # the capture held no sizeable allocation
+
+
+@pytest.mark.parametrize("p_mode,tau", [("amax6", None), ("amax2_or_amax6", None), ("amax2_or_amax6_c8", 0.25),
+                                        ("amax2_or_amax6", 0.004)])
+def test_decode_probability_scale_modes(p_mode, tau, monkeypatch):
+    """Every probability-scale rule the kernel has, and a threshold away from the default, on the
+    grouped-query kernel (the rule and tau are launch arguments read from the environment)."""
+    from bdfp4.workload import build_workload
+
+    monkeypatch.setenv("NVFP4_P_SCALE_MODE", p_mode)
+    if tau is not None:
+        monkeypatch.setenv("NVFP4_P_SCALE_TAU", str(tau))
+    w = build_workload(rows=3, heads_q=8, heads_kv=2, seq_lens=[900, 1700, 140], sink_tokens=16, seed=41)
+    out = _decode(w, terms=2)
+    want, _, _ = _oracle_decode(w, terms=2, scale_mode="amax6", rotate=False, p_mode=p_mode,
+                                tau=oracle.DEFAULT_P_TAU if tau is None else tau)
+    _check(out, want, f"{p_mode} tau={tau}")
+    if tau is not None:
+        # the threshold is live: the default one gives a different answer on the same inputs
+        monkeypatch.delenv("NVFP4_P_SCALE_TAU")
+        assert not torch.equal(_decode(w, terms=2), out)
+
+
+@pytest.mark.parametrize("heads_q,heads_kv", [(16, 2), (32, 2)])
+@pytest.mark.parametrize("num_splits,fused", [(1, False), (2, False), (5, True)])
+def test_decode_wide_groups_with_tail_sink_and_splits(heads_q, heads_kv, num_splits, fused):
+    """Eight and sixteen query heads per KV head over the BF16 tail, the sink, split-KV and the
+    fused merge (the paths the four-head cases above cover for G = 4)."""
+    from bdfp4.workload import build_workload
+
+    lengths = [1300, 129, 700, 2048, 90]
+    w = build_workload(rows=len(lengths), heads_q=heads_q, heads_kv=heads_kv, seq_lens=lengths, sink_tokens=16,
+                       seed=heads_q + num_splits, key_scale_mode="four_six", rotate=True)
+    extra = {}
+    if fused:
+        extra = dict(split_merge_counters=torch.zeros(len(lengths) * heads_kv, dtype=torch.int32, device="cuda"))
+    out = _decode(w, terms=2, scale_mode="four_six", rotate=True, num_splits=num_splits, **extra)
+    want, _, _ = _oracle_decode(w, terms=2, scale_mode="four_six", rotate=True, num_splits=num_splits,
+                                bf16_split=num_splits > 1)
+    _check(out, want, f"G={heads_q // heads_kv} splits={num_splits}")
+
+
+@pytest.mark.parametrize("heads_q,heads_kv,page_tokens", [(8, 2, 128), (16, 2, 128), (16, 2, 64), (32, 2, 128)])
+def test_decode_rescales_when_the_maximum_moves_late(heads_q, heads_kv, page_tokens):
+    """The oldest tokens (reached last) score far above everything before them, so the running
+    maximum moves by more than the stale-maximum rule tolerates near the end of the walk and the
+    sums accumulated so far are rescaled; with eight or more rows per thread the per-row statistics
+    involved live in shared memory."""
+    from bdfp4.workload import build_workload
+
+    w = build_workload(rows=3, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[1500, 700, 2300], sink_tokens=16,
+                       seed=53, loud_prefix=200, page_tokens=page_tokens)
+    out = _decode(w, terms=2)
+    kwargs = dict(terms=2, scale_mode="amax6", rotate=False)
+    if page_tokens == 64:
+        from tests.test_gpu_page64 import _oracle_decode as oracle64
+
+        want = oracle64(w, terms=2, rotate=False)
+    else:
+        want, _, _ = _oracle_decode(w, **kwargs)
+    _check(out, want, f"late maximum, G={heads_q // heads_kv}, {page_tokens}-token pages")
+    # the scenario is the intended one: without the loud prefix the same rows give another answer,
+    # and the oracle with the stale-maximum rule switched off (always move) differs from the gate's
+    quiet = build_workload(rows=3, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[1500, 700, 2300], sink_tokens=16,
+                           seed=53, page_tokens=page_tokens)
+    assert not torch.equal(_decode(quiet, terms=2), out)
+
+
+def test_decode_with_tensor_scales():
+    """FP32 per-tensor scales on K, V and Q (no reference counterpart, so this parity is unpinned:
+    the oracle restates the CUDA path's own definition). 1.0 must leave every byte as it was."""
+    from bdfp4.workload import build_workload
+
+    common = dict(rows=2, heads_q=8, heads_kv=2, seq_lens=[1100, 400], sink_tokens=16, seed=61,
+                  key_scale_mode="four_six", rotate=True)
+    plain = build_workload(**common)
+    ones = build_workload(key_tensor_scale=1.0, value_tensor_scale=1.0, **common)
+    assert torch.equal(plain.blocks, ones.blocks)
+    w = build_workload(key_tensor_scale=3.0, value_tensor_scale=0.37, **common)
+    assert not torch.equal(plain.blocks, w.blocks)
+    kc, ks, vc, vs = _cpu_cache(w)
+    want_plain = _cpu_cache(plain)
+    assert not torch.equal(ks, want_plain[1]) and not torch.equal(vs, want_plain[3])
+    out = _decode(w, terms=2, scale_mode="four_six", rotate=True, tensor_scales=(3.0, 1.7, 0.37))
+    want, _, _ = _oracle_decode(w, terms=2, scale_mode="four_six", rotate=True, query_scale=1.7)
+    _check(out, want, "tensor scales")
+    # the scales cancel: the result is close to the unscaled cache's (not equal: other block scales)
+    base = _decode(plain, terms=2, scale_mode="four_six", rotate=True).float()
+    assert float((out.float() - base).abs().mean() / base.abs().mean()) < 0.1
