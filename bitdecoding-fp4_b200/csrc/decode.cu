@@ -3,6 +3,7 @@
 // itself is decode_kernel.cuh.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"

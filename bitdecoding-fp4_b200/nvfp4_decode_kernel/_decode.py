@@ -28,10 +28,11 @@ CACHE_PAGE_SIZES = (128, 64)
 HEAD_DIM = 128
 SM100_MAJOR = 10
 MAX_QUERY_HEADS_PER_KV_HEAD = 16
-# Pages the split that also merges the BF16 tail and sink is charged for them. The kernel launches
-# that split's CTAs first, and on B200 their head start already covers the two blocks (about 13 us):
-# charges of 8 to 16 pages measured no faster than 0, so the reference's even partition stays.
-BF16_BLOCK_PAGE_COST = 0
+# Pages the split that also merges the BF16 tail and sink is charged for them (the reference's even
+# partition is 0). Measured on B200 with one KV head per GPU (64 rows x 9 splits, every CTA resident at
+# once, so the split that carries the two blocks ends last): 0 -> 131.5-133.1 us per step, 5 -> 129.9,
+# 9 -> 128.0-128.6, 14 -> 131.2. With few long splits per row the charge is lost in the noise.
+BF16_BLOCK_PAGE_COST = 8
 
 
 def split_k_heuristic(rows: int, heads_kv: int, max_pages_per_row: int, *, sms: int) -> int:

@@ -79,7 +79,7 @@ def check_tiles(w, out: torch.Tensor, tiles, **decode_options) -> dict:
     """Compare ``out`` ``[rows, Hq, 128]`` (device) with the oracle on ``tiles`` = [(row, kv_head), ...].
     Returns the worst absolute error and the mean relative error over the sampled tiles, in BF16."""
     ratio = w.heads_q // w.heads_kv
-    errors, magnitudes, worst = [], [], 0.0
+    errors, magnitudes, worst, identical, total = [], [], 0.0, 0, 0
     for row, kv_head in tiles:
         want = oracle_tile(w, row, kv_head, **decode_options).float()
         got = out[row, kv_head * ratio:(kv_head + 1) * ratio].float().cpu()
@@ -89,5 +89,11 @@ def check_tiles(w, out: torch.Tensor, tiles, **decode_options) -> dict:
         worst = max(worst, float(err.max()))
         errors.append(err.mean())
         magnitudes.append(want.abs().mean())
-    mean_rel = float(torch.stack(errors).mean() / torch.stack(magnitudes).mean().clamp_min(1e-12))
-    return {"tiles": len(tiles), "max_abs": worst, "mean_rel": mean_rel}
+        identical += int((err == 0).sum())
+        total += err.numel()
+    mean_abs = float(torch.stack(magnitudes).mean())
+    mean_rel = float(torch.stack(errors).mean() / max(mean_abs, 1e-12))
+    # mean_abs_output and identical say what kind of agreement it was: where one token takes nearly all
+    # of a row's probability the output is that token's dequantized V and agreement is exact
+    return {"tiles": len(tiles), "max_abs": worst, "mean_rel": mean_rel, "mean_abs_output": mean_abs,
+            "identical": f"{identical}/{total}"}

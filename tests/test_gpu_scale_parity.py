@@ -41,12 +41,14 @@ def _build(rows, heads_q, heads_kv, context, page_tokens):
 
 
 def _gate(w, out, tiles, splits, label):
+    from nvfp4_decode_kernel import _decode as decode_module
     from nvfp4_decode_kernel import split_partial_count
 
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     parts = split_partial_count(w.rows, w.heads_kv, splits, residual=True, sms=sms)
     result = tile_check.check_tiles(w, out, tiles, terms=2, scale_mode="amax6", rotate=True, num_splits=splits,
-                                    bf16_split=parts > splits)
+                                    bf16_split=parts > splits,
+                                    bf16_page_cost=decode_module.BF16_BLOCK_PAGE_COST if parts == splits else 0)
     print(f"{label}: {result}")
     assert result["max_abs"] <= MAX_ABS, (label, result)
     assert result["mean_rel"] <= MEAN_REL, (label, result)
