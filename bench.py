@@ -1,22 +1,26 @@
 """Benchmark of the NVFP4 decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 One step = one decode step of one attention layer over the whole batch: the step's query is
 quantized to NVFP4 (two terms), each sequence's new K/V token is written into its BF16 tail
 (fused into the same launch), then paged FP4 decode attention runs over the FP4 pages, the
-BF16 tail and the BF16 sink. The N=1 workload is the Qwen3-4B-shaped configuration: 32 query /
-8 KV heads, head_dim 128, batch 64, 65,536 tokens per sequence, randomly shuffled block table,
-4 sink + 128 recent BF16 tokens, K/V/Q BF16 from N(0,1) with four lognormal(0,1.5) outlier
+BF16 tail and the BF16 sink. The default workload (`gqa`) is the Qwen3-4B-shaped configuration:
+32 query / 8 KV heads, head_dim 128, batch 64, 65,536 tokens per sequence, randomly shuffled block
+table, 4 sink + 128 recent BF16 tokens, K/V/Q BF16 from N(0,1) with four lognormal(0,1.5) outlier
 channels per KV head of K. With N GPUs the KV heads are partitioned over the ranks (as tensor
-parallelism does) with no collective: every rank runs the same batch on its head group, and
-the step time is the maximum over ranks.
+parallelism does), then the rows when ranks remain, with no collective: the step time is the
+maximum over ranks. Other workloads: `cfg1` (batch 4, contexts in [512, 2048]: small enough for the
+CPU arm to run whole), `cfg3` (32 query / 4 KV heads, batch 32, 131,072 tokens), `mixed` (256
+Zipf-length sequences plus one 1M-token sequence split along the KV axis over the ranks, the one
+step with a collective), `mla` (latent-cache decode), `longseq` (the 1M-token sequence alone).
 
-Prints one JSON line (rank 0). `value` is microseconds per step with inputs resident in HBM;
-`e2e` is the same step driven from pinned host buffers, with the host->device copy of the
-step's query and new K/V token and the device->host copy of its output inside the timed region.
-`--impl reference` times the CPU restatement of the reference's algorithm (oracle/) on a bounded
-sample of the same workload, on all host threads.
+Prints one JSON line (rank 0). `value` is microseconds per step with inputs resident in HBM: the
+median over rounds of K steps, rounds repeated until `--min-seconds` of device time are measured;
+`e2e` is the same step driven from pinned host buffers, with the host->device copy of the step's
+query and new K/V token and the device->host copy of its output inside the timed region.
+`--impl reference` times the reference's own CPU model of the step (oracle/_ref, made from the
+reference tree by oracle/make_ref.py; the oracle port when that is absent) on all host threads.
 """
 
 from __future__ import annotations
@@ -27,7 +31,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -40,6 +43,7 @@ import torch  # noqa: E402
 HEADS_Q, HEADS_KV, BATCH, CONTEXT = 32, 8, 64, 65536
 SINK_USED, SINK_ROWS = 4, 16
 WORKLOAD_NAME = "qwen3-4b-shape decode layer: 32q/8kv heads, d128, batch 64, ctx 65536, page {page}"
+LONG_TOKENS = 1 << 20
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -109,6 +113,18 @@ class ClockSampler:
             except Exception:
                 self.process.kill()
 
+    def samples(self) -> list[tuple[float, int]]:
+        """(host time, SM MHz) of every reading; complete once the sampler has been left."""
+        out = []
+        for line in self.lines:
+            fields = line.split()
+            if len(fields) == 3:
+                try:
+                    out.append((float(fields[0]), int(fields[1])))
+                except ValueError:
+                    pass
+        return out
+
     def summary(self) -> dict:
         clocks, reasons, max_mhz = [], set(), None
         for line in self.lines:
@@ -127,157 +143,265 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU arm: the oracle port of the reference's algorithm on a bounded sample
+# Workloads of the grouped-query path
 # ---------------------------------------------------------------------------------------------
 
-def cpu_sample_step(context: int, threads: int, repeats: int = 1, seed: int = 0, page_tokens: int = 64):
-    """One decode step of a (1 row, 1 KV head = 4 query heads, `context` tokens) slice on the CPU.
-
-    The cache is quantized once up front (not timed); the timed step quantizes the query, puts
-    the new K token into the cache basis, and runs kernel-order attention over the FP4 pages, the
-    BF16 tail and the sink, which includes dequantizing every page as the reference's CPU path does.
-    Returns seconds per step.
-    """
-    from oracle import nvfp4_oracle as oracle
-
-    torch.set_num_threads(threads)
+def zipf_lengths(count: int, low: int, high: int, alpha: float, seed: int) -> list[int]:
+    """`count` context lengths on [low, high] with density proportional to length^-alpha (the
+    continuous Zipf / power law, by inverse transform), seeded."""
     gen = torch.Generator().manual_seed(seed)
-    sink, fp4, tail = min(context, SINK_USED), ((context - 1) // 128) * 128, context - ((context - 1) // 128) * 128
-    pages = fp4 // page_tokens
-    k = torch.randn(context, 1, 128, generator=gen)
-    k[:, 0, torch.randperm(128, generator=gen)[:4]] *= torch.exp(1.5 * torch.randn(4, generator=gen))
-    k = k.to(torch.bfloat16)
-    v = torch.randn(context, 1, 128, generator=gen).to(torch.bfloat16)
-    kc, ks = oracle.quantize_key_pages(k[:fp4].reshape(pages, page_tokens, 1, 128), "four_six", rotate=True)
-    vc, vs = oracle.quantize_value_pages(v[:fp4].reshape(pages, page_tokens, 1, 128), "amax6")
-    tail_k = torch.zeros(1, 144, 1, 128, dtype=torch.bfloat16)
-    tail_v = torch.zeros_like(tail_k)
-    basis = oracle.key_cache_basis(k, rotate=True, shift=None)
-    tail_k[0, :tail], tail_v[0, :tail] = basis[fp4:], v[fp4:]
-    tail_k[0, 128:128 + sink], tail_v[0, 128:128 + sink] = basis[:sink], v[:sink]
-    q = torch.randn(1, 4, 128, generator=gen).to(torch.bfloat16)
-    table = torch.arange(pages, dtype=torch.int32)[None]
-    meta = dict(
-        page_table=table, seqused_fp4=torch.tensor([fp4], dtype=torch.int32), tail_key=tail_k, tail_value=tail_v,
-        tail_slot_ids=torch.zeros(1, dtype=torch.int32), seqused_residual=torch.tensor([tail], dtype=torch.int32),
-        seqused_sink=torch.tensor([sink], dtype=torch.int32),
-    )
-    start = time.perf_counter()
-    for _ in range(repeats):
-        qq = oracle.quantize_query(q, 1, scale_mode="amax6", terms=2, rotate=True)
-        tail_k[0, tail - 1] = oracle.key_cache_basis(k[-1:], rotate=True, shift=None)[0]
-        tail_v[0, tail - 1] = v[-1]
-        oracle.decode_reference(query_values=qq["values"], query_padded=qq["padded"], key_codes=kc, key_scales=ks,
-                                value_codes=vc, value_scales=vs, heads_kv=1, softmax_scale=128 ** -0.5, **meta)
-    return (time.perf_counter() - start) / repeats
+    u = torch.rand(count, generator=gen, dtype=torch.float64)
+    a = 1.0 - alpha
+    lengths = (low ** a + u * (high ** a - low ** a)) ** (1.0 / a)
+    return [int(x) for x in lengths.round().clamp(low, high).tolist()]
 
 
-def cpu_baseline(heads_kv_local: int, sample_context: int = 16384, budget_s: float = 12.0,
-                 page_tokens: int = 64) -> dict:
-    """The oracle port timed for about `budget_s` seconds of CPU work on all host threads."""
-    threads = os.cpu_count() or 1
-    cpu_sample_step(2048, threads, page_tokens=page_tokens)  # warm the allocator and thread pool
-    repeats, spent = 0, 0.0
-    while spent < budget_s:
-        spent += cpu_sample_step(sample_context, threads, seed=repeats, page_tokens=page_tokens)
-        repeats += 1
-    seconds = spent / repeats
-    units = BATCH * heads_kv_local * (CONTEXT / sample_context)
+def workload_spec(args) -> dict:
+    """Shape of the named workload: total heads, the rows' context lengths, and its description."""
+    name = args.workload
+    if name == "gqa":
+        heads_q, heads_kv = args.heads_q or HEADS_Q, args.heads_kv or HEADS_KV
+        rows, context = args.batch or BATCH, args.context
+        label = WORKLOAD_NAME.format(page=args.page_tokens)
+        if (context, rows, heads_kv, heads_q) != (CONTEXT, BATCH, HEADS_KV, HEADS_Q):
+            label += f" [shape overridden: batch {rows}, {heads_q}q/{heads_kv}kv heads, context {context}]"
+        return dict(name=name, heads_q=heads_q, heads_kv=heads_kv, lengths=[context] * rows, label=label)
+    if name == "cfg1":
+        gen = torch.Generator().manual_seed(0)
+        lengths = torch.randint(512, 2049, (4,), generator=gen).tolist()
+        return dict(name=name, heads_q=8, heads_kv=2, lengths=lengths,
+                    label=f"small-batch decode layer: 8q/2kv heads, d128, batch 4, contexts uniform in [512, 2048] "
+                          f"(seeded: {lengths}), page {args.page_tokens}")
+    if name == "cfg3":
+        rows, context = args.batch or 32, args.context if args.context != CONTEXT else 131072
+        return dict(name=name, heads_q=32, heads_kv=4, lengths=[context] * rows,
+                    label=f"qwen3-30b-a3b-shape decode layer: 32q/4kv heads (8 query heads per KV head), d128, "
+                          f"batch {rows}, ctx {context}, page {args.page_tokens}")
+    if name == "mixed":
+        rows = args.batch or 256
+        lengths = zipf_lengths(rows, 1024, 131072, 1.2, seed=5)
+        return dict(name=name, heads_q=32, heads_kv=8, lengths=lengths,
+                    label=f"mixed serving step: {rows} sequences of 32q/8kv heads, d128, contexts Zipf(1.2) on "
+                          f"[1K, 128K] ({sum(lengths):,} tokens), page {args.page_tokens}, plus one "
+                          f"{LONG_TOKENS:,}-token sequence split along the KV axis over the ranks")
+    raise SystemExit(f"unknown workload {name!r}")
+
+
+def partition(spec: dict, world: int, rank: int, kv_groups: int = 0) -> dict:
+    """This rank's share: KV heads are dealt out first (contiguous groups, as tensor parallelism does),
+    then, when there are more ranks than KV-head groups, the rows are sharded over the remaining factor.
+    Ragged batches are dealt longest-first in a snake, so that the shards' token counts stay close.
+    No rank needs anything from another."""
+    total_kv = spec["heads_kv"]
+    groups = kv_groups or min(world, total_kv)
+    if world % groups or total_kv % groups:
+        raise SystemExit(f"{total_kv} KV heads / {world} ranks do not partition into {groups} head groups")
+    shards = world // groups
+    rows = len(spec["lengths"])
+    if rows < shards:
+        raise SystemExit(f"{rows} rows cannot be sharded {shards} ways")
+    order = sorted(range(rows), key=lambda r: -spec["lengths"][r])
+    shard_of = {}
+    for position, row in enumerate(order):
+        lap, slot = divmod(position, shards)
+        shard_of[row] = slot if lap % 2 == 0 else shards - 1 - slot
+    mine = [r for r in range(rows) if shard_of[r] == rank // groups]
+    ratio = spec["heads_q"] // total_kv
+    heads_kv = total_kv // groups
+    return dict(heads_kv=heads_kv, heads_q=heads_kv * ratio, lengths=[spec["lengths"][r] for r in mine],
+                text=f"{heads_kv} of {total_kv} KV heads x {len(mine)} of {rows} rows per rank, no collective")
+
+
+def common_config(spec: dict, part_text: str, page_tokens: int) -> dict:
+    """The `config` object both arms print, key for key."""
     return {
-        "value": seconds * units * 1e6,
-        "unit": "us/step",
-        "cores": threads,
-        "kind": "port",
-        "sample": (f"oracle port (PyTorch CPU), {repeats} steps of 1 row x 1 KV head (4 query heads) x "
-                   f"{sample_context} tokens, {seconds:.3f} s each on {threads} threads ({spent:.1f} s in all); "
-                   f"scaled by {units:.0f} (batch x KV heads x context ratio) to the full step"),
+        "workload": spec["label"],
+        "partition": part_text,
+        "sink_tokens": SINK_USED, "recent_tokens": 128,
+        "query": "two NVFP4 terms, Hadamard", "key_scale_mode": "four_six", "value_scale_mode": "amax6",
+        "p_scale_mode": "amax2_or_amax6_c8", "page_tokens": page_tokens,
+        "l2": "the cache walked per step exceeds the 126 MB L2 (or, for the small workloads, is re-read from "
+              "HBM-resident pages after an L2-sized flush write between rounds)",
     }
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's own CPU model (oracle/_ref) or, without it, the oracle port
+# ---------------------------------------------------------------------------------------------
+
+def cpu_step(spec: dict, lengths: list[int], heads_kv: int, budget_s: float, page_tokens: int) -> dict:
+    """Seconds of CPU time for one step of this rank's share. Rows no longer than 4,096 tokens are run
+    whole, every one of them; longer rows are sampled: a slice of one KV head and at most 16,384 tokens is
+    timed for about `budget_s` seconds and scaled by (heads x context ratio), which the result says."""
+    from oracle import cpu_arm
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    ratio = spec["heads_q"] // spec["heads_kv"]
+    cpu_arm.step_seconds(1024, ratio=ratio, page_tokens=page_tokens)  # warm the thread pool and allocator
+    whole = max(lengths) <= 4096
+    if whole:
+        seconds, kind = 0.0, "port"
+        for i, n in enumerate(lengths):
+            s, kind = cpu_arm.step_seconds(n, heads_kv=heads_kv, ratio=ratio, seed=i, page_tokens=page_tokens)
+            seconds += s
+        return dict(seconds=seconds, kind=kind, cores=threads, extrapolated_x=1.0,
+                    sample=f"every row whole: {len(lengths)} rows x {heads_kv} KV heads x {ratio} query heads each, "
+                           f"{seconds:.3f} s on {threads} threads")
+    sample_context = min(16384, max(lengths))
+    spent, repeats, kind = 0.0, 0, "port"
+    while spent < budget_s:
+        s, kind = cpu_arm.step_seconds(sample_context, heads_kv=1, ratio=ratio, seed=repeats, page_tokens=page_tokens)
+        spent += s
+        repeats += 1
+    per_token_head = spent / repeats / sample_context
+    units = sum(lengths) * heads_kv
+    factor = units / sample_context
+    return dict(seconds=per_token_head * units, kind=kind, cores=threads, extrapolated_x=factor,
+                sample=f"{repeats} steps of 1 row x 1 KV head ({ratio} query heads) x {sample_context} tokens, "
+                       f"{spent / repeats:.3f} s each on {threads} threads ({spent:.1f} s in all); scaled by "
+                       f"{factor:.0f} (tokens x KV heads of the rank's step over the sample's): an extrapolation, "
+                       "not a run of the full step")
+
+
+def cpu_baseline_entry(measured: dict) -> dict:
+    return {"value": measured["seconds"] * 1e6, "unit": "us/step", "cores": measured["cores"],
+            "kind": "reference" if measured["kind"] == "reference" else "port",
+            "sample": measured["sample"], "extrapolated_x": measured["extrapolated_x"]}
 
 
 def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """`--impl reference`: the reference's CPU implementation of the step on the host cores (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    heads_local = HEADS_KV // args.gpus
-    threads = os.cpu_count() or 1
-    sample_context = 16384
-    for _ in range(args.warmup):
-        cpu_sample_step(2048, threads, page_tokens=args.page_tokens)
-    # each timed step: the bounded sample repeated for about three seconds of CPU work
-    times = []
-    for i in range(args.steps):
-        spent, repeats = 0.0, 0
-        while spent < 3.0:
-            spent += cpu_sample_step(sample_context, threads, seed=i * 100 + repeats, page_tokens=args.page_tokens)
-            repeats += 1
-        times.append(spent / repeats)
-    seconds = sum(times) / len(times)
-    units = BATCH * heads_local * (CONTEXT / sample_context)
-    value = seconds * units * 1e6
-    line = {
+    spec = workload_spec(args)
+    part = partition(spec, args.gpus, 0, args.kv_groups)
+    for _ in range(min(args.warmup, 2)):
+        cpu_step(spec, part["lengths"][:1], 1, 0.5, args.page_tokens)
+    runs = [cpu_step(spec, part["lengths"], part["heads_kv"], 3.0, args.page_tokens) for _ in range(args.steps)]
+    seconds = statistics.mean(r["seconds"] for r in runs)
+    last = dict(runs[-1], seconds=seconds)
+    value = seconds * 1e6
+    print(json.dumps({
         "impl": "reference", "metric": "decode_attn_us_per_step", "value": value, "unit": "us/step",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": value / 1e3,
-        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAME.format(page=args.page_tokens), "kv_heads_per_rank": heads_local, "sink_tokens": SINK_USED},
-        "cpu_baseline": {
-            "value": value, "unit": "us/step", "cores": threads, "kind": "port",
-            "sample": (f"each step: 1 row x 1 KV head x {sample_context} tokens ({seconds:.3f} s on {threads} threads), "
-                       f"scaled by {units:.0f} to the rank's full step"),
-        },
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate", "data": "synthetic",
+        "config": common_config(spec, part["text"], args.page_tokens),
+        "cpu_baseline": cpu_baseline_entry(last),
+        "reference_gpu_kernel": REFERENCE_GPU_NOTE,
         "e2e": {"value": value, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }
-    print(json.dumps(line))
+    }))
+
+
+REFERENCE_GPU_NOTE = ("unavailable on this box: the reference's CuTeDSL kernels pin nvidia-cutlass-dsl 4.6.0 and the "
+                      "image has 4.5.0; the arm timed here is the reference's CPU model")
 
 
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 
-def run_ours(args) -> None:
+class TimedRounds:
+    """Rounds of K steps, each bracketed by CUDA events on the launching stream and a synchronise, until
+    at least `min_seconds` of device time have been measured; the clock sampler's readings are binned
+    per round, so a burst-clock round and a power-capped one can be told apart."""
+
+    def __init__(self, steps: int, min_seconds: float, sampler: ClockSampler, barrier):
+        self.steps, self.min_seconds, self.sampler, self.barrier = steps, min_seconds, sampler, barrier
+        self.rounds: list[dict] = []
+
+    def run(self, one_step, kernel_events_of=None) -> None:
+        total = 0.0
+        self.barrier()
+        while True:
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            pairs = [] if kernel_events_of is None else [kernel_events_of() for _ in range(self.steps)]
+            self.sampler.open_window()
+            begin.record()
+            for k in range(self.steps):
+                one_step(pairs[k] if pairs else None)
+            end.record()
+            torch.cuda.synchronize()
+            self.sampler.close_window()
+            ms = begin.elapsed_time(end)
+            kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs) if pairs else None
+            self.rounds.append({"ms_per_step": ms / self.steps, "kernel_ms": kernel_ms,
+                                "window": tuple(self.sampler.windows[-1])})
+            total += ms * 1e-3
+            if total >= self.min_seconds or len(self.rounds) >= 2000:
+                break
+        self.barrier()
+
+    def median_ms(self) -> float:
+        return statistics.median(r["ms_per_step"] for r in self.rounds)
+
+    def median_kernel_ms(self) -> float:
+        return statistics.median(r["kernel_ms"] for r in self.rounds)
+
+    def clock_bins(self) -> list[dict]:
+        """Rounds grouped by the median SM clock sampled while they ran (50 MHz bins)."""
+        samples = self.sampler.samples()
+        bins: dict[int, list[float]] = {}
+        for r in self.rounds:
+            lo, hi = r["window"]
+            clocks = [c for t, c in samples if lo <= t <= hi]
+            if clocks:
+                bins.setdefault(int(statistics.median(clocks)) // 50 * 50, []).append(r["ms_per_step"])
+        return [{"sm_mhz_from": mhz, "rounds": len(v), "us_per_step": statistics.median(v) * 1e3,
+                 "us_x_mhz": statistics.median(v) * 1e3 * (mhz + 25)} for mhz, v in sorted(bins.items())]
+
+
+def flush_l2(scratch: torch.Tensor) -> None:
+    scratch.add_(1)
+
+
+def run_gqa(args) -> None:
     import torch.distributed as dist
 
+    import bdfp4
     from bdfp4.workload import build_workload
     from nvfp4_decode_kernel import DecodeTailWrite, fp4_decode, split_partial_count
-    from nvfp4_decode_kernel._decode import _multiprocessor_count
+    from nvfp4_decode_kernel import _decode as decode_module
+    from nvfp4_decode_kernel._quantize import quantize_query
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run, one rank per GPU")
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run, one rank per GPU")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    total_heads_kv, total_heads_q = args.heads_kv or HEADS_KV, args.heads_q or HEADS_Q
-    if total_heads_kv % world or total_heads_q % total_heads_kv:
-        raise SystemExit(f"{total_heads_kv} KV heads do not partition over {world} ranks / {total_heads_q} query heads")
-    heads_kv = total_heads_kv // world
-    heads_q = total_heads_q // world
-    rows, context = args.batch or BATCH, args.context
+    mixed = args.workload == "mixed"
+    if world > 1 or mixed:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    spec = workload_spec(args)
+    kv_groups = args.kv_groups or (min(world, 4) if mixed and world >= 8 else 0)
+    part = partition(spec, world, rank, kv_groups)
+    heads_kv, heads_q, lengths = part["heads_kv"], part["heads_q"], part["lengths"]
+    rows = len(lengths)
+    page_tokens = args.page_tokens
 
-    w = build_workload(rows=rows, heads_q=heads_q, heads_kv=heads_kv, seq_lens=[context] * rows,
-                       sink_tokens=SINK_ROWS, seed=1000 + rank, device=device, key_scale_mode="four_six",
-                       value_scale_mode="amax6", rotate=True, page_tokens=args.page_tokens)
+    w = build_workload(rows=rows, heads_q=heads_q, heads_kv=heads_kv, seq_lens=lengths, sink_tokens=SINK_ROWS,
+                       seed=1000 + rank, device=device, key_scale_mode="four_six", value_scale_mode="amax6",
+                       rotate=True, page_tokens=page_tokens)
     w.seqused_sink.clamp_(max=SINK_USED)
     w.sink_tokens = SINK_USED
     algorithmic_bytes = w.algorithmic_bytes()
-    sms = _multiprocessor_count(local_rank)
-    # split count from the batch width only (never from device lengths): enough partitions to keep
-    # the whole launch resident at four CTAs per SM
-    from nvfp4_decode_kernel._decode import resident_num_splits
-
-    splits = resident_num_splits(rows, heads_kv, sms=sms)
-    if args.splits:
-        splits = args.splits
+    sms = decode_module._multiprocessor_count(local_rank)
+    # split count from the batch width only (never from device lengths): enough partitions to keep the
+    # whole launch resident at four CTAs per SM
+    splits = args.splits or decode_module.resident_num_splits(rows, heads_kv, sms=sms)
     parts = split_partial_count(rows, heads_kv, splits, residual=True, sms=sms)
+    ragged = len(set(lengths)) > 1
+    row_order = torch.argsort(w.seqused_fp4, descending=True).to(torch.int32) if ragged else None
 
     gen = torch.Generator(device=device).manual_seed(77 + rank)
     new_key = torch.randn(rows, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
     new_value = torch.randn(rows, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
-    seq_lens = torch.full((rows,), context, dtype=torch.int32, device=device)
+    seq_lens = torch.tensor(lengths, dtype=torch.int32, device=device)
     scratch = dict(
         query_padded_scratch=torch.zeros(rows, 128, heads_q, 128, dtype=torch.bfloat16, device=device),
         query_fp4_scratch=torch.zeros(rows, 1, heads_q, 64, dtype=torch.uint8, device=device),
@@ -292,15 +416,43 @@ def run_ours(args) -> None:
             scratch["split_merge_counters"] = torch.zeros(rows * heads_kv, dtype=torch.int32, device=device)
     out = torch.empty(rows, heads_q, 128, dtype=torch.bfloat16, device=device)
 
+    # ---- the long sequence of the mixed step: this rank's KV shard of it ------------------------
+    long_step, long_bytes = None, 0
+    if mixed:
+        from bdfp4.distributed import KvShardedDecoder
+
+        shard = LONG_TOKENS // world // 128 * 128
+        wl = build_workload(rows=1, heads_q=HEADS_Q, heads_kv=HEADS_KV, seq_lens=[shard + 128], sink_tokens=SINK_ROWS,
+                            seed=7000 + rank, device=device, key_scale_mode="four_six", value_scale_mode="amax6",
+                            rotate=True, page_tokens=page_tokens)
+        wl.seqused_sink.clamp_(max=SINK_USED)
+        wl.sink_tokens = SINK_USED
+        owner_tail, owner_sink = rank == world - 1, rank == 0
+        zeros = torch.zeros_like(wl.seqused_residual)
+        long_out = torch.empty(1, HEADS_Q, 128, dtype=torch.bfloat16, device=device)
+        long_decoder = KvShardedDecoder(
+            *wl.regions, wl.page_table, wl.seqused_fp4, residual_key_pages_bf16=wl.tail_key[0],
+            residual_value_pages_bf16=wl.tail_value[0], residual_page_ids=wl.slot_ids,
+            seqused_residual=wl.seqused_residual if owner_tail else zeros,
+            seqused_sink=wl.seqused_sink if owner_sink else zeros, heads_q=HEADS_Q, query_terms=2,
+            query_rotation="hadamard", out=long_out)
+        long_bytes = wl.algorithmic_bytes()
+
+        def long_step():
+            return long_decoder(wl.query)
+
     def step(query, key_token, value_token):
         tail = DecodeTailWrite(key_token, value_token, w.tail_key[0], w.tail_value[0], w.slot_ids, seq_lens,
                                w.seqused_fp4, True, None, SINK_ROWS)
-        return fp4_decode(
+        result = fp4_decode(
             query, *w.regions, w.page_table, w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
             residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
             seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, out=out, trusted_metadata=True,
             num_splits=splits, query_terms=2, scale_mode="amax6", query_rotation="hadamard", tail_write=tail,
-            **scratch)
+            row_order=row_order, **scratch)
+        if long_step is not None:
+            long_step()
+        return result
 
     def barrier():
         if world > 1:
@@ -315,13 +467,9 @@ def run_ours(args) -> None:
         return float(t.item())
 
     # ---- device-resident arm ----------------------------------------------------------------
-    # The step's two launches are issued directly (query quantizer with the fused tail write, then
-    # the decode kernel) so that CUDA events on the launching stream can bracket the decode kernel
+    # The step's launches are issued directly (query quantizer with the fused tail write, the decode
+    # kernel, the split merge) so that CUDA events on the launching stream bracket the decode kernel
     # inside the same timed region the step time comes from.
-    import bdfp4
-    from nvfp4_decode_kernel import _decode as decode_module
-    from nvfp4_decode_kernel._quantize import quantize_query
-
     tail = DecodeTailWrite(new_key, new_value, w.tail_key[0], w.tail_value[0], w.slot_ids, seq_lens,
                            w.seqused_fp4, True, None, SINK_ROWS)
 
@@ -342,10 +490,14 @@ def run_ours(args) -> None:
         key_pages_fp4=w.regions[0], key_scales=w.regions[1], value_pages_fp4=w.regions[2], value_scales=w.regions[3],
         fp4_page_table=w.page_table, seqused_fp4=w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
         residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
-        seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, softmax_scale=128 ** -0.5)
+        seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, softmax_scale=128 ** -0.5,
+        row_order=row_order)
+    page_cost = decode_module.BF16_BLOCK_PAGE_COST if parts == splits and splits > 1 else 0
+    if args.bf16_cost >= 0:
+        page_cost = args.bf16_cost
     kernel_args.num_splits = splits
     kernel_args.bf16_split = int(parts > splits)
-    kernel_args.bf16_page_cost = args.bf16_cost if args.bf16_cost >= 0 else decode_module.BF16_BLOCK_PAGE_COST
+    kernel_args.bf16_page_cost = page_cost
     if splits > 1:
         kernel_args.partial_out = scratch["split_partial_scratch"].data_ptr()
         kernel_args.partial_lse = scratch["split_lse_scratch"].data_ptr()
@@ -354,8 +506,13 @@ def run_ours(args) -> None:
     if splits > 1 and args.fused_merge:  # the split launch merges its own partials
         kernel_args.merge_counters = scratch["split_merge_counters"].data_ptr()
     stream = bdfp4.current_stream(device)
+    # the small workloads fit in L2: a write larger than L2 between steps sends their pages back to HBM
+    small = algorithmic_bytes + long_bytes < (256 << 20)
+    l2_scratch = torch.zeros(160 << 20, dtype=torch.uint8, device=device) if small else None
 
     def device_step(events=None):
+        if l2_scratch is not None:
+            flush_l2(l2_scratch)
         quantize_step()
         if events:
             events[0].record()
@@ -365,24 +522,27 @@ def run_ours(args) -> None:
         if splits > 1 and not args.fused_merge:
             bdfp4.combine(scratch["split_partial_scratch"], scratch["split_lse_scratch"], parts, rows, heads_q, out,
                           out.stride(0), stream)
+        if long_step is not None:
+            long_step()
 
     for _ in range(args.warmup):
         device_step()
-    barrier()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    kernel_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                     for _ in range(args.steps)]
     sampler = ClockSampler(local_rank)
     sampler.__enter__()  # samples through both timed regions; left at the end of the end-to-end arm
-    sampler.open_window()
-    begin.record()
-    for pair in kernel_events:
-        device_step(pair)
-    end.record()
-    barrier()
-    sampler.close_window()
-    step_ms = max_over_ranks(begin.elapsed_time(end) / args.steps)
-    kernel_ms = max_over_ranks(statistics.mean(a.elapsed_time(b) for a, b in kernel_events))
+    resident = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    resident.run(device_step, lambda: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+    step_ms = max_over_ranks(resident.median_ms())
+    kernel_ms = max_over_ranks(resident.median_kernel_ms())
+    flush_ms = 0.0
+    if l2_scratch is not None:  # the flush write is inside the step's events: measure it and take it out
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(20):
+            flush_l2(l2_scratch)
+        end.record()
+        torch.cuda.synchronize()
+        flush_ms = begin.elapsed_time(end) / 20
+        step_ms -= flush_ms
 
     # ---- end-to-end arm: host buffers in, host buffer out, copies inside the timed region ------
     # The step's inputs (query, new K token, new V token of every row) sit in one pinned host record
@@ -398,72 +558,70 @@ def run_ours(args) -> None:
     dev_key = dev_in[q_elems:q_elems + kv_elems].view_as(new_key)
     dev_value = dev_in[q_elems + kv_elems:].view_as(new_value)
 
-    # The whole step is captured once into a CUDA graph, as the serving engine captures its uniform
-    # decode batches: the copy in, the plugin call (query quantizer with the fused tail write, the
-    # decode kernel, the split merge when there is one) and the copy out. A step is one replay
-    # and a synchronise.
     def whole_step():
         dev_in.copy_(host_in, non_blocking=True)
         step(dev_query, dev_key, dev_value)
         host_out.copy_(out, non_blocking=True)
 
-    side = torch.cuda.Stream(device=device)
-    side.wait_stream(torch.cuda.current_stream(device))
-    with torch.cuda.stream(side):
-        whole_step()
-    torch.cuda.current_stream(device).wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        whole_step()
+    # The whole step is captured once into a CUDA graph, as the serving engine captures its uniform
+    # decode batches: the copy in, the plugin call and the copy out; a step is one replay and a
+    # synchronise. The mixed step holds a collective, which is launched eagerly instead.
+    graph = None
+    if not mixed:
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            whole_step()
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            whole_step()
 
-    def e2e_step():
-        graph.replay()
+    def e2e_step(_events=None):
+        if l2_scratch is not None:
+            flush_l2(l2_scratch)
+        if graph is not None:
+            graph.replay()
+        else:
+            whole_step()
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
         e2e_step()
-    barrier()
-    sampler.open_window()
-    begin.record()
-    for _ in range(args.steps):
-        e2e_step()
-    end.record()
-    barrier()
-    sampler.close_window()
+    end_to_end = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    end_to_end.run(e2e_step)
     sampler.__exit__(None, None, None)
-    e2e_ms = max_over_ranks(begin.elapsed_time(end) / args.steps)
+    e2e_ms = max_over_ranks(end_to_end.median_ms()) - flush_ms
     h2d = host_in.numel() * 2
     d2h = host_out.numel() * 2
 
     # ---- quantize-on-write throughput (bulk page quantize, K and V) ---------------------------
     from nvfp4_decode_kernel.quantize_kv_kernel import KVCacheWriter
 
-    page_tokens = args.page_tokens
-    q_pages = min(2048 * (128 // page_tokens), w.page_table.numel())
-    source_k = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
-    source_v = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
-    writer = KVCacheWriter(regions=w.regions, key_scale_mode="four_six", value_scale_mode="amax6", rotate_key=True)
-    work_src = torch.arange(q_pages, dtype=torch.int32, device=device) * page_tokens
-    work_dst = w.page_table.reshape(-1)[:q_pages].contiguous()
-    for _ in range(3):
-        writer(source_k, source_v, w.regions, work_src, work_dst)
-    barrier()
-    begin.record()
-    for _ in range(5):
-        writer(source_k, source_v, w.regions, work_src, work_dst)
-    end.record()
-    barrier()
-    quant_ms = begin.elapsed_time(end) / 5
-    quant_bytes = q_pages * heads_kv * 2 * (page_tokens * 256 + page_tokens * 72)
-    quantize_gbs = quant_bytes / (quant_ms * 1e-3) / 1e9
+    q_pages = min(2048 * (128 // page_tokens), int((w.seqused_fp4 // page_tokens).sum()))
+    quantize = None
+    if q_pages >= 64:
+        source_k = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+        source_v = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
+        writer = KVCacheWriter(regions=w.regions, key_scale_mode="four_six", value_scale_mode="amax6", rotate_key=True)
+        work_src = torch.arange(q_pages, dtype=torch.int32, device=device) * page_tokens
+        used = torch.cat([w.page_table[r, :int(w.seqused_fp4[r]) // page_tokens] for r in range(rows)])
+        work_dst = used[:q_pages].contiguous()
+        for _ in range(3):
+            writer(source_k, source_v, w.regions, work_src, work_dst)
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(5):
+            writer(source_k, source_v, w.regions, work_src, work_dst)
+        end.record()
+        barrier()
+        quant_ms = begin.elapsed_time(end) / 5
+        quant_bytes = q_pages * heads_kv * 2 * (page_tokens * 256 + page_tokens * 72)
+        quantize = {"ms": quant_ms, "bytes": quant_bytes, "gb_s": quant_bytes / (quant_ms * 1e-3) / 1e9,
+                    "page_heads": q_pages * heads_kv * 2}
 
-    if world > 1:
-        gathered = [None] * world
-        dist.all_gather_object(gathered, algorithmic_bytes)
-        total_bytes = sum(gathered)
-    else:
-        total_bytes = algorithmic_bytes
     # ---- parity at the benchmarked size, after and outside every timed region ------------------
     verified = None
     if args.verify and rank == 0:
@@ -475,60 +633,71 @@ def run_ours(args) -> None:
         torch.cuda.synchronize()
         verified = tile_check.check_tiles(
             w, result, tiles, terms=2, scale_mode="amax6", rotate=True, num_splits=splits, bf16_split=parts > splits,
-            bf16_page_cost=decode_module.BF16_BLOCK_PAGE_COST if parts == splits else 0)
+            bf16_page_cost=decode_module.BF16_BLOCK_PAGE_COST if parts == splits and splits > 1 else 0)
         verified["tolerance"] = {"max_abs": 1e-2, "mean_rel": 1e-3}
         verified["against"] = "CPU oracle on sampled (row, KV head) tiles of this run's cache"
 
+    total_bytes = algorithmic_bytes
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, algorithmic_bytes)
+        total_bytes = sum(gathered)
     peak, peak_kind = measured_peak_gbs()
     achieved = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
     clocks = sampler.summary()
-    # DRAM traffic per launch from the ncu capture of the same kernel on the 8,192-token case
-    # (dram__bytes_read + dram__bytes_write: 638.7 MB for 630.3 MB of algorithmic bytes with 64-token
-    # pages, 637.9 MB for 630.2 MB with 128-token pages), scaled by the bytes this launch processes;
-    # traffic grows in proportion to the pages walked.
+    # DRAM traffic per launch is an estimate: algorithmic bytes times the ratio ncu measured on the
+    # 8,192-token capture of the same kernel (638.7 / 630.3 MB with 64-token pages, 637.9 / 630.2 MB
+    # with 128-token pages); traffic grows in proportion to the pages walked.
     traffic = algorithmic_bytes * ((638.7 / 630.3) if page_tokens == 64 else (637.9 / 630.2))
     if rank == 0:
+        launches = 2 + (1 if splits > 1 and not args.fused_merge else 0) + (1 if small else 0) + (5 if mixed else 0)
+        config = common_config(spec, part["text"], page_tokens)
         line = {
-            "metric": "decode_attn_us_per_step",
-            "value": step_ms * 1e3,
-            "unit": "us/step",
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": args.warmup,
-            "ms_per_step": step_ms,
-            "higher_is_better": False,
-            "scaling": "strong",
-            "vs_baseline": None,
-            "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate",
-            "data": "synthetic",
-            "config": {
-                "workload": WORKLOAD_NAME.format(page=page_tokens) + (
-                    "" if (context, rows, total_heads_kv, total_heads_q) == (CONTEXT, BATCH, HEADS_KV, HEADS_Q)
-                    else f" [shape overridden: batch {rows}, {total_heads_q}q/{total_heads_kv}kv heads, context {context}]"),
-                "partition": f"{heads_kv} of {total_heads_kv} KV heads per rank, no collective",
-                "sink_tokens": SINK_USED, "recent_tokens": 128, "num_splits": splits,
-                "query": "two NVFP4 terms, Hadamard", "key_scale_mode": "four_six", "p_scale_mode": "amax2_or_amax6_c8",
-                "l2": "inputs (4.8 GB per step over all ranks) exceed the 126 MB L2; no flush needed",
-                "e2e": "every step: one CUDA-graph replay of [H2D of the pinned input record, plugin call, D2H into a pinned buffer], then synchronise",
-            },
-            "hbm_tb_s": total_bytes / (step_ms * 1e-3) / 1e12,
+            "metric": "decode_attn_us_per_step" if not mixed else "mixed_step_us",
+            "value": step_ms * 1e3, "unit": "us/step", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": step_ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate", "data": "synthetic", "config": config,
+            "launch": {"num_splits": splits, "parts": parts, "bf16_page_cost": page_cost,
+                       "row_order": "longest first" if ragged else "index order",
+                       "l2_flush_between_steps": small, "l2_flush_us_removed": flush_ms * 1e3},
+            "timing": {"statistic": "median over rounds of K steps, max over ranks", "rounds": len(resident.rounds),
+                       "timed_region_s": sum(r["ms_per_step"] for r in resident.rounds) * args.steps * 1e-3,
+                       "clock_bins": resident.clock_bins(),
+                       "us_x_median_sm_mhz": step_ms * 1e3 * (clocks["sm_mhz"] or 0)},
+            "hbm_tb_s": (total_bytes + long_bytes * world) / (step_ms * 1e-3) / 1e12,
             "decode_kernel_us": kernel_ms * 1e3,
-            "quantize_gb_s": quantize_gbs,
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                "kernel": "decode_kernel", "algorithmic_bytes_per_launch": algorithmic_bytes,
+                "traffic": traffic, "traffic_source": "estimated from the ncu capture under profiles/ (ratio to "
+                                                      "algorithmic bytes 1.013 / 1.012), not measured in this run",
+                "peak_kind": f"of {peak_kind}", "kernel": "decode_kernel",
+                "algorithmic_bytes_per_launch": algorithmic_bytes,
             },
-            "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (3 if splits > 1 and not args.fused_merge else 2),
+            "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "how": "every step: one CUDA-graph replay of [H2D of the pinned input record, plugin call, D2H "
+                           "into a pinned buffer], then synchronise" if graph is not None else
+                           "every step: H2D of the pinned input record, plugin call (with its collective), D2H into "
+                           "a pinned buffer, then synchronise"},
+            "gpu_launches": args.steps * launches * len(resident.rounds),
             "clocks": clocks,
+            "reference_gpu_kernel": REFERENCE_GPU_NOTE,
         }
+        if quantize is not None:
+            line["quantize_gb_s"] = quantize["gb_s"]
+            line["roofline_quantize"] = {
+                "bound": "hbm", "kernel": "kv_page_kernel (K: Hadamard + four_six search, V: amax6)",
+                "achieved": quantize["gb_s"], "peak": peak, "unit": "GB/s", "frac": quantize["gb_s"] / peak,
+                "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": quantize["bytes"],
+                "units_per_launch": f"{quantize['page_heads']} page-heads x {page_tokens * 328} B "
+                                    "(BF16 in, codes and scales out)", "traffic": None,
+                "note": "the K role is instruction-bound (scale search + 7-level Hadamard), not HBM-bound",
+            }
         if verified is not None:
             line["verified"] = verified
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(heads_kv, page_tokens=page_tokens)
+            line["cpu_baseline"] = cpu_baseline_entry(cpu_step(spec, lengths, heads_kv, 12.0, page_tokens))
         print(json.dumps(line))
-    if world > 1:
+    if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()
 
 
@@ -682,26 +851,13 @@ def run_mla(args) -> None:
         return mla.mla_decode(ql, qr, cache, table, seq_lens, softmax_scale=MLA_SCALE, num_splits=splits,
                               error_word=error, out=result, scratch=scratch)
 
-    # ---- device-resident step: one-token append (3 launches), query quantize, decode (+ merge)
-    stream = torch.cuda.current_stream(device)
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for _ in range(args.warmup):
-        decode(q_latent, q_rope)
-    sampler = ClockSampler(local_rank)
-    sampler.__enter__()
-    barrier()
-    sampler.open_window()
-    begin.record()
-    for _ in range(args.steps):
-        decode(q_latent, q_rope)
-    end.record()
-    barrier()
-    sampler.close_window()
-    step_ms = max_over_ranks(begin.elapsed_time(end) / args.steps)
-    # the decode kernel alone: the same launches with the query already quantized
-    codes, scales = mla.quantize_query(q_latent)
+    # ---- device-resident step: one-token append (3 launches), query quantize, decode (+ merge).
+    # The launches are issued one by one so that CUDA events on the launching stream bracket the decode
+    # kernel inside the very region the step time comes from.
     import bdfp4
 
+    stream = torch.cuda.current_stream(device)
+    codes, scales = scratch.codes, scratch.scales
     a = bdfp4.MlaDecodeArgs()
     a.rows, a.heads_q = rows, MLA_HEADS
     a.query_codes, a.query_scales, a.query_rope = codes.data_ptr(), scales.data_ptr(), q_rope.data_ptr()
@@ -712,22 +868,33 @@ def run_mla(args) -> None:
     a.page_table, a.page_table_stride, a.seq_lens = table.data_ptr(), table.stride(0), seq_lens.data_ptr()
     a.softmax_scale, a.p_scale_mode, a.p_scale_tau = MLA_SCALE, 2, 21.0 / 1024.0
     a.num_splits = splits
-    out = torch.empty(rows, MLA_HEADS, 512, dtype=torch.bfloat16, device=device)
-    partial_out = torch.empty(splits, rows, MLA_HEADS, 512, device=device)
-    partial_lse = torch.empty(splits, rows, MLA_HEADS, device=device)
+    a.error_word = error.data_ptr()
     if splits == 1:
-        a.out = out.data_ptr()
+        a.out = result.data_ptr()
     else:
-        a.partial_out, a.partial_lse = partial_out.data_ptr(), partial_lse.data_ptr()
-    for _ in range(3):
+        a.partial_out, a.partial_lse = scratch.partial_out.data_ptr(), scratch.partial_lse.data_ptr()
+
+    def device_step(events=None):
+        appender.append(cache, new_latent, new_rope, lens_before, table, error_word=error)
+        mla.quantize_query(q_latent, out=(codes, scales))
+        if events:
+            events[0].record()
         bdfp4.mla_decode(a, stream.cuda_stream)
-    barrier()
-    begin.record()
-    for _ in range(args.steps):
-        bdfp4.mla_decode(a, stream.cuda_stream)
-    end.record()
-    barrier()
-    kernel_ms = max_over_ranks(begin.elapsed_time(end) / args.steps)
+        if events:
+            events[1].record()
+        if splits > 1:
+            bdfp4.mla_combine(scratch.partial_out, scratch.partial_lse, splits, rows, MLA_HEADS, result,
+                              stream.cuda_stream)
+
+    for _ in range(args.warmup):
+        device_step()
+    sampler = ClockSampler(local_rank)
+    sampler.__enter__()
+    resident = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    resident.run(device_step, lambda: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+    step_ms = max_over_ranks(resident.median_ms())
+    kernel_ms = max_over_ranks(resident.median_kernel_ms())
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     # ---- end to end: pinned host query in, pinned host output back, every step
     host_q = torch.empty(rows, MLA_HEADS, 576, dtype=torch.bfloat16).pin_memory()
@@ -742,7 +909,7 @@ def run_mla(args) -> None:
     dense_latent = torch.empty(rows, MLA_HEADS, 512, dtype=torch.bfloat16, device=device)
     dense_rope = torch.empty(rows, MLA_HEADS, 64, dtype=torch.bfloat16, device=device)
 
-    def e2e_step():
+    def e2e_step(_events=None):
         device_q.copy_(host_q, non_blocking=True)
         device_new.copy_(host_new, non_blocking=True)
         new_latent.copy_(device_new[:, :512])
@@ -754,16 +921,10 @@ def run_mla(args) -> None:
 
     for _ in range(args.warmup):
         e2e_step()
-    barrier()
-    sampler.open_window()
-    begin.record()
-    for _ in range(args.steps):
-        e2e_step()
-    end.record()
-    barrier()
-    sampler.close_window()
+    end_to_end = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    end_to_end.run(e2e_step)
     sampler.__exit__(None, None, None)
-    e2e_ms = max_over_ranks(begin.elapsed_time(end) / args.steps)
+    e2e_ms = max_over_ranks(end_to_end.median_ms())
 
     tokens = rows * context
     algorithmic = tokens * MLA_TOKEN_BYTES + rows * MLA_HEADS * (576 + 512) * 2
@@ -784,8 +945,14 @@ def run_mla(args) -> None:
                 "step": "append one token per row (stage, re-quantize the open page, rope block), query quantize, decode (+ merge)",
                 "e2e": "every step: H2D of the pinned query and new token, the step, D2H of the output into pinned memory, synchronise",
             },
+            "timing": {"statistic": "median over rounds of K steps, max over ranks", "rounds": len(resident.rounds),
+                       "timed_region_s": sum(r["ms_per_step"] for r in resident.rounds) * args.steps * 1e-3,
+                       "clock_bins": resident.clock_bins()},
             "decode_kernel_us": kernel_ms * 1e3,
             "cache_read_gb_s": cache_bytes / (kernel_ms * 1e-3) / 1e9,
+            "roofline_on_cache_bytes": {"achieved": cache_bytes / (kernel_ms * 1e-3) / 1e9, "peak": peak,
+                                        "frac": cache_bytes / (kernel_ms * 1e-3) / 1e9 / peak,
+                                        "note": "704 B per token: what this cache layout holds and the kernel reads"},
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 # DRAM traffic per launch: both latent copies are read (704 B per token); measured by ncu on
@@ -796,7 +963,7 @@ def run_mla(args) -> None:
             },
             "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": (host_q.numel() + host_new.numel()) * 2,
                     "d2h_bytes_per_step": host_out.numel() * 2},
-            "gpu_launches": args.steps * (5 if splits == 1 else 6),
+            "gpu_launches": args.steps * (5 if splits == 1 else 6) * len(resident.rounds),
             "clocks": sampler.summary(),
             "device_errors": int(error.item()),
         }
@@ -813,13 +980,10 @@ def run_mla(args) -> None:
 # tokens of the Qwen3-4B shape (32 query / 8 KV heads); the one path with a collective
 # ---------------------------------------------------------------------------------------------
 
-LONG_TOKENS = 1 << 20
-
-
 def run_longseq(args) -> None:
     import torch.distributed as dist
 
-    from bdfp4.distributed import decode_kv_sharded
+    from bdfp4.distributed import KvShardedDecoder
     from bdfp4.workload import build_workload
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -843,16 +1007,16 @@ def run_longseq(args) -> None:
     zeros = torch.zeros_like(w.seqused_residual)
     owner_tail, owner_sink = rank == world - 1, rank == 0
     out = torch.empty(1, HEADS_Q, 128, dtype=torch.bfloat16, device=device)
-    workspace: dict = {}
     no_sink = torch.zeros_like(w.seqused_sink)
+    decoder = KvShardedDecoder(
+        *w.regions, w.page_table, w.seqused_fp4, heads_q=HEADS_Q, residual_key_pages_bf16=w.tail_key[0],
+        residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
+        seqused_residual=w.seqused_residual if owner_tail else zeros,
+        seqused_sink=w.seqused_sink if owner_sink else no_sink, query_terms=2, query_rotation="hadamard", out=out,
+        num_splits=args.splits or None)
 
     def step():
-        return decode_kv_sharded(
-            w.query, *w.regions, w.page_table, w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
-            residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
-            seqused_residual=w.seqused_residual if owner_tail else zeros,
-            seqused_sink=w.seqused_sink if owner_sink else no_sink, query_terms=2,
-            query_rotation="hadamard", out=out, num_splits=args.splits or None, workspace=workspace)
+        return decoder(w.query)
 
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(args.warmup):
@@ -900,14 +1064,18 @@ def run_longseq(args) -> None:
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--steps", type=int, default=20, help="steps per timed round")
     parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--min-seconds", type=float, default=1.0,
+                        help="rounds of --steps steps are repeated until this much device time has been measured")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--context", type=int, default=CONTEXT, help="override the context length (profiling only)")
     parser.add_argument("--batch", type=int, default=0, help="override the batch (profiling only)")
     parser.add_argument("--heads-kv", type=int, default=0, help="override the KV head count (profiling only)")
     parser.add_argument("--heads-q", type=int, default=0, help="override the query head count (profiling only)")
     parser.add_argument("--splits", type=int, default=0, help="override the split-KV count")
+    parser.add_argument("--kv-groups", type=int, default=0,
+                        help="ranks along the KV-head axis (default: as many as there are KV heads, then rows)")
     parser.add_argument("--bf16-cost", type=int, default=-1,
                         help="pages split 0 is charged for the tail and sink (default: the library's)")
     parser.add_argument("--page-tokens", type=int, default=64, choices=[64, 128],
@@ -920,12 +1088,15 @@ def main() -> None:
     parser.add_argument("--verify", type=int, default=4, metavar="TILES",
                         help="after the timed regions, compare this many sampled (row, KV head) tiles of one decode "
                              "with the CPU oracle and report the errors (0: skip)")
-    parser.add_argument("--workload", default="gqa", choices=["gqa", "mla", "longseq"],
-                        help="gqa: the headline Qwen3-4B-shaped step; mla: the MLA latent-cache decode configuration; "
-                             "longseq: one 1M-token sequence split along the KV axis over the ranks")
+    parser.add_argument("--workload", default="gqa", choices=["gqa", "cfg1", "cfg3", "mixed", "mla", "longseq"],
+                        help="gqa: the headline Qwen3-4B-shaped step; cfg1: batch 4 with short contexts; cfg3: eight "
+                             "query heads per KV head, 131,072 tokens; mixed: 256 Zipf-length sequences plus one "
+                             "1M-token sequence split along the KV axis; mla: the latent-cache decode; longseq: the "
+                             "1M-token sequence alone")
     args = parser.parse_args()
     if args.warmup < 3:
-        args.warmup = 3
+        print(f"bench.py: --warmup {args.warmup} is below the 3 warm-up steps a reportable number needs; "
+              "running as asked", file=sys.stderr)
     if args.workload == "longseq":
         run_longseq(args)
     elif args.workload == "mla":
@@ -933,7 +1104,7 @@ def main() -> None:
     elif args.impl == "reference":
         run_reference(args)
     else:
-        run_ours(args)
+        run_gqa(args)
 
 
 if __name__ == "__main__":

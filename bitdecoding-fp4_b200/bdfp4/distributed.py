@@ -47,6 +47,113 @@ def split_record(gathered: torch.Tensor, world_size: int, rows: int, heads_q: in
     return outs, lses
 
 
+class KvShardedDecoder:
+    """One rank's side of the KV-sharded decode, with everything that does not change between steps held
+    across them: the shard's cache regions and metadata, the two argument records of the C ABI, the query
+    quantizer's outputs, the split partials, the rank's ``[O | LSE]`` record and the gathered records.
+
+    A step is :meth:`__call__` with the step's query: it writes the query's address into the records and
+    issues the launches back to back on torch's current stream, with no allocation, no validation of
+    device values and no host synchronisation: query quantizer, shard decode (split again inside the rank
+    when ``num_splits > 1``), fold of the rank's parts into its record, ONE ``all_gather`` of the records,
+    merge. This library's kernels are launched with programmatic stream serialization, so each one's CTAs
+    come up while its predecessor drains.
+
+    Pass the BF16 residual arguments only on the rank that owns them (see the module docstring); with
+    ``seqused_sink`` but ``seqused_residual`` zero a rank owns the sink alone.
+    """
+
+    def __init__(self, key_pages_fp4, key_scales, value_pages_fp4, value_scales, fp4_page_table, seqused_fp4, *,
+                 heads_q: int, rows: int = 1, group=None, residual_key_pages_bf16=None,
+                 residual_value_pages_bf16=None, residual_page_ids=None, seqused_residual=None, seqused_sink=None,
+                 softmax_scale: float | None = None, query_terms: int = 2, scale_mode: str = "amax6",
+                 query_rotation: str = "none", out: torch.Tensor | None = None, num_splits: int | None = None):
+        import torch.distributed as dist
+
+        import bdfp4
+        from nvfp4_decode_kernel import _decode
+        from nvfp4_decode_kernel.scale_mode import mode_id
+
+        self.group, self.world = group, dist.get_world_size(group)
+        self.rows, self.heads_q = rows, heads_q
+        heads_kv = key_pages_fp4.shape[2]
+        device = key_pages_fp4.device
+        self.device = device
+        has_residual = residual_key_pages_bf16 is not None
+        if num_splits is None:
+            num_splits = _decode.resident_num_splits(rows, heads_kv, sms=_decode._multiprocessor_count(device.index or 0))
+        self.num_splits = num_splits
+        self.record = record_floats(rows, heads_q)
+        # buffers: whatever the per-call form would allocate
+        u8 = dict(dtype=torch.uint8, device=device)
+        self.codes = [torch.zeros(rows, 1, heads_q, HEAD_DIM // 2, **u8) for _ in range(query_terms)]
+        self.scales = [torch.zeros(rows, 1, heads_q, 2, 32, 4, 4, **u8) for _ in range(query_terms)]
+        # rows past the first of each padded query tile stay zero: written once, here
+        self.padded = torch.zeros(rows, 128, heads_q, HEAD_DIM, dtype=torch.bfloat16, device=device) if has_residual else None
+        self.local = torch.empty(self.record, dtype=torch.float32, device=device)
+        self.gathered = torch.empty(self.world * self.record, dtype=torch.float32, device=device)
+        self.out = out if out is not None else torch.empty(rows, heads_q, HEAD_DIM, dtype=torch.bfloat16, device=device)
+        self.partial_out = self.partial_lse = None
+        if num_splits > 1:
+            self.partial_out = torch.empty(num_splits, rows, heads_q, HEAD_DIM, dtype=torch.float32, device=device)
+            self.partial_lse = torch.empty(num_splits, rows, heads_q, dtype=torch.float32, device=device)
+        # the quantizer's record: only `query` changes between steps
+        q = bdfp4.QuantizeQueryArgs()
+        q.rows, q.heads_q, q.heads_kv = rows, heads_q, heads_kv
+        q.scale_mode, q.rotate = mode_id(scale_mode), int(query_rotation == "hadamard")
+        q.query_codes, q.query_scales = self.codes[0].data_ptr(), self.scales[0].data_ptr()
+        if query_terms == 2:
+            q.query_codes_second, q.query_scales_second = self.codes[1].data_ptr(), self.scales[1].data_ptr()
+        q.query_padded = bdfp4.ptr(self.padded)
+        self.quantize_args = q
+        # the decode record: nothing changes between steps (lengths and tables are read on the device)
+        from nvfp4_decode_kernel._quantize import _scale_view
+
+        a = bdfp4.DecodeArgs()
+        views = [_scale_view(s, heads_kv) for s in self.scales]
+        _decode._fill_args(
+            a, rows=rows, heads_q=heads_q, heads_kv=heads_kv, page_count=key_pages_fp4.shape[0],
+            query_fp4=self.codes[0], query_scales=views[0], query_fp4_second=self.codes[1] if query_terms == 2 else None,
+            query_scales_second=views[1] if query_terms == 2 else None, query_padded_bf16=self.padded,
+            key_pages_fp4=key_pages_fp4, key_scales=key_scales, value_pages_fp4=value_pages_fp4,
+            value_scales=value_scales, fp4_page_table=fp4_page_table, seqused_fp4=seqused_fp4,
+            residual_key_pages_bf16=residual_key_pages_bf16, residual_value_pages_bf16=residual_value_pages_bf16,
+            residual_page_ids=residual_page_ids, seqused_residual=seqused_residual, seqused_sink=seqused_sink,
+            softmax_scale=softmax_scale if softmax_scale is not None else HEAD_DIM ** -0.5)
+        self.lse_offset = rows * heads_q * HEAD_DIM * 4
+        if num_splits <= 1:
+            a.num_splits = 1
+            a.partial_out, a.partial_lse = self.local.data_ptr(), self.local.data_ptr() + self.lse_offset
+        else:
+            a.num_splits, a.bf16_split, a.out = num_splits, 0, None
+            a.partial_out, a.partial_lse = self.partial_out.data_ptr(), self.partial_lse.data_ptr()
+        self.decode_args = a
+        self._keep = (key_pages_fp4, key_scales, value_pages_fp4, value_scales, fp4_page_table, seqused_fp4,
+                      residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids, seqused_residual,
+                      seqused_sink)  # the records hold raw addresses: keep their owners alive
+
+    def __call__(self, query: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+
+        import bdfp4
+
+        if query.dtype is not torch.bfloat16 or tuple(query.shape) != (self.rows, self.heads_q, HEAD_DIM) \
+                or query.stride(-1) != 1 or query.data_ptr() % 16 or query.stride(0) % 8 or query.stride(1) % 8:
+            raise ValueError(f"query must be BF16 [{self.rows}, {self.heads_q}, {HEAD_DIM}] with 16-byte aligned heads")
+        q = self.quantize_args
+        q.query, q.query_row_stride, q.query_head_stride = query.data_ptr(), query.stride(0), query.stride(1)
+        stream = bdfp4.current_stream(self.device)
+        bdfp4.quantize_query(q, stream)
+        bdfp4.decode(self.decode_args, stream)
+        if self.num_splits > 1:
+            bdfp4.combine_record(self.partial_out, self.partial_lse, self.num_splits, self.rows, self.heads_q,
+                                 self.local.data_ptr(), self.local.data_ptr() + self.lse_offset, stream)
+        dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
+        bdfp4.combine_strided(self.gathered.data_ptr(), self.record, self.gathered.data_ptr() + self.lse_offset,
+                              self.record, self.world, self.rows, self.heads_q, self.out, self.out.stride(0), stream)
+        return self.out
+
+
 def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_pages_fp4, value_scales,
                       fp4_page_table: torch.Tensor, seqused_fp4: torch.Tensor, *, group=None,
                       residual_key_pages_bf16=None, residual_value_pages_bf16=None, residual_page_ids=None,
@@ -54,80 +161,24 @@ def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_page
                       query_terms: int = 2, scale_mode: str = "amax6", query_rotation: str = "none",
                       out: torch.Tensor | None = None, num_splits: int | None = None,
                       workspace: dict | None = None) -> torch.Tensor:
-    """Decode attention over a sequence whose FP4 pages are sharded across the ranks of ``group``.
-
-    Every rank passes the same ``query`` and its own shard: local cache regions, a local page table
-    and ``seqused_fp4`` counting only its pages. Pass the BF16 residual arguments only on the rank
-    that owns them (see the module docstring); with ``seqused_sink`` but ``seqused_residual`` zero a
-    rank owns the sink alone. Returns the merged BF16 output on every rank.
-
-    A rank's shard of one long sequence is only ``rows * heads_kv`` independent walks, far fewer than
-    the GPU has SMs, so the shard is itself split along KV into ``num_splits`` parts (default: enough
-    to keep four CTAs per SM resident, from the batch width alone) whose partials the rank folds into
-    its one record before the exchange. ``workspace`` (a dict the caller keeps between steps) holds
-    the buffers a call would otherwise allocate; it is tied to the shapes of its first call.
-    """
-    import torch.distributed as dist
-
-    import bdfp4
-    from nvfp4_decode_kernel import _decode
-    from nvfp4_decode_kernel._quantize import quantize_query
-
-    world = dist.get_world_size(group)
-    rows, heads_q, head_dim = query.shape
-    heads_kv = key_pages_fp4.shape[2]
-    device = query.device
-    has_residual = residual_key_pages_bf16 is not None
-    if num_splits is None:
-        num_splits = _decode.resident_num_splits(rows, heads_kv, sms=_decode._multiprocessor_count(device.index or 0))
-    record = record_floats(rows, heads_q)
+    """Decode attention over a sequence whose FP4 pages are sharded across the ranks of ``group``: the
+    one-call form of :class:`KvShardedDecoder`. Every rank passes the same ``query`` and its own shard.
+    ``workspace`` (a dict the caller keeps between steps) holds the decoder, so that only the first call
+    builds it; it is tied to the tensors of that first call. Returns the merged BF16 output on every rank."""
+    rows, heads_q, _ = query.shape
     ws = workspace if workspace is not None else {}
-    key = (rows, heads_q, world, num_splits, has_residual, device)
+    key = (rows, heads_q, key_pages_fp4.data_ptr(), fp4_page_table.data_ptr(), seqused_fp4.data_ptr(),
+           residual_key_pages_bf16 is not None, None if seqused_residual is None else seqused_residual.data_ptr(),
+           None if seqused_sink is None else seqused_sink.data_ptr(), num_splits, query_terms, scale_mode,
+           query_rotation, None if out is None else out.data_ptr())
     if ws.get("key") != key:
         ws.clear()
         ws["key"] = key
-        # rows past the first of each padded query tile stay zero: written once, here
-        ws["padded"] = (torch.zeros(rows, 128, heads_q, head_dim, dtype=torch.bfloat16, device=device)
-                        if has_residual else None)
-        ws["local"] = torch.empty(record, dtype=torch.float32, device=device)
-        ws["gathered"] = torch.empty(world * record, dtype=torch.float32, device=device)
-        if num_splits > 1:
-            ws["partial_out"] = torch.empty(num_splits, rows, heads_q, HEAD_DIM, dtype=torch.float32, device=device)
-            ws["partial_lse"] = torch.empty(num_splits, rows, heads_q, dtype=torch.float32, device=device)
-    padded = ws["padded"]
-    quantized = quantize_query(query, query_padded_out=padded, heads_kv=heads_kv, query_terms=query_terms,
-                               scale_mode=scale_mode, rotation=query_rotation)
-    second = (quantized[2], quantized[3]) if query_terms == 2 else (None, None)
-    args = bdfp4.DecodeArgs()
-    _decode._fill_args(
-        args, rows=rows, heads_q=heads_q, heads_kv=heads_kv, page_count=key_pages_fp4.shape[0],
-        query_fp4=quantized[0], query_scales=quantized[1], query_fp4_second=second[0],
-        query_scales_second=second[1], query_padded_bf16=padded, key_pages_fp4=key_pages_fp4,
-        key_scales=key_scales, value_pages_fp4=value_pages_fp4, value_scales=value_scales,
-        fp4_page_table=fp4_page_table, seqused_fp4=seqused_fp4,
-        residual_key_pages_bf16=residual_key_pages_bf16, residual_value_pages_bf16=residual_value_pages_bf16,
-        residual_page_ids=residual_page_ids, seqused_residual=seqused_residual, seqused_sink=seqused_sink,
-        softmax_scale=softmax_scale if softmax_scale is not None else head_dim ** -0.5)
-    local, gathered = ws["local"], ws["gathered"]
-    stream = bdfp4.current_stream(device)
-    lse_offset = rows * heads_q * HEAD_DIM * 4
-    if num_splits <= 1:
-        args.num_splits = 1
-        args.partial_out = local.data_ptr()
-        args.partial_lse = local.data_ptr() + lse_offset
-        bdfp4.decode(args, stream)
-    else:
-        partial_out, partial_lse = ws["partial_out"], ws["partial_lse"]
-        args.num_splits = num_splits
-        args.bf16_split = 0
-        args.out = None
-        args.partial_out, args.partial_lse = partial_out.data_ptr(), partial_lse.data_ptr()
-        bdfp4.decode(args, stream)
-        bdfp4.combine_record(partial_out, partial_lse, num_splits, rows, heads_q, local.data_ptr(),
-                             local.data_ptr() + lse_offset, stream)
-    dist.all_gather_into_tensor(gathered, local, group=group)
-    if out is None:
-        out = torch.empty(rows, heads_q, head_dim, dtype=torch.bfloat16, device=device)
-    bdfp4.combine_strided(gathered.data_ptr(), record, gathered.data_ptr() + rows * heads_q * HEAD_DIM * 4, record,
-                          world, rows, heads_q, out, out.stride(0), stream)
-    return out
+        ws["decoder"] = KvShardedDecoder(
+            key_pages_fp4, key_scales, value_pages_fp4, value_scales, fp4_page_table, seqused_fp4, heads_q=heads_q,
+            rows=rows, group=group, residual_key_pages_bf16=residual_key_pages_bf16,
+            residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
+            seqused_residual=seqused_residual, seqused_sink=seqused_sink, softmax_scale=softmax_scale,
+            query_terms=query_terms, scale_mode=scale_mode, query_rotation=query_rotation, out=out,
+            num_splits=num_splits)
+    return ws["decoder"](query)
