@@ -88,17 +88,23 @@ __device__ __forceinline__ void prefetch_l2(const void* address) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(address));
 }
 
-__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Named barriers of the softmax threads: one per softmax group (ids 1, 2, ...; 128 threads each).
+__device__ __forceinline__ void softmax_barrier(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
-__device__ __forceinline__ bool softmax_vote_any(bool pred) {
+template <int THREADS>
+__device__ __forceinline__ void all_softmax_barrier() {
+  asm volatile("bar.sync 15, %0;" ::"n"(THREADS) : "memory");
+}
+
+__device__ __forceinline__ bool softmax_vote_any(bool pred, int id) {
   uint32_t out;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 p, %1, 0;\n\t"
-      "bar.red.or.pred q, 1, 128, p;\n\t"
+      "bar.red.or.pred q, %2, 128, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(out)
-      : "r"((uint32_t)pred)
+      : "r"((uint32_t)pred), "r"(id)
       : "memory");
   return out != 0;
 }
@@ -160,24 +166,26 @@ __device__ __forceinline__ void update_max(SoftmaxState<GP>& st, const float* bl
 // A BF16 block (the rolling tail or the sink) merged with plain FMAs by the 128 softmax threads:
 // thread `t` scores token `t`, then accumulates channel `t`. `rows0` is the first row of the
 // block inside the slot's buffer, positions outside [mask_below, length) are masked.
-template <int GP, int STAGES>
-__device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, STAGES>& sm, const DecodeParams& p, int t,
-                                           int warp_q, int lane, const __nv_bfloat16* key_rows,
-                                           const __nv_bfloat16* value_rows, int mask_below, int length, float shift,
-                                           int& red_buf) {
+// A softmax group of 128 threads runs it for its own R of the tile's rows, which start at `row0` of the
+// shared per-row arrays; `barrier` is the group's named barrier.
+template <int R, typename Smem>
+__device__ __forceinline__ void bf16_block(SoftmaxState<R>& st, Smem& sm, const DecodeParams& p, int t, int warp_q,
+                                           int lane, const __nv_bfloat16* key_rows, const __nv_bfloat16* value_rows,
+                                           int mask_below, int length, float shift, int& red_buf, int row0,
+                                           int barrier) {
   const int64_t row_elems = (int64_t)p.heads_kv * kHeadDim;
-  float s[GP];
+  float s[R];
   const bool valid = t >= mask_below && t < length;
 #pragma unroll
-  for (int j = 0; j < GP; ++j) s[j] = valid ? 0.0f : -INFINITY;
+  for (int j = 0; j < R; ++j) s[j] = valid ? 0.0f : -INFINITY;
   if (length <= 16) {
     // A short block (the sink): eight lanes share a token, two 16-byte loads each, so the scores
     // cost one load round trip; they travel to the token's own thread through p_bf16.
     const int token = t >> 3, chunk = t & 7;
     const bool scored = token >= mask_below && token < length;
-    float dot[GP];
+    float dot[R];
 #pragma unroll
-    for (int j = 0; j < GP; ++j) dot[j] = 0.0f;
+    for (int j = 0; j < R; ++j) dot[j] = 0.0f;
     if (scored) {
       const uint4* kpart = reinterpret_cast<const uint4*>(key_rows + (int64_t)token * row_elems + chunk * 16);
       const uint4 raw[2] = {__ldg(kpart), __ldg(kpart + 1)};
@@ -185,9 +193,9 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
       for (int c = 0; c < 2; ++c) {
         const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
-          const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][chunk * 16 + c * 8]);
-          const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][chunk * 16 + c * 8 + 4]);
+        for (int j = 0; j < R; ++j) {
+          const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[row0 + j][chunk * 16 + c * 8]);
+          const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[row0 + j][chunk * 16 + c * 8 + 4]);
           float a = dot[j];
           a = fmaf(__uint_as_float(w[0] << 16), q0.x, a);
           a = fmaf(__uint_as_float(w[0] & 0xffff0000u), q0.y, a);
@@ -202,18 +210,18 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
       }
     }
 #pragma unroll
-    for (int j = 0; j < GP; ++j) {
+    for (int j = 0; j < R; ++j) {
       dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], 1);
       dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], 2);
       dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], 4);
-      if (chunk == 0) sm.p_bf16[j][token] = dot[j];
+      if (chunk == 0) sm.p_bf16[row0 + j][token] = dot[j];
     }
-    softmax_barrier();
+    softmax_barrier(barrier);
     if (valid) {
 #pragma unroll
-      for (int j = 0; j < GP; ++j) s[j] = sm.p_bf16[j][t];
+      for (int j = 0; j < R; ++j) s[j] = sm.p_bf16[row0 + j][t];
     }
-    softmax_barrier();  // p_bf16 is written again below
+    softmax_barrier(barrier);  // p_bf16 is written again below
   } else if (valid) {
     const uint4* krow = reinterpret_cast<const uint4*>(key_rows + (int64_t)t * row_elems);
     // Eight 16-byte loads are issued before the first is consumed: the block is latency-bound.
@@ -232,9 +240,9 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
           k[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
-          const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][(half * 8 + c) * 8]);
-          const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[j][(half * 8 + c) * 8 + 4]);
+        for (int j = 0; j < R; ++j) {
+          const float4 q0 = *reinterpret_cast<const float4*>(&sm.q_bf16[row0 + j][(half * 8 + c) * 8]);
+          const float4 q1 = *reinterpret_cast<const float4*>(&sm.q_bf16[row0 + j][(half * 8 + c) * 8 + 4]);
           float a = s[j];
           a = fmaf(k[0], q0.x, a);
           a = fmaf(k[1], q0.y, a);
@@ -252,38 +260,38 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
   // Scores and outputs of the FP4 pages stay in the units the MMAs deliver them in; with per-tensor
   // scales the BF16 blocks are brought into those units instead (both factors are exactly 1 without).
 #pragma unroll
-  for (int j = 0; j < GP; ++j) s[j] *= p.bf16_score_scale;
-  float block_max[GP];
+  for (int j = 0; j < R; ++j) s[j] *= p.bf16_score_scale;
+  float block_max[R];
 #pragma unroll
-  for (int j = 0; j < GP; ++j) {
+  for (int j = 0; j < R; ++j) {
     float m = s[j];
 #pragma unroll
     for (int step = 1; step < 32; step <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, step));
     block_max[j] = m;
   }
-  if (lane < GP) {
+  if (lane < R) {
     float mine = block_max[0];
 #pragma unroll
-    for (int j = 1; j < GP; ++j) mine = lane == j ? block_max[j] : mine;
-    sm.red[red_buf][warp_q][lane] = mine;
+    for (int j = 1; j < R; ++j) mine = lane == j ? block_max[j] : mine;
+    sm.red[red_buf][warp_q][row0 + lane] = mine;
   }
-  softmax_barrier();
+  softmax_barrier(barrier);
 #pragma unroll
-  for (int j = 0; j < GP; ++j)
-    block_max[j] = fmaxf(fmaxf(sm.red[red_buf][0][j], sm.red[red_buf][1][j]),
-                         fmaxf(sm.red[red_buf][2][j], sm.red[red_buf][3][j]));
+  for (int j = 0; j < R; ++j)
+    block_max[j] = fmaxf(fmaxf(sm.red[red_buf][0][row0 + j], sm.red[red_buf][1][row0 + j]),
+                         fmaxf(sm.red[red_buf][2][row0 + j], sm.red[red_buf][3][row0 + j]));
   red_buf ^= 1;
-  float acc[GP], max_scaled[GP];
-  update_max<GP>(st, block_max, p.scale_log2, shift, acc, max_scaled);
+  float acc[R], max_scaled[R];
+  update_max<R>(st, block_max, p.scale_log2, shift, acc, max_scaled);
   st.first = false;
 #pragma unroll
-  for (int j = 0; j < GP; ++j) {
+  for (int j = 0; j < R; ++j) {
     const float prob = ex2_approx(s[j] * p.scale_log2 - max_scaled[j]);
     st.row_sum[j] = st.row_sum[j] * acc[j] + prob;
-    sm.p_bf16[j][t] = __bfloat162float(__float2bfloat16_rn(prob));
+    sm.p_bf16[row0 + j][t] = __bfloat162float(__float2bfloat16_rn(prob));
     st.o_acc[j] *= acc[j];
   }
-  softmax_barrier();
+  softmax_barrier(barrier);
   // PV. The loop is bound by load latency, so each lane keeps sixteen 8-byte loads in flight:
   // a warp owns 32 channels, lane = (token phase lane >> 3, channel quad lane & 7) accumulates
   // tokens phase, phase + 4, ... for its four channels. A masked position carries probability
@@ -292,9 +300,9 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
     const int phase = lane >> 3;
     const uint2* vquad = reinterpret_cast<const uint2*>(value_rows + warp_q * 32 + (lane & 7) * 4);
     const int64_t row_quads = row_elems / 4;
-    float part[GP][4];
+    float part[R][4];
 #pragma unroll
-    for (int j = 0; j < GP; ++j) part[j][0] = part[j][1] = part[j][2] = part[j][3] = 0.0f;
+    for (int j = 0; j < R; ++j) part[j][0] = part[j][1] = part[j][2] = part[j][3] = 0.0f;
 #pragma unroll 1
     for (int base = 0; base < length; base += 64) {
       uint2 raw[16];
@@ -306,8 +314,8 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
         const float v0 = __uint_as_float(raw[i].x << 16), v1 = __uint_as_float(raw[i].x & 0xffff0000u);
         const float v2 = __uint_as_float(raw[i].y << 16), v3 = __uint_as_float(raw[i].y & 0xffff0000u);
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
-          const float pj = sm.p_bf16[j][token];
+        for (int j = 0; j < R; ++j) {
+          const float pj = sm.p_bf16[row0 + j][token];
           part[j][0] = fmaf(pj, v0, part[j][0]);
           part[j][1] = fmaf(pj, v1, part[j][1]);
           part[j][2] = fmaf(pj, v2, part[j][2]);
@@ -320,7 +328,7 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
     const bool b3 = (lane >> 3) & 1, b4 = (lane >> 4) & 1;
     const int holder = (lane >> 2) + 8 * ((lane >> 1) & 1) + 16 * (lane & 1);
 #pragma unroll
-    for (int j = 0; j < GP; ++j) {
+    for (int j = 0; j < R; ++j) {
       const float send0 = b3 ? part[j][0] : part[j][2], send1 = b3 ? part[j][1] : part[j][3];
       const float keep0 = b3 ? part[j][2] : part[j][0], keep1 = b3 ? part[j][3] : part[j][1];
       const float pair0 = keep0 + __shfl_xor_sync(0xffffffffu, send0, 8);
@@ -329,16 +337,32 @@ __device__ __forceinline__ void bf16_block(SoftmaxState<GP>& st, DecodeSmem<GP, 
       st.o_acc[j] += __shfl_sync(0xffffffffu, one, holder) * p.bf16_value_scale;
     }
   }
-  softmax_barrier();  // p_bf16 is reused by the next BF16 block
+  softmax_barrier(barrier);  // p_bf16 is reused by the next BF16 block
 }
 
-template <int GP, int TERMS, int STAGES, int PT, bool MX>
-__global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
+// Threads of a CTA: warp 0 copy producer, warp 1 MMA issuer, then SG softmax groups of four warps.
+// A softmax thread owns one token of the step and R = GP / SG of the tile's GP query rows: with
+// SG = 2 the two groups split the rows between them, so each thread's dependent chain per step is
+// that of a tile half as wide. Only SG = 1 is instantiated: for eight query heads per KV head SG = 2
+// measured 30 % slower on B200 (a CTA's step got 1.4x faster, but 320 threads per CTA leave room for
+// three CTAs per SM at 64 registers or two at 96 instead of four at 80, and the CTAs per SM are what
+// hides the step's latency).
+__host__ __device__ constexpr int decode_threads(int sg) { return 64 + 128 * sg; }
+__host__ __device__ constexpr int decode_min_ctas(int stages, int sg) {
+  return sg == 1 ? (stages <= 2 ? 4 : 2) : (stages <= 3 ? 3 : 2);
+}
+
+template <int GP, int TERMS, int STAGES, int PT, bool MX, int SG>
+__global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG))
     decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                   const DecodeParams p) {
   using Smem = DecodeSmem<GP, STAGES>;
   constexpr int KS = Smem::kStages;
-  constexpr int LD = GP;  // columns one tcgen05.ld brings (4, 8 or 16)
+  constexpr int R = GP / SG;   // query rows per softmax thread
+  constexpr int LD = R;        // columns one tcgen05.ld brings (4, 8 or 16)
+  constexpr int kThreads = decode_threads(SG);
+  constexpr int kSoftmaxThreads = 128 * SG;
+  static_assert(GP % SG == 0 && (R == 4 || R == 8 || R == 16), "rows per softmax thread");
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -401,7 +425,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   if (with_bf16) {
     const int64_t row_bytes = (int64_t)p.heads_kv * kHeadDim * 2;
     const int64_t head_offset = ((int64_t)slot * p.tail_slot_stride + kv_head * kHeadDim) * 2;
-    for (int i = tid; i < tail_len * 4; i += 192) {
+    for (int i = tid; i < tail_len * 4; i += kThreads) {
       const char* base = reinterpret_cast<const char*>((i & 2) ? p.tail_value : p.tail_key) + head_offset;
       prefetch_l2(base + (int64_t)(i >> 2) * row_bytes + (i & 1) * 128);
     }
@@ -416,11 +440,11 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     }
     for (int s = 0; s < 2; ++s) {
       tc::mbar_init(&sm.s_full[s], 1);
-      tc::mbar_init(&sm.s_empty[s], 128);
-      tc::mbar_init(&sm.p_full[s], 128);
+      tc::mbar_init(&sm.s_empty[s], kSoftmaxThreads);
+      tc::mbar_init(&sm.p_full[s], kSoftmaxThreads);
       tc::mbar_init(&sm.p_empty[s], 1);
       tc::mbar_init(&sm.o_full[s], 1);
-      tc::mbar_init(&sm.o_empty[s], 128);
+      tc::mbar_init(&sm.o_empty[s], kSoftmaxThreads);
     }
     sm.abort_flag = 0;
     tc::fence_barrier_init();
@@ -431,8 +455,8 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   {
     uint4* blocks[4] = {reinterpret_cast<uint4*>(sm.q_tile), reinterpret_cast<uint4*>(sm.p_tile),
                         reinterpret_cast<uint4*>(sm.q_sf), reinterpret_cast<uint4*>(sm.p_sf)};
-    for (int i = tid; i < 4 * 128; i += 192) blocks[i >> 7][i & 127] = make_uint4(0, 0, 0, 0);
-    for (int i = tid; i < GP * 32; i += 192) reinterpret_cast<uint4*>(sm.q_bf16)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < 4 * 128; i += kThreads) blocks[i >> 7][i & 127] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < GP * 32; i += kThreads) reinterpret_cast<uint4*>(sm.q_bf16)[i] = make_uint4(0, 0, 0, 0);
   }
   __syncthreads();
   // The first ring stages are requested before the rest of the set-up, which then overlaps the
@@ -507,7 +531,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
   dependents_may_launch();
   // Warps 1-5 fetch the query operands: one 16-byte chunk of query codes, one word of query
   // scales and up to two 16-byte chunks of the BF16 query per thread.
-  const int qt = tid - 32;
+  const int qt = tid < 192 ? tid - 32 : -1;  // the 160 threads behind warp 0
   const bool loads_codes = qt >= 0 && qt < TERMS * G * 4;
   // NVFP4: two words per query head and term (one per atom); MXFP4: one (a single atom)
   const bool loads_scales = qt >= 0 && qt < TERMS * G * (MX ? 1 : 2);
@@ -752,11 +776,14 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     // ---- softmax / accumulate -----------------------------------------------------------------
     const int warp_q = warp & 3;        // TMEM lane quarter this warp may read
     const int t = warp_q * 32 + lane;   // token (S^T lane) and channel (O^T lane) of this thread
-    const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
+    const int sgroup = (warp - 2) >> 2;  // softmax group of this warp
+    const int row0 = sgroup * R;         // first of the tile's rows this group owns
+    const int barrier = 1 + sgroup;      // the group's named barrier
+    const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16) + row0;
     const float shift = p.p_mode == BDFP4_P_AMAX2_OR_AMAX6_C8 ? 3.0f : 0.0f;
-    SoftmaxState<GP> st;
+    SoftmaxState<R> st;
 #pragma unroll
-    for (int j = 0; j < GP; ++j) {
+    for (int j = 0; j < R; ++j) {
       st.row_max[j] = -INFINITY;
       st.row_sum[j] = 0.0f;
       st.o_acc[j] = 0.0f;
@@ -770,27 +797,27 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     if (with_bf16) {
       // While page zero has not been sealed the rolling page still holds the sink's tokens.
       const int mask_below = total_pages == 0 ? sink_len : 0;
-      bf16_block<GP, STAGES>(st, sm, p, t, warp_q, lane, tail_k, tail_v, mask_below, tail_len, shift, red_buf);
+      bf16_block<R>(st, sm, p, t, warp_q, lane, tail_k, tail_v, mask_below, tail_len, shift, red_buf, row0, barrier);
     }
 
     // factor the sums accumulated before the previous step are multiplied by when its O^T is folded
     // in: 1 unless that step moved a maximum. Parked in shared memory with the other per-row values
     // when a thread carries eight or more rows; `grew_prev` then says whether to read it at all.
-    float acc_prev[GP];
+    float acc_prev[R];
 #pragma unroll
-    for (int j = 0; j < GP; ++j) acc_prev[j] = 1.0f;
+    for (int j = 0; j < R; ++j) acc_prev[j] = 1.0f;
     bool grew_prev = false;
     // Which row's group maximum this lane ends up holding after the reduce-scatter below: step i
     // hands the upper half of the rows still held to the lanes whose bit i is set.
-    constexpr int LOG = GP == 4 ? 2 : (GP == 8 ? 3 : 4);
+    constexpr int LOG = R == 4 ? 2 : (R == 8 ? 3 : 4);
     int own_row = 0;
 #pragma unroll
-    for (int i = 0; i < LOG; ++i) own_row += ((lane >> i) & 1) * (GP >> (i + 1));
+    for (int i = 0; i < LOG; ++i) own_row += ((lane >> i) & 1) * (R >> (i + 1));
     const float headroom = kRescaleThreshold / p.scale_log2;  // score growth the stale maximum tolerates
-    float threshold[GP];   // a score above this forces the running maximum to move
-    float max_scaled[GP];  // running maximum in log2 units with the c8 shift folded in
+    float threshold[R];   // a score above this forces the running maximum to move
+    float max_scaled[R];  // running maximum in log2 units with the c8 shift folded in
 #pragma unroll
-    for (int j = 0; j < GP; ++j) {
+    for (int j = 0; j < R; ++j) {
       const float safe = st.row_max[j] == -INFINITY ? 0.0f : st.row_max[j];
       max_scaled[j] = safe * p.scale_log2 - shift;
       threshold[j] = 0.0f;
@@ -799,35 +826,36 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
     // With eight or more rows per thread the three per-row arrays (24+ registers of values every
     // thread holds identically) are parked in shared memory for the page loop and read back as
     // broadcasts; they change only when a running maximum moves.
-    constexpr bool kStatsInSmem = GP >= 8;
+    constexpr bool kStatsInSmem = R >= 8 || SG > 1;
     auto refresh_thresholds = [&]() {
       own_max_scaled = max_scaled[0];
 #pragma unroll
-      for (int j = 0; j < GP; ++j) {
+      for (int j = 0; j < R; ++j) {
         threshold[j] = st.row_max[j] + headroom;
         own_max_scaled = own_row == j ? max_scaled[j] : own_max_scaled;
       }
       if constexpr (kStatsInSmem) {
         // every thread writes the same values; the barrier orders them before the next reads
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
-          sm.stat_row_max[j] = st.row_max[j];
-          sm.stat_threshold[j] = threshold[j];
-          sm.stat_max_scaled[j] = max_scaled[j];
+        for (int j = 0; j < R; ++j) {
+          sm.stat_row_max[row0 + j] = st.row_max[j];
+          sm.stat_threshold[row0 + j] = threshold[j];
+          sm.stat_max_scaled[row0 + j] = max_scaled[j];
         }
-        softmax_barrier();
+        softmax_barrier(barrier);
       }
     };
     refresh_thresholds();
     // constant parts of this thread's shared-memory addresses
     const int group = t >> 4;
-    const int sf_offset = (group >> 2) * 512 + own_row * 16 + (group & 3);
-    const bool stores_sf = (lane & 15) < GP;
-    // after the nibble transpose a lane of an 8-lane cluster holds one row's codes for 4 (GP = 4)
-    // or 8 (GP = 8) consecutive tokens
-    const int pack_row = GP == 4 ? (((lane & 1) << 1) | ((lane >> 1) & 1))
+    const int sf_offset = (group >> 2) * 512 + (row0 + own_row) * 16 + (group & 3);
+    const bool stores_sf = (lane & 15) < R;
+    // after the nibble transpose a lane of an 8-lane cluster holds one row's codes for 4 (R = 4)
+    // or 8 (R = 8) consecutive tokens
+    const int pack_row = R == 4 ? (((lane & 1) << 1) | ((lane >> 1) & 1))
                                  : (((lane & 1) << 2) | (lane & 2) | ((lane >> 2) & 1));
-    const int pack_offset = GP == 4 ? swizzle64(pack_row * 64 + (t >> 2) * 2) : swizzle64(pack_row * 64 + (t >> 3) * 4);
+    const int pack_offset = R == 4 ? swizzle64((row0 + pack_row) * 64 + (t >> 2) * 2)
+                                   : swizzle64((row0 + pack_row) * 64 + (t >> 3) * 4);
 
     // The sink is read last; its lines are sent toward L2 a few pages before the loop ends.
     auto prefetch_sink = [&]() {
@@ -846,40 +874,40 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       if (i == num_pages - 3) prefetch_sink();
       tc::mbar_wait(&sm.s_full[b], parity, abort_flag);
       tc::fence_after_sync();
-      float s[GP];
+      float s[R];
       tc::tmem_ld<LD>(lane_base + kColS + kNQ * b, s);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       tc::mbar_arrive(&sm.s_empty[b]);
       if (logical_page == 0 && t < sink_len) {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) s[j] = -INFINITY;
+        for (int j = 0; j < R; ++j) s[j] = -INFINITY;
       }
       // does any row's maximum have to move? one predicate per thread, one barrier-wide OR
       bool grows = true;
       if (!st.first) {
         bool own = *abort_flag != 0;
 #pragma unroll
-        for (int j = 0; j < GP; ++j) own = own || s[j] > (kStatsInSmem ? sm.stat_threshold[j] : threshold[j]);
-        grows = softmax_vote_any(own);
+        for (int j = 0; j < R; ++j) own = own || s[j] > (kStatsInSmem ? sm.stat_threshold[row0 + j] : threshold[j]);
+        grows = softmax_vote_any(own, barrier);
       }
-      float acc[GP];
+      float acc[R];
       // How a row's scale group is reduced. NVFP4 with up to eight rows: a reduce-scatter leaves each
       // lane with ONE row's 16-token group maximum. NVFP4 with sixteen rows: every lane keeps every
       // row's group maximum. MXFP4: the group is the warp's 32 tokens and is reduced where the
       // probabilities are quantized.
-      constexpr bool kScatter = !MX && GP <= 8;
-      constexpr bool kPerRow = !MX && GP > 8;
+      constexpr bool kScatter = !MX && R <= 8;
+      constexpr bool kPerRow = !MX && R > 8;
       float own_group_max;  // maximum of row `own_row` over this lane's 16-token scale group
       if constexpr (kScatter) {
-        // reduce-scatter: GP - 1 shuffles leave each lane with one row's maximum over GP lanes,
+        // reduce-scatter: R - 1 shuffles leave each lane with one row's maximum over R lanes,
         // the remaining butterfly steps finish that row's 16-lane group
-        float held[GP];
+        float held[R];
 #pragma unroll
-        for (int j = 0; j < GP; ++j) held[j] = s[j];
+        for (int j = 0; j < R; ++j) held[j] = s[j];
 #pragma unroll
         for (int step = 0; step < LOG; ++step) {
-          const int half = GP >> (step + 1);
+          const int half = R >> (step + 1);
           const bool upper = (lane >> step) & 1;
 #pragma unroll
           for (int k = 0; k < half; ++k) {
@@ -893,12 +921,12 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         for (int step = LOG; step < 4; ++step)
           own_group_max = fmaxf(own_group_max, __shfl_xor_sync(0xffffffffu, own_group_max, 1 << step));
       } else {
-        own_group_max = 0.0f;  // GP = 16 keeps every row's group maximum (below)
+        own_group_max = 0.0f;  // R = 16 keeps every row's group maximum (below)
       }
-      float group_max[GP];
+      float group_max[R];
       if constexpr (kPerRow) {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
+        for (int j = 0; j < R; ++j) {
           float m = s[j];
 #pragma unroll
           for (int step = 1; step < 16; step <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, step));
@@ -906,13 +934,13 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         }
       }
       if (grows) {
-        float block_max[GP];
+        float block_max[R];
         if constexpr (kScatter) {
           const float warp_max = fmaxf(own_group_max, __shfl_xor_sync(0xffffffffu, own_group_max, 16));
-          if (lane < GP) sm.red[red_buf][warp_q][own_row] = warp_max;
+          if (lane < R) sm.red[red_buf][warp_q][row0 + own_row] = warp_max;
         } else {
 #pragma unroll
-          for (int j = 0; j < GP; ++j) {
+          for (int j = 0; j < R; ++j) {
             if constexpr (kPerRow) {
               block_max[j] = fmaxf(group_max[j], __shfl_xor_sync(0xffffffffu, group_max[j], 16));
             } else {
@@ -922,49 +950,49 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
               block_max[j] = m;
             }
           }
-          if (lane < GP) {
+          if (lane < R) {
             float mine = block_max[0];
 #pragma unroll
-            for (int j = 1; j < GP; ++j) mine = lane == j ? block_max[j] : mine;
-            sm.red[red_buf][warp_q][lane] = mine;
+            for (int j = 1; j < R; ++j) mine = lane == j ? block_max[j] : mine;
+            sm.red[red_buf][warp_q][row0 + lane] = mine;
           }
         }
-        softmax_barrier();
+        softmax_barrier(barrier);
 #pragma unroll
-        for (int j = 0; j < GP; ++j)
-          block_max[j] = fmaxf(fmaxf(sm.red[red_buf][0][j], sm.red[red_buf][1][j]),
-                               fmaxf(sm.red[red_buf][2][j], sm.red[red_buf][3][j]));
+        for (int j = 0; j < R; ++j)
+          block_max[j] = fmaxf(fmaxf(sm.red[red_buf][0][row0 + j], sm.red[red_buf][1][row0 + j]),
+                               fmaxf(sm.red[red_buf][2][row0 + j], sm.red[red_buf][3][row0 + j]));
         red_buf ^= 1;
         if constexpr (kStatsInSmem) {
 #pragma unroll
-          for (int j = 0; j < GP; ++j) st.row_max[j] = sm.stat_row_max[j];
+          for (int j = 0; j < R; ++j) st.row_max[j] = sm.stat_row_max[row0 + j];
         }
-        update_max<GP>(st, block_max, p.scale_log2, shift, acc, max_scaled);
+        update_max<R>(st, block_max, p.scale_log2, shift, acc, max_scaled);
         if constexpr (kStatsInSmem) {
 #pragma unroll
-          for (int j = 0; j < GP; ++j) sm.stat_acc[i & 1][j] = acc[j];
+          for (int j = 0; j < R; ++j) sm.stat_acc[i & 1][row0 + j] = acc[j];
         }
         refresh_thresholds();
         stop = *abort_flag != 0;  // uniform: every thread reads it after the same barrier
 #pragma unroll
-        for (int j = 0; j < GP; ++j) st.row_sum[j] *= acc[j];
+        for (int j = 0; j < R; ++j) st.row_sum[j] *= acc[j];
       } else {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) acc[j] = 1.0f;
+        for (int j = 0; j < R; ++j) acc[j] = 1.0f;
       }
       st.first = false;
-      float prob[GP];
+      float prob[R];
 #pragma unroll
-      for (int j = 0; j < GP; ++j) {
-        prob[j] = ex2_approx(fmaf(s[j], p.scale_log2, -(kStatsInSmem ? sm.stat_max_scaled[j] : max_scaled[j])));
+      for (int j = 0; j < R; ++j) {
+        prob[j] = ex2_approx(fmaf(s[j], p.scale_log2, -(kStatsInSmem ? sm.stat_max_scaled[row0 + j] : max_scaled[j])));
         st.row_sum[j] += prob[j];
       }
       // ---- probabilities -> E2M1 codes on a per-group scale ---------------------------------------
       // First the scaling: prob[j] becomes p / scale of its group, and the group's scale byte is
       // known to the lane that will store it.
       float own_scale = 0.0f;       // kScatter: scale of row `own_row` over this lane's 16-token group
-      float group_scale[GP];        // kPerRow: every row's group scale
-      int mx_exponent[GP];          // MX: every row's E8M0 exponent for this warp's 32 tokens
+      float group_scale[R];        // kPerRow: every row's group scale
+      int mx_exponent[R];          // MX: every row's E8M0 exponent for this warp's 32 tokens
       if constexpr (MX) {
         // The MXFP4 probability operand (src/nvfp4_decode_kernel/reference.py:331-355,
         // fp4_decode_kernel.py:5687-5731): start from the smallest exponent that keeps the group's
@@ -972,7 +1000,7 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         // (sum of errors)^2 / 32 + (sum of squared errors), both sums formed by the warp's butterfly
         // and combined by one FMA.
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
+        for (int j = 0; j < R; ++j) {
           const float value = prob[j];
           const float maximum = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(value)));
           const int upper = mx_round_up_exponent(maximum);
@@ -1001,9 +1029,9 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         const float maximum = ex2_approx(fmaf(own_group_max, p.scale_log2, -own_max_scaled));
         own_scale = probability_scale(maximum, p.p_mode, p.tau);
         const float own_inverse = rcp_approx(fmaxf(own_scale, 1e-20f));
-        const int cluster = lane & ~(GP - 1);
+        const int cluster = lane & ~(R - 1);
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
+        for (int j = 0; j < R; ++j) {
           int source = 0;  // the lane pattern whose own_row is j (bit reversal of j)
 #pragma unroll
           for (int bit = 0; bit < LOG; ++bit) source |= ((j >> (LOG - 1 - bit)) & 1) << bit;
@@ -1011,26 +1039,26 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
+        for (int j = 0; j < R; ++j) {
           const float maximum =
-              ex2_approx(fmaf(group_max[j], p.scale_log2, -(kStatsInSmem ? sm.stat_max_scaled[j] : max_scaled[j])));
+              ex2_approx(fmaf(group_max[j], p.scale_log2, -(kStatsInSmem ? sm.stat_max_scaled[row0 + j] : max_scaled[j])));
           group_scale[j] = probability_scale(maximum, p.p_mode, p.tau);
           prob[j] *= rcp_approx(fmaxf(group_scale[j], 1e-20f));
         }
       }
       // Then the codes into the PV MMA's B operand (rows = query heads, 64 bytes of tokens each).
-      if constexpr (GP <= 8) {
+      if constexpr (R <= 8) {
         // E2M1 codes of this token: one byte per pair of rows, then a nibble transpose across the
         // lanes of an 8-token cluster so that each lane stores one row's run of tokens
         uint32_t codes = 0;
 #pragma unroll
-        for (int j = 0; j < GP; j += 2) codes |= cvt_e2m1x2(prob[j], prob[j + 1]) << (4 * j);
+        for (int j = 0; j < R; j += 2) codes |= cvt_e2m1x2(prob[j], prob[j + 1]) << (4 * j);
         {
           const uint32_t other = __shfl_xor_sync(0xffffffffu, codes, 1);
           const bool odd = lane & 1;
-          const uint32_t even_token = (odd ? other : codes) >> (odd ? 2 * GP : 0);  // rows this lane keeps
-          const uint32_t odd_token = (odd ? codes : other) >> (odd ? 2 * GP : 0);
-          if constexpr (GP == 4) {
+          const uint32_t even_token = (odd ? other : codes) >> (odd ? 2 * R : 0);  // rows this lane keeps
+          const uint32_t odd_token = (odd ? codes : other) >> (odd ? 2 * R : 0);
+          if constexpr (R == 4) {
             codes = (even_token & 0xfu) | ((odd_token & 0xfu) << 4) | ((even_token & 0xf0u) << 4) |
                     ((odd_token & 0xf0u) << 8);
           } else {
@@ -1042,27 +1070,27 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         {
           const uint32_t other = __shfl_xor_sync(0xffffffffu, codes, 2);
           const bool upper = lane & 2;
-          if constexpr (GP == 4) {
+          if constexpr (R == 4) {
             codes = __byte_perm(codes, other, upper ? 0x0015 : 0x0040);
           } else {
             codes = __byte_perm(codes, other, upper ? 0x3726 : 0x5140);
           }
         }
-        if constexpr (GP == 8) {
+        if constexpr (R == 8) {
           const uint32_t other = __shfl_xor_sync(0xffffffffu, codes, 4);
           codes = __byte_perm(codes, other, (lane & 4) ? 0x3276 : 0x5410);
         }
         // the PV MMA of two pages ago must be done with this P buffer
         tc::mbar_wait(&sm.p_empty[b], parity ^ 1, abort_flag);
-        if constexpr (GP == 4) {
+        if constexpr (R == 4) {
           *reinterpret_cast<uint16_t*>(sm.p_tile[b] + pack_offset) = (uint16_t)codes;
         } else {
           *reinterpret_cast<uint32_t*>(sm.p_tile[b] + pack_offset) = codes;
         }
       } else {
-        uint32_t words[GP];
+        uint32_t words[R];
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
+        for (int j = 0; j < R; ++j) {
           uint32_t word = (cvt_e2m1x2(prob[j], 0.0f) & 0xfu) << (4 * (lane & 7));
           word |= __shfl_xor_sync(0xffffffffu, word, 1);
           word |= __shfl_xor_sync(0xffffffffu, word, 2);
@@ -1071,27 +1099,27 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         }
         tc::mbar_wait(&sm.p_empty[b], parity ^ 1, abort_flag);
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
+        for (int j = 0; j < R; ++j) {
           if ((lane & 7) == (j & 7))
-            *reinterpret_cast<uint32_t*>(sm.p_tile[b] + swizzle64(j * 64 + (t >> 3) * 4)) = words[j];
+            *reinterpret_cast<uint32_t*>(sm.p_tile[b] + swizzle64((row0 + j) * 64 + (t >> 3) * 4)) = words[j];
         }
       }
       // And the scale bytes into the operand's scale atom: (row r, group g) at r * 16 + g, the
       // second atom of an NVFP4 step 512 bytes on.
       if constexpr (MX) {
-        if (lane < GP) {
+        if (lane < R) {
           int mine = mx_exponent[0];
 #pragma unroll
-          for (int j = 1; j < GP; ++j) mine = lane == j ? mx_exponent[j] : mine;
-          sm.p_sf[b][lane * 16 + warp_q] = (uint8_t)(mine + 127);
+          for (int j = 1; j < R; ++j) mine = lane == j ? mx_exponent[j] : mine;
+          sm.p_sf[b][(row0 + lane) * 16 + warp_q] = (uint8_t)(mine + 127);
         }
       } else if constexpr (kScatter) {
         if (stores_sf) sm.p_sf[b][sf_offset] = (uint8_t)cvt_e4m3(own_scale);
       } else {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
+        for (int j = 0; j < R; ++j) {
           if ((lane & 15) == j)
-            sm.p_sf[b][(group >> 2) * 512 + j * 16 + (group & 3)] = (uint8_t)cvt_e4m3(group_scale[j]);
+            sm.p_sf[b][(group >> 2) * 512 + (row0 + j) * 16 + (group & 3)] = (uint8_t)cvt_e4m3(group_scale[j]);
         }
       }
       tc::fence_proxy_async_smem();
@@ -1109,26 +1137,26 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
         if constexpr (kStatsInSmem) {
           if (grew_prev) {
 #pragma unroll
-            for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], sm.stat_acc[(i - 1) & 1][j], o[j]);
+            for (int j = 0; j < R; ++j) st.o_acc[j] = fmaf(st.o_acc[j], sm.stat_acc[(i - 1) & 1][row0 + j], o[j]);
           } else {
 #pragma unroll
-            for (int j = 0; j < GP; ++j) st.o_acc[j] += o[j];  // == fma(o_acc, 1, o)
+            for (int j = 0; j < R; ++j) st.o_acc[j] += o[j];  // == fma(o_acc, 1, o)
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < GP; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
+          for (int j = 0; j < R; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
         }
       }
       if constexpr (kStatsInSmem) {
         grew_prev = grows;
       } else {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) acc_prev[j] = acc[j];
+        for (int j = 0; j < R; ++j) acc_prev[j] = acc[j];
       }
     }
     if constexpr (kStatsInSmem) {
 #pragma unroll
-      for (int j = 0; j < GP; ++j) st.row_max[j] = sm.stat_row_max[j];
+      for (int j = 0; j < R; ++j) st.row_max[j] = sm.stat_row_max[row0 + j];
     }
     if (num_pages > 0) {
       const int pb = (num_pages - 1) & 1;
@@ -1139,42 +1167,42 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       tc::tmem_wait_ld();
       tc::fence_before_sync();
 #pragma unroll
-      for (int j = 0; j < GP; ++j) {
-        const float factor = kStatsInSmem ? (grew_prev ? sm.stat_acc[(num_pages - 1) & 1][j] : 1.0f) : acc_prev[j];
+      for (int j = 0; j < R; ++j) {
+        const float factor = kStatsInSmem ? (grew_prev ? sm.stat_acc[(num_pages - 1) & 1][row0 + j] : 1.0f) : acc_prev[j];
         st.o_acc[j] = fmaf(st.o_acc[j], factor, o[j]);
       }
     }
     if (with_bf16 && p.seqused_sink) {
-      bf16_block<GP, STAGES>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,
-                     tail_v + (int64_t)kPage * row_elems, 0, sink_len, shift, red_buf);
+      bf16_block<R>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,
+                    tail_v + (int64_t)kPage * row_elems, 0, sink_len, shift, red_buf, row0, barrier);
     }
 
     // ---- normalise and write ------------------------------------------------------------------
-    float total[GP];
+    float total[R];
 #pragma unroll
-    for (int j = 0; j < GP; ++j) {
+    for (int j = 0; j < R; ++j) {
       float v = st.row_sum[j];
 #pragma unroll
       for (int step = 1; step < 32; step <<= 1) v += __shfl_xor_sync(0xffffffffu, v, step);
       total[j] = v;
     }
-    if (lane < GP) {
+    if (lane < R) {
       float mine = total[0];
 #pragma unroll
-      for (int j = 1; j < GP; ++j) mine = lane == j ? total[j] : mine;
-      sm.sum_red[warp_q][lane] = mine;
+      for (int j = 1; j < R; ++j) mine = lane == j ? total[j] : mine;
+      sm.sum_red[warp_q][row0 + lane] = mine;
     }
-    softmax_barrier();
+    softmax_barrier(barrier);
 #pragma unroll
-    for (int j = 0; j < GP; ++j)
-      total[j] = (sm.sum_red[0][j] + sm.sum_red[1][j]) + (sm.sum_red[2][j] + sm.sum_red[3][j]);
+    for (int j = 0; j < R; ++j)
+      total[j] = (sm.sum_red[0][row0 + j] + sm.sum_red[1][row0 + j]) + (sm.sum_red[2][row0 + j] + sm.sum_red[3][row0 + j]);
     const bool skip = p.num_splits > 1 && part == p.num_splits && p.tail_key == nullptr;
 #pragma unroll
-    for (int j = 0; j < GP; ++j) {
-      if (j < G) {
+    for (int j = 0; j < R; ++j) {
+      if (row0 + j < G) {
         const bool empty = skip || total[j] == 0.0f || total[j] != total[j];
         const float value = empty ? 0.0f : st.o_acc[j] * (1.0f / total[j]) * p.out_scale;
-        const int head = kv_head * G + j;
+        const int head = kv_head * G + row0 + j;
         if (p.out != nullptr) {
           p.out[(int64_t)row * p.out_row_stride + head * kHeadDim + t] = __float2bfloat16_rn(value);
         } else {
@@ -1193,17 +1221,19 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
       // counter; the part that draws the last ticket reads all of them back (from L2) and writes
       // the BF16 output exactly as the separate merge kernel would, in part order, and leaves the
       // counter at zero for the next launch (src/nvfp4_decode_kernel/split_k_combine.py:47-83).
+      // (every softmax group of the CTA must have published before the ticket is drawn: barrier 15
+      // spans all of them)
       __threadfence();
-      softmax_barrier();
+      all_softmax_barrier<kSoftmaxThreads>();
       const int tile = row * p.heads_kv + kv_head;
-      if (t == 0) sm.merge_last = atomicAdd(&p.merge_counters[tile], 1) == p.parts - 1;
-      softmax_barrier();
+      if (t == 0 && sgroup == 0) sm.merge_last = atomicAdd(&p.merge_counters[tile], 1) == p.parts - 1;
+      all_softmax_barrier<kSoftmaxThreads>();
       if (sm.merge_last) {
         __threadfence();
-        if (t == 0) p.merge_counters[tile] = 0;
+        if (t == 0 && sgroup == 0) p.merge_counters[tile] = 0;
         constexpr float kLog2e = 1.4426950408889634f;
         const int64_t lse_stride = (int64_t)p.rows * p.heads_q;
-        for (int j = 0; j < G; ++j) {
+        for (int j = row0; j < min(row0 + R, G); ++j) {  // each group merges the heads it owns
           const int head = kv_head * G + j;
           const float* lse = p.partial_lse + (int64_t)row * p.heads_q + head;
           const float* values = p.partial_out + ((int64_t)row * p.heads_q + head) * kHeadDim + t;
@@ -1236,14 +1266,14 @@ __global__ void __launch_bounds__(192, STAGES <= 2 ? 4 : 2)
 
 // ---- launch ----------------------------------------------------------------------------------
 
-template <int GP, int TERMS, int STAGES, int PT, bool MX>
+template <int GP, int TERMS, int STAGES, int PT, bool MX, int SG = 1>
 static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
                                         cudaStream_t stream) {
   const int smem = (int)sizeof(DecodeSmem<GP, STAGES>) + 1024;
   static PerDeviceOnce configured;
   const int slot = current_device_slot();
   if (slot < 0 || !configured.done[slot]) {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS, STAGES, PT, MX>,
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<GP, TERMS, STAGES, PT, MX, SG>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     if (slot >= 0) configured.done[slot] = true;
@@ -1257,12 +1287,12 @@ static cudaError_t launch_decode_staged(const CUtensorMap& k_map, const CUtensor
   attribute.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(grid);
-  config.blockDim = dim3(192);
+  config.blockDim = dim3(decode_threads(SG));
   config.dynamicSmemBytes = smem;
   config.stream = stream;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, decode_kernel<GP, TERMS, STAGES, PT, MX>, k_map, v_map, p);
+  return cudaLaunchKernelEx(&config, decode_kernel<GP, TERMS, STAGES, PT, MX, SG>, k_map, v_map, p);
 }
 
 // Ring depth follows the grid: a launch with more than two CTAs per SM is given two K and two V
