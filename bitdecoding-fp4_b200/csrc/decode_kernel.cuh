@@ -33,9 +33,9 @@ constexpr int kStageBytes = 8192 + 1024;  // codes + scales of one K or V page-h
 constexpr int kNP = 16;                   // N of the PV MMA (query rows, padded)
 constexpr float kRescaleThreshold = 8.0f;  // src/nvfp4_decode_kernel/fp4_decode_kernel.py:93
 
-// TMEM column map (32-bit columns): two S^T stages and two O^T stages of 16 columns, then the
-// scale-factor blocks, 8 columns (two 4-column atoms) each: Q term 0, Q term 1, K x2, V x2, P x2.
-// 128 columns in all, so four CTAs share an SM's 512.
+// TMEM column map (32-bit columns): two S^T stages of 16 columns, the O^T sum (16 columns, 16 spare),
+// then the scale-factor blocks, 8 columns (two 4-column atoms) each: Q term 0, Q term 1, K x2, V x2,
+// P x2. 128 columns in all, so four CTAs share an SM's 512.
 constexpr int kNQ = 16;  // N of the QK MMA (query heads of one KV head, padded)
 constexpr int kColS = 0;
 constexpr int kColO = 32;
@@ -62,10 +62,10 @@ struct DecodeSmem {
   // the rows' running maxima and the two values derived from them: identical in every softmax
   // thread, so with eight or more rows per thread they live here instead of in registers
   float stat_row_max[GP], stat_threshold[GP], stat_max_scaled[GP];
-  float stat_acc[2][GP];  // rescale factors of the last two steps that moved a maximum
   uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   uint64_t ksf_full[kStages];  // K scale blocks of 64-token pages, which arrive ahead of the codes
-  uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2];
+  uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2];
+  int pv_fresh[2];  // per P buffer: 1 when its PV product starts a new sum in tensor memory, 0 when it adds
   int page_ids[2][32];  // physical pages of the producer's current batch of steps
   uint32_t tmem_base;
   int abort_flag;
@@ -363,6 +363,9 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
   constexpr int kThreads = decode_threads(SG);
   constexpr int kSoftmaxThreads = 128 * SG;
   static_assert(GP % SG == 0 && (R == 4 || R == 8 || R == 16), "rows per softmax thread");
+  // one PV product covers all GP rows, so whether it starts a new sum is one decision per step:
+  // softmax groups deciding separately about their own rows would need a product each
+  static_assert(SG == 1, "the tensor-memory O^T sum needs one softmax group");
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -444,7 +447,6 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
       tc::mbar_init(&sm.p_full[s], kSoftmaxThreads);
       tc::mbar_init(&sm.p_empty[s], 1);
       tc::mbar_init(&sm.o_full[s], 1);
-      tc::mbar_init(&sm.o_empty[s], kSoftmaxThreads);
     }
     sm.abort_flag = 0;
     tc::fence_barrier_init();
@@ -696,15 +698,17 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
           tc::cp_sf_atom(tmem + kColSFV + 8 * b + 4, tc::sf_atom_desc(v_addr + 8192 + 512));
           tc::cp_sf_atom(tmem + kColSFP + 8 * b + 4, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b]) + 512));
         }
-        if (!tc::mbar_wait(&sm.o_empty[b], pair_parity ^ 1, abort_flag)) return false;
-        tc::fence_after_sync();
+        // O^T keeps adding up in tensor memory over the steps that share their running maxima; the
+        // softmax threads say (before they release the P buffer) when a step starts a new sum,
+        // having read the old one back first
+        const bool fresh = *reinterpret_cast<volatile int*>(&sm.pv_fresh[b]) != 0;
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           // 128-token page: one tile of 64-byte rows, K step k at +32 bytes. 64-token pages: one
           // tile of 32-byte rows per page.
           const uint64_t v_desc = PT == 128 ? tc::fp4_tile_desc(v_addr, k) : tc::fp4_half_tile_desc(v_addr + k * 4096);
-          block_mma(tmem + kColO + 16 * b, v_desc, tc::fp4_tile_desc(p_addr, k), idesc_pv, tmem + kColSFV + 8 * b,
-                    tmem + kColSFP + 8 * b, k, k != 0);
+          block_mma(tmem + kColO, v_desc, tc::fp4_tile_desc(p_addr, k), idesc_pv, tmem + kColSFV + 8 * b,
+                    tmem + kColSFP + 8 * b, k, k != 0 || !fresh);
         }
         tc::commit(&sm.o_full[b]);
         tc::commit(&sm.v_empty[s]);
@@ -800,13 +804,10 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
       bf16_block<R>(st, sm, p, t, warp_q, lane, tail_k, tail_v, mask_below, tail_len, shift, red_buf, row0, barrier);
     }
 
-    // factor the sums accumulated before the previous step are multiplied by when its O^T is folded
-    // in: 1 unless that step moved a maximum. Parked in shared memory with the other per-row values
-    // when a thread carries eight or more rows; `grew_prev` then says whether to read it at all.
-    float acc_prev[R];
-#pragma unroll
-    for (int j = 0; j < R; ++j) acc_prev[j] = 1.0f;
-    bool grew_prev = false;
+    // O^T of the FP4 pages adds up in tensor memory, one PV product per step on top of the last. It is
+    // read back only when a running maximum moves (rare under the stale-maximum rule): the sum so far
+    // then joins `o_acc`, everything is rescaled, and the next product starts a new sum.
+    int sum_begin = 0;  // first step of the sum tensor memory currently holds
     // Which row's group maximum this lane ends up holding after the reduce-scatter below: step i
     // hands the upper half of the rows still held to the lanes whose bit i is set.
     constexpr int LOG = R == 4 ? 2 : (R == 8 ? 3 : 4);
@@ -968,17 +969,26 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
           for (int j = 0; j < R; ++j) st.row_max[j] = sm.stat_row_max[row0 + j];
         }
         update_max<R>(st, block_max, p.scale_log2, shift, acc, max_scaled);
-        if constexpr (kStatsInSmem) {
-#pragma unroll
-          for (int j = 0; j < R; ++j) sm.stat_acc[i & 1][row0 + j] = acc[j];
-        }
         refresh_thresholds();
         stop = *abort_flag != 0;  // uniform: every thread reads it after the same barrier
+        if (i > sum_begin) {
+          // the products of steps [sum_begin, i) are issued; the last of them reports on o_full
+          const int pb = (i - 1) & 1;
+          tc::mbar_wait(&sm.o_full[pb], ((i - 1) >> 1) & 1, abort_flag);
+          tc::fence_after_sync();
+          float o[LD];
+          tc::tmem_ld<LD>(lane_base + kColO, o);
+          tc::tmem_wait_ld();
+          tc::fence_before_sync();
 #pragma unroll
-        for (int j = 0; j < R; ++j) st.row_sum[j] *= acc[j];
-      } else {
+          for (int j = 0; j < R; ++j) st.o_acc[j] += o[j];
+        }
+        sum_begin = i;
 #pragma unroll
-        for (int j = 0; j < R; ++j) acc[j] = 1.0f;
+        for (int j = 0; j < R; ++j) {
+          st.o_acc[j] *= acc[j];
+          st.row_sum[j] *= acc[j];
+        }
       }
       st.first = false;
       float prob[R];
@@ -1122,37 +1132,10 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
             sm.p_sf[b][(group >> 2) * 512 + (row0 + j) * 16 + (group & 3)] = (uint8_t)cvt_e4m3(group_scale[j]);
         }
       }
+      if (t == 0) sm.pv_fresh[b] = (grows || i == 0) ? 1 : 0;  // the CTA's first product always starts the sum
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(&sm.p_full[b]);
 
-      if (i > 0) {  // fold in the previous page's O^T
-        const int pb = (i - 1) & 1;
-        tc::mbar_wait(&sm.o_full[pb], ((i - 1) >> 1) & 1, abort_flag);
-        tc::fence_after_sync();
-        float o[LD];
-        tc::tmem_ld<LD>(lane_base + kColO + 16 * pb, o);
-        tc::tmem_wait_ld();
-        tc::fence_before_sync();
-        tc::mbar_arrive(&sm.o_empty[pb]);
-        if constexpr (kStatsInSmem) {
-          if (grew_prev) {
-#pragma unroll
-            for (int j = 0; j < R; ++j) st.o_acc[j] = fmaf(st.o_acc[j], sm.stat_acc[(i - 1) & 1][row0 + j], o[j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < R; ++j) st.o_acc[j] += o[j];  // == fma(o_acc, 1, o)
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < R; ++j) st.o_acc[j] = fmaf(st.o_acc[j], acc_prev[j], o[j]);
-        }
-      }
-      if constexpr (kStatsInSmem) {
-        grew_prev = grows;
-      } else {
-#pragma unroll
-        for (int j = 0; j < R; ++j) acc_prev[j] = acc[j];
-      }
     }
     if constexpr (kStatsInSmem) {
 #pragma unroll
@@ -1163,14 +1146,11 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
       tc::mbar_wait(&sm.o_full[pb], ((num_pages - 1) >> 1) & 1, abort_flag);
       tc::fence_after_sync();
       float o[LD];
-      tc::tmem_ld<LD>(lane_base + kColO + 16 * pb, o);
+      tc::tmem_ld<LD>(lane_base + kColO, o);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
 #pragma unroll
-      for (int j = 0; j < R; ++j) {
-        const float factor = kStatsInSmem ? (grew_prev ? sm.stat_acc[(num_pages - 1) & 1][row0 + j] : 1.0f) : acc_prev[j];
-        st.o_acc[j] = fmaf(st.o_acc[j], factor, o[j]);
-      }
+      for (int j = 0; j < R; ++j) st.o_acc[j] += o[j];  // the sum since the last move of a maximum
     }
     if (with_bf16 && p.seqused_sink) {
       bf16_block<R>(st, sm, p, t, warp_q, lane, tail_k + (int64_t)kPage * row_elems,

@@ -1,22 +1,31 @@
-"""Calibrate static key smoothing, and optionally the probability threshold, before serving
-(src/nvfp4_vllm/calibrate.py of OpenBitSys/BitDecoding-FP4).
+"""Measuring what the cache's quantizer is calibrated with: the key-smoothing mean and, optionally,
+the probability threshold tau. Both come out of ONE long prefill that runs before serving.
 
-Text the model itself generates is tiled across the context window, so that post-RoPE keys are
-sampled at representative positions; subtracting their per-(layer, head, channel) mean lowers the
-quantization error of K and leaves softmax unchanged. The measurement runs inside each worker
-(named ``collective_rpc`` methods), which also writes the sidecar, so no tensor travels through
-the engine client. It must finish before serving: every cached key has to see the same mean.
+Why a prefill of the model's own text: the key mean is taken after RoPE, so it depends on position,
+and a prompt that spans the context window visits the positions serving will see. Eight short
+instructions are completed by the model, the completions are tiled up to the window, and that prompt
+is prefilled once while every attention layer adds its keys to an FP64 sum on the GPU
+(``bdfp4_key_channel_sums``). Subtracting the resulting per-(layer, head, channel) mean from every
+key leaves softmax unchanged (a constant per query) and lowers K's quantization error.
+
+Who does what. The driver process (:func:`calibrate_key_shift`) only sequences the steps and checks
+that the workers agree; the tensors never leave the workers. Each worker exposes the steps as named
+methods (:class:`NVFP4WorkerExtension`, mixed into vLLM's worker through ``worker_extension_cls``),
+and the worker that is rank 0 of its tensor-parallel group writes the sidecar.
+
+Drop-in surface, kept from src/nvfp4_vllm/calibrate.py of OpenBitSys/BitDecoding-FP4:
+``WORKER_EXTENSION_CLS``, the ``nvfp4_*`` method names and their return values,
+``calibrate_key_shift`` / ``set_key_shift_enabled`` and the keys of the summary they return.
 """
 
 from __future__ import annotations
 
 from collections import Counter
-from typing import Any
+from dataclasses import dataclass
+from typing import Any, Iterator
 
 import torch
 
-# vLLM mixes this class into its worker; an engine that is to calibrate is built with
-# worker_extension_cls="nvfp4_vllm.calibrate.NVFP4WorkerExtension" (build_llm does).
 WORKER_EXTENSION_CLS = "nvfp4_vllm.calibrate.NVFP4WorkerExtension"
 
 # Short, varied instructions; the model's own continuations of them are what gets tiled.
@@ -34,124 +43,177 @@ TOKENS_PER_SEED = 256
 CONTEXT_TOKENS = 32_768  # positions the calibration prompt spans, clamped to the engine's window
 
 
-def _runtimes(model: torch.nn.Module) -> list[Any]:
-    """The distinct ``LayerRuntime`` objects the model's NVFP4 attention layers share."""
+# ---------------------------------------------------------------------------------------------
+# worker side
+# ---------------------------------------------------------------------------------------------
+
+def _layer_runtimes(model: torch.nn.Module) -> Iterator[Any]:
+    """Each ``LayerRuntime`` behind the model's NVFP4 attention layers, once (layers share them)."""
     from .impl import NVFP4Impl
 
-    found: list[Any] = []
+    yielded: set[int] = set()
     for module in model.modules():
         impl = getattr(module, "impl", None)
-        runtime = getattr(impl, "runtime", None)
-        if isinstance(impl, NVFP4Impl) and runtime is not None and all(runtime is not other for other in found):
-            found.append(runtime)
-    return found
+        runtime = getattr(impl, "runtime", None) if isinstance(impl, NVFP4Impl) else None
+        if runtime is not None and id(runtime) not in yielded:
+            yielded.add(id(runtime))
+            yield runtime
+
+
+def _whole_model_shift(shift: torch.Tensor, tokens: int, total_kv_heads: int) -> tuple[torch.Tensor, bool]:
+    """(the mean over all KV heads of the model, whether this worker is the one that writes it).
+
+    A tensor-parallel worker holds a contiguous slice of the KV heads. The sidecar stores the model's
+    heads in their original order, which is the ranks' slices side by side, and the loader cuts the
+    same slices out again; so the export is an all-gather along the head axis, written by rank 0.
+    Ranks must have measured the same tokens, or the slices would be means of different things."""
+    if not torch.distributed.is_initialized():
+        return shift, True
+    from vllm.distributed import get_tp_group
+
+    group = get_tp_group()
+    if group.world_size == 1:
+        return shift, True
+    if shift.shape[1] * group.world_size != total_kv_heads:
+        raise ValueError("key-shift export requires unreplicated, evenly partitioned KV heads")
+    seen = group.all_gather(torch.tensor([tokens], dtype=torch.int64, device=shift.device), dim=0)
+    if int(seen.min()) != tokens or int(seen.max()) != tokens:
+        raise ValueError("TP workers disagree on key-shift measurement token counts")
+    return group.all_gather(shift, dim=1), group.rank_in_group == 0
 
 
 class NVFP4WorkerExtension:
-    """Named RPC methods for calibration and cache inspection; workers keep the tensors and return
-    summaries."""
+    """The calibration steps as worker methods. A method acts on every runtime of the worker's model
+    and returns something small: a count, a flag or a summary."""
 
+    # -- inspection ---------------------------------------------------------------------------
     def nvfp4_layer_cache_contract(self) -> dict[str, dict[str, int]]:
-        """What every loaded attention layer reports as its cache dtype and backend."""
-        dtypes, backends = Counter(), Counter()
+        """Histogram of the cache dtype and attention backend the loaded layers report."""
+        dtypes: Counter = Counter()
+        backends: Counter = Counter()
         for module in self.get_model().modules():
-            dtype = getattr(module, "kv_cache_dtype", None)
-            backend = getattr(module, "attn_backend", None)
-            if dtype is None or backend is None:
-                continue
-            dtypes[str(dtype)] += 1
-            backends[str(backend.get_name())] += 1
+            if hasattr(module, "kv_cache_dtype") and hasattr(module, "attn_backend"):
+                dtype, backend = module.kv_cache_dtype, module.attn_backend
+                if dtype is not None and backend is not None:
+                    dtypes[str(dtype)] += 1
+                    backends[str(backend.get_name())] += 1
         return {"layer_cache_dtype_counts": dict(dtypes), "layer_attention_backend_counts": dict(backends)}
 
     def nvfp4_key_shift_is_active(self) -> bool:
-        return all(runtime.active_key_shift is not None for runtime in _runtimes(self.get_model()))
+        return all(runtime.active_key_shift is not None for runtime in _layer_runtimes(self.get_model()))
+
+    # -- key smoothing ------------------------------------------------------------------------
+    def _for_each_runtime(self, action) -> int:
+        count = 0
+        for runtime in _layer_runtimes(self.get_model()):
+            action(runtime)
+            count += 1
+        return count
 
     def nvfp4_set_key_shift_enabled(self, enabled: bool) -> int:
-        runtimes = _runtimes(self.get_model())
-        for runtime in runtimes:
-            runtime.set_key_shift_enabled(enabled)
-        return len(runtimes)
+        return self._for_each_runtime(lambda runtime: runtime.set_key_shift_enabled(enabled))
 
     def nvfp4_begin_key_shift_measurement(self) -> int:
-        runtimes = _runtimes(self.get_model())
-        for runtime in runtimes:
-            runtime.begin_key_shift_measurement()
-        return len(runtimes)
+        return self._for_each_runtime(lambda runtime: runtime.begin_key_shift_measurement())
 
+    def nvfp4_finish_key_shift_measurement(self, save_to: str | None = None) -> dict[str, Any] | None:
+        """Close the measurement on every runtime, switch the mean on, optionally write the sidecar.
+        Returns None on a worker whose model has no NVFP4 layer."""
+        runtimes = list(_layer_runtimes(self.get_model()))
+        if not runtimes:
+            return None
+        tokens = int(runtimes[0].key_shift_tokens)
+        shifts = [runtime.finish_key_shift_measurement() for runtime in runtimes]
+        shift = shifts[0]
+        if save_to is not None:
+            total_heads = self.vllm_config.model_config.get_total_num_kv_heads()
+            shift, is_writer = _whole_model_shift(shift, tokens, total_heads)
+            if is_writer:
+                from safetensors.torch import save_file
+
+                save_file({"key_shift": shift.cpu()}, save_to, metadata={"schema": "1", "source": "calibrate_key_shift"})
+        return {"tokens": tokens, "shape": list(shift.shape), "mean_abs": float(shift.abs().mean()),
+                "saved_to": save_to}
+
+    # -- probability threshold ----------------------------------------------------------------
     def nvfp4_begin_probability_calibration(self, tokens: int, multiplier: float, samples: int) -> None:
         from .probability_calibration import ProbabilityCalibration
 
-        if hasattr(self, "_probability_calibration"):
+        if getattr(self, "_probability_calibration", None) is not None:
             raise RuntimeError("probability calibration is already active")
         collector = ProbabilityCalibration(tokens, multiplier, samples)
         collector.install(self.get_model())
         self._probability_calibration = collector
 
     def nvfp4_end_probability_calibration(self, complete: bool = True) -> list[dict] | None:
-        collector = self._probability_calibration
+        """Unhook the collector; hand back its samples unless the prefill was abandoned."""
+        collector, self._probability_calibration = self._probability_calibration, None
         try:
             return collector.finish() if complete else None
         finally:
             collector.close()
-            del self._probability_calibration
 
-    def nvfp4_finish_key_shift_measurement(self, save_to: str | None = None) -> dict[str, Any] | None:
-        runtimes = _runtimes(self.get_model())
-        if not runtimes:
-            return None
-        tokens = runtimes[0].key_shift_tokens
-        shift = runtimes[0].finish_key_shift_measurement()
-        for other in runtimes[1:]:
-            other.finish_key_shift_measurement()
-        if save_to is not None:
-            shift, writes = self._gather_for_export(shift, tokens)
-            if writes:
-                from safetensors.torch import save_file
 
-                save_file({"key_shift": shift.cpu()}, save_to,
-                          metadata={"schema": "1", "source": "calibrate_key_shift"})
-        return {"tokens": int(tokens), "shape": list(shift.shape), "mean_abs": float(shift.abs().mean()),
-                "saved_to": save_to}
-
-    def _gather_for_export(self, shift: torch.Tensor, tokens: int) -> tuple[torch.Tensor, bool]:
-        """The full-model mean (KV heads of all tensor-parallel ranks, in rank order) and whether
-        this worker writes the sidecar: rank 0 of the group, or the only worker."""
-        if not torch.distributed.is_initialized():
-            return shift, True
-        from vllm.distributed import get_tp_group
-
-        group = get_tp_group()
-        if group.world_size == 1:
-            return shift, True
-        total_heads = self.vllm_config.model_config.get_total_num_kv_heads()
-        if total_heads != shift.shape[1] * group.world_size:
-            raise ValueError("key-shift export requires unreplicated, evenly partitioned KV heads")
-        counts = group.all_gather(torch.tensor([tokens], dtype=torch.int64, device=shift.device), dim=0)
-        if not bool((counts == tokens).all()):
-            raise ValueError("TP workers disagree on key-shift measurement token counts")
-        # original-basis means, KV heads contiguous in rank order: what the loader slices again
-        return group.all_gather(shift, dim=1), group.rank_in_group == 0
-
+# ---------------------------------------------------------------------------------------------
+# driver side
+# ---------------------------------------------------------------------------------------------
 
 def set_key_shift_enabled(llm, enabled: bool) -> bool:
-    """Turn the loaded or measured shift on or off between requests (the vector survives being
-    off, so one engine can answer both ways). Safe only while no request is cached: keys already
-    stored keep the setting they were written under. Returns whether any worker had a runtime."""
-    switched = llm.collective_rpc("nvfp4_set_key_shift_enabled", args=(enabled,))
+    """Switch the loaded or measured mean on or off between requests; the vector itself is kept, so
+    one engine can answer both ways. Only safe while nothing is cached (stored keys keep the setting
+    they were written under), hence the prefix-cache reset. True if any worker had a runtime."""
+    touched = llm.collective_rpc("nvfp4_set_key_shift_enabled", args=(enabled,))
     llm.reset_prefix_cache()
-    return any(switched)
+    return any(touched)
 
 
-def _long_prompt(llm, texts: list[str], context_tokens: int) -> list[int]:
-    """About ``context_tokens`` token ids: ``texts`` joined and tiled. Repetition is fine for a
-    mean; the point of the length is to visit high positions."""
+@dataclass
+class _Engine:
+    """The handful of engine facts the calibration reads, gathered in one place."""
+
+    llm: Any
+
+    @property
+    def config(self):
+        return self.llm.llm_engine.vllm_config
+
+    def window(self) -> int:
+        return self.llm.llm_engine.model_config.max_model_len - 1
+
+    def eager(self) -> bool:
+        return bool(self.config.model_config.enforce_eager)
+
+    def check_exportable(self, runtimes_per_worker: list[int]) -> None:
+        """A sidecar holds the whole model's KV heads in order; only a single tensor-parallel group
+        whose ranks each own an equal, unreplicated share can reassemble that."""
+        parallel = self.config.parallel_config
+        ranks = parallel.tensor_parallel_size
+        heads = self.config.model_config.get_total_num_kv_heads()
+        single_group = parallel.pipeline_parallel_size == 1 and parallel.data_parallel_size == 1
+        every_worker = len(runtimes_per_worker) == ranks and all(runtimes_per_worker)
+        if not (single_group and every_worker and heads >= ranks and heads % ranks == 0):
+            raise ValueError(
+                "key-shift export requires one TP group with unreplicated, "
+                "evenly partitioned KV heads and no pipeline/data parallelism")
+
+
+def _tiled_prompt(tokenizer, texts: list[str], length: int) -> list[int]:
+    """``length`` token ids made of ``texts`` joined by blank lines and repeated. Repetition does not
+    hurt a mean; the length is what matters, because it decides which positions are visited."""
     if not any(text.strip() for text in texts):
         raise ValueError(
-            "the model returned no calibration text to tile, so the mean would be measured over separators"
-        )
-    unit = llm.get_tokenizer().encode("\n\n".join(texts) + "\n\n", add_special_tokens=False)
-    repeats = -(-context_tokens // len(unit))
-    return (unit * repeats)[:context_tokens]
+            "the model returned no calibration text to tile, so the mean would be measured over separators")
+    unit = tokenizer.encode("\n\n".join(texts) + "\n\n", add_special_tokens=False)
+    copies = (length + len(unit) - 1) // len(unit)
+    return (unit * copies)[:length]
+
+
+def _agreeing(items: list, what: str, key=lambda item: item):
+    """All workers must report the same thing; returns it."""
+    first = key(items[0])
+    if any(key(item) != first for item in items[1:]):
+        raise ValueError(f"TP workers disagree on {what}")
+    return first
 
 
 def calibrate_key_shift(llm, *, seeds: tuple[str, ...] = SEEDS, tokens_per_seed: int = TOKENS_PER_SEED,
@@ -160,71 +222,64 @@ def calibrate_key_shift(llm, *, seeds: tuple[str, ...] = SEEDS, tokens_per_seed:
                         probability_samples: int = 8) -> dict[str, Any] | None:
     """Measure the key mean over one long prefill and start subtracting it.
 
-    Returns the measurement summary (token count, shape, mean magnitude, sidecar path), or None
-    when the engine runs no NVFP4 cache. ``save_to`` writes a sidecar reusable through
-    ``additional_config["nvfp4_key_smoothing"]``: it needs one tensor-parallel group with evenly
-    partitioned, unreplicated KV heads and no pipeline or data parallelism; rank 0 writes the
-    gathered full-model tensor. With ``probability_multiplier`` the same prefill also yields the
-    probability threshold (``probability_scaling`` in the result); that needs an eager engine so
-    that the attention hooks run."""
+    Returns rank 0's summary ``{"tokens", "shape", "mean_abs", "saved_to"}`` (plus
+    ``"probability_scaling"``, the tau report, when ``probability_multiplier`` is given), or None when
+    the engine runs no NVFP4 cache. ``save_to`` writes a sidecar that
+    ``additional_config["nvfp4_key_smoothing"]`` loads again. Tau needs an eager engine: its collector
+    is a forward hook, which a captured graph would not run."""
     from vllm import SamplingParams, TokensPrompt
 
-    if probability_multiplier is not None and not llm.llm_engine.vllm_config.model_config.enforce_eager:
+    engine = _Engine(llm)
+    wants_tau = probability_multiplier is not None
+    if wants_tau and not engine.eager():
         raise ValueError("probability calibration requires an eager engine")
     try:
-        found = llm.collective_rpc("nvfp4_begin_key_shift_measurement")
+        runtimes = llm.collective_rpc("nvfp4_begin_key_shift_measurement")
     except AttributeError as error:
         raise RuntimeError(
             f'the engine was built without worker_extension_cls="{WORKER_EXTENSION_CLS}", '
-            "so the K mean cannot be read out of the worker"
-        ) from error
-    if not any(found):
+            "so the K mean cannot be read out of the worker") from error
+    if not any(runtimes):
         return None
     if save_to is not None:
-        config = llm.llm_engine.vllm_config
-        parallel = config.parallel_config
-        ranks = parallel.tensor_parallel_size
-        heads = config.model_config.get_total_num_kv_heads()
-        if (not all(found) or len(found) != ranks or parallel.pipeline_parallel_size != 1
-                or parallel.data_parallel_size != 1 or heads < ranks or heads % ranks):
-            raise ValueError(
-                "key-shift export requires one TP group with unreplicated, "
-                "evenly partitioned KV heads and no pipeline/data parallelism"
-            )
-    sampled = llm.generate(list(seeds),
-                           SamplingParams(temperature=0.0, top_p=1.0, max_tokens=tokens_per_seed, seed=42),
-                           use_tqdm=False)
-    budget = min(context_tokens, llm.llm_engine.model_config.max_model_len - 1)
-    if probability_multiplier is not None:
+        engine.check_exportable(runtimes)
+
+    greedy = dict(temperature=0.0, top_p=1.0, seed=42)
+    completions = llm.generate(list(seeds), SamplingParams(max_tokens=tokens_per_seed, **greedy), use_tqdm=False)
+    texts = [item.prompt + item.outputs[0].text for item in completions]
+    length = min(context_tokens, engine.window())
+    prompt = _tiled_prompt(llm.get_tokenizer(), texts, length)
+
+    if wants_tau:
         llm.collective_rpc("nvfp4_begin_probability_calibration",
-                           args=(budget, probability_multiplier, probability_samples))
+                           args=(length, probability_multiplier, probability_samples))
     try:
-        texts = [output.prompt + output.outputs[0].text for output in sampled]
-        llm.generate(TokensPrompt(prompt_token_ids=_long_prompt(llm, texts, budget)),
-                     SamplingParams(temperature=0.0, max_tokens=1), use_tqdm=False)
+        llm.generate(TokensPrompt(prompt_token_ids=prompt), SamplingParams(temperature=0.0, max_tokens=1),
+                     use_tqdm=False)
     except BaseException:
-        if probability_multiplier is not None:
+        if wants_tau:  # leave no hook behind
             llm.collective_rpc("nvfp4_end_probability_calibration", args=(False,))
         raise
-    report = None
-    if probability_multiplier is not None:
+
+    tau_report = None
+    if wants_tau:
         from .probability_calibration import fit_probability_threshold
 
-        samples = llm.collective_rpc("nvfp4_end_probability_calibration")
-        positions = [row["position"] for row in samples[0]]
-        if len(samples) != len(found) or any([row["position"] for row in worker] != positions for worker in samples):
+        per_worker = llm.collective_rpc("nvfp4_end_probability_calibration")
+        if len(per_worker) != len(runtimes):
             raise ValueError("TP workers disagree on probability calibration samples")
-        report = fit_probability_threshold(samples, probability_multiplier)
-    measurements = llm.collective_rpc("nvfp4_finish_key_shift_measurement", args=(save_to,))
-    measured = measurements[0]
-    if save_to is not None and len(found) > 1:
-        if len(measurements) != len(found) or any(
-            item is None or item["shape"] != measured["shape"] or item["tokens"] != measured["tokens"]
-            or item["saved_to"] != save_to for item in measurements
-        ):
+        _agreeing(per_worker, "probability calibration samples", key=lambda rows: [row["position"] for row in rows])
+        tau_report = fit_probability_threshold(per_worker, probability_multiplier)
+
+    summaries = llm.collective_rpc("nvfp4_finish_key_shift_measurement", args=(save_to,))
+    summary = summaries[0]
+    if save_to is not None and len(runtimes) > 1:
+        if len(summaries) != len(runtimes) or any(item is None for item in summaries):
             raise ValueError("TP workers disagree on the exported key-shift measurement")
-    if report is not None:
-        measured = {**measured, "probability_scaling": report}
-    # keys cached during the measurement were stored unshifted; no later request may read one
+        _agreeing(summaries, "the exported key-shift measurement",
+                  key=lambda item: (item["shape"], item["tokens"], item["saved_to"]))
+    if tau_report is not None:
+        summary = dict(summary, probability_scaling=tau_report)
+    # keys cached while measuring were stored unshifted; nothing served later may read one of them
     llm.reset_prefix_cache()
-    return measured
+    return summary

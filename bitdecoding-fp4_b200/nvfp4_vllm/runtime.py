@@ -286,6 +286,44 @@ class LayerRuntime:
         self._promotion_bases = bases
         return self._promotion
 
+    def attend_decode_rows(self, layer_index: int, rows: int, *, query, key, value, kv_cache, step, out,
+                           softmax_scale: float, query_scale_mode: str) -> None:
+        """Decode attention of the batch's first ``rows`` rows (vLLM sorts the one-token rows to the
+        front) over this layer's FP4 pages, BF16 tail and sink, written into ``out[:rows]``.
+
+        Everything the kernel call needs that lives here goes in from here: the carved cache, the
+        tail buffers, the query and split scratch (so the call allocates nothing), and this layer's
+        share of the key transform for the fused tail write. ``step`` is this step's
+        ``NVFP4Metadata``; its per-row tensors were written on the device by the control kernel this
+        same step, which is why they are passed as trusted: checking them would mean reading them."""
+        from nvfp4_decode_kernel import DecodeTailWrite, fp4_decode
+
+        regions = self.views(layer_index, kv_cache)
+        per_row = {name: getattr(step, name)[:rows]
+                   for name in ("row_to_slot", "seq_lens", "seqused_fp4", "seqused_residual", "seqused_sink")}
+        tail_key, tail_value = self.tail_key[layer_index], self.tail_value[layer_index]
+        new_token = None
+        if self.decode_writes_tail:
+            raw_key, rotate, shift = self.key_write(layer_index, key)
+            new_token = DecodeTailWrite(
+                key=raw_key[:rows], value=value[:rows], tail_key=tail_key, tail_value=tail_value,
+                row_to_slot=per_row["row_to_slot"], seq_lens=per_row["seq_lens"], seqused_fp4=per_row["seqused_fp4"],
+                rotate_key=rotate, key_shift=shift, sink_tokens=SINK_TOKENS)
+        fp4_decode(
+            self.transform_query(query[:rows]), *regions, step.block_table[:rows, :step.decode_page_columns],
+            per_row["seqused_fp4"],
+            residual_key_pages_bf16=tail_key, residual_value_pages_bf16=tail_value,
+            residual_page_ids=per_row["row_to_slot"], seqused_residual=per_row["seqused_residual"],
+            seqused_sink=per_row["seqused_sink"] if SINK_TOKENS else None,
+            softmax_scale=softmax_scale, out=out[:rows], trusted_metadata=True,
+            num_splits=step.decode_num_splits, row_order=step.decode_row_order,
+            query_terms=self.query_terms, scale_mode=query_scale_mode, query_rotation=self.query_rotation,
+            tail_write=new_token,
+            query_padded_scratch=self.query_padded, query_fp4_scratch=self.query_fp4,
+            query_scales_scratch=self.query_scales, query_fp4_second_scratch=self.query_fp4_second,
+            query_scales_second_scratch=self.query_scales_second,
+            split_partial_scratch=self.split_partial, split_lse_scratch=self.split_lse)
+
     def expect_layer(self, layer_index: int) -> None:
         """Refuse a step whose layers do not run in index order: promotion fires after the highest
         index, which is the last layer only if construction order is execution order. The counter

@@ -62,7 +62,8 @@ def _oracle_row(request, layer, query, shift):
 
 
 def test_prefill_decode_promotion_and_slot_reuse():
-    from nvfp4_decode_kernel import DecodeTailWrite, fp4_decode
+    import types
+
     from nvfp4_vllm import layout, promote
     from nvfp4_vllm.control import ControlPlane
     from nvfp4_vllm.runtime import LayerRuntime
@@ -122,23 +123,15 @@ def test_prefill_decode_promotion_and_slot_reuse():
                      row_to_slot=outputs.row_to_slot, layer_index=layer, decode_rows=decode_rows,
                      first_row=decode_rows if runtime.decode_writes_tail else 0)
             if decode_rows:
-                views = runtime.views(layer, caches[layer])
-                tail_write = DecodeTailWrite(
-                    key=raw_key[:decode_rows], value=value[:decode_rows], tail_key=runtime.tail_key[layer],
-                    tail_value=runtime.tail_value[layer], row_to_slot=outputs.row_to_slot[:decode_rows],
-                    seq_lens=seq_lens[:decode_rows], seqused_fp4=outputs.seqused_fp4[:decode_rows],
-                    rotate_key=rotate_key, key_shift=shift, sink_tokens=16)
-                out = fp4_decode(
-                    query=queries.to(device), key_pages_fp4=views[0], key_scales=views[1], value_pages_fp4=views[2],
-                    value_scales=views[3], fp4_page_table=block_table[:decode_rows],
-                    seqused_fp4=outputs.seqused_fp4[:decode_rows], seqused_sink=outputs.seqused_sink[:decode_rows],
-                    residual_key_pages_bf16=runtime.tail_key[layer], residual_value_pages_bf16=runtime.tail_value[layer],
-                    residual_page_ids=outputs.row_to_slot[:decode_rows],
-                    seqused_residual=outputs.seqused_residual[:decode_rows], trusted_metadata=True,
-                    query_padded_scratch=runtime.query_padded, query_fp4_scratch=runtime.query_fp4,
-                    query_scales_scratch=runtime.query_scales, query_fp4_second_scratch=runtime.query_fp4_second,
-                    query_scales_second_scratch=runtime.query_scales_second, query_terms=2, scale_mode="amax6",
-                    query_rotation=runtime.query_rotation, tail_write=tail_write)
+                # the call the plugin's attention layer makes for its decode rows
+                step = types.SimpleNamespace(
+                    row_to_slot=outputs.row_to_slot, seq_lens=seq_lens, seqused_fp4=outputs.seqused_fp4,
+                    seqused_residual=outputs.seqused_residual, seqused_sink=outputs.seqused_sink,
+                    block_table=block_table, decode_page_columns=COLUMNS, decode_num_splits=1, decode_row_order=None)
+                out = torch.empty(decode_rows, HEADS_Q, 128, dtype=torch.bfloat16, device=device)
+                runtime.attend_decode_rows(layer, decode_rows, query=queries.to(device), key=key, value=value,
+                                           kv_cache=caches[layer], step=step, out=out, softmax_scale=128 ** -0.5,
+                                           query_scale_mode="amax6")
                 results.append(out.float().cpu())
                 for i in range(decode_rows):
                     want = _oracle_row(rows[i], layer, queries[i], runtime.key_shift[layer].cpu())
