@@ -307,8 +307,11 @@ class TimedRounds:
     at least `min_seconds` of device time have been measured; the clock sampler's readings are binned
     per round, so a burst-clock round and a power-capped one can be told apart."""
 
-    def __init__(self, steps: int, min_seconds: float, sampler: ClockSampler, barrier):
+    def __init__(self, steps: int, min_seconds: float, sampler: ClockSampler, barrier, agree=None):
         self.steps, self.min_seconds, self.sampler, self.barrier = steps, min_seconds, sampler, barrier
+        # Every rank must run the same number of rounds (a step may hold a collective): the running total
+        # each rank stops on is the maximum over ranks, agreed between rounds and outside the events.
+        self.agree = agree or (lambda seconds: seconds)
         self.rounds: list[dict] = []
 
     def run(self, one_step, kernel_events_of=None) -> None:
@@ -328,7 +331,7 @@ class TimedRounds:
             kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs) if pairs else None
             self.rounds.append({"ms_per_step": ms / self.steps, "kernel_ms": kernel_ms,
                                 "window": tuple(self.sampler.windows[-1])})
-            total += ms * 1e-3
+            total = self.agree(total + ms * 1e-3)
             if total >= self.min_seconds or len(self.rounds) >= 2000:
                 break
         self.barrier()
@@ -354,6 +357,32 @@ class TimedRounds:
 
 def flush_l2(scratch: torch.Tensor) -> None:
     scratch.add_(1)
+
+
+def sustained_copy_gbs(device, seconds: float = 0.8) -> dict:
+    """What a plain device-to-device copy sustains on this GPU right now, for about `seconds`: the same
+    STREAM-style measure as the burst figure the roofline divides by (read + written bytes over the
+    time), but taken back to back so that it runs under whatever clocks a long step runs under."""
+    elems = 1 << 29  # 1 GiB of BF16 in, 1 GiB out
+    a = torch.empty(elems, dtype=torch.bfloat16, device=device)
+    b = torch.empty_like(a)
+    for _ in range(3):
+        b.copy_(a)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    copies = 0
+    begin.record()
+    start = time.time()
+    while time.time() - start < seconds:
+        for _ in range(10):
+            b.copy_(a)
+        copies += 10
+        torch.cuda.synchronize()
+    end.record()
+    torch.cuda.synchronize()
+    gbs = copies * 2 * elems * 2 / (begin.elapsed_time(end) * 1e-3) / 1e9
+    del a, b
+    return {"gb_s": gbs, "seconds": begin.elapsed_time(end) * 1e-3, "copies": copies}
 
 
 def run_gqa(args) -> None:
@@ -529,7 +558,7 @@ def run_gqa(args) -> None:
         device_step()
     sampler = ClockSampler(local_rank)
     sampler.__enter__()  # samples through both timed regions; left at the end of the end-to-end arm
-    resident = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    resident = TimedRounds(args.steps, args.min_seconds, sampler, barrier, max_over_ranks)
     resident.run(device_step, lambda: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
     step_ms = max_over_ranks(resident.median_ms())
     kernel_ms = max_over_ranks(resident.median_kernel_ms())
@@ -589,7 +618,7 @@ def run_gqa(args) -> None:
 
     for _ in range(args.warmup):
         e2e_step()
-    end_to_end = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    end_to_end = TimedRounds(args.steps, args.min_seconds, sampler, barrier, max_over_ranks)
     end_to_end.run(e2e_step)
     sampler.__exit__(None, None, None)
     e2e_ms = max_over_ranks(end_to_end.median_ms()) - flush_ms
@@ -637,6 +666,7 @@ def run_gqa(args) -> None:
         verified["tolerance"] = {"max_abs": 1e-2, "mean_rel": 1e-3}
         verified["against"] = "CPU oracle on sampled (row, KV head) tiles of this run's cache"
 
+    live_copy = sustained_copy_gbs(device) if (rank == 0 and not args.no_live_copy) else None
     total_bytes = algorithmic_bytes
     if world > 1:
         gathered = [None] * world
@@ -672,6 +702,9 @@ def run_gqa(args) -> None:
                                                       "algorithmic bytes 1.013 / 1.012), not measured in this run",
                 "peak_kind": f"of {peak_kind}", "kernel": "decode_kernel",
                 "algorithmic_bytes_per_launch": algorithmic_bytes,
+                # context, not the denominator: the same copy measured back to back in this very run
+                "copy_sustained_in_this_run_gb_s": None if live_copy is None else live_copy["gb_s"],
+                "frac_of_copy_sustained_in_this_run": None if live_copy is None else achieved / live_copy["gb_s"],
             },
             "e2e": {"value": e2e_ms * 1e3, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "every step: one CUDA-graph replay of [H2D of the pinned input record, plugin call, D2H "
@@ -890,7 +923,7 @@ def run_mla(args) -> None:
         device_step()
     sampler = ClockSampler(local_rank)
     sampler.__enter__()
-    resident = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    resident = TimedRounds(args.steps, args.min_seconds, sampler, barrier, max_over_ranks)
     resident.run(device_step, lambda: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
     step_ms = max_over_ranks(resident.median_ms())
     kernel_ms = max_over_ranks(resident.median_kernel_ms())
@@ -921,7 +954,7 @@ def run_mla(args) -> None:
 
     for _ in range(args.warmup):
         e2e_step()
-    end_to_end = TimedRounds(args.steps, args.min_seconds, sampler, barrier)
+    end_to_end = TimedRounds(args.steps, args.min_seconds, sampler, barrier, max_over_ranks)
     end_to_end.run(e2e_step)
     sampler.__exit__(None, None, None)
     e2e_ms = max_over_ranks(end_to_end.median_ms())
@@ -1085,6 +1118,8 @@ def main() -> None:
                         help="merge split-KV partials inside the decode kernel instead of launching the merge "
                              "kernel (measured no faster)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-live-copy", action="store_true",
+                        help="skip the sustained device-to-device copy measured for context beside the roofline")
     parser.add_argument("--verify", type=int, default=4, metavar="TILES",
                         help="after the timed regions, compare this many sampled (row, KV head) tiles of one decode "
                              "with the CPU oracle and report the errors (0: skip)")
