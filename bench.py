@@ -653,13 +653,14 @@ def run_gqa(args) -> None:
 
     # ---- parity at the benchmarked size, after and outside every timed region ------------------
     verified = None
+    if args.verify:  # every rank takes the step (the mixed one holds a collective); rank 0 checks its own
+        result = step(w.query, new_key, new_value)
+        torch.cuda.synchronize()
     if args.verify and rank == 0:
         from oracle import tile_check
 
         torch.manual_seed(0)
         tiles = [(int(torch.randint(rows, (1,))), int(torch.randint(heads_kv, (1,)))) for _ in range(args.verify)]
-        result = step(w.query, new_key, new_value)
-        torch.cuda.synchronize()
         verified = tile_check.check_tiles(
             w, result, tiles, terms=2, scale_mode="amax6", rotate=True, num_splits=splits, bf16_split=parts > splits,
             bf16_page_cost=decode_module.BF16_BLOCK_PAGE_COST if parts == splits and splits > 1 else 0)

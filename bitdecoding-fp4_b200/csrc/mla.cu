@@ -7,26 +7,44 @@
 // along channels (the K-side regions of the paged cache) and once with scales along tokens (the
 // V-side regions), because a block-scaled MMA wants its scales along the contraction axis.
 //
-// A pair of CTAs serves (row, 128 query heads[, split]); each walks the row's pages two at a time
-// (128 tokens per step), computes all the scores, and accumulates one half of the 512 output
-// channels (128 heads x 512 FP32 is the whole of an SM's tensor memory, and the scores need room
-// too). Query heads are the M rows of every MMA, so a head is a lane of tensor memory:
-//   S[head, token]  = sum over 4 chunks  Q_chunk[head, :] . K_chunk[token, :]   8 x mxf4nvf4 (N = 128, K = 64)
-//                   + q_rope[head, :] . rope[token, :]                           4 x kind::f16  (N = 128, K = 16)
+// A pair of CTAs (a cluster of two) serves (row, 128 query heads[, split]) and walks the row's pages
+// two at a time (128 tokens per step). The pair shares the step's work both ways:
+//   - CTA c scores the step's page c: it alone fetches that page's K-side copy and rope keys, forms
+//     S[head, 64 tokens], and turns them into FP4 probabilities;
+//   - CTA c accumulates output channels [256 c, 256 c + 256) over all 128 tokens of the step (128
+//     heads x 512 FP32 is the whole of an SM's tensor memory), so it needs the other CTA's
+//     probabilities too: each CTA forms its half of the step's P operand (the K block of its page)
+//     in its own shared memory and sends it, as one bulk copy, into the peer's. (Plain stores into
+//     the peer's shared memory followed by the proxy fence the tensor core needs cost about 1 us a
+//     step; a bulk copy is written by the async proxy, which the tensor core reads with no fence.)
+// Per step and CTA that is half the score products, half the exponentials and half the K-side bytes
+// of a CTA that scored the whole step by itself. Query heads are the M rows of every MMA, so a head
+// is a lane of tensor memory:
+//   S[head, token]  = sum over 4 chunks  Q_chunk[head, :] . K_chunk[token, :]   8 x mxf4nvf4 (N = 64, K = 64)
+//                   + q_rope[head, :] . rope[token, :]                           4 x kind::f16  (N = 64, K = 16)
 //   O[head, chan]  += P[head, :] . V^T[chan, :]                                  2 x mxf4nvf4 (N = 256, K = 64)
-// Each head has two softmax threads (64 tokens of a step each). A thread reads its scores from
-// tensor memory, forms the probabilities against the stale maximum, quantizes them sixteen at a time
-// (the groups are in its own registers: no shuffles) straight into the shared-memory A operand of the
-// PV product, and keeps a partial sum. A CTA-wide vote catches the rare step in which a maximum may
-// have to move (the stale-maximum rule tolerates 2^8); then the exact rule runs on the scores, the
-// head's threads rescale their share of O in place in tensor memory between two PV products, and the
-// probabilities are formed again. O (256 columns) stays in tensor memory for the whole walk.
-// Tensor memory: S 128 + O 256 + scale factors 112 columns.
+// Each head has four softmax threads per CTA (16 tokens of the page each). A thread reads its scores
+// from tensor memory, forms the probabilities against the stale maximum and quantizes them (the
+// group is in its own registers: no shuffles). A warp that saw a probability large enough that a
+// maximum may have to move (the stale-maximum rule tolerates 2^8) stamps the step's number into a
+// request word that travels with the half. The walk is pipelined by one step: a thread forms step
+// i, then looks at how step i - 1 came out (both halves in place, no request: almost always), then
+// announces step i; so the halves cross between the CTAs while the next ones are formed, and the
+// two CTAs never wait for each other with nothing to do. On a requested step all threads of the
+// pair exchange their maxima (stores into both CTAs' shared memory), apply the exact rule
+// identically, rescale their share of O in place in tensor memory and form steps i - 1 and i
+// again; the PV issuers wait for the second copy. O (256 columns) stays in tensor memory for the
+// whole walk. Three P buffers: one being multiplied, one crossing, one being formed.
+// Tensor memory: S 2 x 64 (the scores of the next step are formed while this step's are still being
+// read) + O 256 + scale factors 112 columns (K scales in two sets, so that the next step's can be
+// copied in while this step's are in use).
 //
-// Warps: 0 issues the bulk copies (lane 0 the K side, lane 1 the V side); 1, 2 and 3 issue the tensor
-// work, one thread each for QK, for PV, and for the K scale atoms (whose two half blocks per step the
-// whole of warp 3 first interleaves); 4-11 are the softmax. Every mbarrier wait is bounded and
-// reports its site in bits [8,16) of the error word.
+// Warps: 0 issues the bulk copies from global memory (lane 0 the K side of the CTA's page, lane 1 the
+// V side of both pages); 1, 2 and 3 issue the tensor work, one thread each for QK, for PV (which also
+// sends the P half to the peer), and for the K scale atoms (which the whole of warp 3 first regroups
+// from the page's 8-byte rows to the 16-byte rows of an atom); 4-19 are the softmax. Every mbarrier
+// wait is bounded and reports its site in bits [8,16) of the error word; a CTA whose peer gave up
+// runs into its own limit and gives up too.
 #include <cmath>
 #include <type_traits>
 
@@ -43,24 +61,30 @@ constexpr int kLatent = 512;
 constexpr int kHalf = 256;    // output channels per CTA
 constexpr int kRope = 64;
 constexpr int kStep = 128;    // tokens per step (two 64-token pages)
-constexpr int kStages = 2;
-constexpr int kSoftmaxGroups = 2;                   // softmax threads per head (2 measured faster than 1 or 4)
-constexpr int kRun = kStep / kSoftmaxGroups;        // tokens of a step one softmax thread owns
+constexpr int kOwn = 64;      // tokens of a step one CTA scores (its page)
+constexpr int kStages = 3;   // K side (the CTA's page of a step)
+constexpr int kVStages = 2;  // V side (both pages of a step)
+constexpr int kPBuffers = 3;  // P operands: one being multiplied, one under way between the CTAs, one being formed
+constexpr int kSoftmaxGroups = 4;                   // softmax threads per head in a CTA (4 measured faster than 2)
+constexpr int kRun = kOwn / kSoftmaxGroups;         // tokens of a step one softmax thread owns
+constexpr int kRunGroups = kRun / 16;
 constexpr int kShare = kHalf / kSoftmaxGroups;      // output columns one softmax thread rescales and writes
 constexpr int kSoftmaxThreads = 128 * kSoftmaxGroups;
+constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;
+constexpr int kSlots = 2 * kSoftmaxGroups;          // softmax threads per head in the pair
 constexpr int kThreads = 128 + kSoftmaxThreads;  // producer, QK, PV and K-scale warps, then the softmax warps
 constexpr float kRescaleThreshold = 8.0f;
 
-constexpr int kColS = 0;       // 128 columns
+constexpr int kColS = 0;       // two buffers of 64 columns
 constexpr int kColO = 128;     // 256 columns
 constexpr int kColSFQ = 384;   // 8 atoms x 4
-constexpr int kColSFK = 416;   // 8 atoms x 4
+constexpr int kColSFK = 416;   // 2 buffers x 4 atoms x 4 (an atom: a chunk's two K blocks, two columns each)
 constexpr int kColSFV = 448;   // 2 buffers x 2 pages x 2 atoms x 4
 constexpr int kColSFP = 480;   // 2 buffers x 2 atoms x 4
 constexpr int kTmemColumns = 512;
 
-constexpr uint32_t kKeyBytes = kChunks * 8192 + 2 * 8192;  // codes of four chunks + two rope blocks
-constexpr uint32_t kKeyScaleBytes = 4096;
+constexpr uint32_t kKeyBytes = kChunks * 4096 + 8192;      // one page: codes of four chunks + its rope block
+constexpr uint32_t kKeyScaleBytes = 2048;
 constexpr uint32_t kValueBytes = 2 * (8192 + 1024);        // this CTA's two chunks of two pages
 
 struct Params {
@@ -88,20 +112,35 @@ struct Params {
   int32_t* error_word;
 };
 
+// One CTA's contribution to a step's P operand: the K block (64 tokens) of the page it scored. It
+// forms it in its own copy and sends that, as one bulk copy, into the peer's.
+struct alignas(1024) PHalf {
+  uint8_t codes[kHeads * 32];  // 128 heads x 32 B, 32 B swizzle
+  uint8_t sf[512];             // the K block's scale atom
+  int examine;                 // step number + 1 of the last step on which the forming CTA asked for the examination
+  int pad[3];
+};
+constexpr uint32_t kPHalfBytes = kHeads * 32 + 512 + 16;
+
 struct Smem {
-  alignas(1024) uint8_t k_codes[kStages][kChunks][8192];  // [chunk][page a | page b], 64 B rows, 64 B swizzle
-  alignas(1024) uint8_t rope[kStages][16384];             // 128 tokens x 128 B, 128 B swizzle
-  alignas(1024) uint8_t v_codes[kStages][2][8192];        // [page][256 ch x 32 B], 32 B swizzle
-  alignas(1024) uint8_t k_sf[kStages][4096];              // two pages' blocks, merged in place into 8 atoms
-  alignas(1024) uint8_t v_sf[kStages][2][1024];           // [page][2 atoms]
+  alignas(1024) uint8_t k_codes[kStages][kChunks][4096];  // [chunk][64 tokens x 64 B], 64 B swizzle
+  alignas(1024) uint8_t rope[kStages][8192];              // 64 tokens x 128 B, 128 B swizzle
+  alignas(1024) uint8_t v_codes[kVStages][2][8192];        // [page][256 ch x 32 B], 32 B swizzle
+  alignas(1024) uint8_t k_sf[kStages][2048];              // the page's block, regrouped in place into 4 atoms
+  alignas(1024) uint8_t v_sf[kVStages][2][1024];           // [page][2 atoms]
   alignas(1024) uint8_t q_tile[kChunks][kHeads * 64];
   alignas(1024) uint8_t q_rope[kHeads * 128];
   alignas(1024) uint8_t q_sf[kChunks * 2][512];
-  alignas(1024) uint8_t p_tile[2][kHeads * 64];
-  alignas(1024) uint8_t p_sf[2][2][512];
-  float red[2][kSoftmaxGroups][kHeads];  // per-head values exchanged between a head's softmax threads
-  uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-  uint64_t s_full, s_empty, o_done, sfk_ready, p_full[2];
+  PHalf p[kPBuffers][2];                                        // [buffer][page = the CTA that forms it]
+  float red[2][kSlots][kHeads];   // maxima exchanged between a head's softmax threads of the pair
+  float sums[kSlots][kHeads];     // their partial sums, at the end
+  uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kVStages], v_empty[kVStages];
+  uint64_t s_full[2], s_empty[2], sfk_ready[2];
+  uint64_t o_done[2];  // PV products of even and of odd steps: the walk looks at them up to two steps late
+  uint64_t p_local[kPBuffers];   // every softmax warp of this CTA has formed its part of the step's P half
+  uint64_t p_remote[kPBuffers];  // the peer's P half of the step has landed here
+  uint64_t again_local, again_remote;  // the same, after a step on which the maxima were examined
+  uint64_t exchange;     // every softmax warp of the pair has stored its maxima (or sums) in both CTAs
   int page_ids[2][32];
   uint32_t tmem_base;
   int abort_flag;
@@ -123,12 +162,15 @@ __device__ __forceinline__ float rcp_approx(float x) {
 
 // A bounded wait that leaves its own number in the abort flag when it is the one that ran out of
 // time; the kernel reports it in bits [8,16) of the error word, so a lost arrival can be located.
+// CLUSTER: the barrier also takes arrivals from the peer CTA, whose writes the wait must acquire.
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool wait_at(int site, uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (tc::mbar_try_wait(bar, parity)) return true;
+  auto done = [&]() { return CLUSTER ? tc::mbar_try_wait_cluster(bar, parity) : tc::mbar_try_wait(bar, parity); };
+  if (done()) return true;
   uint64_t start = 0;
   uint32_t spins = 0;
   while (true) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
+    if (done()) return true;
     if ((++spins & 255u) == 0) {
       if (*abort_flag) return false;
       const uint64_t now = tc::global_timer_ns();
@@ -139,23 +181,6 @@ __device__ __forceinline__ bool wait_at(int site, uint64_t* bar, uint32_t parity
       }
     }
   }
-}
-
-__device__ __forceinline__ void softmax_barrier() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
-}
-
-__device__ __forceinline__ bool softmax_vote_any(bool pred) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 p, %1, 0;\n\t"
-      "bar.red.or.pred q, 1, %2, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(out)
-      : "r"((uint32_t)pred), "n"(kSoftmaxThreads)
-      : "memory");
-  return out != 0;
 }
 
 __device__ __forceinline__ int swizzle64(int offset) { return offset ^ (((offset >> 7) & 3) << 4); }
@@ -169,18 +194,18 @@ __device__ __forceinline__ float probability_scale(float maximum, int p_mode, fl
 
 __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
+  // the dynamic window starts at the same offset in both CTAs, so the aligned struct does too
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
   // ---- which work ---------------------------------------------------------------------------
-  // The two CTAs of a pair are neighbours in the grid, so that they run at the same time and the
-  // second finds in L2 what the first fetched.
-  const int half = blockIdx.x & 1;
-  const int head_block = (blockIdx.x >> 1) % p.head_blocks;
-  const int row = ((blockIdx.x >> 1) / p.head_blocks) % p.rows;
-  const int part = (blockIdx.x >> 1) / (p.head_blocks * p.rows);
+  const int cta = (int)tc::cluster_cta_rank();  // 0 or 1: the page of every step it scores, the output half it owns
+  const int pair = blockIdx.x >> 1;
+  const int head_block = pair % p.head_blocks;
+  const int row = (pair / p.head_blocks) % p.rows;
+  const int part = pair / (p.head_blocks * p.rows);
   const int head0 = head_block * kHeads;
   const int valid_heads = min(kHeads, p.heads_q - head0);
   // a length the row's page-table entries cannot cover is cut to what they cover
@@ -193,22 +218,38 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
   const int last_step = min(first_step + chunk, total_steps);
   const int num_steps = last_step - first_step;
 
+  // this CTA's shared memory as the peer sees its own: same layout, another window of the cluster
+  const uint32_t local_base = tc::smem_u32(&sm);
+  const uint32_t peer_base = tc::cluster_address(local_base, (uint32_t)(cta ^ 1));
+  auto in_peer = [&](const void* mine) { return tc::smem_u32(mine) - local_base + peer_base; };
+
   // ---- set-up -------------------------------------------------------------------------------
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       tc::mbar_init(&sm.k_full[s], 1);
       tc::mbar_init(&sm.ksf_full[s], 1);
       tc::mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
       tc::mbar_init(&sm.v_full[s], 1);
       tc::mbar_init(&sm.v_empty[s], 1);
     }
-    tc::mbar_init(&sm.s_full, 1);
-    tc::mbar_init(&sm.s_empty, kSoftmaxThreads / 32);  // one arrival per softmax warp
-    tc::mbar_init(&sm.o_done, 1);
-    tc::mbar_init(&sm.sfk_ready, 1);
     for (int b = 0; b < 2; ++b) {
-      tc::mbar_init(&sm.p_full[b], kSoftmaxThreads / 32);
+      tc::mbar_init(&sm.s_full[b], 1);
+      tc::mbar_init(&sm.s_empty[b], kSoftmaxWarps);  // one arrival per softmax warp
     }
+    tc::mbar_init(&sm.o_done[0], 1);
+    tc::mbar_init(&sm.o_done[1], 1);
+    tc::mbar_init(&sm.sfk_ready[0], 1);
+    tc::mbar_init(&sm.sfk_ready[1], 1);
+    for (int b = 0; b < kPBuffers; ++b) {
+      tc::mbar_init(&sm.p_local[b], kSoftmaxWarps);
+      tc::mbar_init(&sm.p_remote[b], 1);
+      sm.p[b][0].examine = sm.p[b][1].examine = 0;
+    }
+    tc::mbar_init(&sm.again_local, kSoftmaxWarps);
+    tc::mbar_init(&sm.again_remote, 1);
+    tc::mbar_init(&sm.exchange, 2 * kSoftmaxWarps);
     sm.abort_flag = 0;
     tc::fence_barrier_init();
   }
@@ -247,12 +288,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
   }
   tc::fence_proxy_async_smem();
   tc::fence_before_sync();
-  __syncthreads();
+  // both CTAs: the peer's barriers exist before anything is stored into its shared memory
+  tc::cluster_sync_all();
   tc::fence_after_sync();
   const uint32_t tmem = sm.tmem_base;
   volatile int* abort_flag = &sm.abort_flag;
 
-  auto page_of = [&](int i, int which) {  // page of the i-th step this CTA walks (newest first)
+  auto page_of = [&](int i, int which) {  // page of the i-th step this pair walks (newest first)
     const int step = last_step - 1 - i;
     int entry = 2 * step + which;
     if (entry >= entries) entry = 2 * step;  // an odd page count: the second half is masked anyway
@@ -278,36 +320,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       if (lane < 2) {
         for (int j = 0; j < count && ok; ++j) {
           const int i = base + j;
-          const int s = i % kStages;
-          const uint32_t parity = ((i / kStages) & 1) ^ 1;
           const int page[2] = {sm.page_ids[0][j], sm.page_ids[1][j]};
           if (lane == 0) {
-            ok = wait_at(1, &sm.k_empty[s], parity, abort_flag);
+            const int s = i % kStages;
+            ok = wait_at(1, &sm.k_empty[s], ((i / kStages) & 1) ^ 1, abort_flag);
             if (ok) {
+              const int64_t mine = page[cta];
               tc::mbar_expect_tx(&sm.ksf_full[s], kKeyScaleBytes);
               tc::mbar_expect_tx(&sm.k_full[s], kKeyBytes);
+              tc::bulk_load(sm.k_sf[s], p.k_scales + mine * p.k_scales_pitch, kKeyScaleBytes, &sm.ksf_full[s]);
 #pragma unroll
-              for (int e = 0; e < 2; ++e)
-                tc::bulk_load(sm.k_sf[s] + e * 2048, p.k_scales + (int64_t)page[e] * p.k_scales_pitch, 2048,
-                              &sm.ksf_full[s]);
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c)
-                  tc::bulk_load(sm.k_codes[s][c] + e * 4096, p.k_codes + (int64_t)page[e] * p.k_codes_pitch + c * 4096,
-                                4096, &sm.k_full[s]);
-                tc::bulk_load(sm.rope[s] + e * 8192, p.rope + (int64_t)page[e] * p.rope_pitch, 8192, &sm.k_full[s]);
-              }
+              for (int c = 0; c < kChunks; ++c)
+                tc::bulk_load(sm.k_codes[s][c], p.k_codes + mine * p.k_codes_pitch + c * 4096, 4096, &sm.k_full[s]);
+              tc::bulk_load(sm.rope[s], p.rope + mine * p.rope_pitch, 8192, &sm.k_full[s]);
             }
           } else {
-            ok = wait_at(2, &sm.v_empty[s], parity, abort_flag);
+            const int s = i % kVStages;
+            ok = wait_at(2, &sm.v_empty[s], ((i / kVStages) & 1) ^ 1, abort_flag);
             if (ok) {
               tc::mbar_expect_tx(&sm.v_full[s], kValueBytes);
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
-                tc::bulk_load(sm.v_codes[s][e], p.v_codes + (int64_t)page[e] * p.v_codes_pitch + half * 8192, 8192,
+                tc::bulk_load(sm.v_codes[s][e], p.v_codes + (int64_t)page[e] * p.v_codes_pitch + cta * 8192, 8192,
                               &sm.v_full[s]);
-                tc::bulk_load(sm.v_sf[s][e], p.v_scales + (int64_t)page[e] * p.v_scales_pitch + half * 1024, 1024,
+                tc::bulk_load(sm.v_sf[s][e], p.v_scales + (int64_t)page[e] * p.v_scales_pitch + cta * 1024, 1024,
                               &sm.v_full[s]);
               }
             }
@@ -321,9 +357,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     // bulk copy can write into this CTA's shared memory after it exits.
     if (lane < 2 && *abort_flag) {
       const uint64_t start = tc::global_timer_ns();
-      for (int i = max(0, issued - kStages); i < issued; ++i) {
-        const int s = i % kStages;
-        const uint32_t parity = (i / kStages) & 1;
+      const int depth = lane == 0 ? kStages : kVStages;
+      for (int i = max(0, issued - depth); i < issued; ++i) {
+        const int s = i % depth;
+        const uint32_t parity = (i / depth) & 1;
         if (lane == 0) {
           while (!tc::mbar_try_wait(&sm.k_full[s], parity) && tc::global_timer_ns() - start < tc::kWaitLimitNs) {
           }
@@ -337,13 +374,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     }
   } else if (warp == 1) {
     // ---- score products: one thread ---------------------------------------------------------------
-    // Issuing is what bounds a step (a tcgen05.cp holds its thread for about 50 ns, an MMA for 40),
-    // so the three strands of tensor work are issued by three threads: QK here, PV in warp 2, the K
-    // scale atoms in warp 3. The tensor pipe runs what they issue in arrival order; the strands
-    // touch different accumulators and hand over through mbarriers fed by tcgen05.commit.
+    // Issuing is what bounds the tensor side of a step (a tcgen05.cp holds its thread for about 50 ns,
+    // an MMA for 40), so the three strands of tensor work are issued by three threads: QK here, PV in
+    // warp 2, the K scale atoms in warp 3. The tensor pipe runs what they issue in arrival order; the
+    // strands touch different accumulators and hand over through mbarriers fed by tcgen05.commit.
     if (lane == 0 && num_steps > 0) {
-      constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, kStep);
-      constexpr uint32_t idesc_rope = tc::bf16_idesc(128, kStep);
+      constexpr uint32_t idesc_qk = tc::nvf4_idesc(128, kOwn);
+      constexpr uint32_t idesc_rope = tc::bf16_idesc(128, kOwn);
 #pragma unroll
       for (int a = 0; a < kChunks * 2; ++a)
         tc::cp_sf_atom(tmem + kColSFQ + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.q_sf[a])));
@@ -351,24 +388,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       for (int i = 0; i < num_steps && ok; ++i) {
         const int s = i % kStages;
         ok = wait_at(6, &sm.k_full[s], (i / kStages) & 1, abort_flag);
-        if (ok) ok = wait_at(14, &sm.sfk_ready, i & 1, abort_flag);
-        // the scores of the previous step have been read
-        if (ok) ok = wait_at(7, &sm.s_empty, (i & 1) ^ 1, abort_flag);
+        if (ok) ok = wait_at(14, &sm.sfk_ready[i & 1], (i >> 1) & 1, abort_flag);
+        // the scores of two steps ago, which this buffer held, have been read
+        if (ok) ok = wait_at(7, &sm.s_empty[i & 1], ((i >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc::fence_after_sync();
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
           for (int k = 0; k < 2; ++k)
-            tc::mma_nvf4(tmem + kColS, tc::fp4_tile_desc(tc::smem_u32(sm.q_tile[c]), k),
+            tc::mma_nvf4(tmem + kColS + kOwn * (i & 1), tc::fp4_tile_desc(tc::smem_u32(sm.q_tile[c]), k),
                          tc::fp4_tile_desc(tc::smem_u32(sm.k_codes[s][c]), k), idesc_qk,
-                         tmem + kColSFQ + 4 * (2 * c + k), tmem + kColSFK + 4 * (2 * c + k), (c | k) != 0);
+                         tmem + kColSFQ + 4 * (2 * c + k), tmem + kColSFK + 16 * (i & 1) + 4 * c + 2 * k, (c | k) != 0);
         }
 #pragma unroll
         for (int k = 0; k < kRope / 16; ++k)
-          tc::mma_bf16(tmem + kColS, tc::bf16_tile_desc(tc::smem_u32(sm.q_rope), k),
+          tc::mma_bf16(tmem + kColS + kOwn * (i & 1), tc::bf16_tile_desc(tc::smem_u32(sm.q_rope), k),
                        tc::bf16_tile_desc(tc::smem_u32(sm.rope[s]), k), idesc_rope, true);
-        tc::commit(&sm.s_full);
+        tc::commit(&sm.s_full[i & 1]);
         tc::commit(&sm.k_empty[s]);
       }
     }
@@ -377,30 +414,53 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     if (lane == 0) {
       constexpr uint32_t idesc_pv = tc::nvf4_idesc(128, kHalf);
       bool ok = true;
+      int examined = 0;  // steps so far on which the maxima were examined: the phase of the `again` barriers
       for (int m = 0; m < num_steps && ok; ++m) {
-        const int s = m % kStages;
-        const int b = m & 1;
-        ok = wait_at(3, &sm.v_full[s], (m / kStages) & 1, abort_flag);
-        if (ok) ok = wait_at(4, &sm.p_full[b], (m >> 1) & 1, abort_flag);
+        const int s = m % kVStages;
+        const int b = m % kPBuffers;
+        const uint32_t p_phase = (m / kPBuffers) & 1;
+        const int t = m & 1;  // which set of scale columns in tensor memory
+        ok = wait_at(3, &sm.v_full[s], (m / kVStages) & 1, abort_flag);
+        // this CTA's half goes to the peer as soon as it is formed; the peer's comes the same way
+        if (ok) {
+          tc::mbar_expect_tx(&sm.p_remote[b], kPHalfBytes);
+          ok = wait_at(4, &sm.p_local[b], p_phase, abort_flag);
+        }
+        if (ok) {
+          tc::bulk_copy_to_peer(in_peer(&sm.p[b][cta]), &sm.p[b][cta], kPHalfBytes, in_peer(&sm.p_remote[b]));
+          ok = wait_at(17, &sm.p_remote[b], p_phase, abort_flag);
+        }
+        if (ok && (m == 0 || *const_cast<volatile int*>(&sm.p[b][0].examine) == m + 1 ||
+                   *const_cast<volatile int*>(&sm.p[b][1].examine) == m + 1)) {
+          // the halves are formed again; the first copy has been seen by the peer's threads before
+          // they exchanged maxima, so the source is free and the destination is not being read
+          tc::mbar_expect_tx(&sm.again_remote, kPHalfBytes);
+          ok = wait_at(13, &sm.again_local, examined & 1, abort_flag);
+          if (ok) {
+            tc::bulk_copy_to_peer(in_peer(&sm.p[b][cta]), &sm.p[b][cta], kPHalfBytes, in_peer(&sm.again_remote));
+            ok = wait_at(18, &sm.again_remote, examined & 1, abort_flag);
+          }
+          ++examined;
+        }
         if (!ok) break;
         tc::fence_after_sync();
 #pragma unroll
         for (int a = 0; a < 4; ++a)  // [page][atom of chunk 0, atom of chunk 1]
-          tc::cp_sf_atom(tmem + kColSFV + 16 * b + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.v_sf[s][0]) + a * 512));
+          tc::cp_sf_atom(tmem + kColSFV + 16 * t + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.v_sf[s][0]) + a * 512));
 #pragma unroll
         for (int e = 0; e < 2; ++e)
-          tc::cp_sf_atom(tmem + kColSFP + 8 * b + 4 * e, tc::sf_atom_desc(tc::smem_u32(sm.p_sf[b][e])));
-        const uint32_t p_addr = tc::smem_u32(sm.p_tile[b]);
+          tc::cp_sf_atom(tmem + kColSFP + 8 * t + 4 * e, tc::sf_atom_desc(tc::smem_u32(sm.p[b][e].sf)));
 #pragma unroll
         for (int e = 0; e < 2; ++e)
-          tc::mma_nvf4(tmem + kColO, tc::fp4_tile_desc(p_addr, e), tc::fp4_half_tile_desc(tc::smem_u32(sm.v_codes[s][e])),
-                       idesc_pv, tmem + kColSFP + 8 * b + 4 * e, tmem + kColSFV + 16 * b + 8 * e, m > 0 || e > 0);
-        tc::commit(&sm.o_done);
+          tc::mma_nvf4(tmem + kColO, tc::fp4_half_tile_desc(tc::smem_u32(sm.p[b][e].codes)),
+                       tc::fp4_half_tile_desc(tc::smem_u32(sm.v_codes[s][e])), idesc_pv, tmem + kColSFP + 8 * t + 4 * e,
+                       tmem + kColSFV + 16 * t + 8 * e, m > 0 || e > 0);
+        tc::commit(&sm.o_done[m & 1]);
         tc::commit(&sm.v_empty[s]);
       }
     }
   } else if (warp == 3) {
-    // ---- K scale atoms: the warp interleaves, one thread copies to tensor memory -------------------
+    // ---- K scale atoms: the warp spreads them, one thread copies to tensor memory ------------------
     bool ok = true;
     for (int i = 0; i < num_steps && ok; ++i) {
       const int s = i % kStages;
@@ -408,190 +468,242 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       {
-        // The two pages' scale blocks arrived as [page][chunk][K block][32 rows][8 B]; an atom row
-        // is 16 bytes, tokens 0-63 (first page) in its low half, 64-127 in its high half. Every
-        // lane reads all its pieces before any lane writes, so the exchange is done in place.
+        // The page's scale block arrived as [chunk][K block][32 rows][8 B] (64 tokens: two row quads
+        // of four group scales). An atom row is 16 bytes, with room for four quads, and an N = 64
+        // product reads only two: so one atom carries both K blocks of a chunk, the first in the low
+        // half of every row (tensor-memory columns 0-1 of the atom), the second in the high half
+        // (columns 2-3). Every lane reads all its pieces before any lane writes: done in place.
         uint8_t* sf = sm.k_sf[s];
-        uint2 first[8], second[8];
+        uint2 low[kChunks], high[kChunks];
 #pragma unroll
-        for (int a = 0; a < 8; ++a) {
-          first[a] = *reinterpret_cast<const uint2*>(sf + a * 256 + lane * 8);
-          second[a] = *reinterpret_cast<const uint2*>(sf + 2048 + a * 256 + lane * 8);
+        for (int c = 0; c < kChunks; ++c) {
+          low[c] = *reinterpret_cast<const uint2*>(sf + c * 512 + lane * 8);
+          high[c] = *reinterpret_cast<const uint2*>(sf + c * 512 + 256 + lane * 8);
         }
         __syncwarp();
 #pragma unroll
-        for (int a = 0; a < 8; ++a)
-          *reinterpret_cast<uint4*>(sf + a * 512 + lane * 16) = make_uint4(first[a].x, first[a].y, second[a].x, second[a].y);
+        for (int c = 0; c < kChunks; ++c)
+          *reinterpret_cast<uint4*>(sf + c * 512 + lane * 16) = make_uint4(low[c].x, low[c].y, high[c].x, high[c].y);
         tc::fence_proxy_async_smem();
         __syncwarp();
       }
       if (lane == 0) {
-        // the K scale columns are free once the previous step's score product has completed
-        if (i > 0) ok = wait_at(15, &sm.s_full, (i - 1) & 1, abort_flag);
+        // this set of K scale columns is free once the score product of two steps ago has completed
+        if (i > 1) ok = wait_at(15, &sm.s_full[i & 1], ((i - 2) >> 1) & 1, abort_flag);
         if (ok) {
           tc::fence_after_sync();
 #pragma unroll
-          for (int a = 0; a < 2 * kChunks; ++a)
-            tc::cp_sf_atom(tmem + kColSFK + 4 * a, tc::sf_atom_desc(tc::smem_u32(sm.k_sf[s]) + a * 512));
-          tc::commit(&sm.sfk_ready);
+          for (int c = 0; c < kChunks; ++c)
+            tc::cp_sf_atom(tmem + kColSFK + 16 * (i & 1) + 4 * c, tc::sf_atom_desc(tc::smem_u32(sm.k_sf[s]) + c * 512));
+          tc::commit(&sm.sfk_ready[i & 1]);
         }
       }
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
     }
   } else {
-    // ---- softmax: kSoftmaxGroups threads per query head, each owning a run of the step's tokens ---
+    // ---- softmax: kSoftmaxGroups threads per query head, each owning a run of the page's tokens ---
     const int warp_q = warp & 3;            // TMEM lane quarter this warp may read
-    const int wg = (warp - 4) >> 2;         // which run of kRun tokens of every step
+    const int wg = (warp - 4) >> 2;         // which run of kRun tokens of the CTA's page
     const int h = warp_q * 32 + lane;       // head = TMEM lane of S and O
+    const int slot = cta * kSoftmaxGroups + wg;  // this thread among its head's threads of the pair
     const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
     const float shift = p.p_mode == BDFP4_P_AMAX2_OR_AMAX6_C8 ? 3.0f : 0.0f;
     // A probability this large against the stale maximum means the maximum may have to move; the
     // trigger is a little below the rule's 2^8 so that the rule itself is only ever applied to the
-    // exact scores (the slow path), never to an approximate exponential.
+    // exact scores (the examination), never to an approximate exponential.
     const float trigger_above = exp2f(kRescaleThreshold - 0.25f + shift);
     float row_max = -INFINITY, row_sum = 0.0f, max_scaled = 0.0f;
-    const int p_row = h * 64;
-    const int sf_row = (h & 31) * 16 + (h >> 5) * 4;
-    constexpr int kRunGroups = kRun / 16;
+    // this thread's bytes of its CTA's P half: groups 2 wg, 2 wg + 1 of the page's four
+    // the page's group `n` of a head: 8 bytes of the head's 32-byte row, whose 16-byte halves the swizzle swaps
+    auto p_offset = [&](int n) { return h * 32 + (((n >> 1) ^ ((h >> 2) & 1)) << 4) + (n & 1) * 8; };
+    const int sf_row = (h & 31) * 16 + (h >> 5) * 4 + wg * kRunGroups;
+    int examined = 0;  // steps so far on which the maxima were examined: the phase of `exchange`
 
-    for (int i = 0; i < num_steps; ++i) {
-      const int b = i & 1;
-      const int step = last_step - 1 - i;
-      wait_at(8, &sm.s_full, i & 1, abort_flag);
+    // arrival of this warp on a barrier of both CTAs, after every lane's stores
+    auto warp_arrives = [&](uint64_t* bar) {
+      __syncwarp();
+      if (lane == 0) {
+        tc::mbar_arrive_release_cluster(bar);
+        tc::mbar_arrive_cluster(in_peer(bar));
+      }
+    };
+    // ... on a barrier of this CTA only
+    auto warp_arrives_here = [&](uint64_t* bar) {
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(bar);
+    };
+
+    // The walk is pipelined by one step: iteration i reads the scores of step i and forms its P half
+    // against the maximum in force, and only then looks at how step i - 1 came out in the pair (both
+    // halves in place, nobody asked for the examination: almost always), so the time the halves take
+    // to cross between the CTAs is spent forming. Step i's half is announced after that look; if
+    // step i - 1 had to be examined, both halves are formed again first, in order. The scores of the
+    // step awaiting its outcome stay in registers.
+    float s_prev[kRun], s_cur[kRun];
+    float sum_prev = 0.0f, largest = 0.0f;
+
+    auto load_scores = [&](int i, float* s) {
+      const int sb = i & 1;
+      wait_at(8, &sm.s_full[sb], (i >> 1) & 1, abort_flag);
       tc::fence_after_sync();
-      float s[kRun];
 #pragma unroll
-      for (int q = 0; q < kRunGroups; ++q) tc::tmem_ld16(lane_base + kColS + wg * kRun + 16 * q, s + 16 * q);
+      for (int q = 0; q < kRunGroups; ++q) tc::tmem_ld16(lane_base + kColS + kOwn * sb + wg * kRun + 16 * q, s + 16 * q);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       // one lane arrives for the warp: hundreds of per-thread arrivals on one barrier serialise
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&sm.s_empty);
-      const int valid = seq_len - step * kStep - wg * kRun;  // only the row's last step can be short
+      if (lane == 0) tc::mbar_arrive(&sm.s_empty[sb]);
+      const int step = last_step - 1 - i;
+      const int valid = seq_len - step * kStep - cta * kOwn - wg * kRun;  // only the row's last step can be short
       if (valid < kRun) {
 #pragma unroll
         for (int k = 0; k < kRun; ++k) s[k] = k < valid ? s[k] : -INFINITY;
       }
-      // Probabilities of this thread's run against `max_scaled`, quantized sixteen at a time and
-      // stored as the PV product's A operand with their scale bytes. Forming and quantizing are one
-      // loop so that the exponentials of one group overlap the conversions of the one before.
-      // Returns the run's sum; `largest` is its largest probability. (The PV product of two steps ago
-      // is done with this P buffer: its completion was observed at the end of the previous step.)
-      float largest = 0.0f;
-      auto form_and_store = [&]() -> float {
-        float run_sum = 0.0f;
-        uint64_t scale_bytes = 0;
-        largest = 0.0f;
+    };
+
+    // Probabilities of this thread's run of step i against `max_scaled`, quantized sixteen at a time
+    // and stored into this CTA's P half with their scale bytes. Forming and quantizing are one loop so
+    // that the exponentials of one group overlap the conversions of the one before. Returns the run's
+    // sum; `largest` becomes its largest probability.
+    auto form_and_store = [&](int i, const float* s) -> float {
+      PHalf& half = sm.p[i % kPBuffers][cta];
+      float run_sum = 0.0f;
+      uint32_t scale_bytes = 0;
+      largest = 0.0f;
 #pragma unroll
-        for (int g = 0; g < kRunGroups; ++g) {
-          float prob[16];
+      for (int g = 0; g < kRunGroups; ++g) {
+        float prob[16];
 #pragma unroll
-          for (int k = 0; k < 16; ++k) prob[k] = ex2_approx(fmaf(s[16 * g + k], p.scale_log2, -max_scaled));
-          // sums and maxima as trees: few warps share a scheduler, so a serial chain is paid in full
-          float sum4[4], max4[4];
+        for (int k = 0; k < 16; ++k) prob[k] = ex2_approx(fmaf(s[16 * g + k], p.scale_log2, -max_scaled));
+        // sums and maxima as trees: few warps share a scheduler, so a serial chain is paid in full
+        float sum4[4], max4[4];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            sum4[k] = (prob[k] + prob[k + 4]) + (prob[k + 8] + prob[k + 12]);
-            max4[k] = fmaxf(fmaxf(prob[k], prob[k + 4]), fmaxf(prob[k + 8], prob[k + 12]));
-          }
-          run_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-          const float group_max = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
-          largest = fmaxf(largest, group_max);
-          const float scale = probability_scale(group_max, p.p_mode, p.tau);
-          const float inverse = rcp_approx(fmaxf(scale, 1e-20f));
-          uint32_t words[2] = {0, 0};
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            words[k >> 2] |= cvt_e2m1x2(prob[2 * k] * inverse, prob[2 * k + 1] * inverse) << (8 * (k & 3));
-          *reinterpret_cast<uint2*>(sm.p_tile[b] + swizzle64(p_row + (wg * kRunGroups + g) * 8)) = make_uint2(words[0], words[1]);
-          scale_bytes |= (uint64_t)cvt_e4m3(scale) << (8 * g);
+        for (int k = 0; k < 4; ++k) {
+          sum4[k] = (prob[k] + prob[k + 4]) + (prob[k + 8] + prob[k + 12]);
+          max4[k] = fmaxf(fmaxf(prob[k], prob[k + 4]), fmaxf(prob[k + 8], prob[k + 12]));
         }
-        // this thread's scale bytes: groups wg * kRunGroups ... of the step's eight, four per K block
-        const int first_group = wg * kRunGroups;
-        uint8_t* dst = sm.p_sf[b][first_group >> 2] + sf_row + (first_group & 3);
-        if constexpr (kRunGroups == 1) *dst = (uint8_t)scale_bytes;
-        if constexpr (kRunGroups == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)scale_bytes;
-        if constexpr (kRunGroups == 4) *reinterpret_cast<uint32_t*>(dst) = (uint32_t)scale_bytes;
-        if constexpr (kRunGroups == 8) {  // both K blocks of the step
-          *reinterpret_cast<uint32_t*>(dst) = (uint32_t)scale_bytes;
-          *reinterpret_cast<uint32_t*>(dst + 512) = (uint32_t)(scale_bytes >> 32);
-        }
-        return run_sum;
-      };
-      float run_sum = form_and_store();  // against the stale maximum: almost always final
-      const bool trigger = i == 0 || *abort_flag != 0 || largest > trigger_above;
-      bool observed = false;  // whether this step has already waited for the previous PV product
-      if (softmax_vote_any(trigger)) {
-        // the stale-maximum rule on the exact scores, identically in every thread of a head
-        float run_max = s[0];
+        run_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        const float group_max = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
+        largest = fmaxf(largest, group_max);
+        const float scale = probability_scale(group_max, p.p_mode, p.tau);
+        const float inverse = rcp_approx(fmaxf(scale, 1e-20f));
+        uint32_t words[2] = {0, 0};
 #pragma unroll
-        for (int k = 1; k < kRun; ++k) run_max = fmaxf(run_max, s[k]);
-        sm.red[i & 1][wg][h] = run_max;
-        softmax_barrier();
-        float block_max = sm.red[i & 1][0][h];
-#pragma unroll
-        for (int w = 1; w < kSoftmaxGroups; ++w) block_max = fmaxf(block_max, sm.red[i & 1][w][h]);
-        float acc = 1.0f;
-        if (i == 0) {
-          row_max = block_max;
-          acc = 0.0f;
-        } else if (block_max > row_max) {
-          const float safe = block_max == -INFINITY ? 0.0f : block_max;
-          const float growth = (row_max - safe) * p.scale_log2;
-          if (growth < -kRescaleThreshold) {
-            acc = ex2_approx(growth);
-            row_max = block_max;
-          }
-        }
-        max_scaled = (row_max == -INFINITY ? 0.0f : row_max) * p.scale_log2 - shift;
-        if (i > 0 && __any_sync(0xffffffffu, acc != 1.0f)) {
-          // O so far is rescaled in tensor memory, each thread of a head taking its share of the
-          // columns. Every earlier PV product has completed once the previous step's has, and the
-          // next one is not issued before this step's P has arrived from every thread.
-          wait_at(9, &sm.o_done, (i - 1) & 1, abort_flag);
-          observed = true;
-          tc::fence_after_sync();
-#pragma unroll 1
-          for (int q = 0; q < kShare / 16; ++q) {
-            float o[16];
-            tc::tmem_ld16(lane_base + kColO + wg * kShare + 16 * q, o);
-            tc::tmem_wait_ld();
-#pragma unroll
-            for (int k = 0; k < 16; ++k) o[k] *= acc;
-            tc::tmem_st16(lane_base + kColO + wg * kShare + 16 * q, o);
-          }
-          tc::tmem_wait_st();
-          tc::fence_before_sync();
-        }
-        row_sum *= acc;
-        run_sum = form_and_store();  // again, against the maximum now in force
+        for (int k = 0; k < 8; ++k)
+          words[k >> 2] |= cvt_e2m1x2(prob[2 * k] * inverse, prob[2 * k + 1] * inverse) << (8 * (k & 3));
+        *reinterpret_cast<uint2*>(half.codes + p_offset(wg * kRunGroups + g)) = make_uint2(words[0], words[1]);
+        scale_bytes |= (uint32_t)cvt_e4m3(scale) << (8 * g);
       }
-      row_sum += run_sum;
-      tc::fence_proxy_async_smem();
-      // Every PV product's completion is observed in turn (a parity wait can only tell the current
-      // phase from the one before it): the previous step's here, unless the rescale above already did.
-      if (i > 0 && !observed) wait_at(11, &sm.o_done, (i - 1) & 1, abort_flag);
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&sm.p_full[b]);
+      static_assert(kRunGroups == 1 || kRunGroups == 2, "one or two scale bytes per thread and step");
+      if constexpr (kRunGroups == 1) half.sf[sf_row] = (uint8_t)scale_bytes;
+      if constexpr (kRunGroups == 2) *reinterpret_cast<uint16_t*>(half.sf + sf_row) = (uint16_t)scale_bytes;
+      return run_sum;
+    };
+
+    for (int i = 0; i <= num_steps; ++i) {
+      const bool forming = i < num_steps;
+      float sum_cur = 0.0f;
+      if (forming) {
+        load_scores(i, s_cur);
+        // The P buffer of three steps ago is free: this CTA's PV product of that step was observed an
+        // iteration ago, and the peer had seen that half before it announced the step after it,
+        // which the last look waited for. (Step 0 is always examined: nothing to form yet.)
+        if (i > 0) sum_cur = form_and_store(i, s_cur);
+      }
+      if (i > 0) {
+        // ---- how step j = i - 1 came out
+        const int j = i - 1, bj = j % kPBuffers;
+        // PV products complete in order; every completion is observed in turn (a parity wait can only
+        // tell the current phase from the one before it, and the product of step j may be done already:
+        // hence one barrier for even steps and one for odd)
+        if (j > 0) wait_at(11, &sm.o_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag);
+        wait_at(9, &sm.p_local[bj], (j / kPBuffers) & 1, abort_flag);
+        wait_at(19, &sm.p_remote[bj], (j / kPBuffers) & 1, abort_flag);
+        if (j == 0 || *const_cast<volatile int*>(&sm.p[bj][0].examine) == j + 1 ||
+            *const_cast<volatile int*>(&sm.p[bj][1].examine) == j + 1) {
+          // ---- the examination: the stale-maximum rule on the exact scores of all 128 tokens of
+          // step j, identically in every thread of a head in both CTAs
+          float run_max = s_prev[0];
+#pragma unroll
+          for (int k = 1; k < kRun; ++k) run_max = fmaxf(run_max, s_prev[k]);
+          float* mine = &sm.red[examined & 1][slot][h];
+          *mine = run_max;
+          tc::cluster_store_b32(in_peer(mine), __float_as_uint(run_max));
+          warp_arrives(&sm.exchange);
+          wait_at<true>(10, &sm.exchange, examined & 1, abort_flag);
+          float block_max = sm.red[examined & 1][0][h];
+#pragma unroll
+          for (int w = 1; w < kSlots; ++w) block_max = fmaxf(block_max, sm.red[examined & 1][w][h]);
+          ++examined;
+          float acc = 1.0f;
+          if (j == 0) {
+            row_max = block_max;
+            acc = 0.0f;
+          } else if (block_max > row_max) {
+            const float safe = block_max == -INFINITY ? 0.0f : block_max;
+            const float growth = (row_max - safe) * p.scale_log2;
+            if (growth < -kRescaleThreshold) {
+              acc = ex2_approx(growth);
+              row_max = block_max;
+            }
+          }
+          max_scaled = (row_max == -INFINITY ? 0.0f : row_max) * p.scale_log2 - shift;
+          if (j > 0 && __any_sync(0xffffffffu, acc != 1.0f)) {
+            // O so far is rescaled in tensor memory, each thread of a head taking its share of its
+            // CTA's columns. The PV product of step j - 1 has completed (observed above), and step
+            // j's is not issued before both halves have been formed again.
+            tc::fence_after_sync();
+#pragma unroll 1
+            for (int q = 0; q < kShare / 16; ++q) {
+              float o[16];
+              tc::tmem_ld16(lane_base + kColO + wg * kShare + 16 * q, o);
+              tc::tmem_wait_ld();
+#pragma unroll
+              for (int k = 0; k < 16; ++k) o[k] *= acc;
+              tc::tmem_st16(lane_base + kColO + wg * kShare + 16 * q, o);
+            }
+            tc::tmem_wait_st();
+            tc::fence_before_sync();
+          }
+          row_sum *= acc;
+          // Step j again, against the maximum now in force. (The first copy of this half has been
+          // seen by the peer's threads before they exchanged maxima, so it is no longer being read.)
+          sum_prev = form_and_store(j, s_prev);
+          tc::fence_proxy_async_smem();
+          warp_arrives_here(&sm.again_local);
+          if (forming) sum_cur = form_and_store(i, s_cur);  // and step i, not announced yet
+        }
+        row_sum += sum_prev;
+      }
+      if (forming) {
+        if (i > 0 && __any_sync(0xffffffffu, largest > trigger_above) && lane == 0)
+          *const_cast<volatile int*>(&sm.p[i % kPBuffers][cta].examine) = i + 1;
+        tc::fence_proxy_async_smem();
+        warp_arrives_here(&sm.p_local[i % kPBuffers]);
+#pragma unroll
+        for (int k = 0; k < kRun; ++k) s_prev[k] = s_cur[k];
+        sum_prev = sum_cur;
+      }
     }
 
     // ---- normalise and write ------------------------------------------------------------------
-    softmax_barrier();  // the last slow step's exchange has been read by every thread
-    sm.red[0][wg][h] = row_sum;
-    softmax_barrier();
-    float total = sm.red[0][0][h];
+    sm.sums[slot][h] = row_sum;
+    tc::cluster_store_b32(in_peer(&sm.sums[slot][h]), __float_as_uint(row_sum));
+    warp_arrives(&sm.exchange);
+    wait_at<true>(16, &sm.exchange, examined & 1, abort_flag);
+    float total = sm.sums[0][h];
 #pragma unroll
-    for (int w = 1; w < kSoftmaxGroups; ++w) total += sm.red[0][w][h];
+    for (int w = 1; w < kSlots; ++w) total += sm.sums[w][h];
     const bool empty = num_steps == 0 || total == 0.0f || total != total;
     const float inverse = empty ? 0.0f : 1.0f / total;
     const int64_t head = (int64_t)row * p.heads_q + head0 + h;
-    if (p.out == nullptr && half == 0 && wg == 0 && h < valid_heads) {
+    if (p.out == nullptr && slot == 0 && h < valid_heads) {
       const float safe = row_max == -INFINITY ? 0.0f : row_max;
       p.partial_lse[(int64_t)part * p.rows * p.heads_q + head] =
           empty ? -INFINITY : (safe * p.scale_log2 + log2f(total) - shift) * 0.6931471805599453f;
     }
-    if (num_steps > 0) {
-      wait_at(12, &sm.o_done, (num_steps - 1) & 1, abort_flag);
+    if (num_steps > 0) {  // the loop observed every completion but the last step's
+      wait_at(12, &sm.o_done[(num_steps - 1) & 1], ((num_steps - 1) >> 1) & 1, abort_flag);
       tc::fence_after_sync();
     }
 #pragma unroll 1
@@ -604,7 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
 #pragma unroll
       for (int k = 0; k < 16; ++k) o[k] = empty ? 0.0f : o[k] * inverse;
       if (h < valid_heads) {
-        const int channel = half * kHalf + wg * kShare + 16 * q;
+        const int channel = cta * kHalf + wg * kShare + 16 * q;
         if (p.out != nullptr) {
           uint4 lo, hi;
           lo.x = pack_bf16x2(o[0], o[1]);
@@ -630,8 +742,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
   }
 
   // ---- teardown -------------------------------------------------------------------------------
+  // Neither CTA leaves while the other may still write into its shared memory or arrive on its
+  // barriers: all threads of the pair meet here (every wait above is bounded, so both get here).
+  // Every copy between the two has been waited for by its receiver, unless that gave up: then a copy
+  // may still be under way, so the pair lingers a little and meets once more.
   tc::fence_before_sync();
-  __syncthreads();
+  tc::cluster_sync_all();
+  if (sm.abort_flag) __nanosleep(20000);
+  tc::cluster_sync_all();
   if (tid == 0 && sm.abort_flag && p.error_word)
     atomicOr(p.error_word, (int)BDFP4_DEV_WAIT_TIMEOUT | ((sm.abort_flag & 0xff) << 8));
   if (warp == 1) {
@@ -747,26 +865,38 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* partial_out, 
 
 // Launch with programmatic stream serialization: after a kernel that signals early the CTAs come
 // up and run their preamble while it still runs; after any other kernel this is an ordinary launch.
+// `cluster` > 1 groups that many neighbouring CTAs of the grid into a cluster.
 template <typename... Params, typename... Args>
-static cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                     Args... args) {
-  cudaLaunchAttribute attribute{};
-  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute.val.programmaticStreamSerializationAllowed = 1;
+static cudaError_t launch_overlapped_clusters(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                              cudaStream_t stream, unsigned cluster, Args... args) {
+  cudaLaunchAttribute attributes[2] = {};
+  attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[0].val.programmaticStreamSerializationAllowed = 1;
+  attributes[1].id = cudaLaunchAttributeClusterDimension;
+  attributes[1].val.clusterDim.x = cluster;
+  attributes[1].val.clusterDim.y = 1;
+  attributes[1].val.clusterDim.z = 1;
   cudaLaunchConfig_t config{};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
+  config.attrs = attributes;
+  config.numAttrs = cluster > 1 ? 2 : 1;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+template <typename... Params, typename... Args>
+static cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  return launch_overlapped_clusters(kernel, grid, block, smem, stream, 1u, args...);
 }
 
 }  // namespace mla
 }  // namespace bdfp4
 
 using namespace bdfp4;
+
 
 extern "C" int bdfp4_mla_quantize_query(const void* query, int64_t row_pitch, int32_t rows, int32_t heads_q,
                                         int32_t scale_mode, void* codes, void* scales, void* stream) {
@@ -876,8 +1006,8 @@ extern "C" int bdfp4_mla_decode(const bdfp4_mla_decode_args* a, void* stream_han
   }
   const int64_t grid = (int64_t)a->rows * p.head_blocks * a->num_splits * 2;
   if (grid > 0x7fffffff) return BDFP4_E_TOO_LARGE;
-  return bdfp4::cuda_status(
-      mla::launch_overlapped(mla::decode_kernel, dim3((unsigned)grid), dim3(mla::kThreads), smem, stream, p));
+  return bdfp4::cuda_status(mla::launch_overlapped_clusters(mla::decode_kernel, dim3((unsigned)grid),
+                                                            dim3(mla::kThreads), smem, stream, 2u, p));
 }
 
 extern "C" int bdfp4_mla_combine(const float* partial_out, const float* partial_lse, int32_t parts, int32_t rows,

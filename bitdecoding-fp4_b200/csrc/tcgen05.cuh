@@ -40,6 +40,69 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// ---- a pair of CTAs (a cluster of two) working through each other's shared memory ------------
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+
+// The address, in the cluster's shared window, of `smem_address` as CTA `cta` of the cluster has it.
+__device__ __forceinline__ uint32_t cluster_address(uint32_t smem_address, uint32_t cta) {
+  uint32_t mapped;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(mapped) : "r"(smem_address), "r"(cta));
+  return mapped;
+}
+
+__device__ __forceinline__ void cluster_store_b16(uint32_t cluster_addr, uint16_t v) {
+  asm volatile("st.shared::cluster.b16 [%0], %1;" ::"r"(cluster_addr), "h"(v) : "memory");
+}
+
+__device__ __forceinline__ void cluster_store_b32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void cluster_store_v2(uint32_t cluster_addr, uint32_t x, uint32_t y) {
+  asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(cluster_addr), "r"(x), "r"(y) : "memory");
+}
+
+// One arrival on an mbarrier of another CTA of the cluster; releases this thread's earlier writes
+// (its own shared memory's and the peer's) to whoever acquires the barrier's phase at cluster scope.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Bulk copy from this CTA's shared memory into a peer's (both 16-byte aligned, size a multiple of
+// 16); the bytes are counted on an mbarrier of the peer. Source and destination are accessed by the
+// async proxy: generic-proxy writes of the source need a proxy fence before the copy is issued.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t peer_dst, const void* src, uint32_t bytes, uint32_t peer_bar) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(peer_dst),
+               "r"(smem_u32(src)), "r"(bytes), "r"(peer_bar)
+               : "memory");
+}
+
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
