@@ -212,14 +212,16 @@ def partition(spec: dict, world: int, rank: int, kv_groups: int = 0) -> dict:
                 text=f"{heads_kv} of {total_kv} KV heads x {len(mine)} of {rows} rows per rank, no collective")
 
 
-def common_config(spec: dict, part_text: str, page_tokens: int) -> dict:
+def common_config(spec: dict, part_text: str, page_tokens: int, scale_mode: str = "nvfp4") -> dict:
     """The `config` object both arms print, key for key."""
+    mx = scale_mode.startswith("mxfp4")
     return {
         "workload": spec["label"],
         "partition": part_text,
         "sink_tokens": SINK_USED, "recent_tokens": 128,
-        "query": "two NVFP4 terms, Hadamard", "key_scale_mode": "four_six", "value_scale_mode": "amax6",
-        "p_scale_mode": "amax2_or_amax6_c8", "page_tokens": page_tokens,
+        "query": f"two {'MXFP4' if mx else 'NVFP4'} terms, Hadamard",
+        "key_scale_mode": scale_mode if mx else "four_six", "value_scale_mode": scale_mode if mx else "amax6",
+        "p_scale_mode": "mxfp4 adjacent-exponent search" if mx else "amax2_or_amax6_c8", "page_tokens": page_tokens,
         "l2": "the cache walked per step exceeds the 126 MB L2 (or, for the small workloads, is re-read from "
               "HBM-resident pages after an L2-sized flush write between rounds)",
     }
@@ -273,6 +275,10 @@ def cpu_baseline_entry(measured: dict) -> dict:
 def run_reference(args) -> None:
     """`--impl reference`: the reference's CPU implementation of the step on the host cores (rank 0 only)."""
     if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if args.scale_mode != "nvfp4":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's CPU model timed here is the NVFP4 one; "
+                          "run this arm without --scale-mode"}))
         return
     spec = workload_spec(args)
     part = partition(spec, args.gpus, 0, args.kv_groups)
@@ -389,7 +395,7 @@ def run_gqa(args) -> None:
     import torch.distributed as dist
 
     import bdfp4
-    from bdfp4.workload import build_workload
+    from bdfp4.workload import build_workload, split_lengths
     from nvfp4_decode_kernel import DecodeTailWrite, fp4_decode, split_partial_count
     from nvfp4_decode_kernel import _decode as decode_module
     from nvfp4_decode_kernel._quantize import quantize_query
@@ -413,12 +419,19 @@ def run_gqa(args) -> None:
     rows = len(lengths)
     page_tokens = args.page_tokens
 
+    mx = args.scale_mode.startswith("mxfp4")
+    if mx and page_tokens != 128:
+        raise SystemExit("an MXFP4 cache has 128-token pages: pass --page-tokens 128")
+    key_mode, value_mode, query_mode = (args.scale_mode,) * 3 if mx else ("four_six", "amax6", "amax6")
+    scale_format = "mxfp4" if mx else "nvfp4"
     w = build_workload(rows=rows, heads_q=heads_q, heads_kv=heads_kv, seq_lens=lengths, sink_tokens=SINK_ROWS,
-                       seed=1000 + rank, device=device, key_scale_mode="four_six", value_scale_mode="amax6",
+                       seed=1000 + rank, device=device, key_scale_mode=key_mode, value_scale_mode=value_mode,
                        rotate=True, page_tokens=page_tokens)
     w.seqused_sink.clamp_(max=SINK_USED)
     w.sink_tokens = SINK_USED
     algorithmic_bytes = w.algorithmic_bytes()
+    if mx:  # one E8M0 byte per 32 values instead of one E4M3 byte per 16: 136 bytes per token and head side
+        algorithmic_bytes -= sum(split_lengths(n, SINK_USED)[1] for n in lengths) * heads_kv * 8
     sms = decode_module._multiprocessor_count(local_rank)
     # split count from the batch width only (never from device lengths): enough partitions to keep the
     # whole launch resident at four CTAs per SM
@@ -434,9 +447,10 @@ def run_gqa(args) -> None:
     scratch = dict(
         query_padded_scratch=torch.zeros(rows, 128, heads_q, 128, dtype=torch.bfloat16, device=device),
         query_fp4_scratch=torch.zeros(rows, 1, heads_q, 64, dtype=torch.uint8, device=device),
-        query_scales_scratch=torch.zeros(rows, 1, heads_q, 2, 32, 4, 4, dtype=torch.uint8, device=device),
+        query_scales_scratch=torch.zeros(rows, 1, heads_q, 1 if mx else 2, 32, 4, 4, dtype=torch.uint8, device=device),
         query_fp4_second_scratch=torch.zeros(rows, 1, heads_q, 64, dtype=torch.uint8, device=device),
-        query_scales_second_scratch=torch.zeros(rows, 1, heads_q, 2, 32, 4, 4, dtype=torch.uint8, device=device),
+        query_scales_second_scratch=torch.zeros(rows, 1, heads_q, 1 if mx else 2, 32, 4, 4, dtype=torch.uint8,
+                                                device=device),
     )
     if splits > 1:
         scratch["split_partial_scratch"] = torch.empty(parts * rows * heads_q * 128, device=device)
@@ -477,7 +491,7 @@ def run_gqa(args) -> None:
             query, *w.regions, w.page_table, w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
             residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
             seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, out=out, trusted_metadata=True,
-            num_splits=splits, query_terms=2, scale_mode="amax6", query_rotation="hadamard", tail_write=tail,
+            num_splits=splits, query_terms=2, scale_mode=query_mode, query_rotation="hadamard", tail_write=tail,
             row_order=row_order, **scratch)
         if long_step is not None:
             long_step()
@@ -508,7 +522,7 @@ def run_gqa(args) -> None:
             query_fp4_scratch=scratch["query_fp4_scratch"], query_scales_scratch=scratch["query_scales_scratch"],
             query_fp4_second_scratch=scratch["query_fp4_second_scratch"],
             query_scales_second_scratch=scratch["query_scales_second_scratch"], query_terms=2, rotation="hadamard",
-            tail_write=tail)
+            scale_mode=query_mode, tail_write=tail)
 
     quantized = quantize_step()
     kernel_args = bdfp4.DecodeArgs()
@@ -520,7 +534,7 @@ def run_gqa(args) -> None:
         fp4_page_table=w.page_table, seqused_fp4=w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
         residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
         seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, softmax_scale=128 ** -0.5,
-        row_order=row_order)
+        row_order=row_order, scale_format=scale_format)
     page_cost = decode_module.BF16_BLOCK_PAGE_COST if parts == splits and splits > 1 else 0
     if args.bf16_cost >= 0:
         page_cost = args.bf16_cost
@@ -633,7 +647,7 @@ def run_gqa(args) -> None:
     if q_pages >= 64:
         source_k = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
         source_v = torch.randn(q_pages * page_tokens, heads_kv, 128, generator=gen, device=device).to(torch.bfloat16)
-        writer = KVCacheWriter(regions=w.regions, key_scale_mode="four_six", value_scale_mode="amax6", rotate_key=True)
+        writer = KVCacheWriter(regions=w.regions, key_scale_mode=key_mode, value_scale_mode=value_mode, rotate_key=True)
         work_src = torch.arange(q_pages, dtype=torch.int32, device=device) * page_tokens
         used = torch.cat([w.page_table[r, :int(w.seqused_fp4[r]) // page_tokens] for r in range(rows)])
         work_dst = used[:q_pages].contiguous()
@@ -647,7 +661,7 @@ def run_gqa(args) -> None:
         end.record()
         barrier()
         quant_ms = begin.elapsed_time(end) / 5
-        quant_bytes = q_pages * heads_kv * 2 * (page_tokens * 256 + page_tokens * 72)
+        quant_bytes = q_pages * heads_kv * 2 * (page_tokens * 256 + page_tokens * (68 if mx else 72))
         quantize = {"ms": quant_ms, "bytes": quant_bytes, "gb_s": quant_bytes / (quant_ms * 1e-3) / 1e9,
                     "page_heads": q_pages * heads_kv * 2}
 
@@ -662,7 +676,7 @@ def run_gqa(args) -> None:
         torch.manual_seed(0)
         tiles = [(int(torch.randint(rows, (1,))), int(torch.randint(heads_kv, (1,)))) for _ in range(args.verify)]
         verified = tile_check.check_tiles(
-            w, result, tiles, terms=2, scale_mode="amax6", rotate=True, num_splits=splits, bf16_split=parts > splits,
+            w, result, tiles, terms=2, scale_mode=query_mode, rotate=True, num_splits=splits, bf16_split=parts > splits,
             bf16_page_cost=decode_module.BF16_BLOCK_PAGE_COST if parts == splits and splits > 1 else 0)
         verified["tolerance"] = {"max_abs": 1e-2, "mean_rel": 1e-3}
         verified["against"] = "CPU oracle on sampled (row, KV head) tiles of this run's cache"
@@ -682,12 +696,13 @@ def run_gqa(args) -> None:
     traffic = algorithmic_bytes * ((638.7 / 630.3) if page_tokens == 64 else (637.9 / 630.2))
     if rank == 0:
         launches = 2 + (1 if splits > 1 and not args.fused_merge else 0) + (1 if small else 0) + (5 if mixed else 0)
-        config = common_config(spec, part["text"], page_tokens)
+        config = common_config(spec, part["text"], page_tokens, args.scale_mode)
         line = {
             "metric": "decode_attn_us_per_step" if not mixed else "mixed_step_us",
             "value": step_ms * 1e3, "unit": "us/step", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": step_ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate", "data": "synthetic", "config": config,
+            "dtype": "fp4(e2m1)+ue8m0 / f32 accumulate" if mx else "fp4(e2m1)+ue4m3 / f32 accumulate",
+            "data": "synthetic", "config": config,
             "launch": {"num_splits": splits, "parts": parts, "bf16_page_cost": page_cost,
                        "row_order": "longest first" if ragged else "index order",
                        "l2_flush_between_steps": small, "l2_flush_us_removed": flush_ms * 1e3},
@@ -719,7 +734,7 @@ def run_gqa(args) -> None:
         if quantize is not None:
             line["quantize_gb_s"] = quantize["gb_s"]
             line["roofline_quantize"] = {
-                "bound": "hbm", "kernel": "kv_page_kernel (K: Hadamard + four_six search, V: amax6)",
+                "bound": "hbm", "kernel": f"kv_page_kernel (K: Hadamard + {key_mode}, V: {value_mode})",
                 "achieved": quantize["gb_s"], "peak": peak, "unit": "GB/s", "frac": quantize["gb_s"] / peak,
                 "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": quantize["bytes"],
                 "units_per_launch": f"{quantize['page_heads']} page-heads x {page_tokens * 328} B "
@@ -1112,6 +1127,10 @@ def main() -> None:
                         help="ranks along the KV-head axis (default: as many as there are KV heads, then rows)")
     parser.add_argument("--bf16-cost", type=int, default=-1,
                         help="pages split 0 is charged for the tail and sink (default: the library's)")
+    parser.add_argument("--scale-mode", default="nvfp4",
+                        choices=["nvfp4", "mxfp4_ocp", "mxfp4_round_up", "mxfp4_search"],
+                        help="cache and query format of the GQA workloads: NVFP4 (K four_six, V and Q amax6) or "
+                             "MXFP4 with one E8M0 rule for all three (128-token pages only)")
     parser.add_argument("--page-tokens", type=int, default=64, choices=[64, 128],
                         help="tokens per cache page: 64 as the benchmark configuration names it, or the "
                              "reference's 128")

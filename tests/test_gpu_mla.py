@@ -153,6 +153,13 @@ def test_decode_rescales_when_the_maximum_moves_late():
     _check(w, 128)
 
 
+def test_one_row_at_the_benchmarked_length():
+    # 32,768 tokens, 128 heads: the length the MLA bench line is quoted at (one row of its 64), with a
+    # second short row so that the pair's barriers also see rows of very different lengths in one launch
+    w = _build([32768, 192], 128, 23)
+    _check(w, 128)
+
+
 @pytest.mark.parametrize("num_splits", [2, 5])
 def test_decode_split_and_merge(num_splits):
     w = _build([1024, 200, 64], 64, 19)
