@@ -691,9 +691,9 @@ def run_gqa(args) -> None:
     achieved = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
     clocks = sampler.summary()
     # DRAM traffic per launch is an estimate: algorithmic bytes times the ratio ncu measured on the
-    # 8,192-token capture of the same kernel (638.7 / 630.3 MB with 64-token pages, 637.9 / 630.2 MB
+    # 8,192-token capture of the same kernel (639.8 / 630.3 MB with 64-token pages, 637.9 / 630.2 MB
     # with 128-token pages); traffic grows in proportion to the pages walked.
-    traffic = algorithmic_bytes * ((638.7 / 630.3) if page_tokens == 64 else (637.9 / 630.2))
+    traffic = algorithmic_bytes * ((639.8 / 630.3) if page_tokens == 64 else (637.9 / 630.2))
     if rank == 0:
         launches = 2 + (1 if splits > 1 and not args.fused_merge else 0) + (1 if small else 0) + (5 if mixed else 0)
         config = common_config(spec, part["text"], page_tokens, args.scale_mode)
@@ -715,7 +715,7 @@ def run_gqa(args) -> None:
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "traffic_source": "estimated from the ncu capture under profiles/ (ratio to "
-                                                      "algorithmic bytes 1.013 / 1.012), not measured in this run",
+                                                      "algorithmic bytes 1.015 / 1.012), not measured in this run",
                 "peak_kind": f"of {peak_kind}", "kernel": "decode_kernel",
                 "algorithmic_bytes_per_launch": algorithmic_bytes,
                 # context, not the denominator: the same copy measured back to back in this very run
