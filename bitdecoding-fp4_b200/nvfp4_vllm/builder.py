@@ -22,38 +22,42 @@ MAX_DECODE_SPLITS = 32
 
 
 def decode_num_splits(rows: int, num_kv_heads: int, sms: int) -> int:
-    """Key partitions from the batch width, the KV heads and the SM count alone (so a captured
-    graph replays correctly at any context length): the largest power of two that fits, then filled
-    up to one short of the next power of two while one CTA per (row, KV head) is kept free for the
-    BF16 tail and sink."""
+    """Key partitions of a decode batch, from its width, the KV heads and the SM count only — never
+    from a sequence length, so that a captured graph replays correctly at any context.
+
+    With one CTA per (row, KV head, partition), ``fit`` partitions fill the GPU once. The answer is the
+    largest power of two within ``min(fit, MAX_DECODE_SPLITS)``, raised to ``fit - 1`` (one CTA per
+    row and KV head stays free for the BF16 tail and sink) when that lies strictly between this power
+    of two and the next, i.e. costs no extra level in the merge."""
     if rows < 1:
         return 1
-    per_split = rows * num_kv_heads
-    budget = min(sms // per_split, MAX_DECODE_SPLITS)
-    splits = 1
-    while splits * 2 <= budget:
-        splits *= 2
-    filled = sms // per_split - 1
-    return filled if splits < filled < 2 * splits else splits
+    fit = sms // (rows * num_kv_heads)
+    capped = min(fit, MAX_DECODE_SPLITS)
+    power = 1 << (capped.bit_length() - 1) if capped > 0 else 1
+    return fit - 1 if power < fit - 1 < 2 * power else power
 
 
 def decode_split(common_attn_metadata: CommonAttentionMetadata) -> tuple[int, int]:
-    """Where this step's decode prefix ends, in rows and in tokens, from host-side batch
-    descriptions only. Raises unless the one-token rows are a prefix of the batch (graph-padding
-    rows with no token may only be a suffix of that prefix)."""
-    num_decodes, _, num_decode_tokens, _ = split_decodes_and_prefills(common_attn_metadata, decode_threshold=1)
-    query_start_loc = common_attn_metadata.query_start_loc_cpu
-    num_reqs = common_attn_metadata.num_reqs
-    query_lens = query_start_loc[1:num_reqs + 1] - query_start_loc[:num_reqs]
-    decode_lens = query_lens[:num_decodes]
-    scheduled = int((decode_lens > 0).sum())
-    if not bool((decode_lens[:scheduled] == 1).all()) or not bool((query_lens[num_decodes:] > 1).all()):
+    """(rows, tokens) of this step's decode prefix, checked against the host-side copy of the batch's
+    query offsets (already materialized by the model runner: no synchronization).
+
+    The read path hands the first ``rows`` requests to the decode kernel, so they must be exactly the
+    one-token requests: a prefix of ones, then — when a full graph pads the batch to its captured
+    width — only empty rows, and behind the prefix only requests of more than one token. Anything
+    else means the batch was not reordered, and is refused loudly here rather than decoded wrongly."""
+    rows, _, tokens, _ = split_decodes_and_prefills(common_attn_metadata, decode_threshold=1)
+    offsets = common_attn_metadata.query_start_loc_cpu[:common_attn_metadata.num_reqs + 1]
+    lengths = torch.diff(offsets).tolist()
+    prefix, behind = lengths[:rows], lengths[rows:]
+    live = sum(1 for n in prefix if n > 0)
+    padded_ones = prefix == [1] * live + [0] * (len(prefix) - live)
+    if not padded_ones or any(n <= 1 for n in behind):
         raise ValueError(
             "the NVFP4 read path needs one-token requests at the front of the "
-            f"batch, but query lengths are {query_lens.tolist()} with a decode "
-            f"prefix of {num_decodes}"
+            f"batch, but query lengths are {lengths} with a decode "
+            f"prefix of {rows}"
         )
-    return num_decodes, num_decode_tokens
+    return rows, tokens
 
 
 class NVFP4MetadataBuilder(FlashAttentionMetadataBuilder):
