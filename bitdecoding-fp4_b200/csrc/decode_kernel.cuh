@@ -352,6 +352,56 @@ __host__ __device__ constexpr int decode_min_ctas(int stages, int sg) {
   return sg == 1 ? (stages <= 2 ? 4 : 2) : (stages <= 3 ? 3 : 2);
 }
 
+// MXFP4 probability operand: which rows of a chunk take the lower of their two candidate exponents.
+// `err[4 * row + k]` are this lane's (token's) terms of the four sums of a row: k = 0 the error under
+// the upper exponent, 1 its square, 2 and 3 the same under the lower exponent. The 4 * ROWS values
+// cross the warp's 32 lanes in a reduce-scatter butterfly (each step halves the values a lane holds and
+// doubles the lanes they are summed over), finished by plain butterfly steps, so that lane L ends up
+// with the complete sum of value (L >> SHIFT) & (4 * ROWS - 1); two more exchanges bring mass and squares
+// of a candidate together (cost = mass^2 / 32 + squares, one FMA) and then the two candidates. Returns
+// the warp's ballot of "the lower exponent costs less"; row `r` of the chunk reads bit
+// `mx_verdict_bit<ROWS>(r)`.
+template <int ROWS>
+struct MxButterfly {
+  static_assert(ROWS == 1 || ROWS == 2 || ROWS == 4, "rows per chunk");
+  static constexpr int kValues = 4 * ROWS;
+  static constexpr int kScatterSteps = ROWS == 1 ? 2 : ROWS == 2 ? 3 : 4;
+  static constexpr int kShift = 5 - kScatterSteps;
+};
+
+template <int ROWS>
+__device__ __forceinline__ constexpr int mx_verdict_bit(int row) {
+  return (row * 4) << MxButterfly<ROWS>::kShift;
+}
+
+template <int ROWS>
+__device__ __forceinline__ uint32_t mx_lower_exponent_wins(float (&err)[4 * ROWS], int lane) {
+  using B = MxButterfly<ROWS>;
+#pragma unroll
+  for (int s = 0; s < B::kScatterSteps; ++s) {
+    const int offset = 16 >> s;
+    const int held = B::kValues >> (s + 1);
+    const bool upper_half = (lane & offset) != 0;
+#pragma unroll
+    for (int i = 0; i < held; ++i) {
+      const float keep = upper_half ? err[i + held] : err[i];
+      const float send = upper_half ? err[i] : err[i + held];
+      err[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, offset));
+    }
+  }
+  float total = err[0];
+#pragma unroll
+  for (int offset = 16 >> B::kScatterSteps; offset >= 1; offset >>= 1)
+    total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, offset));
+  const float partner = __shfl_xor_sync(0xffffffffu, total, 1 << B::kShift);  // mass <-> squares of a candidate
+  const bool holds_mass = ((lane >> B::kShift) & 1) == 0;
+  const float mass = holds_mass ? total : partner, squares = holds_mass ? partner : total;
+  const float cost = __fmaf_rn(mass * 0.03125f, mass, squares);
+  const float other = __shfl_xor_sync(0xffffffffu, cost, 2 << B::kShift);     // upper <-> lower candidate
+  const bool holds_lower = ((lane >> (B::kShift + 1)) & 1) != 0;
+  return __ballot_sync(0xffffffffu, holds_lower ? cost < other : other < cost);
+}
+
 template <int GP, int TERMS, int STAGES, int PT, bool MX, int SG>
 __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG))
     decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -1009,29 +1059,37 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
         // maximum at or below six; take the exponent below it when that lowers
         // (sum of errors)^2 / 32 + (sum of squared errors), both sums formed by the warp's butterfly
         // and combined by one FMA.
+        // Rows are taken four at a time: their 16 error sums (mass and squares under each of the two
+        // exponents) cross the warp in ONE reduce-scatter butterfly of 18 shuffles instead of twenty
+        // per row.
+        constexpr int kChunk = R < 4 ? R : 4;
 #pragma unroll
-        for (int j = 0; j < R; ++j) {
-          const float value = prob[j];
-          const float maximum = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(value)));
-          const int upper = mx_round_up_exponent(maximum);
-          const int lower = max(upper - 1, -127);
-          const float scaled_upper = value * mx_power_of_two(-upper), scaled_lower = value * mx_power_of_two(-lower);
-          const float read_upper = e2m1x2_to_float2(cvt_e2m1x2(scaled_upper, 0.0f)).x * mx_power_of_two(upper);
-          const float read_lower = e2m1x2_to_float2(cvt_e2m1x2(scaled_lower, 0.0f)).x * mx_power_of_two(lower);
-          float mass_upper = __fsub_rn(read_upper, value), mass_lower = __fsub_rn(read_lower, value);
-          float squares_upper = __fmul_rn(mass_upper, mass_upper), squares_lower = __fmul_rn(mass_lower, mass_lower);
+        for (int base = 0; base < R; base += kChunk) {
+          float err[4 * kChunk], scaled_upper[kChunk], scaled_lower[kChunk];
+          int upper[kChunk];
 #pragma unroll
-          for (int step = 1; step < 32; step <<= 1) {
-            mass_upper = __fadd_rn(mass_upper, __shfl_xor_sync(0xffffffffu, mass_upper, step));
-            mass_lower = __fadd_rn(mass_lower, __shfl_xor_sync(0xffffffffu, mass_lower, step));
-            squares_upper = __fadd_rn(squares_upper, __shfl_xor_sync(0xffffffffu, squares_upper, step));
-            squares_lower = __fadd_rn(squares_lower, __shfl_xor_sync(0xffffffffu, squares_lower, step));
+          for (int j = 0; j < kChunk; ++j) {
+            const float value = prob[base + j];
+            const float maximum = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(value)));
+            upper[j] = mx_round_up_exponent(maximum);
+            const int lower = max(upper[j] - 1, -127);
+            scaled_upper[j] = value * mx_power_of_two(-upper[j]);
+            scaled_lower[j] = value * mx_power_of_two(-lower);
+            const float read_upper = e2m1x2_to_float2(cvt_e2m1x2(scaled_upper[j], 0.0f)).x * mx_power_of_two(upper[j]);
+            const float read_lower = e2m1x2_to_float2(cvt_e2m1x2(scaled_lower[j], 0.0f)).x * mx_power_of_two(lower);
+            const float mass_upper = __fsub_rn(read_upper, value), mass_lower = __fsub_rn(read_lower, value);
+            err[4 * j + 0] = mass_upper;
+            err[4 * j + 1] = __fmul_rn(mass_upper, mass_upper);
+            err[4 * j + 2] = mass_lower;
+            err[4 * j + 3] = __fmul_rn(mass_lower, mass_lower);
           }
-          const float cost_upper = __fmaf_rn(mass_upper * 0.03125f, mass_upper, squares_upper);
-          const float cost_lower = __fmaf_rn(mass_lower * 0.03125f, mass_lower, squares_lower);
-          const bool take_lower = cost_lower < cost_upper;
-          mx_exponent[j] = take_lower ? lower : upper;
-          prob[j] = take_lower ? scaled_lower : scaled_upper;
+          const uint32_t verdict = mx_lower_exponent_wins<kChunk>(err, lane);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            const bool take_lower = (verdict >> mx_verdict_bit<kChunk>(j)) & 1u;
+            mx_exponent[base + j] = take_lower ? max(upper[j] - 1, -127) : upper[j];
+            prob[base + j] = take_lower ? scaled_lower[j] : scaled_upper[j];
+          }
         }
       } else if constexpr (kScatter) {
         // the lane holding a row's group maximum turns it into the group's scale once; the
@@ -1213,20 +1271,42 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
         if (t == 0 && sgroup == 0) p.merge_counters[tile] = 0;
         constexpr float kLog2e = 1.4426950408889634f;
         const int64_t lse_stride = (int64_t)p.rows * p.heads_q;
+        // This CTA sits on the launch's critical path (every tile's last part ends with the kernel),
+        // so its reads must not queue behind one another: all the tile's LSEs come in with one
+        // parallel load into shared memory (the first K stage, long consumed), and a head's partial
+        // values are fetched eight parts at a time before any of them is used. The arithmetic and its
+        // order are those of the merge kernel.
+        float* staged = reinterpret_cast<float*>(sm.k_stage[0]);  // [part][G]
+        const int staged_parts = min(p.parts, (int)(sizeof(sm.k_stage[0]) / sizeof(float)) / G);
+        for (int i = t; i < staged_parts * R; i += 128) {
+          const int s = i / R, j = row0 + i % R;
+          if (j < G) staged[s * G + j] = __ldcg(p.partial_lse + s * lse_stride + (int64_t)row * p.heads_q + kv_head * G + j);
+        }
+        softmax_barrier(barrier);
         for (int j = row0; j < min(row0 + R, G); ++j) {  // each group merges the heads it owns
           const int head = kv_head * G + j;
           const float* lse = p.partial_lse + (int64_t)row * p.heads_q + head;
           const float* values = p.partial_out + ((int64_t)row * p.heads_q + head) * kHeadDim + t;
+          auto lse_of = [&](int s) { return s < staged_parts ? staged[s * G + j] : __ldcg(lse + s * lse_stride); };
           float lse_max = -INFINITY;
-          for (int s = 0; s < p.parts; ++s) lse_max = fmaxf(lse_max, __ldcg(lse + s * lse_stride));
+          for (int s = 0; s < p.parts; ++s) lse_max = fmaxf(lse_max, lse_of(s));
           if (lse_max == -INFINITY) lse_max = 0.0f;
           float weight_sum = 0.0f;
-          for (int s = 0; s < p.parts; ++s) weight_sum += exp2f(__ldcg(lse + s * lse_stride) * kLog2e - lse_max * kLog2e);
+          for (int s = 0; s < p.parts; ++s) weight_sum += exp2f(lse_of(s) * kLog2e - lse_max * kLog2e);
           const float inverse = (weight_sum == 0.0f || weight_sum != weight_sum) ? 0.0f : 1.0f / weight_sum;
           float acc = 0.0f;
-          for (int s = 0; s < p.parts; ++s) {
-            const float scale = exp2f(__ldcg(lse + s * lse_stride) * kLog2e - lse_max * kLog2e) * inverse;
-            if (scale > 0.0f) acc = acc + scale * __ldcg(values + s * lse_stride * kHeadDim);
+          for (int s0 = 0; s0 < p.parts; s0 += 8) {
+            float fetched[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              fetched[u] = s0 + u < p.parts ? __ldcg(values + (s0 + u) * lse_stride * kHeadDim) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              if (s0 + u < p.parts) {
+                const float scale = exp2f(lse_of(s0 + u) * kLog2e - lse_max * kLog2e) * inverse;
+                if (scale > 0.0f) acc = acc + scale * fetched[u];
+              }
+            }
           }
           p.merged_out[(int64_t)row * p.out_row_stride + head * kHeadDim + t] = __float2bfloat16_rn(acc);
         }
