@@ -493,7 +493,7 @@ def run_gqa(args) -> None:
             residual_value_pages_bf16=wl.tail_value[0], residual_page_ids=wl.slot_ids,
             seqused_residual=wl.seqused_residual if owner_tail else zeros,
             seqused_sink=wl.seqused_sink if owner_sink else zeros, heads_q=HEADS_Q, query_terms=2,
-            query_rotation="hadamard", out=long_out)
+            query_rotation="hadamard", out=long_out, exchange=args.exchange)
         long_bytes = wl.algorithmic_bytes()
 
         def long_step():
@@ -710,7 +710,8 @@ def run_gqa(args) -> None:
     # with 128-token pages); traffic grows in proportion to the pages walked.
     traffic = algorithmic_bytes * ((639.8 / 630.3) if page_tokens == 64 else (637.9 / 630.2))
     if rank == 0:
-        launches = 2 + (1 if splits > 1 and not args.fused_merge else 0) + (1 if small else 0) + (5 if mixed else 0)
+        launches = (2 + (1 if splits > 1 and not args.fused_merge else 0) + (1 if small else 0) +
+                    ((3 if args.exchange == "peer" else 5) if mixed else 0))
         config = common_config(spec, part["text"], page_tokens, args.scale_mode)
         line = {
             "metric": "decode_attn_us_per_step" if not mixed else "mixed_step_us",
@@ -761,6 +762,8 @@ def run_gqa(args) -> None:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_entry(cpu_step(spec, lengths, heads_kv, 12.0, page_tokens))
         print(json.dumps(line))
+    if mixed:
+        long_decoder.close()
     if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()
 
@@ -1077,7 +1080,7 @@ def run_longseq(args) -> None:
         residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
         seqused_residual=w.seqused_residual if owner_tail else zeros,
         seqused_sink=w.seqused_sink if owner_sink else no_sink, query_terms=2, query_rotation="hadamard", out=out,
-        num_splits=args.splits or None)
+        num_splits=args.splits or None, exchange=args.exchange)
 
     def step():
         return decoder(w.query)
@@ -1111,9 +1114,13 @@ def run_longseq(args) -> None:
             "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)+ue4m3 / f32 accumulate", "data": "synthetic",
             "config": {"workload": f"one sequence of {shard * world + 128:,} tokens, 32 query / 8 KV heads, {args.page_tokens}-token "
                                    f"pages, split along the KV axis over {world} ranks; per step: query quantize, shard "
-                                   "decode (split again inside the rank), local merge, one all-gather of [O | LSE] "
-                                   "records, merge",
-                       "tokens_per_rank": shard},
+                                   "decode (split again inside the rank), then " +
+                                   ("ONE kernel that folds the rank's parts, stores its [O | LSE] record into every "
+                                    "rank's memory over NVLink, waits for the others' and merges"
+                                    if args.exchange == "peer" else
+                                    "local merge, one NCCL all-gather of [O | LSE] records, merge"),
+                       "tokens_per_rank": shard, "exchange": args.exchange},
+            "gpu_launches": args.steps * (3 if args.exchange == "peer" else 4),
             "hbm_tb_s": shard_bytes * world / (step_ms * 1e-3) / 1e12,
             "roofline": {"bound": "hbm", "achieved": shard_bytes / (step_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": shard_bytes / (step_ms * 1e-3) / 1e9 / peak, "traffic": None,
@@ -1121,8 +1128,8 @@ def run_longseq(args) -> None:
                          "algorithmic_bytes_per_launch": shard_bytes},
             "clocks": sampler.summary(),
         }))
+    decoder.close()
     dist.destroy_process_group()
-
 
 
 def main() -> None:
@@ -1138,6 +1145,10 @@ def main() -> None:
     parser.add_argument("--heads-kv", type=int, default=0, help="override the KV head count (profiling only)")
     parser.add_argument("--heads-q", type=int, default=0, help="override the query head count (profiling only)")
     parser.add_argument("--splits", type=int, default=0, help="override the split-KV count")
+    parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                        help="the exchange step of the KV-sharded sequence (longseq, mixed): 'peer' = one kernel "
+                             "that stores the [O | LSE] records into the other ranks' memory and merges "
+                             "(bdfp4_exchange_merge), 'nccl' = fold kernel + all-gather + merge kernel")
     parser.add_argument("--kv-groups", type=int, default=0,
                         help="ranks along the KV-head axis (default: as many as there are KV heads, then rows)")
     parser.add_argument("--bf16-cost", type=int, default=-1,

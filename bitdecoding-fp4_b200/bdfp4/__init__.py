@@ -44,6 +44,12 @@ EXPORTS = (
     "bdfp4_mla_append",
     "bdfp4_mla_decode",
     "bdfp4_mla_combine",
+    "bdfp4_exchange_bytes",
+    "bdfp4_peer_alloc",
+    "bdfp4_peer_open",
+    "bdfp4_peer_close",
+    "bdfp4_peer_free",
+    "bdfp4_exchange_merge",
 )
 
 
@@ -158,6 +164,19 @@ class ControlArgs(Structure):
     ]
 
 
+class ExchangeArgs(Structure):
+    """``struct bdfp4_exchange_args``."""
+
+    _fields_ = [
+        ("partial_out", c_void_p), ("partial_lse", c_void_p),
+        ("parts", c_int32), ("rows", c_int32), ("heads_q", c_int32), ("world", c_int32), ("rank", c_int32),
+        ("step", ctypes.c_uint32),
+        ("regions", c_void_p * 8),
+        ("out", c_void_p), ("out_row_stride", c_int64),
+        ("error_word", c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -213,6 +232,18 @@ def library() -> ctypes.CDLL:
     lib.bdfp4_mla_decode.restype = c_int32
     lib.bdfp4_mla_decode.argtypes = [POINTER(MlaDecodeArgs), c_void_p]
     lib.bdfp4_mla_combine.restype = c_int32
+    lib.bdfp4_exchange_bytes.restype = c_int64
+    lib.bdfp4_exchange_bytes.argtypes = [c_int32, c_int32, c_int32]
+    lib.bdfp4_peer_alloc.restype = c_int32
+    lib.bdfp4_peer_alloc.argtypes = [c_int64, POINTER(c_void_p), c_void_p]
+    lib.bdfp4_peer_open.restype = c_int32
+    lib.bdfp4_peer_open.argtypes = [c_void_p, POINTER(c_void_p)]
+    lib.bdfp4_peer_close.restype = c_int32
+    lib.bdfp4_peer_close.argtypes = [c_void_p]
+    lib.bdfp4_peer_free.restype = c_int32
+    lib.bdfp4_peer_free.argtypes = [c_void_p]
+    lib.bdfp4_exchange_merge.restype = c_int32
+    lib.bdfp4_exchange_merge.argtypes = [POINTER(ExchangeArgs), c_void_p]
     lib.bdfp4_mla_combine.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p]
     lib.bdfp4_decode_split_static.restype = c_int32
     lib.bdfp4_decode_split_static.argtypes = [POINTER(DecodeArgs), c_void_p]
@@ -284,6 +315,42 @@ def combine_strided(partial_out_ptr: int, out_part_stride: int, partial_lse_ptr:
         library().bdfp4_combine_strided(partial_out_ptr, out_part_stride, partial_lse_ptr, lse_part_stride, parts,
                                         rows, heads_q, ptr(out), out_row_stride, stream),
     )
+
+
+def exchange_bytes(world: int, rows: int, heads_q: int) -> int:
+    """Bytes of one rank's exchange region for :func:`exchange_merge`."""
+    size = int(library().bdfp4_exchange_bytes(world, rows, heads_q))
+    if size <= 0:
+        raise ValueError(f"no exchange region for world={world}, rows={rows}, heads_q={heads_q}")
+    return size
+
+
+def peer_alloc(size: int) -> tuple[int, bytes]:
+    """A zeroed device allocation other processes of this node can map: (address, 64-byte IPC handle)."""
+    local = c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    check("bdfp4_peer_alloc", library().bdfp4_peer_alloc(size, ctypes.byref(local), handle))
+    return int(local.value), handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    """Map another process's :func:`peer_alloc` allocation into this one; returns its address here."""
+    mapped = c_void_p()
+    check("bdfp4_peer_open", library().bdfp4_peer_open(ctypes.create_string_buffer(handle, 64), ctypes.byref(mapped)))
+    return int(mapped.value)
+
+
+def peer_close(address: int) -> None:
+    check("bdfp4_peer_close", library().bdfp4_peer_close(address))
+
+
+def peer_free(address: int) -> None:
+    check("bdfp4_peer_free", library().bdfp4_peer_free(address))
+
+
+def exchange_merge(args: ExchangeArgs, stream: int) -> None:
+    """Fold, send to every rank, wait for every rank, merge: the KV-shard exchange as one launch."""
+    check("bdfp4_exchange_merge", library().bdfp4_exchange_merge(ctypes.byref(args), stream))
 
 
 def decode_split_static(args: DecodeArgs, stream: int) -> None:

@@ -47,6 +47,43 @@ def split_record(gathered: torch.Tensor, world_size: int, rows: int, heads_q: in
     return outs, lses
 
 
+class PeerExchange:
+    """The exchange regions of a process group's ranks on one node, for ``bdfp4_exchange_merge``: this
+    rank's region (allocated by the library, zeroed) and every other rank's mapped into this process
+    through CUDA IPC. Building one is a collective call (the 64-byte handles travel by
+    ``all_gather_object``) and allocates: set-up only. ``close()`` unmaps and frees; call it on every
+    rank before the process group goes away."""
+
+    def __init__(self, rows: int, heads_q: int, group=None):
+        import torch.distributed as dist
+
+        import bdfp4
+
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.rows, self.heads_q = rows, heads_q
+        self.bytes = bdfp4.exchange_bytes(self.world, rows, heads_q)
+        self.local, handle = bdfp4.peer_alloc(self.bytes)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.regions = [self.local if r == self.rank else bdfp4.peer_open(handles[r]) for r in range(self.world)]
+        self.step = 0
+        dist.barrier(group)  # nobody stores into a region before everyone has mapped it
+
+    def next_step(self) -> int:
+        """The stamp of the next exchange: 1, 2, ... (never 0), the same on every rank."""
+        self.step = self.step % 0xFFFFFFFF + 1
+        return self.step
+
+    def close(self) -> None:
+        import bdfp4
+
+        for r, address in enumerate(self.regions):
+            if r != self.rank:
+                bdfp4.peer_close(address)
+        bdfp4.peer_free(self.local)
+        self.regions = []
+
+
 class KvShardedDecoder:
     """One rank's side of the KV-sharded decode, with everything that does not change between steps held
     across them: the shard's cache regions and metadata, the two argument records of the C ABI, the query
@@ -59,6 +96,10 @@ class KvShardedDecoder:
     merge. This library's kernels are launched with programmatic stream serialization, so each one's CTAs
     come up while its predecessor drains.
 
+    With ``exchange="peer"`` (ranks of one node, one process per GPU) the last three are ONE launch,
+    ``bdfp4_exchange_merge``: each rank stores its record straight into the other ranks' memory over
+    NVLink and merges what arrives in its own; same results, bit for bit. Call :meth:`close` at the end.
+
     Pass the BF16 residual arguments only on the rank that owns them (see the module docstring); with
     ``seqused_sink`` but ``seqused_residual`` zero a rank owns the sink alone.
     """
@@ -67,7 +108,8 @@ class KvShardedDecoder:
                  heads_q: int, rows: int = 1, group=None, residual_key_pages_bf16=None,
                  residual_value_pages_bf16=None, residual_page_ids=None, seqused_residual=None, seqused_sink=None,
                  softmax_scale: float | None = None, query_terms: int = 2, scale_mode: str = "amax6",
-                 query_rotation: str = "none", out: torch.Tensor | None = None, num_splits: int | None = None):
+                 query_rotation: str = "none", out: torch.Tensor | None = None, num_splits: int | None = None,
+                 exchange: str = "nccl"):
         import torch.distributed as dist
 
         import bdfp4
@@ -81,7 +123,10 @@ class KvShardedDecoder:
         self.device = device
         has_residual = residual_key_pages_bf16 is not None
         if num_splits is None:
-            num_splits = _decode.resident_num_splits(rows, heads_kv, sms=_decode._multiprocessor_count(device.index or 0))
+            # a shard of one sequence is only `heads_kv` walks: cut it until the launch fills the GPU at four
+            # CTAs per SM (the default cap of 32 parts would leave one or two CTAs per SM here)
+            num_splits = _decode.resident_num_splits(rows, heads_kv, sms=_decode._multiprocessor_count(device.index or 0),
+                                                     max_splits=128)
         self.num_splits = num_splits
         self.record = record_floats(rows, heads_q)
         # buffers: whatever the per-call form would allocate
@@ -128,6 +173,25 @@ class KvShardedDecoder:
             a.num_splits, a.bf16_split, a.out = num_splits, 0, None
             a.partial_out, a.partial_lse = self.partial_out.data_ptr(), self.partial_lse.data_ptr()
         self.decode_args = a
+        # exchange="peer": fold, exchange and merge are ONE kernel storing into the peers' memory
+        # (bdfp4_exchange_merge) instead of fold kernel + NCCL all-gather + merge kernel
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        self.peers = None
+        if exchange == "peer":
+            self.peers = PeerExchange(rows, heads_q, group)
+            x = bdfp4.ExchangeArgs()
+            x.rows, x.heads_q, x.world, x.rank = rows, heads_q, self.world, self.peers.rank
+            if num_splits > 1:
+                x.partial_out, x.partial_lse, x.parts = self.partial_out.data_ptr(), self.partial_lse.data_ptr(), num_splits
+            else:
+                x.partial_out, x.partial_lse, x.parts = self.local.data_ptr(), self.local.data_ptr() + self.lse_offset, 1
+            for r, address in enumerate(self.peers.regions):
+                x.regions[r] = address
+            x.out, x.out_row_stride = self.out.data_ptr(), self.out.stride(0)
+            self.error = torch.zeros(1, dtype=torch.int32, device=device)
+            x.error_word = self.error.data_ptr()
+            self.exchange_args = x
         self._keep = (key_pages_fp4, key_scales, value_pages_fp4, value_scales, fp4_page_table, seqused_fp4,
                       residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids, seqused_residual,
                       seqused_sink)  # the records hold raw addresses: keep their owners alive
@@ -145,6 +209,10 @@ class KvShardedDecoder:
         stream = bdfp4.current_stream(self.device)
         bdfp4.quantize_query(q, stream)
         bdfp4.decode(self.decode_args, stream)
+        if self.peers is not None:
+            self.exchange_args.step = self.peers.next_step()
+            bdfp4.exchange_merge(self.exchange_args, stream)
+            return self.out
         if self.num_splits > 1:
             bdfp4.combine_record(self.partial_out, self.partial_lse, self.num_splits, self.rows, self.heads_q,
                                  self.local.data_ptr(), self.local.data_ptr() + self.lse_offset, stream)
@@ -152,6 +220,13 @@ class KvShardedDecoder:
         bdfp4.combine_strided(self.gathered.data_ptr(), self.record, self.gathered.data_ptr() + self.lse_offset,
                               self.record, self.world, self.rows, self.heads_q, self.out, self.out.stride(0), stream)
         return self.out
+
+
+    def close(self) -> None:
+        """Release the peer mappings (a collective-free call, but make it on every rank)."""
+        if self.peers is not None:
+            self.peers.close()
+            self.peers = None
 
 
 def decode_kv_sharded(query: torch.Tensor, key_pages_fp4, key_scales, value_pages_fp4, value_scales,

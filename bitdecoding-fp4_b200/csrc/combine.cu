@@ -4,6 +4,7 @@
 // (src/nvfp4_decode_kernel/split_k_combine.py:47-83).
 #include "common.cuh"
 #include "host.h"
+#include "merge.cuh"
 
 namespace bdfp4 {
 
@@ -17,25 +18,13 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ 
   const int channel = threadIdx.x;
   const float* lse = partial_lse + (int64_t)row * heads_q + head;
   const float* values = partial_out + ((int64_t)row * heads_q + head) * kHeadDim + channel;
-  constexpr float kLog2e = 1.4426950408889634f;
   // Launched with programmatic stream serialization: the CTAs may be resident before the decode
   // launch that writes the partials has finished, so its results are waited for here; the launch
   // behind this one (the next step's query quantizer) may then bring its CTAs up in turn.
   wait_for_prior_kernels();
   dependents_may_launch();
 
-  float lse_max = -INFINITY;
-  for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, lse[s * lse_stride]);
-  if (lse_max == -INFINITY) lse_max = 0.0f;
-  float weight_sum = 0.0f;
-  for (int s = 0; s < parts; ++s) weight_sum += exp2f(lse[s * lse_stride] * kLog2e - lse_max * kLog2e);
-  const float inverse = (weight_sum == 0.0f || weight_sum != weight_sum) ? 0.0f : 1.0f / weight_sum;
-  float acc = 0.0f;
-  // split order, so a given set of partials always sums to the same bits
-  for (int s = 0; s < parts; ++s) {
-    const float scale = exp2f(lse[s * lse_stride] * kLog2e - lse_max * kLog2e) * inverse;
-    if (scale > 0.0f) acc = acc + scale * values[s * out_stride];
-  }
+  const float acc = fold_parts(values, out_stride, lse, lse_stride, parts, channel, nullptr);
   out[(int64_t)row * out_row_stride + head * kHeadDim + channel] = __float2bfloat16_rn(acc);
 }
 
@@ -52,24 +41,12 @@ __global__ void __launch_bounds__(128) combine_record_kernel(const float* __rest
   const int64_t lse_stride = (int64_t)rows * heads_q;
   const float* lse = partial_lse + (int64_t)row * heads_q + head;
   const float* values = partial_out + ((int64_t)row * heads_q + head) * kHeadDim + channel;
-  constexpr float kLog2e = 1.4426950408889634f;
   wait_for_prior_kernels();
   dependents_may_launch();
-  float lse_max = -INFINITY;
-  for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, lse[s * lse_stride]);
-  const bool empty = lse_max == -INFINITY;
-  if (empty) lse_max = 0.0f;
-  float weight_sum = 0.0f;
-  for (int s = 0; s < parts; ++s) weight_sum += exp2f(lse[s * lse_stride] * kLog2e - lse_max * kLog2e);
-  const float inverse = (weight_sum == 0.0f || weight_sum != weight_sum) ? 0.0f : 1.0f / weight_sum;
-  float acc = 0.0f;
-  for (int s = 0; s < parts; ++s) {
-    const float scale = exp2f(lse[s * lse_stride] * kLog2e - lse_max * kLog2e) * inverse;
-    if (scale > 0.0f) acc = acc + scale * values[s * lse_stride * kHeadDim];
-  }
+  float folded_lse;
+  const float acc = fold_parts(values, lse_stride * kHeadDim, lse, lse_stride, parts, channel, &folded_lse);
   record_out[((int64_t)row * heads_q + head) * kHeadDim + channel] = acc;
-  if (channel == 0)
-    record_lse[(int64_t)row * heads_q + head] = (empty || inverse == 0.0f) ? -INFINITY : lse_max + logf(weight_sum);
+  if (channel == 0) record_lse[(int64_t)row * heads_q + head] = folded_lse;
 }
 
 // After a decode launch of this library (which lets its dependents launch early) the merge's CTAs are

@@ -336,6 +336,42 @@ int bdfp4_combine_strided(const float* partial_out, int64_t out_part_stride, con
                           int64_t out_row_stride, void* stream);
 
 /*
+ * The exchange step of a KV-axis shard as one kernel over peer memory (no counterpart in the
+ * reference, which has no multi-GPU path; it replaces bdfp4_combine_record + an all-gather +
+ * bdfp4_combine_strided). Every rank owns an exchange region of bdfp4_exchange_bytes(world, rows,
+ * heads_q) bytes, allocated with bdfp4_peer_alloc (zeroed; exported as a 64-byte CUDA IPC handle) and
+ * mapped by the other ranks with bdfp4_peer_open. One call per rank and step: the kernel folds this
+ * rank's `parts` split partials (layout of bdfp4_decode's partial_out / partial_lse) into its [O | LSE]
+ * record, stores the record into every rank's region (plain stores to peer addresses), flags it, waits
+ * - at most two seconds, then BDFP4_DEV_WAIT_TIMEOUT in `error_word` - for the other ranks' records
+ * of the same `step` to arrive in its own region, and merges them in rank order into `out` (BF16
+ * [rows][out_row_stride]) with the arithmetic of bdfp4_combine. `step` must change on every call and
+ * never be 0; all ranks pass the same value. One process per GPU: the kernels of different ranks wait
+ * for each other and must not share a GPU. The peer_* calls allocate, map and synchronise: set-up only.
+ */
+typedef struct bdfp4_exchange_args {
+  const float* partial_out; /* this rank's split partials, [parts][rows][heads_q][128] */
+  const float* partial_lse; /* [parts][rows][heads_q], natural log */
+  int32_t parts;
+  int32_t rows;
+  int32_t heads_q;
+  int32_t world; /* 1..8 */
+  int32_t rank;
+  uint32_t step;
+  void* regions[8]; /* every rank's exchange region as mapped in this process; regions[rank] is the own one */
+  void* out;
+  int64_t out_row_stride;
+  int32_t* error_word; /* optional */
+} bdfp4_exchange_args;
+
+int64_t bdfp4_exchange_bytes(int32_t world, int32_t rows, int32_t heads_q);
+int bdfp4_peer_alloc(int64_t bytes, void** local, void* handle /* 64 bytes out */);
+int bdfp4_peer_open(const void* handle /* 64 bytes */, void** mapped);
+int bdfp4_peer_close(void* mapped);
+int bdfp4_peer_free(void* local);
+int bdfp4_exchange_merge(const bdfp4_exchange_args* args, void* stream);
+
+/*
  * One step of the device-side slot table that maps the rows of a batch to BF16 tail slots and
  * derives each row's sink / FP4 / rolling-tail lengths and promotion target, with no value read
  * back to the host. Replaces ControlPlane.prepare and its Triton kernel _control_kernel

@@ -163,6 +163,24 @@ def _nccl_worker(rank, world, port, result_dir):
     torch.save(out.cpu(), os.path.join(result_dir, f"out{rank}.pt"))
     if rank == 0:
         torch.save(_oracle_sharded(w, world, 3), os.path.join(result_dir, "want.pt"))
+    # the same exchange as ONE kernel over peer memory: identical bits, on every one of several steps
+    # (the two record sets alternate), with the rank's parts folded in the kernel and without parts
+    from bdfp4.distributed import KvShardedDecoder
+
+    same = True
+    for splits in (3, 1):
+        kwargs = dict(heads_q=8, rows=1, residual_key_pages_bf16=w.tail_key[0], residual_value_pages_bf16=w.tail_value[0],
+                      residual_page_ids=w.slot_ids, seqused_residual=residual, seqused_sink=sink, query_terms=2,
+                      num_splits=splits)
+        through_nccl = KvShardedDecoder(*w.regions, table, used, **kwargs)(w.query).clone()
+        peer = KvShardedDecoder(*w.regions, table, used, exchange="peer", **kwargs)
+        for _ in range(5):
+            got = peer(w.query)
+            torch.cuda.synchronize()
+            same = same and torch.equal(got, through_nccl) and int(peer.error.item()) == 0
+        dist.barrier()
+        peer.close()
+    torch.save(torch.tensor(same), os.path.join(result_dir, f"peer_same{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -182,3 +200,45 @@ def test_shards_as_nccl_ranks(tmp_path):
     for out in outs:
         _check(out, want)
         assert torch.equal(out, outs[0])  # every rank merges the same records in the same order
+    assert all(bool(torch.load(tmp_path / f"peer_same{r}.pt")) for r in range(world))
+
+
+def test_exchange_kernel_alone_on_one_rank():
+    """`bdfp4_exchange_merge` with a world of one (its own region only, nothing to wait for): the fold and
+    the merge give the bits of `bdfp4_combine` on the same partials, step after step; argument checks."""
+    import bdfp4
+
+    torch.manual_seed(5)
+    parts, rows, hq = 3, 2, 8
+    partial_out = torch.randn(parts, rows, hq, 128, device="cuda")
+    partial_lse = torch.randn(parts, rows, hq, device="cuda") * 3
+    partial_lse[1, 0, 3] = float("-inf")  # a part that saw no token
+    want = torch.empty(rows, hq, 128, dtype=torch.bfloat16, device="cuda")
+    stream = bdfp4.current_stream(want.device)
+    bdfp4.combine(partial_out, partial_lse, parts, rows, hq, want, want.stride(0), stream)
+    region, _ = bdfp4.peer_alloc(bdfp4.exchange_bytes(1, rows, hq))
+    try:
+        got = torch.zeros_like(want)
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        a = bdfp4.ExchangeArgs()
+        a.partial_out, a.partial_lse, a.parts = partial_out.data_ptr(), partial_lse.data_ptr(), parts
+        a.rows, a.heads_q, a.world, a.rank = rows, hq, 1, 0
+        a.regions[0] = region
+        a.out, a.out_row_stride, a.error_word = got.data_ptr(), got.stride(0), error.data_ptr()
+        for step in (1, 2, 3):
+            got.zero_()
+            a.step = step
+            bdfp4.exchange_merge(a, stream)
+            torch.cuda.synchronize()
+            assert int(error.item()) == 0
+            # folding first and merging one record is the merge of the parts up to FP32 rounding of
+            # the record: compare in BF16 with one ulp of slack
+            assert torch.allclose(got.float(), want.float(), rtol=2 ** -7, atol=1e-6)
+        a.step = 0
+        with pytest.raises(bdfp4.KernelError):
+            bdfp4.exchange_merge(a, stream)
+        a.step, a.world = 4, 9
+        with pytest.raises(bdfp4.KernelError):
+            bdfp4.exchange_merge(a, stream)
+    finally:
+        bdfp4.peer_free(region)
