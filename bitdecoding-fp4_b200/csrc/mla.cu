@@ -23,25 +23,28 @@
 //   S[head, token]  = sum over 4 chunks  Q_chunk[head, :] . K_chunk[token, :]   8 x mxf4nvf4 (N = 64, K = 64)
 //                   + q_rope[head, :] . rope[token, :]                           4 x kind::f16  (N = 64, K = 16)
 //   O[head, chan]  += P[head, :] . V^T[chan, :]                                  2 x mxf4nvf4 (N = 256, K = 64)
-// Each head has four softmax threads per CTA (16 tokens of the page each). A thread reads its scores
-// from tensor memory, forms the probabilities against the stale maximum and quantizes them (the
-// group is in its own registers: no shuffles). A warp that saw a probability large enough that a
-// maximum may have to move (the stale-maximum rule tolerates 2^8) stamps the step's number into a
-// request word that travels with the half. The walk is pipelined by one step: a thread forms step
-// i, then looks at how step i - 1 came out (both halves in place, no request: almost always), then
-// announces step i; so the halves cross between the CTAs while the next ones are formed, and the
-// two CTAs never wait for each other with nothing to do. On a requested step all threads of the
-// pair exchange their maxima (stores into both CTAs' shared memory), apply the exact rule
-// identically, rescale their share of O in place in tensor memory and form steps i - 1 and i
-// again; the PV issuers wait for the second copy. O (256 columns) stays in tensor memory for the
-// whole walk. Three P buffers: one being multiplied, one crossing, one being formed.
+// Each head has four softmax threads per CTA, in two teams that take the steps in turns (team = step
+// parity): a thread forms 32 tokens of every other step, the group of sixteen in its own registers
+// (no shuffles), and looks at the outcome of EVERY step. A thread reads its scores from tensor
+// memory, forms the probabilities against the stale maximum and quantizes them. A warp that saw a
+// probability large enough that a maximum may have to move (the stale-maximum rule tolerates 2^8)
+// stamps the step's number into a request word that travels with the half. The last warp of a team
+// to finish a half sends it (the PV issuer only waits for both halves: the crossing, about 650
+// cycles, stays out of its loop). The walk is pipelined by one step: a thread forms step i (if it
+// is its team's), then looks at how step i - 1 came out (both halves in place, no request: almost
+// always), then announces step i; so the halves cross between the CTAs while the next ones are
+// formed. On a requested step the threads that formed it publish their maxima (stores into both
+// CTAs' shared memory), all threads of the pair apply the exact rule identically and rescale their
+// share of O in place in tensor memory, steps i - 1 and i are formed again by their teams, and the
+// PV issuers wait for the second copy. O (256 columns) stays in tensor memory for the whole walk.
+// Three P buffers: one being multiplied, one crossing, one being formed.
 // Tensor memory: S 2 x 64 (the scores of the next step are formed while this step's are still being
 // read) + O 256 + scale factors 112 columns (K scales in two sets, so that the next step's can be
 // copied in while this step's are in use).
 //
 // Warps: 0 issues the bulk copies from global memory (lane 0 the K side of the CTA's page, lane 1 the
-// V side of both pages); 1, 2 and 3 issue the tensor work, one thread each for QK, for PV (which also
-// sends the P half to the peer), and for the K scale atoms (which the whole of warp 3 first regroups
+// V side of both pages); 1, 2 and 3 issue the tensor work, one thread each for QK, for PV, and for
+// the K scale atoms (which the whole of warp 3 first regroups
 // from the page's 8-byte rows to the 16-byte rows of an atom); 4-19 are the softmax. Every mbarrier
 // wait is bounded and reports its site in bits [8,16) of the error word; a CTA whose peer gave up
 // runs into its own limit and gives up too.
@@ -65,13 +68,17 @@ constexpr int kOwn = 64;      // tokens of a step one CTA scores (its page)
 constexpr int kStages = 3;   // K side (the CTA's page of a step)
 constexpr int kVStages = 2;  // V side (both pages of a step)
 constexpr int kPBuffers = 3;  // P operands: one being multiplied, one under way between the CTAs, one being formed
-constexpr int kSoftmaxGroups = 4;                   // softmax threads per head in a CTA (4 measured faster than 2)
-constexpr int kRun = kOwn / kSoftmaxGroups;         // tokens of a step one softmax thread owns
+constexpr int kSoftmaxGroups = 4;                   // softmax threads per head in a CTA
+constexpr int kTeams = 2;                           // the softmax warps take the steps in turns: team = step % kTeams
+constexpr int kTeamGroups = kSoftmaxGroups / kTeams;  // softmax threads per head that form a given step
+constexpr int kRun = kOwn / kTeamGroups;            // tokens of a step one of them owns
 constexpr int kRunGroups = kRun / 16;
 constexpr int kShare = kHalf / kSoftmaxGroups;      // output columns one softmax thread rescales and writes
 constexpr int kSoftmaxThreads = 128 * kSoftmaxGroups;
 constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;
+constexpr int kTeamWarps = kSoftmaxWarps / kTeams;
 constexpr int kSlots = 2 * kSoftmaxGroups;          // softmax threads per head in the pair
+constexpr int kStepSlots = 2 * kTeamGroups;         // ... of which these form a given step
 constexpr int kThreads = 128 + kSoftmaxThreads;  // producer, QK, PV and K-scale warps, then the softmax warps
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -132,7 +139,7 @@ struct Smem {
   alignas(1024) uint8_t q_rope[kHeads * 128];
   alignas(1024) uint8_t q_sf[kChunks * 2][512];
   PHalf p[kPBuffers][2];                                        // [buffer][page = the CTA that forms it]
-  float red[2][kSlots][kHeads];   // maxima exchanged between a head's softmax threads of the pair
+  float red[2][kStepSlots][kHeads];  // maxima exchanged between the threads of the pair that formed a step
   float sums[kSlots][kHeads];     // their partial sums, at the end
   uint64_t k_full[kStages], ksf_full[kStages], k_empty[kStages], v_full[kVStages], v_empty[kVStages];
   uint64_t s_full[2], s_empty[2], sfk_ready[2];
@@ -140,7 +147,8 @@ struct Smem {
   uint64_t p_local[kPBuffers];   // every softmax warp of this CTA has formed its part of the step's P half
   uint64_t p_remote[kPBuffers];  // the peer's P half of the step has landed here
   uint64_t again_local, again_remote;  // the same, after a step on which the maxima were examined
-  uint64_t exchange;     // every softmax warp of the pair has stored its maxima (or sums) in both CTAs
+  uint64_t exchange;     // every softmax warp of the pair has stored its maxima (if it formed the step) or its sums
+  int formed[kPBuffers], formed_again;  // softmax warps that have finished a half: the last one sends it
   int page_ids[2][32];
   uint32_t tmem_base;
   int abort_flag;
@@ -236,18 +244,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&sm.s_full[b], 1);
-      tc::mbar_init(&sm.s_empty[b], kSoftmaxWarps);  // one arrival per softmax warp
+      tc::mbar_init(&sm.s_empty[b], kTeamWarps);  // one arrival per softmax warp of the step's team
     }
     tc::mbar_init(&sm.o_done[0], 1);
     tc::mbar_init(&sm.o_done[1], 1);
     tc::mbar_init(&sm.sfk_ready[0], 1);
     tc::mbar_init(&sm.sfk_ready[1], 1);
     for (int b = 0; b < kPBuffers; ++b) {
-      tc::mbar_init(&sm.p_local[b], kSoftmaxWarps);
+      tc::mbar_init(&sm.p_local[b], kTeamWarps);
       tc::mbar_init(&sm.p_remote[b], 1);
       sm.p[b][0].examine = sm.p[b][1].examine = 0;
+      sm.formed[b] = 0;
     }
-    tc::mbar_init(&sm.again_local, kSoftmaxWarps);
+    tc::mbar_init(&sm.again_local, kTeamWarps);
+    sm.formed_again = 0;
     tc::mbar_init(&sm.again_remote, 1);
     tc::mbar_init(&sm.exchange, 2 * kSoftmaxWarps);
     sm.abort_flag = 0;
@@ -421,25 +431,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
         const uint32_t p_phase = (m / kPBuffers) & 1;
         const int t = m & 1;  // which set of scale columns in tensor memory
         ok = wait_at(3, &sm.v_full[s], (m / kVStages) & 1, abort_flag);
-        // this CTA's half goes to the peer as soon as it is formed; the peer's comes the same way
-        if (ok) {
-          tc::mbar_expect_tx(&sm.p_remote[b], kPHalfBytes);
-          ok = wait_at(4, &sm.p_local[b], p_phase, abort_flag);
-        }
-        if (ok) {
-          tc::bulk_copy_to_peer(in_peer(&sm.p[b][cta]), &sm.p[b][cta], kPHalfBytes, in_peer(&sm.p_remote[b]));
-          ok = wait_at(17, &sm.p_remote[b], p_phase, abort_flag);
-        }
+        // both halves of the step's P operand: this CTA's (formed here) and the peer's (sent by the last
+        // of its warps to finish forming it)
+        if (ok) ok = wait_at(4, &sm.p_local[b], p_phase, abort_flag);
+        if (ok) ok = wait_at(17, &sm.p_remote[b], p_phase, abort_flag);
         if (ok && (m == 0 || *const_cast<volatile int*>(&sm.p[b][0].examine) == m + 1 ||
                    *const_cast<volatile int*>(&sm.p[b][1].examine) == m + 1)) {
-          // the halves are formed again; the first copy has been seen by the peer's threads before
-          // they exchanged maxima, so the source is free and the destination is not being read
-          tc::mbar_expect_tx(&sm.again_remote, kPHalfBytes);
+          // the halves are formed again and sent again
           ok = wait_at(13, &sm.again_local, examined & 1, abort_flag);
-          if (ok) {
-            tc::bulk_copy_to_peer(in_peer(&sm.p[b][cta]), &sm.p[b][cta], kPHalfBytes, in_peer(&sm.again_remote));
-            ok = wait_at(18, &sm.again_remote, examined & 1, abort_flag);
-          }
+          if (ok) ok = wait_at(18, &sm.again_remote, examined & 1, abort_flag);
           ++examined;
         }
         if (!ok) break;
@@ -503,7 +503,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
   } else {
     // ---- softmax: kSoftmaxGroups threads per query head, each owning a run of the page's tokens ---
     const int warp_q = warp & 3;            // TMEM lane quarter this warp may read
-    const int wg = (warp - 4) >> 2;         // which run of kRun tokens of the CTA's page
+    const int wg = (warp - 4) >> 2;         // this thread among its head's kSoftmaxGroups threads of the CTA
+    const int team = wg / kTeamGroups;      // it forms the steps i with i % kTeams == team ...
+    const int member = wg % kTeamGroups;    // ... and of those, this run of kRun tokens of the CTA's page
     const int h = warp_q * 32 + lane;       // head = TMEM lane of S and O
     const int slot = cta * kSoftmaxGroups + wg;  // this thread among its head's threads of the pair
     const uint32_t lane_base = tmem + ((uint32_t)(warp_q * 32) << 16);
@@ -516,7 +518,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     // this thread's bytes of its CTA's P half: groups 2 wg, 2 wg + 1 of the page's four
     // the page's group `n` of a head: 8 bytes of the head's 32-byte row, whose 16-byte halves the swizzle swaps
     auto p_offset = [&](int n) { return h * 32 + (((n >> 1) ^ ((h >> 2) & 1)) << 4) + (n & 1) * 8; };
-    const int sf_row = (h & 31) * 16 + (h >> 5) * 4 + wg * kRunGroups;
+    const int sf_row = (h & 31) * 16 + (h >> 5) * 4 + member * kRunGroups;
+    const int step_slot = cta * kTeamGroups + member;  // this thread among those of the pair that form its steps
     int examined = 0;  // steps so far on which the maxima were examined: the phase of `exchange`
 
     // arrival of this warp on a barrier of both CTAs, after every lane's stores
@@ -527,10 +530,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
         tc::mbar_arrive_cluster(in_peer(bar));
       }
     };
-    // ... on a barrier of this CTA only
-    auto warp_arrives_here = [&](uint64_t* bar) {
+    // This warp has formed (and proxy-fenced) its part of the P half in buffer `b`: it says so on `local`
+    // for this CTA's readers, and the last warp of the team to get here sends the whole half into the
+    // peer's buffer, counted on the peer's `remote` barrier, after announcing on this CTA's own `remote`
+    // barrier that the peer's half is expected. Sending from here, rather than from the PV issuer, keeps
+    // the crossing (about 650 cycles) out of that thread's loop.
+    auto half_is_formed = [&](int b, uint64_t* local, uint64_t* remote, int* counter) {
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(bar);
+      if (lane == 0) {
+        tc::mbar_arrive(local);
+        __threadfence_block();
+        const int before = atomicAdd(counter, 1);
+        if (before == kTeamWarps - 1) {
+          __threadfence_block();
+          *counter = 0;
+          tc::mbar_expect_tx(remote, kPHalfBytes);
+          tc::bulk_copy_to_peer(in_peer(&sm.p[b][cta]), &sm.p[b][cta], kPHalfBytes, in_peer(remote));
+        }
+      }
     };
 
     // The walk is pipelined by one step: iteration i reads the scores of step i and forms its P half
@@ -539,22 +556,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     // to cross between the CTAs is spent forming. Step i's half is announced after that look; if
     // step i - 1 had to be examined, both halves are formed again first, in order. The scores of the
     // step awaiting its outcome stay in registers.
-    float s_prev[kRun], s_cur[kRun];
-    float sum_prev = 0.0f, largest = 0.0f;
+    float s_own[kRun];   // the scores of the last step this thread formed, until its outcome is known
+    float sum_own = 0.0f, largest = 0.0f;
 
     auto load_scores = [&](int i, float* s) {
       const int sb = i & 1;
       wait_at(8, &sm.s_full[sb], (i >> 1) & 1, abort_flag);
       tc::fence_after_sync();
 #pragma unroll
-      for (int q = 0; q < kRunGroups; ++q) tc::tmem_ld16(lane_base + kColS + kOwn * sb + wg * kRun + 16 * q, s + 16 * q);
+      for (int q = 0; q < kRunGroups; ++q) tc::tmem_ld16(lane_base + kColS + kOwn * sb + member * kRun + 16 * q, s + 16 * q);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       // one lane arrives for the warp: hundreds of per-thread arrivals on one barrier serialise
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sm.s_empty[sb]);
       const int step = last_step - 1 - i;
-      const int valid = seq_len - step * kStep - cta * kOwn - wg * kRun;  // only the row's last step can be short
+      const int valid = seq_len - step * kStep - cta * kOwn - member * kRun;  // only the row's last step can be short
       if (valid < kRun) {
 #pragma unroll
         for (int k = 0; k < kRun; ++k) s[k] = k < valid ? s[k] : -INFINITY;
@@ -591,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           words[k >> 2] |= cvt_e2m1x2(prob[2 * k] * inverse, prob[2 * k + 1] * inverse) << (8 * (k & 3));
-        *reinterpret_cast<uint2*>(half.codes + p_offset(wg * kRunGroups + g)) = make_uint2(words[0], words[1]);
+        *reinterpret_cast<uint2*>(half.codes + p_offset(member * kRunGroups + g)) = make_uint2(words[0], words[1]);
         scale_bytes |= (uint32_t)cvt_e4m3(scale) << (8 * g);
       }
       static_assert(kRunGroups == 1 || kRunGroups == 2, "one or two scale bytes per thread and step");
@@ -601,18 +618,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
     };
 
     for (int i = 0; i <= num_steps; ++i) {
-      const bool forming = i < num_steps;
-      float sum_cur = 0.0f;
-      if (forming) {
-        load_scores(i, s_cur);
+      const bool mine = i < num_steps && i % kTeams == team;  // this thread's team forms step i
+      if (mine) {
+        load_scores(i, s_own);
         // The P buffer of three steps ago is free: this CTA's PV product of that step was observed an
         // iteration ago, and the peer had seen that half before it announced the step after it,
         // which the last look waited for. (Step 0 is always examined: nothing to form yet.)
-        if (i > 0) sum_cur = form_and_store(i, s_cur);
+        sum_own = i > 0 ? form_and_store(i, s_own) : 0.0f;
       }
       if (i > 0) {
-        // ---- how step j = i - 1 came out
+        // ---- how step j = i - 1 came out (every thread looks at every step, whoever formed it)
         const int j = i - 1, bj = j % kPBuffers;
+        const bool formed_j = j % kTeams == team;
         // PV products complete in order; every completion is observed in turn (a parity wait can only
         // tell the current phase from the one before it, and the product of step j may be done already:
         // hence one barrier for even steps and one for odd)
@@ -622,18 +639,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
         if (j == 0 || *const_cast<volatile int*>(&sm.p[bj][0].examine) == j + 1 ||
             *const_cast<volatile int*>(&sm.p[bj][1].examine) == j + 1) {
           // ---- the examination: the stale-maximum rule on the exact scores of all 128 tokens of
-          // step j, identically in every thread of a head in both CTAs
-          float run_max = s_prev[0];
+          // step j, identically in every thread of a head in both CTAs. The threads that formed the
+          // step still hold its scores and publish their maxima; all threads read them.
+          if (formed_j) {
+            float run_max = s_own[0];
 #pragma unroll
-          for (int k = 1; k < kRun; ++k) run_max = fmaxf(run_max, s_prev[k]);
-          float* mine = &sm.red[examined & 1][slot][h];
-          *mine = run_max;
-          tc::cluster_store_b32(in_peer(mine), __float_as_uint(run_max));
+            for (int k = 1; k < kRun; ++k) run_max = fmaxf(run_max, s_own[k]);
+            float* slot_of_mine = &sm.red[examined & 1][step_slot][h];
+            *slot_of_mine = run_max;
+            tc::cluster_store_b32(in_peer(slot_of_mine), __float_as_uint(run_max));
+          }
+          // every warp arrives, also those with nothing to publish: a phase of this barrier can then
+          // not complete before every warp has seen the one before it
           warp_arrives(&sm.exchange);
           wait_at<true>(10, &sm.exchange, examined & 1, abort_flag);
           float block_max = sm.red[examined & 1][0][h];
 #pragma unroll
-          for (int w = 1; w < kSlots; ++w) block_max = fmaxf(block_max, sm.red[examined & 1][w][h]);
+          for (int w = 1; w < kStepSlots; ++w) block_max = fmaxf(block_max, sm.red[examined & 1][w][h]);
           ++examined;
           float acc = 1.0f;
           if (j == 0) {
@@ -666,23 +688,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const Params p) {
             tc::fence_before_sync();
           }
           row_sum *= acc;
-          // Step j again, against the maximum now in force. (The first copy of this half has been
-          // seen by the peer's threads before they exchanged maxima, so it is no longer being read.)
-          sum_prev = form_and_store(j, s_prev);
-          tc::fence_proxy_async_smem();
-          warp_arrives_here(&sm.again_local);
-          if (forming) sum_cur = form_and_store(i, s_cur);  // and step i, not announced yet
+          if (formed_j) {
+            // Step j again, against the maximum now in force. (The first copy of this half has been
+            // seen by the peer's threads before they passed the exchange, so it is no longer being read.)
+            sum_own = form_and_store(j, s_own);
+            tc::fence_proxy_async_smem();
+            half_is_formed(bj, &sm.again_local, &sm.again_remote, &sm.formed_again);
+          }
+          if (mine) sum_own = form_and_store(i, s_own);  // and step i, formed above but not announced yet
         }
-        row_sum += sum_prev;
+        if (formed_j) row_sum += sum_own;
       }
-      if (forming) {
+      if (mine) {
         if (i > 0 && __any_sync(0xffffffffu, largest > trigger_above) && lane == 0)
           *const_cast<volatile int*>(&sm.p[i % kPBuffers][cta].examine) = i + 1;
         tc::fence_proxy_async_smem();
-        warp_arrives_here(&sm.p_local[i % kPBuffers]);
-#pragma unroll
-        for (int k = 0; k < kRun; ++k) s_prev[k] = s_cur[k];
-        sum_prev = sum_cur;
+        half_is_formed(i % kPBuffers, &sm.p_local[i % kPBuffers], &sm.p_remote[i % kPBuffers], &sm.formed[i % kPBuffers]);
       }
     }
 
