@@ -65,7 +65,7 @@ def split_k_heuristic(rows: int, heads_kv: int, max_pages_per_row: int, *, sms: 
     return best
 
 
-def resident_num_splits(rows: int, heads_kv: int, *, sms: int, ctas_per_sm: int = 4, max_splits: int = 32) -> int:
+def resident_num_splits(rows: int, heads_kv: int, *, sms: int, ctas_per_sm: int = 4, max_splits: int = 64) -> int:
     """Split count that keeps the whole launch resident at ``ctas_per_sm`` CTAs per SM.
 
     The decode kernel is bound by HBM only while enough independent CTAs stream at once: each CTA's
@@ -73,7 +73,8 @@ def resident_num_splits(rows: int, heads_kv: int, *, sms: int, ctas_per_sm: int 
     variant fits) hide it. With few (row, KV head) tiles (a small batch, or a KV-head slice of a
     tensor-parallel rank) this asks for more partitions than ``split_k_heuristic`` or the serving
     plugin's ``decode_num_splits`` would. Like them it uses the batch width only, never device
-    lengths, so it is safe under CUDA-graph replay. Not part of the reference's API.
+    lengths, so it is safe under CUDA-graph replay. Not part of the reference's API. (16 tiles of eight
+    query heads per KV head, one rank of eight of a 32 x 131,072 batch: 32 parts 111 us, 37 parts 106 us.)
     """
     tiles = rows * heads_kv
     if tiles < 1 or sms < 1:
