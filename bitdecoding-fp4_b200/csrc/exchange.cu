@@ -18,7 +18,7 @@
 // system scope and reads the records with loads that bypass L1. Every wait is bounded: a record that
 // has not arrived after two seconds is left out and BDFP4_DEV_WAIT_TIMEOUT is set in the error word.
 //
-// No multicast and no bulk/TMA copies are used: ordinary stores to peer addresses.
+// Peer memory is touched with ordinary stores only: no bulk or tensor-map copies, no NVLink reductions.
 #include "common.cuh"
 #include "host.h"
 #include "merge.cuh"
