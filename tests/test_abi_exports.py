@@ -73,9 +73,9 @@ def test_struct_sizes_match_the_header(lib):
 
     import bdfp4
 
-    source = '#include <stdio.h>\n#include "bdfp4.h"\nint main(void){printf("%zu %zu %zu %zu\\n", ' \
+    source = '#include <stdio.h>\n#include "bdfp4.h"\nint main(void){printf("%zu %zu %zu %zu %zu\\n", ' \
              "sizeof(bdfp4_kv_write_args), sizeof(bdfp4_quantize_query_args), sizeof(bdfp4_decode_args), " \
-             "sizeof(bdfp4_mla_decode_args));return 0;}\n"
+             "sizeof(bdfp4_mla_decode_args), sizeof(bdfp4_exchange_args));return 0;}\n"
     with tempfile.TemporaryDirectory() as tmp:
         src = Path(tmp) / "sizes.c"
         src.write_text(source)
@@ -83,4 +83,22 @@ def test_struct_sizes_match_the_header(lib):
         subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
         sizes = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     assert sizes == [ctypes.sizeof(bdfp4.KvWriteArgs), ctypes.sizeof(bdfp4.QuantizeQueryArgs),
-                     ctypes.sizeof(bdfp4.DecodeArgs), ctypes.sizeof(bdfp4.MlaDecodeArgs)]
+                     ctypes.sizeof(bdfp4.DecodeArgs), ctypes.sizeof(bdfp4.MlaDecodeArgs),
+                     ctypes.sizeof(bdfp4.ExchangeArgs)]
+
+
+def test_exchange_region_size_and_argument_checks(lib):
+    """The exchange region holds two sets of one 132-float record and one flag word per (source rank,
+    row, head); a world outside 1..8, a step of zero and missing pointers are refused on the host."""
+    import bdfp4
+
+    assert bdfp4.exchange_bytes(4, 1, 32) == 2 * 4 * 32 * (132 * 4 + 4)
+    assert lib.bdfp4_exchange_bytes(9, 1, 32) == 0 and lib.bdfp4_exchange_bytes(0, 1, 32) == 0
+    with pytest.raises(ValueError):
+        bdfp4.exchange_bytes(9, 1, 32)
+    assert lib.bdfp4_exchange_merge(None, None) == bdfp4.E_ARG
+    a = bdfp4.ExchangeArgs()
+    a.rows, a.heads_q, a.world, a.rank, a.parts, a.step = 1, 8, 2, 0, 1, 1
+    assert lib.bdfp4_exchange_merge(ctypes.byref(a), None) == bdfp4.E_ARG  # no partials, no regions, no output
+    assert lib.bdfp4_peer_alloc(0, None, None) == bdfp4.E_ARG
+    assert lib.bdfp4_peer_open(None, None) == bdfp4.E_ARG
