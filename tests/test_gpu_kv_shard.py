@@ -242,3 +242,47 @@ def test_exchange_kernel_alone_on_one_rank():
             bdfp4.exchange_merge(a, stream)
     finally:
         bdfp4.peer_free(region)
+
+
+def test_exchange_reports_a_rank_that_never_sends():
+    """Failure detection without a fault: a world of two in which the other rank takes no part. Its flag
+    is never written, so the kernel's bounded wait (two seconds) runs out: it reports
+    DEV_WAIT_TIMEOUT in the error word, leaves that rank out of the merge and returns; the context
+    stays usable (the next, complete exchange on the same regions gives the right answer)."""
+    import bdfp4
+
+    torch.manual_seed(9)
+    rows, hq = 1, 8
+    partial_out = torch.randn(1, rows, hq, 128, device="cuda")
+    partial_lse = torch.randn(1, rows, hq, device="cuda")
+    want = torch.empty(rows, hq, 128, dtype=torch.bfloat16, device="cuda")
+    stream = bdfp4.current_stream(want.device)
+    bdfp4.combine(partial_out, partial_lse, 1, rows, hq, want, want.stride(0), stream)
+    size = bdfp4.exchange_bytes(2, rows, hq)
+    mine, _ = bdfp4.peer_alloc(size)
+    silent, _ = bdfp4.peer_alloc(size)  # stands for the other rank's region; nobody runs as that rank
+    try:
+        got = torch.zeros_like(want)
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        a = bdfp4.ExchangeArgs()
+        a.partial_out, a.partial_lse, a.parts = partial_out.data_ptr(), partial_lse.data_ptr(), 1
+        a.rows, a.heads_q, a.world, a.rank, a.step = rows, hq, 2, 0, 1
+        a.regions[0], a.regions[1] = mine, silent
+        a.out, a.out_row_stride, a.error_word = got.data_ptr(), got.stride(0), error.data_ptr()
+        bdfp4.exchange_merge(a, stream)
+        torch.cuda.synchronize()
+        assert int(error.item()) & bdfp4.DEV_WAIT_TIMEOUT
+        assert torch.equal(got, want)  # only this rank's record was merged
+        # the context is intact: a world of one (fresh region) completes at once, without a report
+        error.zero_()
+        got.zero_()
+        alone, _ = bdfp4.peer_alloc(bdfp4.exchange_bytes(1, rows, hq))
+        a.world, a.step = 1, 2
+        a.regions[0] = alone
+        bdfp4.exchange_merge(a, stream)
+        torch.cuda.synchronize()
+        bdfp4.peer_free(alone)
+        assert int(error.item()) == 0 and torch.equal(got, want)
+    finally:
+        bdfp4.peer_free(mine)
+        bdfp4.peer_free(silent)
