@@ -1,6 +1,6 @@
 """Recipe for ``oracle/_ref``: the reference's own CPU model of the path, made importable.
 
-    python oracle/make_ref.py [--reference /root/reference]
+    python oracle/make_ref.py [--reference <checkout of OpenBitSys/BitDecoding-FP4>]
 
 TEST INFRASTRUCTURE. OpenBitSys/BitDecoding-FP4 is pure Python; the CPU model of its quantizers and
 of its decode-order attention is ``src/nvfp4_decode_kernel/reference.py`` with its two small

@@ -1,8 +1,8 @@
 """Generate tests/golden/calibration_vectors.json from the reference's own calibration code.
 
-Run in a container where OpenBitSys/BitDecoding-FP4 is mounted (default /root/reference):
+Run in a container where OpenBitSys/BitDecoding-FP4 is mounted (see --reference):
 
-    python tests/golden/make_calibration_golden.py [--reference /root/reference]
+    python tests/golden/make_calibration_golden.py [--reference <checkout of OpenBitSys/BitDecoding-FP4>]
 
 It imports ``src/nvfp4_decode_kernel/reference.py`` (``online_probability_scale_statistics``) and
 ``src/nvfp4_vllm/probability_calibration.py`` (``threshold_for_code``,

@@ -1,6 +1,6 @@
 """Golden vectors for the device-side control plane, from the reference's own Triton kernels.
 
-    python tests/golden/make_control_golden.py [--reference /root/reference]
+    python tests/golden/make_control_golden.py [--reference <checkout of OpenBitSys/BitDecoding-FP4>]
 
 Runs ``_control_kernel`` (src/nvfp4_vllm/control.py), ``_work_table_kernel`` and
 ``_tail_reset_kernel`` (src/nvfp4_vllm/write.py) of the mounted reference under Triton's CPU

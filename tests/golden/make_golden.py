@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ from the reference's own CPU code.
 
-Run in a container where OpenBitSys/BitDecoding-FP4 is mounted (default /root/reference):
+Run in a container where OpenBitSys/BitDecoding-FP4 is mounted (see --reference):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <checkout of OpenBitSys/BitDecoding-FP4>]
 
 It imports ``src/nvfp4_decode_kernel/reference.py`` (pure PyTorch, CPU), feeds it seeded
 inputs, and stores inputs and outputs in ``tests/golden/reference_vectors.npz``. The tests

@@ -1,6 +1,6 @@
 """Generate tests/golden/mxfp4_vectors.npz from the reference's own CPU code.
 
-    python tests/golden/make_mxfp4_golden.py [--reference /root/reference]
+    python tests/golden/make_mxfp4_golden.py [--reference <checkout of OpenBitSys/BitDecoding-FP4>]
 
 Imports ``src/nvfp4_decode_kernel/reference.py`` of OpenBitSys/BitDecoding-FP4 (pure PyTorch, CPU),
 feeds ``mxfp4_quantize`` (three rules) and ``mxfp4_probability_quantize`` seeded and adversarial
