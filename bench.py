@@ -188,16 +188,16 @@ def workload_spec(args) -> dict:
     raise SystemExit(f"unknown workload {name!r}")
 
 
-def ragged_num_splits(lengths: list[int], heads_kv: int, sms: int, limit: int = 16) -> int:
-    """Key partitions for a batch of very unequal lengths, from lengths the host knows (the scheduler's).
-    Unsplit, the longest row is one CTA's walk and bounds the launch however little the other rows hold:
-    every row is therefore cut into enough parts that the longest part is about what one resident CTA
-    would walk if the batch were spread evenly at four CTAs per SM. (More parts than that lose again:
-    every short row is cut as often, and its parts are mostly set-up. One GPU, 256 Zipf rows x 8 KV
-    heads: 1 part 1,272 us, 3 parts 992 us, 5 parts 1,029 us, 8 parts 1,129 us, 12 parts 1,301 us.)"""
+def ragged_row_splits(lengths: list[int], heads_kv: int, sms: int, limit: int = 16) -> list[int]:
+    """Parts per row for a batch of very unequal lengths (`row_splits` of the decode call): a row is cut
+    into parts of about a third of the share of one resident CTA, so the long rows no longer bound the
+    launch and the short ones are not cut into set-up."""
     steps = [max(1, n // 128) for n in lengths]
-    even_share = sum(steps) * heads_kv / (4 * sms)
-    return max(1, min(limit, math.ceil(max(steps) / max(1.0, even_share))))
+    # a third of that share per part: the parts of a row start one launch wave apart (the grid is part-major),
+    # so finer parts balance better. One GPU, 256 Zipf rows x 8 KV heads, batch kernel: one share per part
+    # 1,110 us, a half 986 us, a third 968 us, a quarter 982 us; three parts for every row 990 us.
+    target = max(1.0, sum(steps) * heads_kv / (4 * sms) / 3)
+    return [max(1, min(limit, math.ceil(n / target))) for n in steps]
 
 
 def partition(spec: dict, world: int, rank: int, kv_groups: int = 0) -> dict:
@@ -450,9 +450,14 @@ def run_gqa(args) -> None:
     # whole launch resident at four CTAs per SM
     splits = args.splits or decode_module.resident_num_splits(rows, heads_kv, sms=sms)
     ragged = len(set(lengths)) > 1
+    row_parts = None
     if ragged and not args.splits:
-        splits = max(splits, ragged_num_splits(lengths, heads_kv, sms))
+        # every row gets the parts its own length calls for; the launch has as many as the longest
+        row_parts = ragged_row_splits(lengths, heads_kv, sms)
+        splits = max(splits if max(row_parts) > 1 else 1, max(row_parts))
+        row_parts = [min(n, splits) for n in row_parts]
     parts = split_partial_count(rows, heads_kv, splits, residual=True, sms=sms)
+    row_splits = torch.tensor(row_parts, dtype=torch.int32, device=device) if row_parts and splits > 1 else None
     row_order = torch.argsort(w.seqused_fp4, descending=True).to(torch.int32) if ragged else None
 
     gen = torch.Generator(device=device).manual_seed(77 + rank)
@@ -507,7 +512,7 @@ def run_gqa(args) -> None:
             residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
             seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, out=out, trusted_metadata=True,
             num_splits=splits, query_terms=2, scale_mode=query_mode, query_rotation="hadamard", tail_write=tail,
-            row_order=row_order, **scratch)
+            row_order=row_order, row_splits=row_splits, **scratch)
         if long_step is not None:
             long_step()
         return result
@@ -549,7 +554,7 @@ def run_gqa(args) -> None:
         fp4_page_table=w.page_table, seqused_fp4=w.seqused_fp4, residual_key_pages_bf16=w.tail_key[0],
         residual_value_pages_bf16=w.tail_value[0], residual_page_ids=w.slot_ids,
         seqused_residual=w.seqused_residual, seqused_sink=w.seqused_sink, softmax_scale=128 ** -0.5,
-        row_order=row_order, scale_format=scale_format)
+        row_order=row_order, scale_format=scale_format, row_splits=row_splits)
     page_cost = decode_module.BF16_BLOCK_PAGE_COST if parts == splits and splits > 1 else 0
     if args.bf16_cost >= 0:
         page_cost = args.bf16_cost
@@ -692,6 +697,7 @@ def run_gqa(args) -> None:
         tiles = [(int(torch.randint(rows, (1,))), int(torch.randint(heads_kv, (1,)))) for _ in range(args.verify)]
         verified = tile_check.check_tiles(
             w, result, tiles, terms=2, scale_mode=query_mode, rotate=True, num_splits=splits, bf16_split=parts > splits,
+            row_splits=row_parts if row_splits is not None else None,
             bf16_page_cost=decode_module.BF16_BLOCK_PAGE_COST if parts == splits and splits > 1 else 0)
         verified["tolerance"] = {"max_abs": 1e-2, "mean_rel": 1e-3}
         verified["against"] = "CPU oracle on sampled (row, KV head) tiles of this run's cache"
@@ -720,6 +726,8 @@ def run_gqa(args) -> None:
             "dtype": "fp4(e2m1)+ue8m0 / f32 accumulate" if mx else "fp4(e2m1)+ue4m3 / f32 accumulate",
             "data": "synthetic", "config": config,
             "launch": {"num_splits": splits, "parts": parts, "bf16_page_cost": page_cost,
+                       "row_splits": None if row_splits is None else
+                       {"min": min(row_parts), "max": max(row_parts), "ctas_with_work": sum(row_parts) * heads_kv},
                        "row_order": "longest first" if ragged else "index order",
                        "l2_flush_between_steps": small, "l2_flush_us_removed": flush_ms * 1e3},
             "timing": {"statistic": "median over rounds of K steps, max over ranks", "rounds": len(resident.rounds),

@@ -129,6 +129,7 @@ class DecodeArgs(Structure):
         ("row_order", c_void_p),
         ("scale_format", c_int32),
         ("key_tensor_scale", c_float), ("query_tensor_scale", c_float), ("value_tensor_scale", c_float),
+        ("row_splits", c_void_p),
     ]
 
 

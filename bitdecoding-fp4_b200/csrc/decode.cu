@@ -221,6 +221,7 @@ extern "C" int bdfp4_decode(const bdfp4_decode_args* a, void* stream_handle) {
   p.merge_counters = merges ? a->merge_counters : nullptr;
   p.merged_out = merges ? static_cast<__nv_bfloat16*>(a->out) : nullptr;
   p.row_order = a->row_order;
+  p.row_splits = (a->num_splits > 1 && a->merge_counters == nullptr) ? a->row_splits : nullptr;
 
   const bool two = a->query_codes_second != nullptr;
   cudaError_t e;

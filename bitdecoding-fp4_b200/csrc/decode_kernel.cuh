@@ -450,17 +450,29 @@ __global__ void __launch_bounds__(decode_threads(SG), decode_min_ctas(STAGES, SG
       // Split 0 also merges the tail and the sink when they have no split of their own; it is
       // then charged `bf16_page_cost` pages for them, so that every split ends at the same time
       // (cost 0 is the even partition of src/nvfp4_decode_kernel/fp4_decode_kernel.py:4686-4746).
+      // A row may be cut into fewer parts than the launch has (`row_splits`): its further parts
+      // find no pages.
+      const int row_parts = p.row_splits ? min(max(p.row_splits[row], 1), p.num_splits) : p.num_splits;
       const int bias = (with_bf16 && !p.bf16_split) ? p.bf16_page_cost : 0;
-      const int chunk = (total_pages + bias + p.num_splits - 1) / p.num_splits;
+      const int chunk = (total_pages + bias + row_parts - 1) / row_parts;
       const int first_chunk = max(chunk - bias, 0);
       first_page = part == 0 ? 0 : min(first_chunk + (part - 1) * chunk, total_pages);
-      last_page = min(first_page + (part == 0 ? first_chunk : chunk), total_pages);
+      last_page = part < row_parts ? min(first_page + (part == 0 ? first_chunk : chunk), total_pages) : first_page;
       with_bf16 = with_bf16 && !p.bf16_split && part == 0;
     } else {
       first_page = last_page = 0;
     }
   }
   const int num_pages = last_page - first_page;
+  if (p.row_splits && p.num_splits > 1 && num_pages == 0 && !with_bf16) {
+    // A part with nothing to walk (rows cut into fewer parts than the launch has): it owes the merge
+    // an LSE of -inf for each of its heads and nothing else, so it leaves before any set-up. The
+    // buffers it writes are free: the launch before this one waited for its own predecessors (among
+    // them the previous merge) before it let this launch start.
+    if (tid < p.ratio)
+      p.partial_lse[((int64_t)part * p.rows + row) * p.heads_q + kv_head * p.ratio + tid] = -INFINITY;
+    return;
+  }
   int slot = -1, tail_len = 0, sink_len = 0;
   if (p.tail_key) {
     slot = p.tail_slot_ids[row];

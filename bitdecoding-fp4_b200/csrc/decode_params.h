@@ -53,6 +53,7 @@ struct DecodeParams {
   int32_t* merge_counters;
   __nv_bfloat16* merged_out;
   const int32_t* row_order;  // launch position -> row (longest rows first), or null
+  const int32_t* row_splits;  // parts per row (1..num_splits), or null: num_splits for every row
 };
 
 // One launch of decode_kernel<GP, TERMS, STAGES, PT, MX> with GP the smallest of 4, 8, 16 that holds

@@ -351,7 +351,7 @@ def _fill_args(
     query_scales_second, query_padded_bf16, key_pages_fp4, key_scales, value_pages_fp4, value_scales,
     fp4_page_table, seqused_fp4, residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids,
     seqused_residual, seqused_sink, softmax_scale, row_order=None, scale_format: str = "nvfp4",
-    tensor_scales=(1.0, 1.0, 1.0),
+    tensor_scales=(1.0, 1.0, 1.0), row_splits=None,
 ) -> None:
     a.rows, a.heads_q, a.heads_kv = rows, heads_q, heads_kv
     a.query_codes, a.query_scales = query_fp4.data_ptr(), query_scales.data_ptr()
@@ -377,6 +377,7 @@ def _fill_args(
     a.softmax_scale = float(softmax_scale)
     a.p_scale_mode, a.p_scale_tau = _p_scale_arguments(scale_format)
     a.row_order = bdfp4.ptr(row_order)
+    a.row_splits = bdfp4.ptr(row_splits)
     a.scale_format = bdfp4.FORMAT_MXFP4 if scale_format == "mxfp4" else bdfp4.FORMAT_NVFP4
     a.key_tensor_scale, a.query_tensor_scale, a.value_tensor_scale = (float(x) for x in tensor_scales)
 
@@ -428,13 +429,14 @@ def decode_fp4_split(
     query_padded_bf16=None, residual_key_pages_bf16=None, residual_value_pages_bf16=None,
     residual_page_ids=None, seqused_residual=None, seqused_sink=None, has_bf16=None, out=None,
     split_partial_scratch=None, split_lse_scratch=None, scale_format: str = "nvfp4",
-    split_merge_counters=None, row_order=None, tensor_scales=(1.0, 1.0, 1.0),
+    split_merge_counters=None, row_order=None, tensor_scales=(1.0, 1.0, 1.0), row_splits=None,
 ):
     """Split-KV decode: ``num_splits`` CTAs per (row, KV head) write FP32 partials and LSEs,
     then one combine launch produces the BF16 output, or, given ``split_merge_counters`` (INT32,
     at least ``rows * heads_kv`` zeros), the last CTA of each (row, KV head) merges them itself.
     Arguments are assumed validated by ``decode_fp4(validate_only=True)``. Supplied scratch makes
-    the call allocation-free."""
+    the call allocation-free. ``row_splits`` (INT32 ``[rows]``, each in ``1..num_splits``; no reference
+    counterpart) cuts row ``r`` into ``row_splits[r]`` parts only: for ragged batches."""
     device = query_fp4.device
     rows, _, heads_q, _ = query_fp4.shape
     page_count, _, heads_kv, _ = key_pages_fp4.shape
@@ -477,8 +479,11 @@ def decode_fp4_split(
         seqused_fp4=seqused_fp4, residual_key_pages_bf16=residual_key_pages_bf16,
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, seqused_sink=seqused_sink, softmax_scale=softmax_scale,
-        row_order=row_order, scale_format=scale_format, tensor_scales=tensor_scales,
+        row_order=row_order, scale_format=scale_format, tensor_scales=tensor_scales, row_splits=row_splits,
     )
+    if row_splits is not None and (row_splits.dtype is not torch.int32 or row_splits.device != device
+                                   or tuple(row_splits.shape) != (rows,) or not row_splits.is_contiguous()):
+        raise ValueError("row_splits must be contiguous INT32 CUDA with shape [rows]")
     a.num_splits = num_splits
     a.bf16_split = int(parts > num_splits)
     a.bf16_page_cost = BF16_BLOCK_PAGE_COST if has_residual and parts == num_splits else 0

@@ -119,7 +119,7 @@ def fp4_decode_impl(
     query_fp4_scratch=None, query_scales_scratch=None, query_fp4_second_scratch=None,
     query_scales_second_scratch=None, split_partial_scratch=None, split_lse_scratch=None, query_terms=1,
     scale_mode=DEFAULT_SCALE_MODE, query_rotation="none", tail_write: DecodeTailWrite | None = None,
-    split_merge_counters=None, row_order=None, tensor_scales=None,
+    split_merge_counters=None, row_order=None, tensor_scales=None, row_splits=None,
 ):
     from ._decode import decode_fp4, decode_fp4_split
 
@@ -179,4 +179,4 @@ def fp4_decode_impl(
     decode_fp4(**common, out_indices=out_indices, trusted_metadata=trusted_metadata, validate_only=True)
     return decode_fp4_split(
         **common, num_splits=num_splits, split_partial_scratch=split_partial_scratch,
-        split_lse_scratch=split_lse_scratch, split_merge_counters=split_merge_counters)
+        split_lse_scratch=split_lse_scratch, split_merge_counters=split_merge_counters, row_splits=row_splits)

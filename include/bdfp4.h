@@ -306,6 +306,12 @@ typedef struct bdfp4_decode_args {
   float key_tensor_scale;
   float query_tensor_scale;
   float value_tensor_scale;
+  /* Parts per row, no reference counterpart: int32 [rows] (device memory), each in 1..num_splits; row r
+   * is cut into row_splits[r] parts and the launch's remaining parts of that row find no pages, write
+   * an LSE of -inf and leave at once. For ragged batches: the long rows are cut finely enough to
+   * bound the launch while the short ones are not cut into set-up. NULL: num_splits parts for every
+   * row. Ignored with num_splits == 1 or merge_counters. */
+  const int32_t* row_splits;
 } bdfp4_decode_args;
 
 int bdfp4_decode(const bdfp4_decode_args* args, void* stream);

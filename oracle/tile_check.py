@@ -76,11 +76,15 @@ def oracle_tile(w, row: int, kv_head: int, *, terms: int, scale_mode: str, rotat
 
 
 def check_tiles(w, out: torch.Tensor, tiles, **decode_options) -> dict:
-    """Compare ``out`` ``[rows, Hq, 128]`` (device) with the oracle on ``tiles`` = [(row, kv_head), ...].
+    """Compare ``out`` ``[rows, Hq, 128]`` (device) with the oracle on ``tiles`` = [(row, kv_head), ...];
+    ``row_splits`` (a list with one part count per row) replaces ``num_splits`` row by row.
     Returns the worst absolute error and the mean relative error over the sampled tiles, in BF16."""
     ratio = w.heads_q // w.heads_kv
     errors, magnitudes, worst, identical, total = [], [], 0.0, 0, 0
+    row_splits = decode_options.pop("row_splits", None)  # per-row part counts (a list), if the launch used them
     for row, kv_head in tiles:
+        if row_splits is not None:
+            decode_options["num_splits"] = int(row_splits[row])
         want = oracle_tile(w, row, kv_head, **decode_options).float()
         got = out[row, kv_head * ratio:(kv_head + 1) * ratio].float().cpu()
         if not torch.isfinite(got).all():

@@ -214,6 +214,24 @@ def test_decode_fused_split_merge(rows, num_splits, page_tokens):
         _decode(w, terms=2, num_splits=num_splits, split_merge_counters=counters[:rows])
 
 
+def test_decode_rows_cut_into_different_numbers_of_parts():
+    """`row_splits`: in one launch of four parts a row is cut into its own number of parts; its further
+    parts leave with an LSE of -inf. A row cut into k parts gives the bits of a launch with k parts for
+    every row (same page ranges, and the merge passes over -inf parts), and agrees with the oracle."""
+    from bdfp4.workload import build_workload
+
+    w = build_workload(rows=3, heads_q=8, heads_kv=2, seq_lens=[2300, 700, 1500], sink_tokens=16, seed=12)
+    cuts = [4, 2, 3]
+    got = _decode(w, terms=2, num_splits=4, row_splits=torch.tensor(cuts, dtype=torch.int32, device="cuda"))
+    for row, parts in enumerate(cuts):
+        uniform = _decode(w, terms=2, num_splits=parts)
+        assert torch.equal(got[row], uniform[row]), (row, parts)
+        want, _, _ = _oracle_decode(w, terms=2, scale_mode="amax6", rotate=False, num_splits=parts, bf16_split=True)
+        _check(got[row], want[row], f"row {row} in {parts} parts")
+    with pytest.raises(ValueError):
+        _decode(w, terms=2, num_splits=4, row_splits=torch.tensor(cuts, dtype=torch.int64, device="cuda"))
+
+
 def test_decode_row_order_changes_nothing():
     """A launch order (longest rows first) never changes the result; a non-permutation is refused
     unless the metadata is trusted."""
